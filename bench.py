@@ -1,0 +1,391 @@
+"""Benchmark of the Newton constraint solve: world-steps/s on N B200s.
+
+A "step" is one ``solve_with_scratch`` over one batch of worlds (the humanoid of
+BASELINE.json's second config: nv 34, njmax 64, 8192 worlds per GPU).  Inputs are
+seeded synthetic solver states with that model's shapes; several distinct batches
+are rotated so that consecutive steps never find their inputs in L2.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One JSON line is printed by rank 0.  ``--impl reference`` times the CPU
+restatement of the reference's solver (the oracle) on all host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import copy
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "newton_solver_world_steps_per_s"
+UNIT = "world-steps/s"
+# dram__bytes_read.sum + dram__bytes_write.sum of one newton_kernel launch at the
+# bench workload, from the ncu capture summarised under profiles/ (None: not captured)
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=200)
+    p.add_argument("--warmup", type=int, default=10)
+    p.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    p.add_argument("--workload", default="humanoid", choices=["humanoid", "snu", "g1"])
+    p.add_argument("--nworld", type=int, default=8192, help="worlds per GPU")
+    p.add_argument("--batches", type=int, default=4, help="distinct input batches rotated per GPU")
+    p.add_argument("--iterations", type=int, default=50)
+    p.add_argument("--ls-iterations", type=int, default=50)
+    p.add_argument("--tolerance", type=float, default=1e-8)
+    p.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline sample length")
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+def workload_config(args, m, d):
+    return {
+        "workload": f"{args.workload}: nv {m.nv}, nv_pad {m.nv_pad}, njmax {d.njmax}, "
+        f"{args.nworld} worlds per GPU, one Newton solve per step "
+        f"(iterations<={args.iterations}, ls_iterations<={args.ls_iterations}, tol {args.tolerance:g})",
+        "worlds_per_gpu": args.nworld,
+        "nv": m.nv,
+        "njmax": d.njmax,
+        "batches_rotated": args.batches,
+        "l2": f"inputs of {args.batches} distinct batches rotate (> 126 MB L2 in total)",
+        "sharding": "by world, no collective on the data path",
+    }
+
+
+def algorithmic_bytes(m, d) -> int:
+    """Compulsory HBM bytes of one solve of batch ``d``: inputs read once, results
+    written once, independent of the iteration count."""
+    nefc = np.minimum(d.nefc, d.njmax).astype(np.int64)
+    nv, nM = m.nv, m.nM
+    read = nefc * nv + 3 * nefc + nM + 3 * nv + 3  # J; D, aref, frictionloss; M; 3 dof vectors; nefc/ne/nf
+    write = 3 * nv + 2 * nefc + 2  # qacc, Ma, qfrc_constraint; force, state; niter, overflow
+    return int(4 * (read + write).sum())
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self.thread.join(timeout=5)
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, r[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_batches(args, rank):
+    from instantmimic_b200 import synthetic
+
+    out = []
+    for b in range(args.batches):
+        m, d, _ = synthetic.make_workload(
+            args.workload, args.nworld, seed=1000 * rank + b, iterations=args.iterations,
+            ls_iterations=args.ls_iterations, tolerance=args.tolerance)
+        out.append((m, d))
+    return out
+
+
+def run_reference(args):
+    """The reference's CPU path for this solve, restated (oracle), on all host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+
+    oracle.build()
+    cores = os.cpu_count() or 1
+    batches = make_batches(args, 0)
+    m = batches[0][0]
+    work = [copy.deepcopy(d) for _, d in batches]
+    for k in range(min(args.warmup, 2)):
+        oracle.solve(m, work[k % len(work)], threads=cores)
+    steps = args.steps
+    # bounded: stop once a few minutes are used; the steps actually timed are reported
+    elapsed, done = 0.0, 0
+    for k in range(steps):
+        dd = copy.deepcopy(batches[k % len(batches)][1])
+        t1 = time.perf_counter()
+        oracle.solve(m, dd, threads=cores)
+        elapsed += time.perf_counter() - t1
+        done += 1
+        if elapsed > 150.0:
+            break
+    value = args.nworld * done / elapsed
+    line = {
+        "impl": "reference",
+        "metric": METRIC,
+        "value": value,
+        "unit": UNIT,
+        "n_gpus": args.gpus,
+        "steps": done,
+        "warmup": min(args.warmup, 2),
+        "ms_per_step": 1e3 * elapsed / done,
+        "higher_is_better": True,
+        "scaling": "weak",
+        "vs_baseline": None,
+        "dtype": "f32",
+        "data": "synthetic",
+        "config": workload_config(args, m, batches[0][1]),
+        "cpu_baseline": {
+            "value": value,
+            "unit": UNIT,
+            "cores": cores,
+            "kind": "port",
+            "sample": f"{done} steps of {args.nworld} worlds, OpenMP over worlds",
+        },
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "CPU restatement of the reference solver (MuJoCo / mujoco-warp are not installed)",
+    }
+    print(json.dumps(line))
+
+
+def cpu_baseline(args, batches):
+    from oracle import oracle
+
+    oracle.build()
+    cores = os.cpu_count() or 1
+    m = batches[0][0]
+    elapsed, solved, k = 0.0, 0, 0
+    while elapsed < args.cpu_seconds:
+        dd = copy.deepcopy(batches[k % len(batches)][1])
+        t = time.perf_counter()
+        oracle.solve(m, dd, threads=cores)
+        elapsed += time.perf_counter() - t
+        solved += args.nworld
+        k += 1
+    return {
+        "value": solved / elapsed,
+        "unit": UNIT,
+        "cores": cores,
+        "kind": "port",
+        "sample": f"{k} solves of {args.nworld} worlds ({elapsed:.1f} s), OpenMP over worlds, {cores} threads",
+    }
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    from instantmimic_b200 import _lib, mjw_model
+    from instantmimic_b200 import mjw_step_optimized as runtime
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    _lib.lib()
+
+    host = make_batches(args, rank)
+    m_host = host[0][0]
+    md = mjw_model.to_device(m_host, device)
+    dev = [mjw_model.to_device(d, device) for _, d in host]
+    scratch = [runtime.make_optimized_fwd_position_scratch(md, dd, device) for dd in dev]
+    nb = len(dev)
+
+    def step(k):
+        runtime.solve_with_scratch(md, dev[k % nb], scratch[k % nb], use_optimized_kernel=True)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(x: float) -> float:
+        if world == 1:
+            return x
+        t = torch.tensor([x], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    for k in range(args.warmup):
+        step(k)
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local) as clocks:
+        barrier()
+        e0.record()
+        for k in range(args.steps):
+            step(k)
+        e1.record()
+        barrier()
+    ms = max_over_ranks(e0.elapsed_time(e1))
+    value = world * args.nworld * args.steps / (ms * 1e-3)
+    niter = np.concatenate([dd.solver_niter.cpu().numpy() for dd in dev])
+
+    # ---- end to end: host buffers in, host results out, every step -----------
+    e2e = None
+    if not args.no_e2e:
+        in_names = ["nefc", "ne", "nf", "qacc_smooth", "qacc_warmstart", "qfrc_smooth", "M"]
+        efc_in = ["J", "D", "aref", "frictionloss"]
+        out_names = ["qacc", "qfrc_constraint", "solver_niter"]
+        efc_out = ["force", "state", "Ma"]
+        pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()  # noqa: E731
+        hin = [
+            ({n: pin(getattr(d, n)) for n in in_names}, {n: pin(getattr(d.efc, n)) for n in efc_in})
+            for _, d in host
+        ]
+        hout = ({n: pin(getattr(host[0][1], n)) for n in out_names},
+                {n: pin(getattr(host[0][1].efc, n)) for n in efc_out})
+        dd, sc = dev[0], scratch[0]
+        h2d = sum(t.numel() * t.element_size() for part in hin[0] for t in part.values())
+        d2h = sum(t.numel() * t.element_size() for part in hout for t in part.values())
+
+        def e2e_step(k):
+            a, b = hin[k % nb]
+            for n, t in a.items():
+                getattr(dd, n).copy_(t, non_blocking=True)
+            for n, t in b.items():
+                getattr(dd.efc, n).copy_(t, non_blocking=True)
+            runtime.solve_with_scratch(md, dd, sc, use_optimized_kernel=True)
+            for n, t in hout[0].items():
+                t.copy_(getattr(dd, n), non_blocking=True)
+            for n, t in hout[1].items():
+                t.copy_(getattr(dd.efc, n), non_blocking=True)
+            torch.cuda.synchronize()  # the caller reads the results
+
+        e2e_steps = min(args.steps, 50)
+        for k in range(3):
+            e2e_step(k)
+        barrier()
+        t0 = time.perf_counter()
+        for k in range(e2e_steps):
+            e2e_step(k)
+        barrier()
+        dt = max_over_ranks(time.perf_counter() - t0)
+        e2e = {
+            "value": world * args.nworld * e2e_steps / dt,
+            "unit": UNIT,
+            "h2d_bytes_per_step": int(h2d),
+            "d2h_bytes_per_step": int(d2h),
+            "steps": e2e_steps,
+            "ms_per_step": 1e3 * dt / e2e_steps,
+        }
+
+    if rank == 0:
+        from instantmimic_b200.mjw_kernels import newton_fusion
+
+        info = newton_fusion.solve_call(md, dev[0], scratch[0].solver_context, scratch[0].solver_nsolving,
+                                        cache_on=scratch[0]).launch_info()
+        alg = float(np.mean([algorithmic_bytes(m_host, d) for _, d in host]))
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        if peaks_file.exists():
+            peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
+        else:
+            peak, peak_src = 6650.0, "fallback"
+        launch_s = (ms * 1e-3) / args.steps
+        achieved = alg / launch_s / 1e9
+        line = {
+            "metric": METRIC,
+            "value": value,
+            "unit": UNIT,
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": ms / args.steps,
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "f32",
+            "data": "synthetic",
+            "config": workload_config(args, m_host, host[0][1]),
+            "clocks": clocks.summary(),
+            "e2e": e2e,
+            "gpu_launches": 2 * args.steps,
+            "roofline": {
+                "kernel": "newton_kernel<resident>" if info.j_resident else "newton_kernel<streamed>",
+                "bound": "hbm",
+                "achieved": achieved,
+                "peak": peak,
+                "peak_source": peak_src,
+                "unit": "GB/s",
+                "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "algorithmic_bytes_per_launch": alg,
+                "launch_ms": launch_s * 1e3,
+            },
+            "solver": {
+                "niter_mean": float(niter.mean()),
+                "niter_max": int(niter.max()),
+                "smem_bytes_per_world": int(info.smem_bytes),
+            },
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline(args, host)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,282 @@
+/*
+ * imnewton.h -- C ABI of the B200-native Newton constraint solver.
+ *
+ * Every entry point replaces one interface of InstantMimic's MuJoCo-Warp step
+ * (reference paths are given per declaration, relative to the InstantMimic
+ * source tree).  The structs are plain-old-data: device pointers, extents and
+ * element strides of buffers that the CALLER owns.  The library allocates no
+ * device memory; plans (index tables) are uploaded once by the caller and
+ * passed as pointers.  All work is enqueued on the CUDA stream handed in and
+ * no call synchronises, so every entry point may be recorded into a CUDA
+ * graph like the Warp launches it stands in for.
+ *
+ * Return value: 0 on success, a negative ImnStatus when host-side validation
+ * fails (nothing is launched).  Device-side conditions never surface here: they
+ * go to the per-world `overflow` bits and to the sparse-pattern violation
+ * counter exactly as the reference does.
+ *
+ * Conventions shared by all structs
+ *   - W = nworld, nv = degrees of freedom, P = nv_pad, R = njmax.
+ *   - every array is world-major; `*_ld` fields are the stride, in ELEMENTS,
+ *     between consecutive worlds (or rows where stated).
+ *   - float is IEEE binary32; int is int32_t; flags are uint8_t (0/1).
+ */
+#ifndef IMNEWTON_H_
+#define IMNEWTON_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define IMN_ABI_VERSION 1
+
+typedef enum ImnStatus {
+  IMN_OK = 0,
+  IMN_ERR_NULL = -1,        /* a required pointer is NULL                      */
+  IMN_ERR_SHAPE = -2,       /* nv / nv_pad / njmax / stride out of range       */
+  IMN_ERR_UNSUPPORTED = -3, /* model outside the fused path's eligibility      */
+  IMN_ERR_LAUNCH = -4,      /* cudaGetLastError() after the launch             */
+  IMN_ERR_LIMIT = -5        /* size beyond a stated fixed maximum              */
+} ImnStatus;
+
+/* mujoco ConstraintState values (efc.state). */
+enum {
+  IMN_STATE_SATISFIED = 0,
+  IMN_STATE_QUADRATIC = 1,
+  IMN_STATE_LINEARNEG = 2,
+  IMN_STATE_LINEARPOS = 3
+};
+
+/* Model-side constants of the solve: the fields of mujoco_warp `Model` that
+ * solve_with_scratch reads (mjw_step_optimized.py:2588-2680,
+ * newton_fusion.py:330-409). */
+typedef struct ImnModel {
+  int32_t nv;
+  int32_t nv_pad;        /* roundup(nv + 1, 16) on the Newton path             */
+  int32_t nM;            /* number of stored entries of M (CSR over ancestors) */
+  int32_t iterations;    /* opt.iterations                                     */
+  int32_t ls_iterations; /* opt.ls_iterations                                  */
+  int32_t warmstart;     /* !(opt.disableflags & WARMSTART)                    */
+  /* per-world option arrays, indexed world % n (newton_stages.py:183-186)      */
+  int32_t n_tolerance, n_ls_tolerance, n_meaninertia;
+  const float* opt_tolerance;
+  const float* opt_ls_tolerance;
+  const float* stat_meaninertia;
+  /* M in CSR over each dof's ancestors, root first, diagonal last
+   * (tree_ldl.py:3-8): rowadr[nv], rownnz[nv], colind[nM]                      */
+  const int32_t* M_rowadr;
+  const int32_t* M_rownnz;
+  const int32_t* M_colind;
+  /* full symmetric rows for M*v: rowadr[nv+1], col[], madr[]
+   * (newton_fusion.py:171-176, 378-380)                                        */
+  const int32_t* M_mulm_rowadr;
+  const int32_t* M_mulm_col;
+  const int32_t* M_mulm_madr;
+  /* constants that live in the upstream solver module                         */
+  float alpha_noise_eps;          /* solver._ALPHA_NOISE_EPS                    */
+  int32_t overflow_iterations;    /* types.OverflowType.ITERATIONS bit          */
+  int32_t overflow_ls_iterations; /* types.OverflowType.LS_ITERATIONS bit       */
+  int32_t warn_overflow;          /* opt.warn_overflow mask (device printf)     */
+} ImnModel;
+
+/* Data-side buffers of one batch of worlds: the fields of mujoco_warp `Data`
+ * that the solve reads and writes (newton_fusion.py:330-395). */
+typedef struct ImnData {
+  int32_t nworld;
+  int32_t njmax;
+  const int32_t* nefc; /* (W) */
+  const int32_t* ne;   /* (W) */
+  const int32_t* nf;   /* (W) */
+  /* (W, nv) inputs, stride dof_ld */
+  const float* qacc_smooth;
+  const float* qacc_warmstart;
+  const float* qfrc_smooth;
+  int64_t dof_ld;
+  /* efc.J (W, R, >=nv): world stride J_ld_world, row stride J_ld_row */
+  const float* efc_J;
+  int64_t J_ld_world;
+  int64_t J_ld_row;
+  /* (W, R) row arrays, stride efc_ld */
+  const float* efc_D;
+  const float* efc_aref;
+  const float* efc_frictionloss;
+  int64_t efc_ld;
+  /* M (W, nM), stride M_ld */
+  const float* M;
+  int64_t M_ld;
+  /* outputs */
+  float* qacc;            /* (W, nv)  stride dof_ld */
+  float* qfrc_constraint; /* (W, nv)  stride dof_ld */
+  float* efc_Ma;          /* (W, nv)  stride dof_ld */
+  float* efc_force;       /* (W, R)   stride efc_ld */
+  int32_t* efc_state;     /* (W, R)   stride efc_ld */
+  int32_t* solver_niter;  /* (W) */
+  int32_t* overflow;      /* (W), bits are OR-ed in */
+} ImnData;
+
+/* Static-pattern sparse L'DL of the Hessian: the tables that
+ * sparse_hessian.build_plan (sparse_hessian.py:229-402) bakes into generated
+ * source, here as device arrays.  Names follow the SH_* tables.  */
+typedef struct ImnSparsePlan {
+  int32_t nv, nv_pad, block;
+  int32_t nfac;    /* factor slots (rows of L incl. diagonal)                  */
+  int32_t nslots;  /* nfac + nv (augmented right-hand-side row)                */
+  int32_t nlevels;
+  int32_t nentries, nruns, nback;
+  const uint16_t* lvl_ptr;  /* SH_LP  [nlevels+1]                              */
+  const uint8_t* lvl_team;  /* SH_LT  [nlevels]                                */
+  const uint16_t* ent_slot; /* SH_ES  [nentries]                               */
+  const int16_t* ent_col;   /* SH_EC  [nentries]                               */
+  const uint16_t* run_ptr;  /* SH_RP  [nentries+1]                             */
+  const uint32_t* run_ab;   /* SH_RAB [nruns]                                  */
+  const uint32_t* run_kl;   /* SH_RKL [nruns]                                  */
+  const uint16_t* orig;     /* SH_ORIG[nv]                                     */
+  const uint16_t* b_lvl;    /* SH_BL  [nlevels+1]                              */
+  const uint16_t* b_slot;   /* SH_BS  [nback]                                  */
+  const uint16_t* b_src;    /* SH_BI  [nback]                                  */
+  const uint16_t* b_dst;    /* SH_BJ  [nback]                                  */
+  const int32_t* pair;      /* SH_PAIR[nv*nv]                                  */
+  const uint16_t* f_lvl;    /* SH_FL  [nlevels+1]                              */
+  const uint16_t* f_row;    /* SH_FR  [nv]                                     */
+  const uint16_t* row_start;/* SH_RS  [nv]                                     */
+  const uint16_t* rk_ptr;   /* SH_RKP [nv+1]                                   */
+  const uint16_t* rk;       /* SH_RK  []                                       */
+  const uint32_t* pmask;    /* SH_PM  [nv*words]                               */
+  const uint16_t* s_a;      /* SH_SA  [nfac]                                   */
+  const uint16_t* s_b;      /* SH_SB  [nfac]                                   */
+  const int32_t* s_m;       /* SH_SM  [nfac]                                   */
+  const uint32_t* gat;      /* SH_GAT [nfac] (non-fused path)                  */
+} ImnSparsePlan;
+
+/* Solver context: the arrays mujoco_warp's `_create_solver_context` allocates
+ * (mjw_step_optimized.py:2517) plus newton_dof_union
+ * (newton_fusion.py:301-304).  The fused kernel keeps its working set in
+ * shared memory; any pointer that is non-NULL receives the final value of the
+ * corresponding quantity when a world finishes, so a caller that inspects the
+ * context (the reference's tests do) still finds it.  NULL pointers are
+ * skipped.  `hfactor` is REQUIRED only on the sparse path (it carries the
+ * violation counter). */
+typedef struct ImnCtx {
+  float* Jaref; /* (W, R) stride efc_ld of ImnData */
+  float* jv;    /* (W, R) */
+  float* search; /* (W, nv) stride dof_ld */
+  float* mv;     /* (W, nv) */
+  float* grad;   /* (W, grad_ld) */
+  int64_t grad_ld;
+  float* h;       /* (W, P, P) dense Hessian, upper triangle maintained */
+  float* hfactor; /* (W, P, P) dense upper factor | packed sparse layout */
+  float* search_dot;
+  float* grad_dot;
+  float* grad_scale;
+  float* newton_decrement;
+  float* improvement;
+  float* alpha;
+  uint8_t* done;
+  uint8_t* search_unchanged;
+  uint8_t* ls_exhausted;
+  int32_t* quad_changed_ids;   /* (W, R) stride efc_ld */
+  int32_t* quad_changed_count; /* (W) */
+  int32_t* state_changed_count;/* (W) */
+  int32_t* dof_union;          /* (W, nv + 1) */
+  int32_t* nsolving;           /* (1): nworld minus the worlds that finished */
+  const ImnSparsePlan* sparse_plan; /* HOST pointer or NULL (dense factor)    */
+} ImnCtx;
+
+/* Tree-structured L'DL plan (tree_ldl.py:47-57, 105-170) as an instruction
+ * list instead of generated source.  One instruction is four int32:
+ * {op, a, b, c}; see imn_tree_ldl_solve.  */
+typedef struct ImnTreePlan {
+  int32_t nv, nM;
+  int32_t groups;       /* warps per block of 32 worlds                        */
+  int32_t ntrunk;       /* trunk dofs                                          */
+  int32_t ntrunk_entries;
+  int32_t nslot;        /* per-world scratch slots in shared memory            */
+  const int32_t* prog;      /* device: concatenated instruction streams        */
+  const int32_t* prog_ptr;  /* device: [3*groups + 2] stream offsets           */
+  int32_t owner;        /* group that finishes the trunk                       */
+} ImnTreePlan;
+
+/* Blocked dense Cholesky of M gathered by index
+ * (indexed_factor.py:15-173, mjw_step_optimized.py:893-955). */
+typedef struct ImnBlockedPlan {
+  int32_t nv;
+  int32_t pad;            /* roundup(nv, 16)                                   */
+  const int32_t* indices; /* device (pad*pad) block-major gather; nM = zero    */
+  const float* identity;  /* device (256): ones on the padded diagonal         */
+  int32_t nM;
+} ImnBlockedPlan;
+
+/* ---- entry points ------------------------------------------------------- */
+
+/* Replaces solve_with_scratch's monolithic fused branch:
+ * _solve_monolithic_with_scratch (mjw_step_optimized.py:2588-2680) =
+ * _solve_init_dof + newton_fusion.init_context (newton_fusion.py:431-472) +
+ * newton_fusion.run (newton_fusion.py:330-409) + qfrc_constraint_from_grad
+ * (newton_fusion.py:522-539), as ONE persistent kernel.  `stream` is a
+ * cudaStream_t. */
+int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, void* stream);
+
+/* Replaces the rowless branch of solve_with_scratch
+ * (mjw_step_optimized.py:2692-2699): qacc = qacc_smooth, efc.Ma = M qacc,
+ * qfrc_constraint = 0, solver_niter = 0 for every world. */
+int imn_rowless_handoff(const ImnModel* m, const ImnData* d, void* stream);
+
+/* Replaces support.mul_m through the preallocated call
+ * (mjw_step_optimized.py:2252-2255): out = M v per world. */
+int imn_mul_m(const ImnModel* m, const float* M, int64_t M_ld, const float* v,
+              int64_t v_ld, float* out, int64_t out_ld, int32_t nworld, void* stream);
+
+/* Replaces tree_ldl.tree_factor_solve (tree_ldl.py:419-433): x = M^-1 y with
+ * M in the model's ancestor CSR; nothing but x is written. */
+int imn_tree_ldl_solve(const ImnTreePlan* plan, const float* M, int64_t M_ld,
+                       const float* y, int64_t y_ld, float* x, int64_t x_ld,
+                       int32_t nworld, void* stream);
+
+/* Replaces factor_solve_indexed_cholesky_kernel and its multi-RHS variants
+ * (indexed_factor.py:176-214, 217-391, 394-493;
+ * mjw_step_optimized.py:958-993).
+ *   mode 0: factor M into U (W, pad, pad) and solve rhs_count columns
+ *   mode 1: solve with the U already stored
+ * y and x are (W, nv, rhs_count) contiguous; `active` (W) may be NULL; worlds
+ * whose flag is 0 are left untouched.  U is caller-owned scratch. */
+int imn_blocked_dense_factor_solve(const ImnBlockedPlan* plan, const float* M,
+                                   int64_t M_ld, const float* y, float* U, float* x,
+                                   const int32_t* active, int32_t nworld,
+                                   int32_t rhs_count, int32_t mode, void* stream);
+
+/* Replaces sparse_hessian_upstream_factor, the sparse factor of the
+ * non-fused iteration (sparse_hessian.py:849-894): mode 4 gathers the dense H
+ * and factors, mode 5 solves with the stored factor.  hfactor layout:
+ * [0,nfac) N, [nfac,nfac+nv) 1/D.  search is (W, nv), grad (W, grad_ld). */
+int imn_sparse_factor_nonfused(const ImnSparsePlan* plan, const uint8_t* done,
+                               const float* grad, int64_t grad_ld, const float* h,
+                               const int32_t* quad_changed,
+                               const int32_t* state_changed, float* hfactor,
+                               float* search, int64_t search_ld, float* search_dot,
+                               float* decrement, int32_t nworld,
+                               int32_t skip_unchanged, int32_t skip_noflip,
+                               void* stream);
+
+/* Launch geometry the library would use for (m, d): block width of one world
+ * (newton_fusion.newton_block_dim, newton_fusion.py:325-327), worlds per CTA,
+ * dynamic shared memory per CTA, whether J stays resident in shared memory. */
+typedef struct ImnLaunchInfo {
+  int32_t world_threads;
+  int32_t worlds_per_cta;
+  int32_t smem_bytes;
+  int32_t j_resident;
+  int32_t grid;
+} ImnLaunchInfo;
+int imn_launch_info(const ImnModel* m, const ImnData* d, const ImnCtx* ctx,
+                    ImnLaunchInfo* out);
+
+/* Text of the last validation failure on the calling thread. */
+const char* imn_last_error(void);
+int imn_abi_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* IMNEWTON_H_ */

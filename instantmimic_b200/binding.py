@@ -1,0 +1,156 @@
+"""Builds the C-ABI structs of ``include/imnewton.h`` from Model / Data / context
+objects.  Works on any array type ``arrays.addr`` understands, so the same code
+describes device buffers for the CUDA library and host buffers for the oracle
+used by the tests."""
+
+from __future__ import annotations
+
+import ctypes as C
+from typing import Any
+
+from . import abi, types
+from .arrays import addr, elem_strides, length, shape
+
+
+def _upstream_constants() -> tuple[float, int, int]:
+    """(_ALPHA_NOISE_EPS, OverflowType.ITERATIONS, OverflowType.LS_ITERATIONS) from a
+    live mujoco-warp when importable, else this package's defaults."""
+    try:  # pragma: no cover - mujoco_warp is not installed in the build image
+        from mujoco_warp._src import solver as up_solver
+        from mujoco_warp._src import types as up_types
+
+        return (
+            float(up_solver._ALPHA_NOISE_EPS),
+            int(up_types.OverflowType.ITERATIONS),
+            int(up_types.OverflowType.LS_ITERATIONS),
+        )
+    except Exception:
+        return (
+            float(types.ALPHA_NOISE_EPS),
+            int(types.OverflowType.ITERATIONS),
+            int(types.OverflowType.LS_ITERATIONS),
+        )
+
+
+def model_struct(m: Any) -> abi.ImnModel:
+    eps, ovf_it, ovf_ls = _upstream_constants()
+    s = abi.ImnModel()
+    s.nv = int(m.nv)
+    s.nv_pad = int(m.nv_pad)
+    s.nM = int(shape(m.M_colind)[0])
+    s.iterations = int(m.opt.iterations)
+    s.ls_iterations = int(m.opt.ls_iterations)
+    s.warmstart = 0 if (int(m.opt.disableflags) & int(types.DisableBit.WARMSTART)) else 1
+    s.n_tolerance = length(m.opt.tolerance)
+    s.n_ls_tolerance = length(m.opt.ls_tolerance)
+    s.n_meaninertia = length(m.stat.meaninertia)
+    s.opt_tolerance = addr(m.opt.tolerance)
+    s.opt_ls_tolerance = addr(m.opt.ls_tolerance)
+    s.stat_meaninertia = addr(m.stat.meaninertia)
+    s.M_rowadr = addr(m.M_rowadr)
+    s.M_rownnz = addr(m.M_rownnz)
+    s.M_colind = addr(m.M_colind)
+    s.M_mulm_rowadr = addr(m.M_mulm_rowadr)
+    s.M_mulm_col = addr(m.M_mulm_col)
+    s.M_mulm_madr = addr(m.M_mulm_madr)
+    s.alpha_noise_eps = eps
+    s.overflow_iterations = ovf_it
+    s.overflow_ls_iterations = ovf_ls
+    s.warn_overflow = int(getattr(m.opt, "warn_overflow", 0) or 0)
+    return s
+
+
+def _row_ld(a: Any) -> int:
+    st = elem_strides(a)
+    if st[-1] != 1:
+        raise ValueError("solver buffers need a unit innermost stride")
+    return st[0]
+
+
+def _same_ld(name: str, arrays: list[Any]) -> int:
+    lds = {_row_ld(a) for a in arrays if a is not None}
+    if len(lds) != 1:
+        raise ValueError(f"{name} arrays must share one world stride, got {sorted(lds)}")
+    return lds.pop()
+
+
+def data_struct(m: Any, d: Any) -> abi.ImnData:
+    s = abi.ImnData()
+    s.nworld = int(d.nworld)
+    s.njmax = int(d.njmax)
+    s.nefc, s.ne, s.nf = addr(d.nefc), addr(d.ne), addr(d.nf)
+    s.qacc_smooth = addr(d.qacc_smooth)
+    s.qacc_warmstart = addr(d.qacc_warmstart)
+    s.qfrc_smooth = addr(d.qfrc_smooth)
+    s.dof_ld = _same_ld(
+        "dof",
+        [d.qacc_smooth, d.qacc_warmstart, d.qfrc_smooth, d.qacc, d.qfrc_constraint, d.efc.Ma],
+    )
+    s.efc_J = addr(d.efc.J)
+    js = elem_strides(d.efc.J)
+    if js[2] != 1:
+        raise ValueError("efc.J needs a unit innermost stride")
+    s.J_ld_world, s.J_ld_row = js[0], js[1]
+    s.efc_D = addr(d.efc.D)
+    s.efc_aref = addr(d.efc.aref)
+    s.efc_frictionloss = addr(d.efc.frictionloss)
+    s.efc_ld = _same_ld(
+        "efc", [d.efc.D, d.efc.aref, d.efc.frictionloss, d.efc.force, d.efc.state]
+    )
+    s.M = addr(d.M)
+    s.M_ld = _row_ld(d.M)
+    s.qacc = addr(d.qacc)
+    s.qfrc_constraint = addr(d.qfrc_constraint)
+    s.efc_Ma = addr(d.efc.Ma)
+    s.efc_force = addr(d.efc.force)
+    s.efc_state = addr(d.efc.state)
+    s.solver_niter = addr(d.solver_niter)
+    s.overflow = addr(d.overflow)
+    return s
+
+
+_CTX_WORLD_ARRAYS = (
+    "search_dot",
+    "grad_dot",
+    "grad_scale",
+    "newton_decrement",
+    "improvement",
+    "alpha",
+    "done",
+    "search_unchanged",
+    "ls_exhausted",
+    "quad_changed_count",
+    "state_changed_count",
+)
+
+
+def ctx_struct(d_struct: abi.ImnData, ctx: Any, nsolving: Any, sparse_plan_struct=None) -> abi.ImnCtx:
+    """``ctx`` may omit any array (attribute missing or None): the kernel then skips
+    writing it back."""
+    s = abi.ImnCtx()
+
+    def get(name):
+        return getattr(ctx, name, None) if ctx is not None else None
+
+    for name in ("Jaref", "jv", "quad_changed_ids"):
+        a = get(name)
+        if a is not None and _row_ld(a) != d_struct.efc_ld:
+            raise ValueError(f"ctx.{name} must share the world stride of the efc arrays")
+        setattr(s, name, addr(a))
+    for name in ("search", "mv"):
+        a = get(name)
+        if a is not None and _row_ld(a) != d_struct.dof_ld:
+            raise ValueError(f"ctx.{name} must share the world stride of the dof arrays")
+        setattr(s, name, addr(a))
+    g = get("grad")
+    s.grad = addr(g)
+    s.grad_ld = _row_ld(g) if g is not None else 0
+    s.h = addr(get("h"))
+    s.hfactor = addr(get("hfactor"))
+    for name in _CTX_WORLD_ARRAYS:
+        setattr(s, name, addr(get(name)))
+    s.dof_union = addr(get("newton_dof_union"))
+    s.nsolving = addr(nsolving)
+    if sparse_plan_struct is not None:
+        s.sparse_plan = C.pointer(sparse_plan_struct)
+    return s

@@ -1,0 +1,90 @@
+// imn_api.cu -- error text, ABI version and the two small per-dof kernels
+// (rowless hand-off, M v).
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "imn_common.cuh"
+
+namespace imn {
+
+static thread_local char g_error[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+}
+
+// One warp per world; M's row is read once into shared memory, then every lane
+// forms the running sums of its dofs over the symmetric row tables.
+__global__ void __launch_bounds__(128) mul_m_kernel(const int nv, const int nM, const int* __restrict__ rowadr,
+                                                    const int* __restrict__ col, const int* __restrict__ madr,
+                                                    const float* __restrict__ M, const int64_t M_ld,
+                                                    const float* __restrict__ v, const int64_t v_ld,
+                                                    float* __restrict__ out, const int64_t out_ld,
+                                                    float* __restrict__ copy_to, int* __restrict__ niter,
+                                                    float* __restrict__ zero, const int nworld) {
+  extern __shared__ float sm[];
+  const int lane = threadIdx.x & 31, slot = threadIdx.x >> 5;
+  const int w = blockIdx.x * (blockDim.x >> 5) + slot;
+  if (w >= nworld) return;
+  float* Ms = sm + slot * (nM + nv);
+  float* vs = Ms + nM;
+  for (int e = lane; e < nM; e += 32) Ms[e] = M[(size_t)w * M_ld + e];
+  for (int i = lane; i < nv; i += 32) {
+    const float x = v[(size_t)w * v_ld + i];
+    vs[i] = x;
+    if (copy_to) copy_to[(size_t)w * v_ld + i] = x;
+    if (zero) zero[(size_t)w * v_ld + i] = 0.0f;
+  }
+  if (niter && lane == 0) niter[w] = 0;
+  __syncwarp();
+  for (int i = lane; i < nv; i += 32) {
+    float s = 0.0f;
+    for (int k = rowadr[i]; k < rowadr[i + 1]; ++k) s = fmaf(Ms[madr[k]], vs[col[k]], s);
+    out[(size_t)w * out_ld + i] = s;
+  }
+}
+
+static int launch_mul_m(const ImnModel* m, const float* M, int64_t M_ld, const float* v, int64_t v_ld,
+                        float* out, int64_t out_ld, float* copy_to, int* niter, float* zero, int nworld,
+                        cudaStream_t stream) {
+  if (nworld == 0) return IMN_OK;
+  const int wpc = 4;
+  const size_t bytes = (size_t)wpc * (m->nM + m->nv) * sizeof(float);
+  if (bytes > 48 * 1024) return set_error("mul_m: nM %d too large", m->nM), IMN_ERR_LIMIT;
+  mul_m_kernel<<<(nworld + wpc - 1) / wpc, wpc * 32, bytes, stream>>>(
+      m->nv, m->nM, m->M_mulm_rowadr, m->M_mulm_col, m->M_mulm_madr, M, M_ld, v, v_ld, out, out_ld, copy_to,
+      niter, zero, nworld);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("mul_m: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  return IMN_OK;
+}
+
+}  // namespace imn
+
+extern "C" const char* imn_last_error(void) { return imn::g_error; }
+extern "C" int imn_abi_version(void) { return IMN_ABI_VERSION; }
+
+extern "C" int imn_mul_m(const ImnModel* m, const float* M, int64_t M_ld, const float* v, int64_t v_ld,
+                         float* out, int64_t out_ld, int32_t nworld, void* stream) {
+  if (!m || !M || !v || !out || !m->M_mulm_rowadr || !m->M_mulm_col || !m->M_mulm_madr)
+    return imn::set_error("imn_mul_m: NULL argument"), IMN_ERR_NULL;
+  if (m->nv <= 0 || nworld < 0 || M_ld < m->nM || v_ld < m->nv || out_ld < m->nv)
+    return imn::set_error("imn_mul_m: bad extent or stride"), IMN_ERR_SHAPE;
+  return imn::launch_mul_m(m, M, M_ld, v, v_ld, out, out_ld, nullptr, nullptr, nullptr, nworld,
+                           (cudaStream_t)stream);
+}
+
+extern "C" int imn_rowless_handoff(const ImnModel* m, const ImnData* d, void* stream) {
+  if (!m || !d) return imn::set_error("imn_rowless_handoff: NULL struct"), IMN_ERR_NULL;
+  if (!d->qacc_smooth || !d->qacc || !d->efc_Ma || !d->qfrc_constraint || !d->solver_niter || !d->M ||
+      !m->M_mulm_rowadr || !m->M_mulm_col || !m->M_mulm_madr)
+    return imn::set_error("imn_rowless_handoff: a required pointer is NULL"), IMN_ERR_NULL;
+  if (m->nv <= 0 || d->nworld < 0 || d->dof_ld < m->nv || d->M_ld < m->nM)
+    return imn::set_error("imn_rowless_handoff: bad extent or stride"), IMN_ERR_SHAPE;
+  // qacc = qacc_smooth, Ma = M qacc, qfrc_constraint = 0, niter = 0
+  return imn::launch_mul_m(m, d->M, d->M_ld, d->qacc_smooth, d->dof_ld, d->efc_Ma, d->dof_ld, d->qacc,
+                           d->solver_niter, d->qfrc_constraint, d->nworld, (cudaStream_t)stream);
+}

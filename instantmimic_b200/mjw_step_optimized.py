@@ -1,0 +1,150 @@
+"""Step-pipeline entry points of the Newton solve and the M-side factor/solve.
+
+Same names, arguments and error behaviour as the functions of the reference's
+``src/instantmimic/utils/mjw_step_optimized.py`` that sit on the solver path:
+``solve_with_scratch`` (:2683-2742), ``make_optimized_fwd_position_scratch``
+(solver part, :2510-2585), ``_factor_solve_i_dense`` (:1030-1070).  Everything is
+a launch of hand-written CUDA through the C ABI; there is no other code path.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Any
+
+from . import _lib, binding
+from .mjw_kernels import newton_fusion
+
+
+class SolverContext:
+    """The arrays of upstream ``solver._create_solver_context`` that the fused path
+    can report (call site mjw_step_optimized.py:2517).  The kernel keeps its
+    working set on chip; these buffers receive the final values per world."""
+
+    def __init__(self, m: Any, d: Any, device: Any, *, with_matrices: bool = False):
+        import torch
+
+        W, nv, R, P = d.nworld, m.nv, d.njmax, m.nv_pad
+        f = lambda *s: torch.zeros(s, dtype=torch.float32, device=device)  # noqa: E731
+        i = lambda *s: torch.zeros(s, dtype=torch.int32, device=device)  # noqa: E731
+        b = lambda *s: torch.zeros(s, dtype=torch.uint8, device=device)  # noqa: E731
+        self.Jaref, self.jv = f(W, R), f(W, R)
+        self.search, self.mv = f(W, nv), f(W, nv)
+        self.grad = f(W, P)
+        self.h = f(W, P, P) if with_matrices else None
+        self.hfactor = f(W, P, P) if with_matrices else None
+        self.search_dot, self.grad_dot, self.grad_scale = f(W), f(W), f(W)
+        self.newton_decrement, self.improvement, self.alpha = f(W), f(W), f(W)
+        self.done, self.search_unchanged, self.ls_exhausted = b(W), b(W), b(W)
+        self.quad_changed_ids = i(W, R)
+        self.quad_changed_count, self.state_changed_count = i(W), i(W)
+        self.sparse_hessian_plan = None
+
+
+@dataclass
+class OptimizedFwdPositionScratch:
+    """Solver-facing part of the reference's scratch object
+    (mjw_step_optimized.py:459-519)."""
+
+    solver_context: Any = None
+    solver_nsolving: Any = None
+    solver_uses_compact: bool = False
+    constraint_free: bool = False
+    mul_m_call: Any = None
+    dense_factor_solve: Any = None
+    tree_factor_solve: Any = None
+    unroll_solver_iterations: bool = False
+
+
+def mul_m(m: Any, d: Any, res: Any, vec: Any, stream=None) -> None:
+    """res = M vec per world (upstream ``support.mul_m`` through the preallocated
+    call, mjw_step_optimized.py:2252-2255)."""
+    from .arrays import addr, elem_strides
+
+    ms = binding.model_struct(m)
+    rc = _lib.lib().imn_mul_m(
+        C.byref(ms), addr(d.M), elem_strides(d.M)[0], addr(vec), elem_strides(vec)[0], addr(res),
+        elem_strides(res)[0], int(d.nworld), _lib.current_stream_handle(stream),
+    )
+    _lib.check(rc, "imn_mul_m")
+
+
+def make_optimized_fwd_position_scratch(
+    m: Any,
+    d: Any,
+    device: Any = "cuda",
+    *,
+    include_optimized_kernel_scratch: bool = True,
+    with_matrices: bool = False,
+) -> OptimizedFwdPositionScratch:
+    """Solver context, nsolving counter and the M-side factor/solve plans."""
+    import torch
+
+    from .mjw_kernels import indexed_factor, tree_ldl
+
+    ctx = nsolving = None
+    if d.njmax > 0 and m.nv > 0:
+        ctx = SolverContext(m, d, device, with_matrices=with_matrices)
+        newton_fusion.attach_scratch(m, d, ctx, device)
+        nsolving = torch.zeros((1,), dtype=torch.int32, device=device)
+    return OptimizedFwdPositionScratch(
+        solver_context=ctx,
+        solver_nsolving=nsolving,
+        mul_m_call=mul_m,
+        dense_factor_solve=indexed_factor.create_blocked_dense_factor_solve_scratch(m, d, device),
+        tree_factor_solve=(
+            tree_ldl.create_tree_factor_solve_scratch(m, device)
+            if include_optimized_kernel_scratch
+            else None
+        ),
+    )
+
+
+def _solver_compact_enabled(m: Any) -> bool:
+    return bool(getattr(m, "solver_compact", False))
+
+
+def _rowless_handoff(m: Any, d: Any, stream=None) -> None:
+    ms = binding.model_struct(m)
+    ds = binding.data_struct(m, d)
+    rc = _lib.lib().imn_rowless_handoff(C.byref(ms), C.byref(ds), _lib.current_stream_handle(stream))
+    _lib.check(rc, "imn_rowless_handoff")
+
+
+def solve_with_scratch(
+    m: Any,
+    d: Any,
+    scratch: OptimizedFwdPositionScratch,
+    *,
+    use_optimized_kernel: bool = False,
+    stream=None,
+) -> None:
+    """Solve the constraints of every world (mjw_step_optimized.py:2683-2742).
+
+    ``use_optimized_kernel`` selects between the reference's stock and fused Warp
+    launches; both compute the same solve, and here both are the one CUDA kernel.
+    Sleeping-island (compact) contexts are not part of this path and raise."""
+    if getattr(scratch, "constraint_free", False) or d.njmax == 0 or m.nv == 0:
+        # MuJoCo's nefc == 0 result; implicit integration reads efc.Ma = M qacc.
+        if m.nv:
+            _rowless_handoff(m, d, stream)
+        else:
+            d.solver_niter.zero_()
+        return
+    ctx = scratch.solver_context
+    nsolving = scratch.solver_nsolving
+    if ctx is None or nsolving is None:
+        raise RuntimeError("optimized solver scratch is not initialized")
+    expected_compact = _solver_compact_enabled(m)
+    if bool(scratch.solver_uses_compact) != expected_compact:
+        raise RuntimeError("optimized solver scratch layout no longer matches model")
+    if expected_compact:
+        raise RuntimeError("compact (sleeping-island) solves are outside this solver's path")
+    if not newton_fusion.eligible(m, ctx, compact=False):
+        raise RuntimeError(
+            "model is outside the fused Newton path (dense pyramidal Newton, 0 < nv <= 79, "
+            "nv_pad % 16 == 0, CUDA buffers); no other solver path exists here"
+        )
+    del use_optimized_kernel
+    newton_fusion.solve_call(m, d, ctx, nsolving, cache_on=scratch)(stream)

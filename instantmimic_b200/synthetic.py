@@ -1,0 +1,310 @@
+"""Seeded synthetic solver inputs with the shapes of the reference's models.
+
+The reference obtains ``efc.*``, ``M`` and ``qfrc_smooth`` from MuJoCo-Warp's
+collision and constraint pipeline, which is not part of this package.  The
+generators here produce inputs with the same layout, sizes and value ranges:
+kinematic trees transcribed from the reference's model files (dof counts and
+parent structure only), tree-structured SPD mass matrices, pyramidal contact rows
+in groups of four that touch the ancestor chain of one body, joint-limit rows on
+single dofs, and optional equality / friction-loss rows.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+
+from .mjw_model import Data, Model, make_data, put_model
+
+
+def _tree_from_joints(joints):
+    """joints: list of (ndof, parent_joint_index or -1) -> (dof_parentid, body_of_dof)."""
+    parent, body, last = [], [], []
+    for j, (ndof, pj) in enumerate(joints):
+        prev = last[pj] if pj >= 0 else -1
+        for _ in range(ndof):
+            parent.append(prev)
+            prev = len(parent) - 1
+            body.append(j + 1)
+        last.append(prev)
+    return np.asarray(parent, np.int32), np.asarray(body, np.int32)
+
+
+def humanoid_tree():
+    """The PD humanoid of data/humanoid/mjcf/humanoid_pd.xml:50-127: free root, 8 ball
+    joints, 4 hinges, nv 34."""
+    joints = [
+        (6, -1),  # 0 pelvis (free)
+        (3, 0),  # 1 abdomen
+        (3, 1),  # 2 neck
+        (3, 1),  # 3 right shoulder
+        (1, 3),  # 4 right elbow
+        (3, 1),  # 5 left shoulder
+        (1, 5),  # 6 left elbow
+        (3, 0),  # 7 right hip
+        (1, 7),  # 8 right knee
+        (3, 8),  # 9 right ankle
+        (3, 0),  # 10 left hip
+        (1, 10),  # 11 left knee
+        (3, 11),  # 12 left ankle
+    ]
+    return _tree_from_joints(joints)
+
+
+def snu_like_tree():
+    """Shape stand-in for the SNU muscle humanoid (nv 56: free root, 14 ball joints,
+    8 hinges; data/snu_humanoid/mjcf/include/body.xml:52-897)."""
+    joints = [(6, -1)]
+    # spine: 3 balls, then neck and head balls
+    joints += [(3, 0), (3, 1), (3, 2), (3, 3), (3, 4)]
+    # arms off the upper spine: clavicle ball, shoulder ball, elbow hinge, wrist hinge
+    for _ in range(2):
+        base = len(joints)
+        joints += [(3, 3), (3, base), (1, base + 1), (1, base + 2)]
+    # legs off the pelvis: hip ball, knee hinge, ankle ball, toe hinge
+    for _ in range(2):
+        base = len(joints)
+        joints += [(3, 0), (1, base), (3, base + 1), (1, base + 2)]
+    # 5 + 2*2 + 2*2 = 13 balls so far; one more ball (jaw) and 0 more hinges: 8 hinges
+    joints += [(3, 5)]
+    parent, body = _tree_from_joints(joints)
+    assert parent.size == 56, parent.size
+    return parent, body
+
+
+def g1_like_tree():
+    """Shape stand-in for the Unitree G1 (nv 35: free root and 29 hinges in chains of
+    6/6/3/7/7; the model itself is not distributed with the reference)."""
+    joints = [(6, -1)]
+    for _ in range(2):  # legs, 6 hinges each
+        prev = 0
+        for _ in range(6):
+            joints.append((1, prev))
+            prev = len(joints) - 1
+    prev = 0
+    for _ in range(3):  # waist
+        joints.append((1, prev))
+        prev = len(joints) - 1
+    waist = prev
+    for _ in range(2):  # arms, 7 hinges each
+        prev = waist
+        for _ in range(7):
+            joints.append((1, prev))
+            prev = len(joints) - 1
+    parent, body = _tree_from_joints(joints)
+    assert parent.size == 35
+    return parent, body
+
+
+def limb_tree(nv: int, limbs: int = 4):
+    """Free root plus ``limbs`` hinge chains sharing the remaining dofs."""
+    if nv < 6:
+        return _tree_from_joints([(nv, -1)])
+    joints = [(6, -1)]
+    rest = nv - 6
+    per, extra = divmod(rest, limbs)
+    for c in range(limbs):
+        prev = 0
+        for _ in range(per + (1 if c < extra else 0)):
+            joints.append((1, prev))
+            prev = len(joints) - 1
+    return _tree_from_joints(joints)
+
+
+def chain_tree(nv: int):
+    """Free root, then ball joints and hinges in one chain (the layout of the
+    reference's parity models, tests/test_mjw_newton_fusion.py:99-115)."""
+    balls, hinges = divmod(max(nv - 6, 0), 3)
+    joints = [(min(nv, 6), -1)]
+    for _ in range(balls):
+        joints.append((3, len(joints) - 1))
+    for _ in range(hinges):
+        joints.append((1, len(joints) - 1))
+    return _tree_from_joints(joints)
+
+
+def multi_chain_tree(chains: int, nv: int):
+    """``chains`` separate floating chains (tests/test_mjw_newton_fusion.py:118-142)."""
+    per, extra = divmod(nv, chains)
+    joints = []
+    for c in range(chains):
+        n = per + (1 if c < extra else 0)
+        joints.append((6, -1))
+        for _ in range(n - 6):
+            joints.append((1, len(joints) - 1))
+    return _tree_from_joints(joints)
+
+
+def ancestor_masks(dof_parentid: np.ndarray) -> np.ndarray:
+    """mask[d, a] = True when a is d or one of its ancestors."""
+    nv = dof_parentid.size
+    mask = np.zeros((nv, nv), bool)
+    for d in range(nv):
+        p = d
+        while p >= 0:
+            mask[d, p] = True
+            p = int(dof_parentid[p])
+    return mask
+
+
+def random_mass_matrices(m: Model, nworld: int, rng: np.random.Generator):
+    """(W, nM) CSR values of M = L^T D L, L unit lower on the ancestor pattern with
+    N(0, 0.3) entries and D ~ U(0.5, 2); also returns the dense matrices."""
+    nv, nM = m.nv, m.nM
+    rows = np.asarray(m.M_hinit_i)
+    cols = np.asarray(m.M_colind)
+    offdiag = rows != cols
+    out = np.empty((nworld, nM), np.float32)
+    dense_all = np.empty((nworld, nv, nv), np.float32)
+    chunk = max(1, min(nworld, (1 << 24) // max(nv * nv, 1)))
+    for lo in range(0, nworld, chunk):
+        hi = min(nworld, lo + chunk)
+        n = hi - lo
+        L = np.zeros((n, nv, nv), np.float32)
+        vals = rng.normal(0.0, 0.3, (n, nM)).astype(np.float32)
+        L[:, rows[offdiag], cols[offdiag]] = vals[:, offdiag]
+        L[:, np.arange(nv), np.arange(nv)] = 1.0
+        D = rng.uniform(0.5, 2.0, (n, nv)).astype(np.float32)
+        dense = np.einsum("wki,wk,wkj->wij", L, D, L, optimize=True).astype(np.float32)
+        dense = 0.5 * (dense + dense.transpose(0, 2, 1))
+        out[lo:hi] = dense[:, rows, cols]
+        dense_all[lo:hi] = dense
+    return out, dense_all
+
+
+def make_problem(
+    m: Model,
+    nworld: int,
+    njmax: int,
+    seed: int = 0,
+    *,
+    nefc_range: tuple[int, int] | None = None,
+    ne: int = 0,
+    nf: int = 0,
+    rows: str = "contacts",
+    rowless_fraction: float = 0.0,
+    warmstart_scale: float = 0.1,
+    poison: bool = False,
+    d_range: tuple[float, float] = (0.1, 10.0),
+) -> tuple[Data, np.ndarray]:
+    """Seeded solver inputs for ``nworld`` worlds; returns (Data, dense M).
+
+    rows = "contacts": inequality rows come in groups of four pyramid edges
+    (Jn +- mu Jt1, Jn +- mu Jt2) on the ancestor chain of one random dof, followed by
+    single-dof joint-limit rows.  rows = "generic": every row is N(0,1) on the union
+    of the ancestor chains of one or two random dofs.  Rows [0, ne) are equality rows,
+    [ne, ne+nf) friction-loss rows on single dofs.  ``poison`` fills rows at and
+    beyond nefc with NaN so that a kernel that reads them is caught.
+    """
+    rng = np.random.default_rng(seed)
+    nv = m.nv
+    d = make_data(m, nworld, njmax)
+    parent = np.asarray(m.dof_parentid)
+    masks = ancestor_masks(parent).astype(np.float32)
+    lo, hi = nefc_range if nefc_range is not None else (njmax // 4, njmax)
+    hi = min(hi, njmax)
+    lo = min(max(lo, ne + nf), hi)
+    nefc = rng.integers(lo, hi + 1, nworld).astype(np.int32)
+    if rowless_fraction > 0:
+        nefc[rng.random(nworld) < rowless_fraction] = 0
+    d.nefc[:] = nefc
+    d.ne[:] = np.where(nefc > 0, ne, 0)
+    d.nf[:] = np.where(nefc > 0, nf, 0)
+    Mv, Mdense = random_mass_matrices(m, nworld, rng)
+    d.M[:] = Mv
+
+    J = d.efc.J
+    R = njmax
+    if rows == "generic":
+        a = rng.integers(0, nv, (nworld, R))
+        b = rng.integers(0, nv, (nworld, R))
+        two = rng.random((nworld, R)) < 0.5
+        mask = masks[a]
+        mask = np.maximum(mask, masks[b] * two[..., None])
+        J[:] = rng.normal(0.0, 1.0, (nworld, R, nv)).astype(np.float32) * mask
+    else:
+        ncon = (R + 3) // 4
+        body = rng.integers(0, nv, (nworld, ncon))
+        mk = masks[body]  # (W, ncon, nv)
+        jn = rng.normal(0.0, 1.0, (nworld, ncon, nv)).astype(np.float32) * mk
+        jt1 = rng.normal(0.0, 1.0, (nworld, ncon, nv)).astype(np.float32) * mk
+        jt2 = rng.normal(0.0, 1.0, (nworld, ncon, nv)).astype(np.float32) * mk
+        mu = rng.uniform(0.5, 1.0, (nworld, ncon, 1)).astype(np.float32)
+        quad = np.stack([jn + mu * jt1, jn - mu * jt1, jn + mu * jt2, jn - mu * jt2], axis=2)
+        J[:] = quad.reshape(nworld, ncon * 4, nv)[:, :R]
+        # the last rows of every world are joint limits on one dof each
+        nlim = rng.integers(0, 7, nworld)
+        for w in range(nworld):
+            k = int(min(nlim[w], max(int(nefc[w]) - ne - nf, 0)))
+            if k:
+                r0 = int(nefc[w]) - k
+                dofs = rng.integers(min(6, nv - 1), nv, k)
+                J[w, r0 : r0 + k] = 0.0
+                J[w, np.arange(r0, r0 + k), dofs] = rng.choice([-1.0, 1.0], k)
+    if ne:
+        a = rng.integers(0, nv, (nworld, ne))
+        J[:, :ne] = rng.normal(0.0, 1.0, (nworld, ne, nv)).astype(np.float32) * masks[a]
+    if nf:
+        dofs = rng.integers(0, nv, (nworld, nf))
+        J[:, ne : ne + nf] = 0.0
+        wi = np.repeat(np.arange(nworld), nf)
+        ri = np.tile(np.arange(ne, ne + nf), nworld)
+        J[wi, ri, dofs.reshape(-1)] = 1.0
+        d.efc.frictionloss[:, ne : ne + nf] = rng.uniform(0.1, 1.0, (nworld, nf)).astype(np.float32)
+    d.efc.D[:] = rng.uniform(d_range[0], d_range[1], (nworld, R)).astype(np.float32)
+    d.efc.aref[:] = rng.normal(0.0, 1.0, (nworld, R)).astype(np.float32)
+
+    qs = rng.normal(0.0, 1.0, (nworld, nv)).astype(np.float32)
+    d.qacc_smooth[:] = qs
+    d.qfrc_smooth[:] = np.einsum("wij,wj->wi", Mdense.astype(np.float64), qs.astype(np.float64)).astype(
+        np.float32
+    )
+    d.qacc_warmstart[:] = qs + warmstart_scale * rng.normal(0.0, 1.0, (nworld, nv)).astype(np.float32)
+    if poison:
+        beyond = np.arange(R)[None, :] >= nefc[:, None]
+        J[beyond] = np.nan
+        d.efc.D[beyond] = np.nan
+        d.efc.aref[beyond] = np.nan
+    return d, Mdense
+
+
+# Named workloads (BASELINE.json configs; see make_workload).
+WORKLOADS = {
+    # name: (tree, njmax, nefc_range, iterations, ls_iterations)
+    "humanoid": (humanoid_tree, 64, (16, 64)),
+    "snu": (snu_like_tree, 128, (24, 128)),
+    "g1": (g1_like_tree, 250, (16, 200)),
+}
+
+
+def make_workload(
+    name: str,
+    nworld: int,
+    seed: int = 0,
+    *,
+    iterations: int = 50,
+    ls_iterations: int = 50,
+    tolerance: float = 1e-8,
+    rowless_fraction: float = 0.0,
+) -> tuple[Model, Data, np.ndarray]:
+    """(Model, Data, dense M) of a named workload on the host."""
+    tree, njmax, nefc_range = WORKLOADS[name]
+    parent, body = tree()
+    m = put_model(
+        parent,
+        iterations=iterations,
+        ls_iterations=ls_iterations,
+        tolerance=tolerance,
+        body_of_dof=body,
+    )
+    d, Mdense = make_problem(
+        m, nworld, njmax, seed, nefc_range=nefc_range, rowless_fraction=rowless_fraction
+    )
+    return m, d, Mdense
+
+
+def make_sweep_point(nv: int, nefc: int, nworld: int, seed: int = 0, **opts):
+    """One point of the isolated sweep: generic rows, ne = nf = 0, R = nefc."""
+    parent, body = limb_tree(nv)
+    m = put_model(parent, body_of_dof=body, **opts)
+    d, Mdense = make_problem(m, nworld, nefc, seed, nefc_range=(nefc, nefc), rows="generic")
+    return m, d, Mdense

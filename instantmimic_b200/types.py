@@ -1,0 +1,55 @@
+"""Enumerations and constants of the solver interface.
+
+Values follow MuJoCo's public headers (mjtConstraintState, mjtCone, mjtSolver,
+mjtIntegrator, mjtDisableBit); the reference reads them from
+``mujoco_warp._src.types`` (src/instantmimic/utils/mjw_kernels/private.py:8-55).
+``OverflowType`` and ``ALPHA_NOISE_EPS`` belong to mujoco-warp 3.16.0, whose
+source is not available; the values here are this package's defaults and the
+adapter overrides them from the live upstream module when one is importable.
+"""
+
+from __future__ import annotations
+
+import enum
+
+
+class ConstraintState(enum.IntEnum):
+    SATISFIED = 0
+    QUADRATIC = 1
+    LINEARNEG = 2
+    LINEARPOS = 3
+    CONE = 4
+
+
+class ConeType(enum.IntEnum):
+    PYRAMIDAL = 0
+    ELLIPTIC = 1
+
+
+class SolverType(enum.IntEnum):
+    PGS = 0
+    CG = 1
+    NEWTON = 2
+
+
+class IntegratorType(enum.IntEnum):
+    EULER = 0
+    RK4 = 1
+    IMPLICIT = 2
+    IMPLICITFAST = 3
+    DISCRETE = 4
+
+
+class DisableBit(enum.IntFlag):
+    WARMSTART = 1 << 8
+
+
+class OverflowType(enum.IntFlag):
+    ITERATIONS = 1
+    LS_ITERATIONS = 2
+    BROADPHASE = 4
+
+
+MJ_MINVAL = 1e-15
+MJ_MAXVAL = 1e10
+ALPHA_NOISE_EPS = 1e-6
