@@ -74,6 +74,9 @@ typedef struct ImnModel {
   const int32_t* M_mulm_rowadr;
   const int32_t* M_mulm_col;
   const int32_t* M_mulm_madr;
+  /* the same table, one word per entry: col | madr << 16 (2 nM - nv entries);
+   * built once per model by the host layer                                    */
+  const uint32_t* M_mulm_pack;
   /* constants that live in the upstream solver module                         */
   float alpha_noise_eps;          /* solver._ALPHA_NOISE_EPS                    */
   int32_t overflow_iterations;    /* types.OverflowType.ITERATIONS bit          */

@@ -45,6 +45,7 @@ class ImnModel(C.Structure):
         ("M_mulm_rowadr", P),
         ("M_mulm_col", P),
         ("M_mulm_madr", P),
+        ("M_mulm_pack", P),
         ("alpha_noise_eps", F32),
         ("overflow_iterations", I32),
         ("overflow_ls_iterations", I32),

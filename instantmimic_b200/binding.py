@@ -32,6 +32,34 @@ def _upstream_constants() -> tuple[float, int, int]:
         )
 
 
+def _mulm_pack(m: Any):
+    """The packed M_mulm table of a model; built once (and cached on the model) for
+    Model objects that come from mujoco-warp and do not carry it."""
+    pack = getattr(m, "M_mulm_pack", None)
+    if pack is None:
+        pack = getattr(m, "_imn_mulm_pack", None)
+    if pack is None:
+        import numpy as np
+
+        from .mjw_model import pack_mulm
+
+        col, madr = m.M_mulm_col, m.M_mulm_madr
+        to_np = lambda a: a.numpy() if hasattr(a, "numpy") and not hasattr(a, "data_ptr") else (  # noqa: E731
+            a.cpu().numpy() if hasattr(a, "cpu") else np.asarray(a))
+        host = pack_mulm(to_np(col), to_np(madr))
+        if isinstance(col, np.ndarray):
+            pack = host
+        else:
+            import torch
+
+            pack = torch.from_numpy(host).to("cuda")
+        try:
+            m._imn_mulm_pack = pack
+        except AttributeError:
+            pass
+    return pack
+
+
 def model_struct(m: Any) -> abi.ImnModel:
     eps, ovf_it, ovf_ls = _upstream_constants()
     s = abi.ImnModel()
@@ -53,6 +81,7 @@ def model_struct(m: Any) -> abi.ImnModel:
     s.M_mulm_rowadr = addr(m.M_mulm_rowadr)
     s.M_mulm_col = addr(m.M_mulm_col)
     s.M_mulm_madr = addr(m.M_mulm_madr)
+    s.M_mulm_pack = addr(_mulm_pack(m))
     s.alpha_noise_eps = eps
     s.overflow_iterations = ovf_it
     s.overflow_ls_iterations = ovf_ls

@@ -8,54 +8,104 @@
 //
 // B200 mapping.  The solve is latency-bound small dense algebra (nv <= 79), not a
 // tensor-core contraction, so the design goal is to touch HBM exactly once: a CTA
-// is one warp that owns one world, loads that world's J, M and row data into
-// shared memory with coalesced reads, keeps the Hessian, its Cholesky factor and
-// every vector on chip for all iterations, and writes the results once.  A warp
-// needs no block barrier (only __syncwarp), lane reductions are shuffle trees,
-// and the hardware CTA scheduler balances worlds whose iteration counts differ.
-// Worlds with more rows than fit on chip stream J through a 32-row staging tile.
+// is one warp that owns one world.  Its J, M and row data arrive in shared memory
+// through TMA bulk copies (cp.async.bulk, one mbarrier), the Hessian, its
+// Cholesky factor and every vector stay on chip for all iterations, and the
+// results are written once.  A warp needs no block barrier (only __syncwarp),
+// lane reductions are shuffle trees, and the hardware CTA scheduler balances
+// worlds whose iteration counts differ.  Worlds with more rows than fit on chip
+// stream J through a 32-row staging tile.
 //
 // Arithmetic contract.  Every value that decides an active set or an iteration
 // count is formed by the same float32 operations in the same order as the CPU
 // oracle used by the tests: explicit fmaf chains in ascending index order,
-// shuffle-down trees for lane sums, IEEE sqrt and division.
+// shuffle-down trees for lane sums, IEEE sqrt and division.  Blocking, register
+// tiling and the lane mapping never change the order in which one value
+// receives its terms.
 #include <stdio.h>
 
 #include "imn_common.cuh"
 
 namespace imn {
 
+// Phase timers, compiled only into the profiling build (-DIMN_PROFILE).
+#ifdef IMN_PROFILE
+__device__ unsigned long long g_prof[16];
+#define PROF_DECL long long prof_t = clock64(); long long prof_acc[12] = {0}
+#define PROF(k) do { const long long t_ = clock64(); prof_acc[k] += t_ - prof_t; prof_t = t_; } while (0)
+#define PROF_FLUSH do { if (lane == 0) for (int k_ = 0; k_ < 12; ++k_) atomicAdd(&g_prof[k_], (unsigned long long)prof_acc[k_]); } while (0)
+#else
+#define PROF_DECL
+#define PROF(k)
+#define PROF_FLUSH
+#endif
+
+// Internal error bit OR-ed into `overflow` when the input copies of a world do not
+// complete within the wait limit (the world is left unsolved).
+#define IMN_OVERFLOW_COPY_TIMEOUT (1 << 30)
+
 struct Geom {
-  int nv, njmax, ldj, lda, nM, bd;
+  int nv, njmax, ldj, ldu, nM, bd;
   int jrows;  // rows of J held in shared memory (njmax when resident, else 32)
-  // offsets in 4-byte words
-  int oJ, oA, oVec, oM, oRowF, oRowI, oUni, total;
+  // offsets in 4-byte words; every region starts on a 16-byte boundary
+  int oBar, oJ, oA, oVec, nv4, oM, oRowF, oRowI, r4, oUni, total;
 };
 
-__host__ __device__ inline int odd_up(int n) { return n | 1; }
+static inline int up4(int n) { return (n + 3) & ~3; }
 
 static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident) {
   Geom g;
   g.nv = m.nv;
   g.njmax = d.njmax;
-  g.ldj = odd_up(m.nv);
-  g.lda = odd_up(m.nv + 1);
+  g.ldj = (int)d.J_ld_row;
+  g.ldu = up4(m.nv + 1);
   g.nM = m.nM;
   g.bd = m.nv_pad >= 64 ? 64 : 32;
   g.jrows = resident ? d.njmax : 32;
+  g.nv4 = up4(m.nv);
+  g.r4 = up4(d.njmax);
   int o = 0;
-  g.oJ = o, o += g.jrows * g.ldj;
-  g.oA = o, o += (m.nv + 1) * g.lda;
-  g.oVec = o, o += 8 * m.nv;
-  g.oM = o, o += m.nM;
-  g.oRowF = o, o += 5 * d.njmax;
-  g.oRowI = o, o += 3 * d.njmax;
-  g.oUni = o, o += m.nv + 1;
+  g.oBar = o, o += 4;
+  g.oJ = o, o += up4(g.jrows * g.ldj);
+  g.oA = o, o += (m.nv + 1) * g.ldu;
+  g.oVec = o, o += 8 * g.nv4;
+  g.oM = o, o += up4(m.nM);
+  g.oRowF = o, o += 5 * g.r4;
+  g.oRowI = o, o += 3 * g.r4;
+  g.oUni = o, o += up4(m.nv + 1);
   g.total = o;
   return g;
 }
 
-// ---- row cost pieces (see oracle/newton_oracle.c for the statement) ---------
+// ---- TMA bulk copy + mbarrier (sm_90+ PTX) -----------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(void* bar, int count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, void* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   smem_u32(dst)),
+               "l"(src), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(void* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// ---- row cost pieces (the statement is in oracle/newton_oracle.c) -------------
 __device__ __forceinline__ int row_zone(float x, bool fr, float rf) {
   if (fr) return x <= -rf ? IMN_STATE_LINEARNEG : (x >= rf ? IMN_STATE_LINEARPOS : IMN_STATE_QUADRATIC);
   return x >= 0.0f ? IMN_STATE_SATISFIED : IMN_STATE_QUADRATIC;
@@ -66,39 +116,58 @@ __device__ __forceinline__ float zone_cost(int z, float x, float D, float f, flo
   if (z == IMN_STATE_LINEARPOS) return f * (-0.5f * rf + x);
   return 0.0f;
 }
-__device__ __forceinline__ Vec3 zone_slope(int z, float x, float D, float f, float jv) {
-  if (z == IMN_STATE_QUADRATIC) {
-    const float jvD = jv * D;
-    return v3(0.0f, jvD * x, jv * jvD);
-  }
-  if (z == IMN_STATE_LINEARNEG) return v3(0.0f, -f * jv, 0.0f);
-  if (z == IMN_STATE_LINEARPOS) return v3(0.0f, f * jv, 0.0f);
+// One constraint row prepared for repeated evaluation along the search direction.
+struct Row {
+  float D, ja, j, f, rf, jvD, h, q1r, cost0;
+  int z0;
+  bool fr, valid;
+};
+__device__ __forceinline__ Row make_row(bool valid, bool fr, float f, float D, float ja, float j) {
+  Row r;
+  r.valid = valid, r.fr = fr, r.f = fr ? f : 0.0f, r.D = D, r.ja = ja, r.j = j;
+  r.rf = fr ? safe_div(f, D) : 0.0f;
+  r.z0 = row_zone(ja, fr, r.rf);
+  r.jvD = j * D;
+  r.h = j * r.jvD;
+  r.q1r = r.jvD * ja;
+  r.cost0 = zone_cost(r.z0, ja, D, r.f, r.rf);
+  return r;
+}
+// (cost, slope, curvature) at alpha = 0
+__device__ __forceinline__ Vec3 row_at_zero(const Row& r) {
+  if (!r.valid) return v3(0.0f, 0.0f, 0.0f);
+  if (r.z0 == IMN_STATE_QUADRATIC) return v3(r.cost0, r.q1r, r.h);
+  if (r.z0 == IMN_STATE_LINEARNEG) return v3(r.cost0, -r.f * r.j, 0.0f);
+  if (r.z0 == IMN_STATE_LINEARPOS) return v3(r.cost0, r.f * r.j, 0.0f);
   return v3(0.0f, 0.0f, 0.0f);
 }
-__device__ __forceinline__ Vec3 eval_row_zero(bool fr, float f, float D, float jaref, float jv) {
-  const float rf = fr ? safe_div(f, D) : 0.0f;
-  const int z = row_zone(jaref, fr, rf);
-  Vec3 r = zone_slope(z, jaref, D, f, jv);
-  r.c0 = zone_cost(z, jaref, D, f, rf);
-  return r;
-}
-__device__ __forceinline__ Vec3 eval_row(bool fr, float f, float alpha, float D, float jaref,
-                                         float jv) {
-  const float rf = fr ? safe_div(f, D) : 0.0f;
-  const float x = fmaf(alpha, jv, jaref);
-  const int z0 = row_zone(jaref, fr, rf), z = row_zone(x, fr, rf);
-  Vec3 r = zone_slope(z, x, D, f, jv);
-  if (z != z0) {
-    r.c0 = zone_cost(z, x, D, f, rf) - zone_cost(z0, jaref, D, f, rf);
-  } else if (z == IMN_STATE_QUADRATIC) {
-    const float jvD = jv * D;
-    r.c0 = alpha * fmaf(0.5f * alpha, jv * jvD, jvD * jaref);
-  } else if (z == IMN_STATE_LINEARNEG) {
-    r.c0 = -f * (alpha * jv);
-  } else if (z == IMN_STATE_LINEARPOS) {
-    r.c0 = f * (alpha * jv);
+// (cost(alpha) - cost(0), slope, curvature) at alpha
+__device__ __forceinline__ Vec3 row_at(const Row& r, float alpha) {
+  if (!r.valid) return v3(0.0f, 0.0f, 0.0f);
+  const float x = fmaf(alpha, r.j, r.ja);
+  if (!r.fr) {
+    const bool on = x < 0.0f, on0 = r.z0 == IMN_STATE_QUADRATIC;
+    float c = 0.0f;
+    if (on && on0)
+      c = alpha * fmaf(0.5f * alpha, r.h, r.q1r);
+    else if (on != on0)
+      c = (on ? ((0.5f * r.D) * x) * x : 0.0f) - r.cost0;
+    return v3(c, on ? r.jvD * x : 0.0f, on ? r.h : 0.0f);
   }
-  return r;
+  const int z = row_zone(x, true, r.rf);
+  Vec3 o = v3(0.0f, 0.0f, 0.0f);
+  if (z == IMN_STATE_QUADRATIC) o.c1 = r.jvD * x, o.c2 = r.h;
+  if (z == IMN_STATE_LINEARNEG) o.c1 = -r.f * r.j;
+  if (z == IMN_STATE_LINEARPOS) o.c1 = r.f * r.j;
+  if (z != r.z0)
+    o.c0 = zone_cost(z, x, r.D, r.f, r.rf) - r.cost0;
+  else if (z == IMN_STATE_QUADRATIC)
+    o.c0 = alpha * fmaf(0.5f * alpha, r.h, r.q1r);
+  else if (z == IMN_STATE_LINEARNEG)
+    o.c0 = -r.f * (alpha * r.j);
+  else
+    o.c0 = r.f * (alpha * r.j);
+  return o;
 }
 __device__ __forceinline__ Vec3 eval_quad(float q1, float q2, float alpha) {
   return v3(fmaf(alpha, q1, (alpha * alpha) * q2) + 0.0f, fmaf(2.0f * alpha, q2, q1), 2.0f * q2);
@@ -149,14 +218,27 @@ __device__ __forceinline__ float logical_block_sum(int n, int bd, int lane, F te
   return s;
 }
 
-// First-warp reduction of the line search plus "+0" per later logical warp.
-__device__ __forceinline__ float ls_sum(float v, int bd) {
-  float s = warp_tree_sum(v);
-  if (bd == 64) s = s + 0.0f;
-  return s;
+// Shuffle-down trees of N values at once (independent chains interleave), lane 0
+// broadcast, then "+0" per later logical warp of the line search
+// (newton_stages.py:39-49).
+template <int N>
+__device__ __forceinline__ void ls_sum(float (&v)[N], int bd) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+#pragma unroll
+    for (int k = 0; k < N; ++k) v[k] = v[k] + __shfl_down_sync(IMN_FULL_MASK, v[k], off);
+  }
+#pragma unroll
+  for (int k = 0; k < N; ++k) {
+    v[k] = __shfl_sync(IMN_FULL_MASK, v[k], 0);
+    if (bd == 64) v[k] = v[k] + 0.0f;
+  }
 }
-__device__ __forceinline__ Vec3 ls_sum(Vec3 v, int bd) {
-  return v3(ls_sum(v.c0, bd), ls_sum(v.c1, bd), ls_sum(v.c2, bd));
+
+// advance an upper-triangle pair (i <= j), enumerated column by column, by `step`
+__device__ __forceinline__ void pair_advance(int& i, int& j, int step) {
+  i += step;
+  while (i > j) i -= j + 1, ++j;
 }
 
 template <bool JRES>
@@ -165,193 +247,291 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x;
   const int w = blockIdx.x;
-  const int nv = g.nv, ldj = g.ldj, lda = g.lda, bd = g.bd, R = g.njmax;
+  const int nv = g.nv, ldj = g.ldj, ldu = g.ldu, bd = g.bd, R = g.njmax, nv4 = g.nv4, r4 = g.r4;
 
+  void* bar = smem + g.oBar;
   float* Jsm = smem + g.oJ;
-  float* A = smem + g.oA;  // H[r][c] at A[r*lda+c] (r<=c); U[r][c] at A[(c+1)*lda+r] (r<=c)
+  // A is (nv+1) x ldu.  U[r][c] (r <= c <= nv; column nv carries the right-hand
+  // side) lives at A[r*ldu + c]; H[r][c] (r <= c < nv) at A[(c+1)*ldu + r].
+  float* A = smem + g.oA;
   float* qacc = smem + g.oVec;
-  float* Ma = qacc + nv;
-  float* search = Ma + nv;
-  float* mv = search + nv;
-  float* grad = mv + nv;
-  float* qfs = grad + nv;
-  float* ysm = qfs + nv;
-  float* xsm = ysm + nv;
+  float* Ma = qacc + nv4;
+  float* search = Ma + nv4;
+  float* mv = search + nv4;
+  float* grad = mv + nv4;
+  float* qfs = grad + nv4;
+  float* xsm = qfs + nv4;
+  float* dinv = xsm + nv4;
   float* Msm = smem + g.oM;
   float* Jaref = smem + g.oRowF;
-  float* jv = Jaref + R;
-  float* Dsm = jv + R;
-  float* floss = Dsm + R;
-  float* force = floss + R;
+  float* jv = Jaref + r4;
+  float* Dsm = jv + r4;
+  float* floss = Dsm + r4;
+  float* force = floss + r4;
   int* state = reinterpret_cast<int*>(smem + g.oRowI);
-  int* ids = state + R;
-  int* act = ids + R;
+  int* ids = state + r4;
+  int* frows = ids + r4;  // rows with a nonzero force, ascending
   int* uni = reinterpret_cast<int*>(smem + g.oUni);
 
+  PROF_DECL;
   const int nefc_in = d.nefc[w];
   const int nefc = min(R, nefc_in);
   const int ne = d.ne[w], nf = d.nf[w], nef = ne + nf;
   const bool rowless = nefc_in == 0;
   const size_t dofo = (size_t)w * d.dof_ld, efco = (size_t)w * d.efc_ld;
   const float* Jg = d.efc_J + (size_t)w * d.J_ld_world;
-  const int ldjg = (int)d.J_ld_row;
 
-  // ---- load (coalesced, once) ------------------------------------------------
+  // ---- load: TMA bulk copies for the 16-byte-aligned bulk of every array, plain
+  // loads for the ragged ends -----------------------------------------------------
   {
     const float* q0 = (m.warmstart && !rowless) ? d.qacc_warmstart : d.qacc_smooth;
-    for (int i = lane; i < nv; i += 32) {
-      qacc[i] = q0[dofo + i];
-      qfs[i] = d.qfrc_smooth[dofo + i];
-      search[i] = 0.0f, mv[i] = 0.0f, grad[i] = 0.0f;
-    }
-    for (int i = lane; i <= nv; i += 32) uni[i] = 0;
-    const float* Mg = d.M + (size_t)w * d.M_ld;
-    for (int e = lane; e < g.nM; e += 32) Msm[e] = Mg[e];
-    for (int r = lane; r < nefc; r += 32) {
-      Dsm[r] = d.efc_D[efco + r];
-      floss[r] = d.efc_frictionloss[efco + r];
-      jv[r] = 0.0f;
-    }
-    if (JRES) {
-      int rr = 0, cc = lane;
-      while (cc >= nv) cc -= nv, ++rr;
-      while (rr < nefc) {
-        Jsm[rr * ldj + cc] = Jg[(size_t)rr * ldjg + cc];
-        cc += 32;
-        while (cc >= nv) cc -= nv, ++rr;
+    struct Src {
+      float* dst;
+      const float* src;
+      int n;
+    };
+    const Src srcs[7] = {
+        {Jsm, Jg, JRES ? nefc * ldj : 0},
+        {Msm, d.M + (size_t)w * d.M_ld, g.nM},
+        {Dsm, d.efc_D + efco, nefc},
+        {floss, d.efc_frictionloss + efco, nefc},
+        {jv, d.efc_aref + efco, nefc},  // aref is parked in jv until Jaref is formed
+        {qacc, q0 + dofo, nv},
+        {qfs, d.qfrc_smooth + dofo, nv},
+    };
+    if (lane == 0) mbar_init(bar, 1);
+    __syncwarp();
+    uint32_t tx = 0;
+#pragma unroll
+    for (int k = 0; k < 7; ++k)
+      if ((reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0) tx += (uint32_t)(srcs[k].n & ~3) * 4u;
+    if (lane == 0) {
+      mbar_expect_tx(bar, tx);
+#pragma unroll
+      for (int k = 0; k < 7; ++k) {
+        const uint32_t bytes =
+            (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0 ? (uint32_t)(srcs[k].n & ~3) * 4u : 0u;
+        if (bytes) bulk_g2s(srcs[k].dst, srcs[k].src, bytes, bar);
       }
+    }
+#pragma unroll
+    for (int k = 0; k < 7; ++k) {
+      const int done_n = (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0 ? (srcs[k].n & ~3) : 0;
+      for (int i = done_n + lane; i < srcs[k].n; i += 32) srcs[k].dst[i] = srcs[k].src[i];
+    }
+    for (int i = lane; i < nv; i += 32) search[i] = 0.0f, mv[i] = 0.0f, grad[i] = 0.0f;
+    for (int i = lane; i <= nv; i += 32) uni[i] = 0;
+    // bounded wait for the copies
+    bool arrived = false;
+    for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) arrived = mbar_try_wait(bar, 0);
+    if (!arrived) {
+      if (lane == 0) d.overflow[w] |= IMN_OVERFLOW_COPY_TIMEOUT;
+      return;
     }
   }
   __syncwarp();
+  PROF(0);
 
   // stage rows [base, base+32) of J when it is not resident
   auto tile = [&](int base) -> const float* {
     if (JRES) return Jsm + base * ldj;
     __syncwarp();
-    const int rows = min(32, nefc - base);
-    int rr = 0, cc = lane;
-    while (cc >= nv) cc -= nv, ++rr;
-    while (rr < rows) {
-      Jsm[rr * ldj + cc] = Jg[(size_t)(base + rr) * ldjg + cc];
-      cc += 32;
-      while (cc >= nv) cc -= nv, ++rr;
-    }
+    const int n = min(32, nefc - base) * ldj;
+    const float* src = Jg + (size_t)base * ldj;
+    for (int i = lane; i < n; i += 32) Jsm[i] = src[i];
     __syncwarp();
     return Jsm;
   };
-  auto Jat = [&](int r, int i) -> float {
-    return JRES ? Jsm[r * ldj + i] : Jg[(size_t)r * ldjg + i];
-  };
+  auto Jat = [&](int r, int i) -> float { return JRES ? Jsm[r * ldj + i] : Jg[(size_t)r * ldj + i]; };
   // out = M v over the symmetric rows (newton_fusion.py:171-176)
   auto mul_m = [&](const float* v, float* out) {
     for (int i = lane; i < nv; i += 32) {
       float s = 0.0f;
-      const int k1 = m.M_mulm_rowadr[i + 1];
-      for (int k = m.M_mulm_rowadr[i]; k < k1; ++k) s = fmaf(Msm[m.M_mulm_madr[k]], v[m.M_mulm_col[k]], s);
+      const int k1 = __ldg(m.M_mulm_rowadr + i + 1);
+      int k = __ldg(m.M_mulm_rowadr + i);
+      for (; k + 4 <= k1; k += 4) {
+        const uint32_t p0 = __ldg(m.M_mulm_pack + k), p1 = __ldg(m.M_mulm_pack + k + 1);
+        const uint32_t p2 = __ldg(m.M_mulm_pack + k + 2), p3 = __ldg(m.M_mulm_pack + k + 3);
+        const float a0 = Msm[p0 >> 16], a1 = Msm[p1 >> 16], a2 = Msm[p2 >> 16], a3 = Msm[p3 >> 16];
+        const float b0 = v[p0 & 0xFFFF], b1 = v[p1 & 0xFFFF], b2 = v[p2 & 0xFFFF], b3 = v[p3 & 0xFFFF];
+        s = fmaf(a0, b0, s);
+        s = fmaf(a1, b1, s);
+        s = fmaf(a2, b2, s);
+        s = fmaf(a3, b3, s);
+      }
+      for (; k < k1; ++k) {
+        const uint32_t p = __ldg(m.M_mulm_pack + k);
+        s = fmaf(Msm[p >> 16], v[p & 0xFFFF], s);
+      }
       out[i] = s;
     }
   };
   // one running sum per row of J v; above 50 dofs in 20-dof partials
-  // (newton_stages.py:157-174); first_minus is subtracted from the first partial
+  // (newton_stages.py:157-174); `minus` is subtracted from the first partial
   auto row_dots = [&](const float* v, float* out, const float* minus) {
     for (int base = 0; base < nefc; base += 32) {
       const float* Jt = tile(base);
       const int r = base + lane;
       if (r < nefc) {
         const float* Jr = Jt + lane * ldj;
+        const float sub = minus ? minus[r] : 0.0f;
         float res;
         if (nv > 50) {
           float total = 0.0f;
           for (int s0 = 0; s0 < nv; s0 += 20) {
             float p = 0.0f;
             const int e = min(s0 + 20, nv);
+#pragma unroll 4
             for (int i = s0; i < e; ++i) p = fmaf(Jr[i], v[i], p);
             if (s0 == 0)
-              total = minus ? p - minus[efco + r] : 0.0f + p;
+              total = minus ? p - sub : 0.0f + p;
             else
               total = total + p;
           }
           res = total;
         } else {
           float p = 0.0f;
+#pragma unroll 8
           for (int i = 0; i < nv; ++i) p = fmaf(Jr[i], v[i], p);
-          res = minus ? p - minus[efco + r] : p;
+          res = minus ? p - sub : p;
         }
         out[r] = res;
       }
+      if (!JRES) __syncwarp();
     }
   };
-  // grad = Ma - qfrc_smooth - J^T force, grad_dot (newton_stages.py:785-795)
-  auto full_gradient = [&]() -> float {
+  // grad = Ma - qfrc_smooth - J^T force over the rows with a nonzero force
+  // (a zero force leaves the running sums unchanged), then grad_dot
+  // (newton_stages.py:785-795)
+  auto full_gradient = [&](int nfr) -> float {
     float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
     const int i0 = lane, i1 = lane + 32, i2 = lane + 64;
-    for (int base = 0; base < nefc; base += 32) {
-      const float* Jt = tile(base);
-      const int rows = JRES ? nefc : min(32, nefc - base);
-      for (int rr = 0; rr < rows; ++rr) {
-        const float f = force[base + rr];
-        if (f != 0.0f) {
-          const float* Jr = Jt + rr * ldj;
-          if (i0 < nv) s0 = fmaf(Jr[i0], f, s0);
-          if (i1 < nv) s1 = fmaf(Jr[i1], f, s1);
-          if (i2 < nv) s2 = fmaf(Jr[i2], f, s2);
-        }
+    const bool h1 = i1 < nv, h2 = i2 < nv;
+    if (JRES) {
+      int a = 0;
+      for (; a + 2 <= nfr; a += 2) {
+        const int ra = frows[a], rb = frows[a + 1];
+        const float fa = force[ra], fb = force[rb];
+        const float* Ja = Jsm + ra * ldj;
+        const float* Jb = Jsm + rb * ldj;
+        if (i0 < nv) s0 = fmaf(Jb[i0], fb, fmaf(Ja[i0], fa, s0));
+        if (h1) s1 = fmaf(Jb[i1], fb, fmaf(Ja[i1], fa, s1));
+        if (h2) s2 = fmaf(Jb[i2], fb, fmaf(Ja[i2], fa, s2));
       }
-      if (JRES) break;
-    }
-    if (i0 < nv) grad[i0] = (Ma[i0] - qfs[i0]) - s0;
-    if (i1 < nv) grad[i1] = (Ma[i1] - qfs[i1]) - s1;
-    if (i2 < nv) grad[i2] = (Ma[i2] - qfs[i2]) - s2;
-    __syncwarp();
-    return logical_block_sum(nv, bd, lane, [&](int i, float a) { return fmaf(grad[i], grad[i], a); });
-  };
-  // Upper Cholesky with the right-hand side as one more column, then the back
-  // substitution (newton_stages.py:546-609).  Returns (sum x^2, sum grad x).
-  auto factor_solve = [&](bool factor, float& sum0, float& sum1) {
-    if (factor) {
-      for (int r = 0; r < nv; ++r) {
-        const float* colr = A + (r + 1) * lda;
-        float acc[3];
-        float diag = 0.0f;
-#pragma unroll
-        for (int k = 0; k < 3; ++k) {
-          const int c = r + lane + 32 * k;
-          if (c <= nv) {
-            float a = c < nv ? A[r * lda + c] : grad[r];
-            const float* colc = c < nv ? A + (c + 1) * lda : ysm;
-            for (int t = 0; t < r; ++t) a = fmaf(-colr[t], colc[t], a);
-            acc[k] = a;
-            if (c == r) diag = sqrtf(a);
-          }
-        }
-        diag = __shfl_sync(IMN_FULL_MASK, diag, 0);
-#pragma unroll
-        for (int k = 0; k < 3; ++k) {
-          const int c = r + lane + 32 * k;
-          if (c <= nv) {
-            float* colc = c < nv ? A + (c + 1) * lda : ysm;
-            colc[r] = (c == r) ? diag : acc[k] / diag;
-          }
+      if (a < nfr) {
+        const int ra = frows[a];
+        const float fa = force[ra];
+        const float* Ja = Jsm + ra * ldj;
+        if (i0 < nv) s0 = fmaf(Ja[i0], fa, s0);
+        if (h1) s1 = fmaf(Ja[i1], fa, s1);
+        if (h2) s2 = fmaf(Ja[i2], fa, s2);
+      }
+    } else {
+      int a = 0;
+      for (int base = 0; base < nefc; base += 32) {
+        const float* Jt = tile(base);
+        for (; a < nfr && frows[a] < base + 32; ++a) {
+          const int r = frows[a];
+          const float f = force[r];
+          const float* Jr = Jt + (r - base) * ldj;
+          if (i0 < nv) s0 = fmaf(Jr[i0], f, s0);
+          if (h1) s1 = fmaf(Jr[i1], f, s1);
+          if (h2) s2 = fmaf(Jr[i2], f, s2);
         }
         __syncwarp();
       }
+    }
+    if (i0 < nv) grad[i0] = (Ma[i0] - qfs[i0]) - s0;
+    if (h1) grad[i1] = (Ma[i1] - qfs[i1]) - s1;
+    if (h2) grad[i2] = (Ma[i2] - qfs[i2]) - s2;
+    __syncwarp();
+    return logical_block_sum(nv, bd, lane, [&](int i, float a) { return fmaf(grad[i], grad[i], a); });
+  };
+
+  // Upper Cholesky H = U^T U with the right-hand side as column nv (forward solve),
+  // then back substitution (newton_stages.py:546-609).  Left-looking in blocks of
+  // 16 rows: a block first takes the updates of all earlier rows (independent
+  // running sums, register-tiled four rows at a time), then finishes row by row.
+  // Every entry still receives its terms in ascending row order.
+  auto factor_solve = [&](bool factor, float& sum0, float& sum1) {
+    if (factor) {
+      for (int b0 = 0; b0 < nv; b0 += 16) {
+        const int b1 = min(b0 + 16, nv);
+        // phase 1: terms of rows t < b0
+        for (int r0 = b0; r0 < b1; r0 += 4) {
+          for (int c = r0 + lane; c <= nv; c += 32) {
+            float a0, a1, a2, a3;
+            if (c < nv) {
+              const float* Hc = A + (c + 1) * ldu;
+              a0 = Hc[r0];
+              a1 = (r0 + 1 <= c) ? Hc[r0 + 1] : 0.0f;
+              a2 = (r0 + 2 <= c) ? Hc[r0 + 2] : 0.0f;
+              a3 = (r0 + 3 <= c) ? Hc[r0 + 3] : 0.0f;
+            } else {
+              a0 = grad[r0];
+              a1 = r0 + 1 < nv ? grad[r0 + 1] : 0.0f;
+              a2 = r0 + 2 < nv ? grad[r0 + 2] : 0.0f;
+              a3 = r0 + 3 < nv ? grad[r0 + 3] : 0.0f;
+            }
+#pragma unroll 4
+            for (int t = 0; t < b0; ++t) {
+              const float* Ut = A + t * ldu;
+              const float uc = Ut[c];
+              const float4 ur = *reinterpret_cast<const float4*>(Ut + r0);  // r0 % 4 == 0
+              a0 = fmaf(-ur.x, uc, a0);
+              a1 = fmaf(-ur.y, uc, a1);
+              a2 = fmaf(-ur.z, uc, a2);
+              a3 = fmaf(-ur.w, uc, a3);
+            }
+            A[r0 * ldu + c] = a0;
+            if (r0 + 1 < b1 && r0 + 1 <= c) A[(r0 + 1) * ldu + c] = a1;
+            if (r0 + 2 < b1 && r0 + 2 <= c) A[(r0 + 2) * ldu + c] = a2;
+            if (r0 + 3 < b1 && r0 + 3 <= c) A[(r0 + 3) * ldu + c] = a3;
+          }
+        }
+        __syncwarp();
+        // phase 2: terms of rows b0 <= t < r, pivot, scale
+        for (int r = b0; r < b1; ++r) {
+          float acc[3];
+          float dg = 0.0f;
+#pragma unroll
+          for (int k = 0; k < 3; ++k) {
+            const int c = r + lane + 32 * k;
+            if (c <= nv) {
+              float a = A[r * ldu + c];
+              for (int t = b0; t < r; ++t) a = fmaf(-A[t * ldu + r], A[t * ldu + c], a);
+              acc[k] = a;
+              if (k == 0 && lane == 0) dg = sqrtf(a);
+            }
+          }
+          dg = __shfl_sync(IMN_FULL_MASK, dg, 0);
+          const float rinv = 1.0f / dg;
+#pragma unroll
+          for (int k = 0; k < 3; ++k) {
+            const int c = r + lane + 32 * k;
+            if (c <= nv) A[r * ldu + c] = (c == r) ? dg : acc[k] * rinv;
+          }
+          if (lane == 0) dinv[r] = rinv;
+          __syncwarp();
+        }
+      }
     } else {
-      // forward substitution with the stored factor: updates reach each
-      // unknown in ascending order, as in the factor's augmented column
+      // forward substitution with the stored factor; an unknown receives its
+      // terms in ascending order exactly as the factor's carried column does
       float acc[3];
 #pragma unroll
       for (int k = 0; k < 3; ++k) acc[k] = (lane + 32 * k) < nv ? grad[lane + 32 * k] : 0.0f;
       for (int t = 0; t < nv; ++t) {
         const int k0 = t >> 5;
-        float mine = k0 == 0 ? acc[0] : (k0 == 1 ? acc[1] : acc[2]);
-        float yt = 0.0f;
-        if ((t & 31) == lane) yt = mine / A[(t + 1) * lda + t];
+        const float mine = k0 == 0 ? acc[0] : (k0 == 1 ? acc[1] : acc[2]);
+        float yt = mine * dinv[t];
         yt = __shfl_sync(IMN_FULL_MASK, yt, t & 31);
-        if (lane == 0) ysm[t] = yt;
+        if (lane == 0) A[t * ldu + nv] = yt;
+        const float* Ut = A + t * ldu;
 #pragma unroll
         for (int k = 0; k < 3; ++k) {
           const int r = lane + 32 * k;
-          if (r > t && r < nv) acc[k] = fmaf(-A[(r + 1) * lda + t], yt, acc[k]);
+          if (r > t && r < nv) acc[k] = fmaf(-Ut[r], yt, acc[k]);
         }
       }
       __syncwarp();
@@ -361,16 +541,17 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
     for (int b0 = ((nv - 1) / 16) * 16; b0 >= 0; b0 -= 16) {
       const int b1 = min(b0 + 16, nv);
       const int r = b0 + lane;
-      float acc = 0.0f;
+      const float* Ur = A + r * ldu;
+      float acc = 0.0f, di = 0.0f;
       if (r < b1) {
-        acc = ysm[r];
-        for (int c = b1; c < nv; ++c) acc = fmaf(-A[(c + 1) * lda + r], xsm[c], acc);
+        acc = Ur[nv];
+        di = dinv[r];
+#pragma unroll 4
+        for (int c = b1; c < nv; ++c) acc = fmaf(-Ur[c], xsm[c], acc);
       }
       for (int c = b1 - 1; c >= b0; --c) {
-        float xc = 0.0f;
-        if (r == c) xc = acc / A[(c + 1) * lda + c];
-        xc = __shfl_sync(IMN_FULL_MASK, xc, c - b0);
-        if (r < c && r >= b0) acc = fmaf(-A[(c + 1) * lda + r], xc, acc);
+        const float xc = __shfl_sync(IMN_FULL_MASK, acc * di, c - b0);
+        if (r < c) acc = fmaf(-Ur[c], xc, acc);
         if (lane == 0) xsm[c] = xc;
       }
       __syncwarp();
@@ -382,69 +563,88 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   };
 
   // ---- init ----------------------------------------------------------------
-  row_dots(qacc, Jaref, d.efc_aref);
+  row_dots(qacc, Jaref, jv);  // Jaref = J qacc - aref (aref parked in jv)
   mul_m(qacc, Ma);
   __syncwarp();
 
   float search_dot = 0.0f, grad_dot = 0.0f, grad_scale = 1.0f, decrement = 0.0f;
   float improvement = 0.0f, alpha = 0.0f;
-  int quad_count = 0, state_count = 0, niter = 0, overflow = 0;
+  int quad_count = 0, state_count = 0, niter = 0, overflow = 0, nfr = 0;
   bool search_unchanged = false, ls_exhausted = false;
 
   if (!rowless) {
-    // _update_constraint: force / state of every row, and the list of QUADRATIC rows
-    int nact = 0;
+    // _update_constraint: force / state of every row; rows with a force, ascending
     for (int base = 0; base < nefc; base += 32) {
       const int r = base + lane;
-      int st = IMN_STATE_SATISFIED;
+      float f = 0.0f;
       if (r < nefc) {
         const bool is_eq = r < ne, is_fr = !is_eq && r < nef;
-        float f;
+        int st;
         eval_constraint(is_eq, is_fr, Jaref[r], Dsm[r], is_fr ? floss[r] : 0.0f, f, st);
         force[r] = f;
         state[r] = st;
+        jv[r] = 0.0f;
       }
-      const unsigned mask = __ballot_sync(IMN_FULL_MASK, r < nefc && st == IMN_STATE_QUADRATIC);
-      if (r < nefc && st == IMN_STATE_QUADRATIC) act[nact + __popc(mask & ((1u << lane) - 1u))] = r;
-      nact += __popc(mask);
+      const unsigned mask = __ballot_sync(IMN_FULL_MASK, f != 0.0f);
+      if (f != 0.0f) frows[nfr + __popc(mask & ((1u << lane) - 1u))] = r;
+      nfr += __popc(mask);
     }
     __syncwarp();
-    grad_dot = full_gradient();
+    PROF(1);
+    grad_dot = full_gradient(nfr);
+    PROF(2);
     // H = M + J^T diag(D, QUADRATIC rows) J on the upper triangle, rows ascending
-    for (int e = lane; e < (nv + 1) * lda; e += 32) A[e] = 0.0f;
+    for (int e = lane; e < (nv + 1) * ldu; e += 32) A[e] = 0.0f;
     __syncwarp();
     for (int i = lane; i < nv; i += 32) {
       // the symmetric row of dof i lists every stored entry (i, c); keep c >= i
-      const int k1 = m.M_mulm_rowadr[i + 1];
-      for (int k = m.M_mulm_rowadr[i]; k < k1; ++k) {
-        const int c = m.M_mulm_col[k];
-        if (c >= i) A[i * lda + c] = Msm[m.M_mulm_madr[k]];
+      const int k1 = __ldg(m.M_mulm_rowadr + i + 1);
+      for (int k = __ldg(m.M_mulm_rowadr + i); k < k1; ++k) {
+        const uint32_t p = __ldg(m.M_mulm_pack + k);
+        const int c = p & 0xFFFF;
+        if (c >= i) A[(c + 1) * ldu + i] = Msm[p >> 16];
       }
     }
     __syncwarp();
     const int npair = nv * (nv + 1) / 2;
-    for (int base = 0; base < nefc; base += 32) {
-      const float* Jt = tile(base);
-      const int row_hi = JRES ? nefc : min(base + 32, nefc);
-      for (int e = lane; e < npair; e += 32) {
-        int cj = (int)((sqrtf((float)(8 * e + 1)) - 1.0f) * 0.5f);
-        while ((cj + 1) * (cj + 2) / 2 <= e) ++cj;
-        while (cj * (cj + 1) / 2 > e) --cj;
-        const int i = e - cj * (cj + 1) / 2;
-        float v = A[i * lda + cj];
-        for (int a = 0; a < nact; ++a) {
-          const int r = act[a];
-          if (r < base) continue;
-          if (r >= row_hi) break;
-          const float* Jr = Jt + (r - base) * ldj;
-          v = fmaf(Jr[i] * Dsm[r], Jr[cj], v);
+    {
+      int a_lo = 0;
+      for (int base = 0; base < nefc; base += 32) {
+        const float* Jt = tile(base);
+        const int row_hi = JRES ? nefc : min(base + 32, nefc);
+        int a_hi = a_lo;
+        while (a_hi < nfr && frows[a_hi] < row_hi) ++a_hi;
+        // two entries per lane per pass so that their running sums overlap
+        int i0 = lane, j0 = 0, i1 = lane + 32, j1 = 0;
+        pair_advance(i0, j0, 0);
+        pair_advance(i1, j1, 0);
+        for (int e = lane; e < npair; e += 64) {
+          const bool two = e + 32 < npair;
+          float v0 = A[(j0 + 1) * ldu + i0];
+          float v1 = two ? A[(j1 + 1) * ldu + i1] : 0.0f;
+          const int i1c = two ? i1 : i0, j1c = two ? j1 : j0;
+          for (int a = a_lo; a < a_hi; ++a) {
+            const int r = frows[a];
+            if (state[r] != IMN_STATE_QUADRATIC) continue;
+            const float Dr = Dsm[r];
+            const float* Jr = Jt + (r - base) * ldj;
+            v0 = fmaf(Jr[i0] * Dr, Jr[j0], v0);
+            v1 = fmaf(Jr[i1c] * Dr, Jr[j1c], v1);
+          }
+          A[(j0 + 1) * ldu + i0] = v0;
+          if (two) A[(j1 + 1) * ldu + i1] = v1;
+          pair_advance(i0, j0, 64);
+          pair_advance(i1, j1, 64);
         }
-        A[i * lda + cj] = v;
+        a_lo = a_hi;
+        if (JRES) break;
+        __syncwarp();
       }
-      if (JRES) break;
     }
     __syncwarp();
+    PROF(3);
     factor_solve(true, search_dot, decrement);
+    PROF(4);
   }
 
   // ---- Newton iterations (newton_fusion.py:170-296) -----------------------------
@@ -459,27 +659,43 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
       row_dots(search, jv, nullptr);
     }
     __syncwarp();
+    PROF(5);
     // ---- exact line search (newton_stages.py:182-367) ------------------------
     float noise_floor;
     bool ls_converged;
     {
       const float snorm = sqrtf(search_dot);
       const float gtol = fmaxf(tolerance * ls_tolerance * snorm * scale, 1e-06f);
-      float g0 = 0.0f, g1 = 0.0f;
+      float gq[2] = {0.0f, 0.0f};
       for (int i = lane; i < nv; i += 32) {
-        g0 = fmaf(search[i], Ma[i] - qfs[i], g0);
-        g1 = fmaf(0.5f * search[i], mv[i], g1);
+        gq[0] = fmaf(search[i], Ma[i] - qfs[i], gq[0]);
+        gq[1] = fmaf(0.5f * search[i], mv[i], gq[1]);
       }
       for (int r = lane; r < ne; r += 32) {
         const float jvD = jv[r] * Dsm[r];
-        g0 = fmaf(jvD, Jaref[r], g0);
-        g1 = fmaf(0.5f * jv[r], jvD, g1);
+        gq[0] = fmaf(jvD, Jaref[r], gq[0]);
+        gq[1] = fmaf(0.5f * jv[r], jvD, gq[1]);
       }
-      const float q1 = ls_sum(g0, bd), q2 = ls_sum(g1, bd);
-      Vec3 acc = v3(0.0f, 0.0f, 0.0f);
-      for (int r = ne + lane; r < nefc; r += 32)
-        acc = acc + eval_row_zero(r < nef, floss[r], Dsm[r], Jaref[r], jv[r]);
-      const Vec3 rows = ls_sum(acc, bd);
+      ls_sum(gq, bd);
+      const float q1 = gq[0], q2 = gq[1];
+      // the lane's first two rows stay in registers; further rows are re-read
+      const int ra = ne + lane, rb = ra + 32;
+      const Row rowa = ra < nefc ? make_row(true, ra < nef, floss[ra], Dsm[ra], Jaref[ra], jv[ra])
+                                 : make_row(false, false, 0.0f, 1.0f, 0.0f, 0.0f);
+      const Row rowb = rb < nefc ? make_row(true, rb < nef, floss[rb], Dsm[rb], Jaref[rb], jv[rb])
+                                 : make_row(false, false, 0.0f, 1.0f, 0.0f, 0.0f);
+      const bool more = ne + 64 < nefc;
+      float p[3];
+      {
+        Vec3 acc = v3(0.0f, 0.0f, 0.0f) + row_at_zero(rowa);  // running sums start at zero
+        acc = acc + row_at_zero(rowb);
+        if (more)
+          for (int r = rb + 32; r < nefc; r += 32)
+            acc = acc + row_at_zero(make_row(true, r < nef, floss[r], Dsm[r], Jaref[r], jv[r]));
+        p[0] = acc.c0, p[1] = acc.c1, p[2] = acc.c2;
+      }
+      ls_sum(p, bd);
+      const Vec3 rows = v3(p[0], p[1], p[2]);
       const Vec3 p0 = v3(0.0f, q1, 2.0f * q2) + rows;
       const Vec3 p0_delta = v3(0.0f, p0.c1, p0.c2);
       const float q1_abs = sqrtf(2.0f * fmaxf(rows.c0, 0.0f) * fmaxf(rows.c2, 0.0f)) + fabsf(q1);
@@ -490,10 +706,14 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
       const float lo_alpha_in = -safe_div(p0.c1, p0.c2);
       Vec3 lo_in = v3(0.0f, 0.0f, 0.0f);
       if (!ls_converged) {
-        Vec3 a1 = v3(0.0f, 0.0f, 0.0f);
-        for (int r = ne + lane; r < nefc; r += 32)
-          a1 = a1 + eval_row(r < nef, floss[r], lo_alpha_in, Dsm[r], Jaref[r], jv[r]);
-        lo_in = eval_quad(q1, q2, lo_alpha_in) + ls_sum(a1, bd);
+        Vec3 acc = v3(0.0f, 0.0f, 0.0f) + row_at(rowa, lo_alpha_in);
+        acc = acc + row_at(rowb, lo_alpha_in);
+        if (more)
+          for (int r = rb + 32; r < nefc; r += 32)
+            acc = acc + row_at(make_row(true, r < nef, floss[r], Dsm[r], Jaref[r], jv[r]), lo_alpha_in);
+        p[0] = acc.c0, p[1] = acc.c1, p[2] = acc.c2;
+        ls_sum(p, bd);
+        lo_in = eval_quad(q1, q2, lo_alpha_in) + v3(p[0], p[1], p[2]);
         if (fabsf(lo_in.c1) < gtol_accept && lo_in.c0 < 0.0f) {
           ls_converged = true;
           alpha = lo_alpha_in;
@@ -510,17 +730,23 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
           const float a_lo = lo_alpha - safe_div(lo.c1, lo.c2);
           const float a_hi = hi_alpha - safe_div(hi.c1, hi.c2);
           const float a_mid = 0.5f * (lo_alpha + hi_alpha);
-          Vec3 s_lo = v3(0.0f, 0.0f, 0.0f), s_hi = s_lo, s_mid = s_lo;
-          for (int r = ne + lane; r < nefc; r += 32) {
-            const bool fr = r < nef;
-            const float f = floss[r], D = Dsm[r], ja = Jaref[r], j = jv[r];
-            s_lo = s_lo + eval_row(fr, f, a_lo, D, ja, j);
-            s_hi = s_hi + eval_row(fr, f, a_hi, D, ja, j);
-            s_mid = s_mid + eval_row(fr, f, a_mid, D, ja, j);
-          }
-          const Vec3 lo_next = eval_quad(q1, q2, a_lo) + ls_sum(s_lo, bd);
-          const Vec3 hi_next = eval_quad(q1, q2, a_hi) + ls_sum(s_hi, bd);
-          const Vec3 mid = eval_quad(q1, q2, a_mid) + ls_sum(s_mid, bd);
+          const Vec3 z3 = v3(0.0f, 0.0f, 0.0f);
+          Vec3 s_lo = z3 + row_at(rowa, a_lo), s_hi = z3 + row_at(rowa, a_hi), s_mid = z3 + row_at(rowa, a_mid);
+          s_lo = s_lo + row_at(rowb, a_lo);
+          s_hi = s_hi + row_at(rowb, a_hi);
+          s_mid = s_mid + row_at(rowb, a_mid);
+          if (more)
+            for (int r = rb + 32; r < nefc; r += 32) {
+              const Row rr = make_row(true, r < nef, floss[r], Dsm[r], Jaref[r], jv[r]);
+              s_lo = s_lo + row_at(rr, a_lo);
+              s_hi = s_hi + row_at(rr, a_hi);
+              s_mid = s_mid + row_at(rr, a_mid);
+            }
+          float q[9] = {s_lo.c0, s_lo.c1, s_lo.c2, s_hi.c0, s_hi.c1, s_hi.c2, s_mid.c0, s_mid.c1, s_mid.c2};
+          ls_sum(q, bd);
+          const Vec3 lo_next = eval_quad(q1, q2, a_lo) + v3(q[0], q[1], q[2]);
+          const Vec3 hi_next = eval_quad(q1, q2, a_hi) + v3(q[3], q[4], q[5]);
+          const Vec3 mid = eval_quad(q1, q2, a_mid) + v3(q[6], q[7], q[8]);
           const bool conv_lo = fabsf(lo_next.c1) < gtol_accept && lo_next.c0 < 0.0f;
           const bool conv_hi = fabsf(hi_next.c1) < gtol_accept && hi_next.c0 < 0.0f;
           const bool conv_mid = fabsf(mid.c1) < gtol_accept && mid.c0 < 0.0f;
@@ -570,6 +796,7 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
         }
       }
     }
+    PROF(6);
     // ---- move, re-evaluate rows, list QUADRATIC flips (newton_stages.py:373-426)
     for (int i = lane; i < nv; i += 32) {
       qacc[i] = fmaf(alpha, search[i], qacc[i]);
@@ -577,14 +804,15 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
     }
     quad_count = 0;
     state_count = 0;
+    nfr = 0;
     for (int base = 0; base < nefc; base += 32) {
       const int r = base + lane;
       bool flip = false, changed = false;
+      float f = 0.0f;
       if (r < nefc) {
         const float nj = rounded_step(Jaref[r], alpha, jv[r]);
         Jaref[r] = nj;
         const bool is_eq = r < ne, is_fr = !is_eq && r < nef;
-        float f;
         int ns;
         eval_constraint(is_eq, is_fr, nj, Dsm[r], is_fr ? floss[r] : 0.0f, f, ns);
         const int old = state[r];
@@ -593,10 +821,14 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
         flip = (old == IMN_STATE_QUADRATIC) != (ns == IMN_STATE_QUADRATIC);
         changed = old != ns;
       }
+      const unsigned below = (1u << lane) - 1u;
       const unsigned fm = __ballot_sync(IMN_FULL_MASK, flip);
-      if (flip) ids[quad_count + __popc(fm & ((1u << lane) - 1u))] = r;
+      if (flip) ids[quad_count + __popc(fm & below)] = r;
       quad_count += __popc(fm);
       state_count += __popc(__ballot_sync(IMN_FULL_MASK, changed));
+      const unsigned nz = __ballot_sync(IMN_FULL_MASK, f != 0.0f);
+      if (f != 0.0f) frows[nfr + __popc(nz & below)] = r;
+      nfr += __popc(nz);
     }
     ls_exhausted = fabsf(alpha) < noise_floor;
     if (ls_exhausted) state_count += 1;
@@ -607,6 +839,7 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
       overflow |= m.overflow_ls_iterations;
     }
     __syncwarp();
+    PROF(7);
     // ---- gradient (newton_stages.py:745-798) and factor (newton_stages.py:629-740)
     const bool changed = state_count != 0;
     search_unchanged = !changed;
@@ -618,7 +851,8 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
       decrement *= rsq;
       grad_scale = ns;
     } else {
-      grad_dot = full_gradient();
+      grad_dot = full_gradient(nfr);
+      PROF(8);
       decrement = 0.0f;
       grad_scale = 1.0f;
       if (quad_count > 0) {
@@ -635,11 +869,11 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
         }
         if (lane == 0) uni[nv] = n;
         __syncwarp();
-        for (int e = lane; e < n * (n + 1) / 2; e += 32) {
-          int cj = (int)((sqrtf((float)(8 * e + 1)) - 1.0f) * 0.5f);
-          while ((cj + 1) * (cj + 2) / 2 <= e) ++cj;
-          while (cj * (cj + 1) / 2 > e) --cj;
-          const int row = uni[e - cj * (cj + 1) / 2], col = uni[cj];
+        const int npu = n * (n + 1) / 2;
+        int pi = lane, pj = 0;
+        pair_advance(pi, pj, 0);
+        for (int e = lane; e < npu; e += 32) {
+          const int row = uni[pi], col = uni[pj];
           float delta = 0.0f;
           for (int t = 0; t < quad_count; ++t) {
             const int r = ids[t];
@@ -648,11 +882,14 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
             if (state[r] != IMN_STATE_QUADRATIC) da = -da;
             if (a != 0.0f && b != 0.0f) delta = fmaf(da, b, delta);
           }
-          if (delta != 0.0f) A[row * lda + col] = A[row * lda + col] + delta;
+          if (delta != 0.0f) A[(col + 1) * ldu + row] = A[(col + 1) * ldu + row] + delta;
+          pair_advance(pi, pj, 32);
         }
         __syncwarp();
       }
+      PROF(9);
       factor_solve(quad_count > 0, search_dot, decrement);
+      PROF(10);
     }
     // ---- convergence (newton_fusion.py:267-295) -------------------------------
     ++niter;
@@ -693,12 +930,13 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
     const size_t ho = (size_t)w * m.nv_pad * m.nv_pad;
     if (cx.h)
       for (int r = 0; r < nv; ++r)
-        for (int c = r + lane; c < nv; c += 32) cx.h[ho + (size_t)r * m.nv_pad + c] = A[r * lda + c];
+        for (int c = r + lane; c < nv; c += 32) cx.h[ho + (size_t)r * m.nv_pad + c] = A[(c + 1) * ldu + r];
     if (cx.hfactor && !cx.sparse_plan)
       for (int r = 0; r < nv; ++r)
-        for (int c = r + lane; c < nv; c += 32)
-          cx.hfactor[ho + (size_t)r * m.nv_pad + c] = A[(c + 1) * lda + r];
+        for (int c = r + lane; c < nv; c += 32) cx.hfactor[ho + (size_t)r * m.nv_pad + c] = A[r * ldu + c];
   }
+  PROF(11);
+  PROF_FLUSH;
   if (lane == 0) {
     d.solver_niter[w] = niter;
     if (overflow) d.overflow[w] |= overflow;
@@ -735,16 +973,20 @@ static int validate(const ImnModel* m, const ImnData* d, const ImnCtx* cx) {
   if (m->iterations <= 0) return set_error("imn_solve: iterations must be positive"), IMN_ERR_UNSUPPORTED;
   if (m->n_tolerance <= 0 || m->n_ls_tolerance <= 0 || m->n_meaninertia <= 0)
     return set_error("imn_solve: empty option array"), IMN_ERR_SHAPE;
-  const void* need[] = {m->opt_tolerance, m->opt_ls_tolerance, m->stat_meaninertia, m->M_rowadr,
-                        m->M_colind, m->M_mulm_rowadr, m->M_mulm_col, m->M_mulm_madr, d->nefc, d->ne,
-                        d->nf, d->qacc_smooth, d->qacc_warmstart, d->qfrc_smooth, d->efc_J, d->efc_D,
-                        d->efc_aref, d->efc_frictionloss, d->M, d->qacc, d->qfrc_constraint, d->efc_Ma,
-                        d->efc_force, d->efc_state, d->solver_niter, d->overflow};
+  const void* need[] = {m->opt_tolerance, m->opt_ls_tolerance, m->stat_meaninertia, m->M_mulm_rowadr,
+                        m->M_mulm_pack, d->nefc, d->ne, d->nf, d->qacc_smooth, d->qacc_warmstart,
+                        d->qfrc_smooth, d->efc_J, d->efc_D, d->efc_aref, d->efc_frictionloss, d->M, d->qacc,
+                        d->qfrc_constraint, d->efc_Ma, d->efc_force, d->efc_state, d->solver_niter,
+                        d->overflow};
   for (const void* p : need)
     if (!p) return set_error("imn_solve: a required Model/Data pointer is NULL"), IMN_ERR_NULL;
   if (d->dof_ld < m->nv || d->J_ld_row < m->nv || d->efc_ld < d->njmax || d->M_ld < m->nM ||
       d->J_ld_world < (int64_t)d->njmax * d->J_ld_row)
     return set_error("imn_solve: a stride is smaller than its extent"), IMN_ERR_SHAPE;
+  if (d->J_ld_row > 4 * (int64_t)m->nv + 64)
+    return set_error("imn_solve: efc.J row stride %lld is far larger than nv %d", (long long)d->J_ld_row, m->nv),
+           IMN_ERR_SHAPE;
+  if (m->nM >= (1 << 16)) return set_error("imn_solve: nM exceeds 16-bit indices"), IMN_ERR_LIMIT;
   if (cx->grad && cx->grad_ld < m->nv) return set_error("imn_solve: ctx.grad stride < nv"), IMN_ERR_SHAPE;
   if (cx->sparse_plan) return set_error("imn_solve: sparse plan not supported by this kernel"), IMN_ERR_UNSUPPORTED;
   return IMN_OK;
@@ -766,6 +1008,25 @@ static int plan_launch(const ImnModel* m, const ImnData* d, Geom* g, bool* resid
 }
 
 }  // namespace imn
+
+#ifdef IMN_PROFILE
+extern "C" int imn_debug_profile(unsigned long long* out, int reset) {
+  cudaMemcpyFromSymbol(out, imn::g_prof, sizeof(unsigned long long) * 16);
+  if (reset) {
+    unsigned long long z[16] = {0};
+    cudaMemcpyToSymbol(imn::g_prof, z, sizeof z);
+  }
+  return 0;
+}
+extern "C" int imn_debug_occupancy(int bytes, int resident) {
+  int n = 0;
+  if (resident)
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel<true>, 32, bytes);
+  else
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel<false>, 32, bytes);
+  return n;
+}
+#endif
 
 extern "C" int imn_launch_info(const ImnModel* m, const ImnData* d, const ImnCtx* cx, ImnLaunchInfo* out) {
   if (!out) return imn::set_error("imn_launch_info: NULL out"), IMN_ERR_NULL;
@@ -794,9 +1055,15 @@ extern "C" int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* cx, 
   if (rc) return rc;
   const int bytes = g.total * 4;
   auto kern = res ? imn::newton_kernel<true> : imn::newton_kernel<false>;
-  if (bytes > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
-    if (e != cudaSuccess) return imn::set_error("imn_solve: cudaFuncSetAttribute: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  {
+    // many one-warp CTAs share an SM: ask for the largest shared-memory carve-out,
+    // otherwise the driver sizes it for a single CTA
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess && bytes > 48 * 1024)
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess)
+      return imn::set_error("imn_solve: cudaFuncSetAttribute: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
   }
   if (cx->nsolving) imn::fill_nsolving<<<1, 1, 0, stream>>>(cx->nsolving, d->nworld);
   kern<<<d->nworld, 32, bytes, stream>>>(*m, *d, *cx, g);

@@ -66,6 +66,7 @@ class Model:
     M_mulm_rowadr: Any
     M_mulm_col: Any
     M_mulm_madr: Any
+    M_mulm_pack: Any  # col | madr << 16 per entry of the M_mulm tables
     block_dim: SimpleNamespace = field(
         default_factory=lambda: SimpleNamespace(linesearch_iterative=32)
     )
@@ -156,6 +157,15 @@ def mulm_tables(rowadr, rownnz, colind, nv: int):
     return as32(adr), as32(col), as32(madr)
 
 
+def pack_mulm(col, madr) -> np.ndarray:
+    """One word per entry of the M_mulm tables: col | madr << 16."""
+    col = np.asarray(col).astype(np.int64)
+    madr = np.asarray(madr).astype(np.int64)
+    if col.size and (col.max() >= 1 << 16 or madr.max() >= 1 << 16):
+        raise ValueError("M_mulm indices exceed 16 bits")
+    return (col | (madr << 16)).astype(np.uint32).view(np.int32)
+
+
 def put_model(
     dof_parentid,
     *,
@@ -210,6 +220,7 @@ def put_model(
         M_mulm_rowadr=madr_row,
         M_mulm_col=mcol,
         M_mulm_madr=madr,
+        M_mulm_pack=pack_mulm(mcol, madr),
         body_parentid=body_parentid,
         body_dofadr=body_dofadr,
         body_dofnum=body_dofnum,

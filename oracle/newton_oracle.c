@@ -229,15 +229,20 @@ static void factor_solve(World* w, int factor, float sums[2]) {
   const float* H = w->H;
   for (int r = 0; r < nv; ++r) {
     if (factor) {
-      for (int c = r; c < nv; ++c) {
-        float acc = H[r * nv + c];
+      float acc = H[r * nv + r];
+      for (int t = 0; t < r; ++t) acc = fmaf(-U[t * nv + r], U[t * nv + r], acc);
+      const float d = sqrtf(acc);
+      const float rinv = 1.0f / d; /* the row is scaled by the reciprocal pivot */
+      U[r * nv + r] = d;
+      for (int c = r + 1; c < nv; ++c) {
+        acc = H[r * nv + c];
         for (int t = 0; t < r; ++t) acc = fmaf(-U[t * nv + r], U[t * nv + c], acc);
-        U[r * nv + c] = (c == r) ? sqrtf(acc) : acc / U[r * nv + r];
+        U[r * nv + c] = acc * rinv;
       }
     }
     float acc = w->grad[r];
     for (int t = 0; t < r; ++t) acc = fmaf(-U[t * nv + r], y[t], acc);
-    y[r] = acc / U[r * nv + r];
+    y[r] = acc * (1.0f / U[r * nv + r]);
   }
   for (int r = nv - 1; r >= 0; --r) {
     const int tile_end = ((r / 16) + 1) * 16 < nv ? ((r / 16) + 1) * 16 : nv;
@@ -246,7 +251,7 @@ static void factor_solve(World* w, int factor, float sums[2]) {
      * then the row's own diagonal block from its last column inwards */
     for (int c = tile_end; c < nv; ++c) acc = fmaf(-U[r * nv + c], x[c], acc);
     for (int c = tile_end - 1; c > r; --c) acc = fmaf(-U[r * nv + c], x[c], acc);
-    x[r] = acc / U[r * nv + r];
+    x[r] = acc * (1.0f / U[r * nv + r]);
   }
   float p0[64], p1[64];
   for (int t = 0; t < w->bd; ++t) {
