@@ -14,7 +14,9 @@
 // results are written once.  A warp needs no block barrier (only __syncwarp),
 // lane reductions are shuffle trees, and the hardware CTA scheduler balances
 // worlds whose iteration counts differ.  Worlds with more rows than fit on chip
-// stream J through a 32-row staging tile.
+// stream J through a 32-row staging tile.  The initialisation runs through the
+// same code as an iteration (as "iteration 0" without a line search): the kernel
+// is bound by instruction fetch and latency, so every stage exists once.
 //
 // Arithmetic contract.  Every value that decides an active set or an iteration
 // count is formed by the same float32 operations in the same order as the CPU
@@ -24,16 +26,17 @@
 // receives its terms.
 #include <stdio.h>
 
-#include "imn_common.cuh"
+#include "imn_newton_factor.cuh"
+#include "imn_newton_ls.cuh"
 
 namespace imn {
 
 // Phase timers, compiled only into the profiling build (-DIMN_PROFILE).
 #ifdef IMN_PROFILE
 __device__ unsigned long long g_prof[16];
-#define PROF_DECL long long prof_t = clock64(); long long prof_acc[12] = {0}
+#define PROF_DECL long long prof_t = clock64(); long long prof_acc[16] = {0}; s.prof_acc = prof_acc; s.prof_t = &prof_t
 #define PROF(k) do { const long long t_ = clock64(); prof_acc[k] += t_ - prof_t; prof_t = t_; } while (0)
-#define PROF_FLUSH do { if (lane == 0) for (int k_ = 0; k_ < 12; ++k_) atomicAdd(&g_prof[k_], (unsigned long long)prof_acc[k_]); } while (0)
+#define PROF_FLUSH do { if (lane == 0) for (int k_ = 0; k_ < 16; ++k_) atomicAdd(&g_prof[k_], (unsigned long long)prof_acc[k_]); } while (0)
 #else
 #define PROF_DECL
 #define PROF(k)
@@ -77,209 +80,48 @@ static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident) {
   return g;
 }
 
-// ---- TMA bulk copy + mbarrier (sm_90+ PTX) -----------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(void* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(void* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, void* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-                   smem_u32(dst)),
-               "l"(src), "r"(bytes), "r"(smem_u32(bar))
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(void* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// ---- row cost pieces (the statement is in oracle/newton_oracle.c) -------------
-__device__ __forceinline__ int row_zone(float x, bool fr, float rf) {
-  if (fr) return x <= -rf ? IMN_STATE_LINEARNEG : (x >= rf ? IMN_STATE_LINEARPOS : IMN_STATE_QUADRATIC);
-  return x >= 0.0f ? IMN_STATE_SATISFIED : IMN_STATE_QUADRATIC;
-}
-__device__ __forceinline__ float zone_cost(int z, float x, float D, float f, float rf) {
-  if (z == IMN_STATE_QUADRATIC) return ((0.5f * D) * x) * x;
-  if (z == IMN_STATE_LINEARNEG) return f * (-0.5f * rf - x);
-  if (z == IMN_STATE_LINEARPOS) return f * (-0.5f * rf + x);
-  return 0.0f;
-}
-// One constraint row prepared for repeated evaluation along the search direction.
-struct Row {
-  float D, ja, j, f, rf, jvD, h, q1r, cost0;
-  int z0;
-  bool fr, valid;
-};
-__device__ __forceinline__ Row make_row(bool valid, bool fr, float f, float D, float ja, float j) {
-  Row r;
-  r.valid = valid, r.fr = fr, r.f = fr ? f : 0.0f, r.D = D, r.ja = ja, r.j = j;
-  r.rf = fr ? safe_div(f, D) : 0.0f;
-  r.z0 = row_zone(ja, fr, r.rf);
-  r.jvD = j * D;
-  r.h = j * r.jvD;
-  r.q1r = r.jvD * ja;
-  r.cost0 = zone_cost(r.z0, ja, D, r.f, r.rf);
-  return r;
-}
-// (cost, slope, curvature) at alpha = 0
-__device__ __forceinline__ Vec3 row_at_zero(const Row& r) {
-  if (!r.valid) return v3(0.0f, 0.0f, 0.0f);
-  if (r.z0 == IMN_STATE_QUADRATIC) return v3(r.cost0, r.q1r, r.h);
-  if (r.z0 == IMN_STATE_LINEARNEG) return v3(r.cost0, -r.f * r.j, 0.0f);
-  if (r.z0 == IMN_STATE_LINEARPOS) return v3(r.cost0, r.f * r.j, 0.0f);
-  return v3(0.0f, 0.0f, 0.0f);
-}
-// (cost(alpha) - cost(0), slope, curvature) at alpha
-__device__ __forceinline__ Vec3 row_at(const Row& r, float alpha) {
-  if (!r.valid) return v3(0.0f, 0.0f, 0.0f);
-  const float x = fmaf(alpha, r.j, r.ja);
-  if (!r.fr) {
-    const bool on = x < 0.0f, on0 = r.z0 == IMN_STATE_QUADRATIC;
-    float c = 0.0f;
-    if (on && on0)
-      c = alpha * fmaf(0.5f * alpha, r.h, r.q1r);
-    else if (on != on0)
-      c = (on ? ((0.5f * r.D) * x) * x : 0.0f) - r.cost0;
-    return v3(c, on ? r.jvD * x : 0.0f, on ? r.h : 0.0f);
-  }
-  const int z = row_zone(x, true, r.rf);
-  Vec3 o = v3(0.0f, 0.0f, 0.0f);
-  if (z == IMN_STATE_QUADRATIC) o.c1 = r.jvD * x, o.c2 = r.h;
-  if (z == IMN_STATE_LINEARNEG) o.c1 = -r.f * r.j;
-  if (z == IMN_STATE_LINEARPOS) o.c1 = r.f * r.j;
-  if (z != r.z0)
-    o.c0 = zone_cost(z, x, r.D, r.f, r.rf) - r.cost0;
-  else if (z == IMN_STATE_QUADRATIC)
-    o.c0 = alpha * fmaf(0.5f * alpha, r.h, r.q1r);
-  else if (z == IMN_STATE_LINEARNEG)
-    o.c0 = -r.f * (alpha * r.j);
-  else
-    o.c0 = r.f * (alpha * r.j);
-  return o;
-}
-__device__ __forceinline__ Vec3 eval_quad(float q1, float q2, float alpha) {
-  return v3(fmaf(alpha, q1, (alpha * alpha) * q2) + 0.0f, fmaf(2.0f * alpha, q2, q1), 2.0f * q2);
-}
-__device__ __forceinline__ bool in_bracket(Vec3 x, Vec3 y) {
-  return (x.c1 < y.c1 && y.c1 < 0.0f) || (x.c1 > y.c1 && y.c1 > 0.0f);
-}
-__device__ __forceinline__ void eval_constraint(bool is_eq, bool is_fr, float jaref, float D,
-                                                float floss, float& force, int& state) {
-  if (is_eq) {
-    force = -D * jaref, state = IMN_STATE_QUADRATIC;
-    return;
-  }
-  if (is_fr) {
-    const float rf = safe_div(floss, D);
-    if (jaref <= -rf) {
-      force = floss, state = IMN_STATE_LINEARNEG;
-      return;
-    }
-    if (jaref >= rf) {
-      force = -floss, state = IMN_STATE_LINEARPOS;
-      return;
-    }
-    force = -D * jaref, state = IMN_STATE_QUADRATIC;
-    return;
-  }
-  if (jaref >= 0.0f) {
-    force = 0.0f, state = IMN_STATE_SATISFIED;
-    return;
-  }
-  force = -D * jaref, state = IMN_STATE_QUADRATIC;
-}
-
-// One value per thread of the reference's logical block (32 or 64 threads),
-// each thread summing its strided elements, then Warp's block reduction: a tree
-// per warp and the later warp added to the first (newton_stages.py:34-38).  The
-// physical warp plays both logical warps when bd == 64.
-template <class F>
-__device__ __forceinline__ float logical_block_sum(int n, int bd, int lane, F term) {
-  float a = 0.0f;
-  for (int i = lane; i < n; i += bd) a = term(i, a);
-  float s = warp_tree_sum(a);
-  if (bd == 64) {
-    float b = 0.0f;
-    for (int i = lane + 32; i < n; i += 64) b = term(i, b);
-    s = s + warp_tree_sum(b);
-  }
-  return s;
-}
-
-// Shuffle-down trees of N values at once (independent chains interleave), lane 0
-// broadcast, then "+0" per later logical warp of the line search
-// (newton_stages.py:39-49).
-template <int N>
-__device__ __forceinline__ void ls_sum(float (&v)[N], int bd) {
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) {
-#pragma unroll
-    for (int k = 0; k < N; ++k) v[k] = v[k] + __shfl_down_sync(IMN_FULL_MASK, v[k], off);
-  }
-#pragma unroll
-  for (int k = 0; k < N; ++k) {
-    v[k] = __shfl_sync(IMN_FULL_MASK, v[k], 0);
-    if (bd == 64) v[k] = v[k] + 0.0f;
-  }
-}
-
-// advance an upper-triangle pair (i <= j), enumerated column by column, by `step`
-__device__ __forceinline__ void pair_advance(int& i, int& j, int step) {
-  i += step;
-  while (i > j) i -= j + 1, ++j;
-}
-
 template <bool JRES>
 __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnData d, const ImnCtx cx,
                                                     const Geom g) {
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x;
   const int w = blockIdx.x;
-  const int nv = g.nv, ldj = g.ldj, ldu = g.ldu, bd = g.bd, R = g.njmax, nv4 = g.nv4, r4 = g.r4;
+  const int nv = g.nv, R = g.njmax, nv4 = g.nv4, r4 = g.r4;
 
   void* bar = smem + g.oBar;
-  float* Jsm = smem + g.oJ;
-  // A is (nv+1) x ldu.  U[r][c] (r <= c <= nv; column nv carries the right-hand
-  // side) lives at A[r*ldu + c]; H[r][c] (r <= c < nv) at A[(c+1)*ldu + r].
-  float* A = smem + g.oA;
-  float* qacc = smem + g.oVec;
-  float* Ma = qacc + nv4;
-  float* search = Ma + nv4;
-  float* mv = search + nv4;
-  float* grad = mv + nv4;
-  float* qfs = grad + nv4;
-  float* xsm = qfs + nv4;
-  float* dinv = xsm + nv4;
-  float* Msm = smem + g.oM;
-  float* Jaref = smem + g.oRowF;
-  float* jv = Jaref + r4;
-  float* Dsm = jv + r4;
-  float* floss = Dsm + r4;
-  float* force = floss + r4;
-  int* state = reinterpret_cast<int*>(smem + g.oRowI);
-  int* ids = state + r4;
-  int* frows = ids + r4;  // rows with a nonzero force, ascending
-  int* uni = reinterpret_cast<int*>(smem + g.oUni);
+  World s;
+  s.nv = nv, s.ldj = g.ldj, s.ldu = g.ldu, s.bd = g.bd, s.lane = lane, s.nM = g.nM;
+  s.Jsm = smem + g.oJ;
+  s.A = smem + g.oA;
+  s.qacc = smem + g.oVec;
+  s.Ma = s.qacc + nv4;
+  s.search = s.Ma + nv4;
+  s.mv = s.search + nv4;
+  s.grad = s.mv + nv4;
+  s.qfs = s.grad + nv4;
+  s.xsm = s.qfs + nv4;
+  s.dinv = s.xsm + nv4;
+  s.Msm = smem + g.oM;
+  s.Jaref = smem + g.oRowF;
+  s.jv = s.Jaref + r4;
+  s.Dsm = s.jv + r4;
+  s.floss = s.Dsm + r4;
+  s.force = s.floss + r4;
+  s.state = reinterpret_cast<int*>(smem + g.oRowI);
+  s.ids = s.state + r4;
+  s.frows = s.ids + r4;  // rows with a nonzero force, ascending
+  s.uni = reinterpret_cast<int*>(smem + g.oUni);
+  s.mulm_rowadr = m.M_mulm_rowadr;
+  s.mulm_pack = m.M_mulm_pack;
 
   PROF_DECL;
   const int nefc_in = d.nefc[w];
   const int nefc = min(R, nefc_in);
-  const int ne = d.ne[w], nf = d.nf[w], nef = ne + nf;
+  const int ne = d.ne[w], nef = ne + d.nf[w];
+  s.nefc = nefc, s.ne = ne, s.nef = nef;
   const bool rowless = nefc_in == 0;
   const size_t dofo = (size_t)w * d.dof_ld, efco = (size_t)w * d.efc_ld;
-  const float* Jg = d.efc_J + (size_t)w * d.J_ld_world;
+  s.Jg = d.efc_J + (size_t)w * d.J_ld_world;
 
   // ---- load: TMA bulk copies for the 16-byte-aligned bulk of every array, plain
   // loads for the ragged ends -----------------------------------------------------
@@ -291,13 +133,13 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
       int n;
     };
     const Src srcs[7] = {
-        {Jsm, Jg, JRES ? nefc * ldj : 0},
-        {Msm, d.M + (size_t)w * d.M_ld, g.nM},
-        {Dsm, d.efc_D + efco, nefc},
-        {floss, d.efc_frictionloss + efco, nefc},
-        {jv, d.efc_aref + efco, nefc},  // aref is parked in jv until Jaref is formed
-        {qacc, q0 + dofo, nv},
-        {qfs, d.qfrc_smooth + dofo, nv},
+        {s.Jsm, s.Jg, JRES ? nefc * s.ldj : 0},
+        {s.Msm, d.M + (size_t)w * d.M_ld, g.nM},
+        {s.Dsm, d.efc_D + efco, nefc},
+        {s.floss, d.efc_frictionloss + efco, nefc},
+        {s.jv, d.efc_aref + efco, nefc},  // aref is parked in jv until Jaref is formed
+        {s.qacc, q0 + dofo, nv},
+        {s.qfs, d.qfrc_smooth + dofo, nv},
     };
     if (lane == 0) mbar_init(bar, 1);
     __syncwarp();
@@ -317,12 +159,16 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
 #pragma unroll
     for (int k = 0; k < 7; ++k) {
       const int done_n = (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0 ? (srcs[k].n & ~3) : 0;
+#pragma unroll 1
       for (int i = done_n + lane; i < srcs[k].n; i += 32) srcs[k].dst[i] = srcs[k].src[i];
     }
-    for (int i = lane; i < nv; i += 32) search[i] = 0.0f, mv[i] = 0.0f, grad[i] = 0.0f;
-    for (int i = lane; i <= nv; i += 32) uni[i] = 0;
+#pragma unroll 1
+    for (int i = lane; i < nv; i += 32) s.search[i] = 0.0f, s.mv[i] = 0.0f, s.grad[i] = 0.0f;
+#pragma unroll 1
+    for (int i = lane; i <= nv; i += 32) s.uni[i] = 0;
     // bounded wait for the copies
     bool arrived = false;
+#pragma unroll 1
     for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) arrived = mbar_try_wait(bar, 0);
     if (!arrived) {
       if (lane == 0) d.overflow[w] |= IMN_OVERFLOW_COPY_TIMEOUT;
@@ -332,516 +178,86 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   __syncwarp();
   PROF(0);
 
-  // stage rows [base, base+32) of J when it is not resident
-  auto tile = [&](int base) -> const float* {
-    if (JRES) return Jsm + base * ldj;
-    __syncwarp();
-    const int n = min(32, nefc - base) * ldj;
-    const float* src = Jg + (size_t)base * ldj;
-    for (int i = lane; i < n; i += 32) Jsm[i] = src[i];
-    __syncwarp();
-    return Jsm;
-  };
-  auto Jat = [&](int r, int i) -> float { return JRES ? Jsm[r * ldj + i] : Jg[(size_t)r * ldj + i]; };
-  // out = M v over the symmetric rows (newton_fusion.py:171-176)
-  auto mul_m = [&](const float* v, float* out) {
-    for (int i = lane; i < nv; i += 32) {
-      float s = 0.0f;
-      const int k1 = __ldg(m.M_mulm_rowadr + i + 1);
-      int k = __ldg(m.M_mulm_rowadr + i);
-      for (; k + 4 <= k1; k += 4) {
-        const uint32_t p0 = __ldg(m.M_mulm_pack + k), p1 = __ldg(m.M_mulm_pack + k + 1);
-        const uint32_t p2 = __ldg(m.M_mulm_pack + k + 2), p3 = __ldg(m.M_mulm_pack + k + 3);
-        const float a0 = Msm[p0 >> 16], a1 = Msm[p1 >> 16], a2 = Msm[p2 >> 16], a3 = Msm[p3 >> 16];
-        const float b0 = v[p0 & 0xFFFF], b1 = v[p1 & 0xFFFF], b2 = v[p2 & 0xFFFF], b3 = v[p3 & 0xFFFF];
-        s = fmaf(a0, b0, s);
-        s = fmaf(a1, b1, s);
-        s = fmaf(a2, b2, s);
-        s = fmaf(a3, b3, s);
-      }
-      for (; k < k1; ++k) {
-        const uint32_t p = __ldg(m.M_mulm_pack + k);
-        s = fmaf(Msm[p >> 16], v[p & 0xFFFF], s);
-      }
-      out[i] = s;
-    }
-  };
-  // one running sum per row of J v; above 50 dofs in 20-dof partials
-  // (newton_stages.py:157-174); `minus` is subtracted from the first partial
-  auto row_dots = [&](const float* v, float* out, const float* minus) {
-    for (int base = 0; base < nefc; base += 32) {
-      const float* Jt = tile(base);
-      const int r = base + lane;
-      if (r < nefc) {
-        const float* Jr = Jt + lane * ldj;
-        const float sub = minus ? minus[r] : 0.0f;
-        float res;
-        if (nv > 50) {
-          float total = 0.0f;
-          for (int s0 = 0; s0 < nv; s0 += 20) {
-            float p = 0.0f;
-            const int e = min(s0 + 20, nv);
-#pragma unroll 4
-            for (int i = s0; i < e; ++i) p = fmaf(Jr[i], v[i], p);
-            if (s0 == 0)
-              total = minus ? p - sub : 0.0f + p;
-            else
-              total = total + p;
-          }
-          res = total;
-        } else {
-          float p = 0.0f;
-#pragma unroll 8
-          for (int i = 0; i < nv; ++i) p = fmaf(Jr[i], v[i], p);
-          res = minus ? p - sub : p;
-        }
-        out[r] = res;
-      }
-      if (!JRES) __syncwarp();
-    }
-  };
-  // grad = Ma - qfrc_smooth - J^T force over the rows with a nonzero force
-  // (a zero force leaves the running sums unchanged), then grad_dot
-  // (newton_stages.py:785-795)
-  auto full_gradient = [&](int nfr) -> float {
-    float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
-    const int i0 = lane, i1 = lane + 32, i2 = lane + 64;
-    const bool h1 = i1 < nv, h2 = i2 < nv;
-    if (JRES) {
-      int a = 0;
-      for (; a + 2 <= nfr; a += 2) {
-        const int ra = frows[a], rb = frows[a + 1];
-        const float fa = force[ra], fb = force[rb];
-        const float* Ja = Jsm + ra * ldj;
-        const float* Jb = Jsm + rb * ldj;
-        if (i0 < nv) s0 = fmaf(Jb[i0], fb, fmaf(Ja[i0], fa, s0));
-        if (h1) s1 = fmaf(Jb[i1], fb, fmaf(Ja[i1], fa, s1));
-        if (h2) s2 = fmaf(Jb[i2], fb, fmaf(Ja[i2], fa, s2));
-      }
-      if (a < nfr) {
-        const int ra = frows[a];
-        const float fa = force[ra];
-        const float* Ja = Jsm + ra * ldj;
-        if (i0 < nv) s0 = fmaf(Ja[i0], fa, s0);
-        if (h1) s1 = fmaf(Ja[i1], fa, s1);
-        if (h2) s2 = fmaf(Ja[i2], fa, s2);
-      }
-    } else {
-      int a = 0;
-      for (int base = 0; base < nefc; base += 32) {
-        const float* Jt = tile(base);
-        for (; a < nfr && frows[a] < base + 32; ++a) {
-          const int r = frows[a];
-          const float f = force[r];
-          const float* Jr = Jt + (r - base) * ldj;
-          if (i0 < nv) s0 = fmaf(Jr[i0], f, s0);
-          if (h1) s1 = fmaf(Jr[i1], f, s1);
-          if (h2) s2 = fmaf(Jr[i2], f, s2);
-        }
-        __syncwarp();
-      }
-    }
-    if (i0 < nv) grad[i0] = (Ma[i0] - qfs[i0]) - s0;
-    if (h1) grad[i1] = (Ma[i1] - qfs[i1]) - s1;
-    if (h2) grad[i2] = (Ma[i2] - qfs[i2]) - s2;
-    __syncwarp();
-    return logical_block_sum(nv, bd, lane, [&](int i, float a) { return fmaf(grad[i], grad[i], a); });
-  };
-
-  // Upper Cholesky H = U^T U with the right-hand side as column nv (forward solve),
-  // then back substitution (newton_stages.py:546-609).  Left-looking in blocks of
-  // 16 rows: a block first takes the updates of all earlier rows (independent
-  // running sums, register-tiled four rows at a time), then finishes row by row.
-  // Every entry still receives its terms in ascending row order.
-  auto factor_solve = [&](bool factor, float& sum0, float& sum1) {
-    if (factor) {
-      for (int b0 = 0; b0 < nv; b0 += 16) {
-        const int b1 = min(b0 + 16, nv);
-        // phase 1: terms of rows t < b0
-        for (int r0 = b0; r0 < b1; r0 += 4) {
-          for (int c = r0 + lane; c <= nv; c += 32) {
-            float a0, a1, a2, a3;
-            if (c < nv) {
-              const float* Hc = A + (c + 1) * ldu;
-              a0 = Hc[r0];
-              a1 = (r0 + 1 <= c) ? Hc[r0 + 1] : 0.0f;
-              a2 = (r0 + 2 <= c) ? Hc[r0 + 2] : 0.0f;
-              a3 = (r0 + 3 <= c) ? Hc[r0 + 3] : 0.0f;
-            } else {
-              a0 = grad[r0];
-              a1 = r0 + 1 < nv ? grad[r0 + 1] : 0.0f;
-              a2 = r0 + 2 < nv ? grad[r0 + 2] : 0.0f;
-              a3 = r0 + 3 < nv ? grad[r0 + 3] : 0.0f;
-            }
-#pragma unroll 4
-            for (int t = 0; t < b0; ++t) {
-              const float* Ut = A + t * ldu;
-              const float uc = Ut[c];
-              const float4 ur = *reinterpret_cast<const float4*>(Ut + r0);  // r0 % 4 == 0
-              a0 = fmaf(-ur.x, uc, a0);
-              a1 = fmaf(-ur.y, uc, a1);
-              a2 = fmaf(-ur.z, uc, a2);
-              a3 = fmaf(-ur.w, uc, a3);
-            }
-            A[r0 * ldu + c] = a0;
-            if (r0 + 1 < b1 && r0 + 1 <= c) A[(r0 + 1) * ldu + c] = a1;
-            if (r0 + 2 < b1 && r0 + 2 <= c) A[(r0 + 2) * ldu + c] = a2;
-            if (r0 + 3 < b1 && r0 + 3 <= c) A[(r0 + 3) * ldu + c] = a3;
-          }
-        }
-        __syncwarp();
-        // phase 2: terms of rows b0 <= t < r, pivot, scale
-        for (int r = b0; r < b1; ++r) {
-          float acc[3];
-          float dg = 0.0f;
-#pragma unroll
-          for (int k = 0; k < 3; ++k) {
-            const int c = r + lane + 32 * k;
-            if (c <= nv) {
-              float a = A[r * ldu + c];
-              for (int t = b0; t < r; ++t) a = fmaf(-A[t * ldu + r], A[t * ldu + c], a);
-              acc[k] = a;
-              if (k == 0 && lane == 0) dg = sqrtf(a);
-            }
-          }
-          dg = __shfl_sync(IMN_FULL_MASK, dg, 0);
-          const float rinv = 1.0f / dg;
-#pragma unroll
-          for (int k = 0; k < 3; ++k) {
-            const int c = r + lane + 32 * k;
-            if (c <= nv) A[r * ldu + c] = (c == r) ? dg : acc[k] * rinv;
-          }
-          if (lane == 0) dinv[r] = rinv;
-          __syncwarp();
-        }
-      }
-    } else {
-      // forward substitution with the stored factor; an unknown receives its
-      // terms in ascending order exactly as the factor's carried column does
-      float acc[3];
-#pragma unroll
-      for (int k = 0; k < 3; ++k) acc[k] = (lane + 32 * k) < nv ? grad[lane + 32 * k] : 0.0f;
-      for (int t = 0; t < nv; ++t) {
-        const int k0 = t >> 5;
-        const float mine = k0 == 0 ? acc[0] : (k0 == 1 ? acc[1] : acc[2]);
-        float yt = mine * dinv[t];
-        yt = __shfl_sync(IMN_FULL_MASK, yt, t & 31);
-        if (lane == 0) A[t * ldu + nv] = yt;
-        const float* Ut = A + t * ldu;
-#pragma unroll
-        for (int k = 0; k < 3; ++k) {
-          const int r = lane + 32 * k;
-          if (r > t && r < nv) acc[k] = fmaf(-Ut[r], yt, acc[k]);
-        }
-      }
-      __syncwarp();
-    }
-    // back substitution, 16-row blocks from the last: later blocks' columns in
-    // ascending order first, then the block's own columns from its last inwards
-    for (int b0 = ((nv - 1) / 16) * 16; b0 >= 0; b0 -= 16) {
-      const int b1 = min(b0 + 16, nv);
-      const int r = b0 + lane;
-      const float* Ur = A + r * ldu;
-      float acc = 0.0f, di = 0.0f;
-      if (r < b1) {
-        acc = Ur[nv];
-        di = dinv[r];
-#pragma unroll 4
-        for (int c = b1; c < nv; ++c) acc = fmaf(-Ur[c], xsm[c], acc);
-      }
-      for (int c = b1 - 1; c >= b0; --c) {
-        const float xc = __shfl_sync(IMN_FULL_MASK, acc * di, c - b0);
-        if (r < c) acc = fmaf(-Ur[c], xc, acc);
-        if (lane == 0) xsm[c] = xc;
-      }
-      __syncwarp();
-    }
-    sum0 = logical_block_sum(nv, bd, lane, [&](int i, float a) { return fmaf(xsm[i], xsm[i], a); });
-    sum1 = logical_block_sum(nv, bd, lane, [&](int i, float a) { return fmaf(grad[i], xsm[i], a); });
-    for (int i = lane; i < nv; i += 32) search[i] = -xsm[i];
-    __syncwarp();
-  };
-
-  // ---- init ----------------------------------------------------------------
-  row_dots(qacc, Jaref, jv);  // Jaref = J qacc - aref (aref parked in jv)
-  mul_m(qacc, Ma);
-  __syncwarp();
-
   float search_dot = 0.0f, grad_dot = 0.0f, grad_scale = 1.0f, decrement = 0.0f;
   float improvement = 0.0f, alpha = 0.0f;
-  int quad_count = 0, state_count = 0, niter = 0, overflow = 0, nfr = 0;
+  int quad_count = 0, state_count = 0, niter = 0, overflow = 0;
   bool search_unchanged = false, ls_exhausted = false;
-
-  if (!rowless) {
-    // _update_constraint: force / state of every row; rows with a force, ascending
-    for (int base = 0; base < nefc; base += 32) {
-      const int r = base + lane;
-      float f = 0.0f;
-      if (r < nefc) {
-        const bool is_eq = r < ne, is_fr = !is_eq && r < nef;
-        int st;
-        eval_constraint(is_eq, is_fr, Jaref[r], Dsm[r], is_fr ? floss[r] : 0.0f, f, st);
-        force[r] = f;
-        state[r] = st;
-        jv[r] = 0.0f;
-      }
-      const unsigned mask = __ballot_sync(IMN_FULL_MASK, f != 0.0f);
-      if (f != 0.0f) frows[nfr + __popc(mask & ((1u << lane) - 1u))] = r;
-      nfr += __popc(mask);
-    }
-    __syncwarp();
-    PROF(1);
-    grad_dot = full_gradient(nfr);
-    PROF(2);
-    // H = M + J^T diag(D, QUADRATIC rows) J on the upper triangle, rows ascending
-    for (int e = lane; e < (nv + 1) * ldu; e += 32) A[e] = 0.0f;
-    __syncwarp();
-    for (int i = lane; i < nv; i += 32) {
-      // the symmetric row of dof i lists every stored entry (i, c); keep c >= i
-      const int k1 = __ldg(m.M_mulm_rowadr + i + 1);
-      for (int k = __ldg(m.M_mulm_rowadr + i); k < k1; ++k) {
-        const uint32_t p = __ldg(m.M_mulm_pack + k);
-        const int c = p & 0xFFFF;
-        if (c >= i) A[(c + 1) * ldu + i] = Msm[p >> 16];
-      }
-    }
-    __syncwarp();
-    const int npair = nv * (nv + 1) / 2;
-    {
-      int a_lo = 0;
-      for (int base = 0; base < nefc; base += 32) {
-        const float* Jt = tile(base);
-        const int row_hi = JRES ? nefc : min(base + 32, nefc);
-        int a_hi = a_lo;
-        while (a_hi < nfr && frows[a_hi] < row_hi) ++a_hi;
-        // two entries per lane per pass so that their running sums overlap
-        int i0 = lane, j0 = 0, i1 = lane + 32, j1 = 0;
-        pair_advance(i0, j0, 0);
-        pair_advance(i1, j1, 0);
-        for (int e = lane; e < npair; e += 64) {
-          const bool two = e + 32 < npair;
-          float v0 = A[(j0 + 1) * ldu + i0];
-          float v1 = two ? A[(j1 + 1) * ldu + i1] : 0.0f;
-          const int i1c = two ? i1 : i0, j1c = two ? j1 : j0;
-          for (int a = a_lo; a < a_hi; ++a) {
-            const int r = frows[a];
-            if (state[r] != IMN_STATE_QUADRATIC) continue;
-            const float Dr = Dsm[r];
-            const float* Jr = Jt + (r - base) * ldj;
-            v0 = fmaf(Jr[i0] * Dr, Jr[j0], v0);
-            v1 = fmaf(Jr[i1c] * Dr, Jr[j1c], v1);
-          }
-          A[(j0 + 1) * ldu + i0] = v0;
-          if (two) A[(j1 + 1) * ldu + i1] = v1;
-          pair_advance(i0, j0, 64);
-          pair_advance(i1, j1, 64);
-        }
-        a_lo = a_hi;
-        if (JRES) break;
-        __syncwarp();
-      }
-    }
-    __syncwarp();
-    PROF(3);
-    factor_solve(true, search_dot, decrement);
-    PROF(4);
-  }
-
-  // ---- Newton iterations (newton_fusion.py:170-296) -----------------------------
-  bool done = rowless;
   const float tolerance = m.opt_tolerance[w % m.n_tolerance];
   const float ls_tolerance = m.opt_ls_tolerance[w % m.n_ls_tolerance];
   const float scale = m.stat_meaninertia[w % m.n_meaninertia] * (float)nv;
-  const float eps = m.alpha_noise_eps;
-  while (!done) {
-    if (!search_unchanged) {
-      mul_m(search, mv);
-      row_dots(search, jv, nullptr);
-    }
+
+  // Pass 0 is the initialisation (newton_fusion.py:431-472): Jaref = J qacc - aref,
+  // Ma = M qacc, row states, gradient, full Hessian, factor, first search direction.
+  // Every later pass is one Newton iteration (newton_fusion.py:170-296).
+#pragma unroll 1
+  for (bool first = true;; first = false) {
+    if (first)
+      products<JRES>(s, s.qacc, s.Ma, s.Jaref, s.jv);
+    else if (!search_unchanged)
+      products<JRES>(s, s.search, s.mv, s.jv, nullptr);
     __syncwarp();
     PROF(5);
-    // ---- exact line search (newton_stages.py:182-367) ------------------------
-    float noise_floor;
-    bool ls_converged;
-    {
-      const float snorm = sqrtf(search_dot);
-      const float gtol = fmaxf(tolerance * ls_tolerance * snorm * scale, 1e-06f);
-      float gq[2] = {0.0f, 0.0f};
+    if (rowless) break;
+    float noise_floor = 0.0f;
+    bool ls_converged = true;
+    if (!first) {
+      const LineSearchResult ls =
+          line_search(s, search_dot, tolerance, ls_tolerance, scale, m.alpha_noise_eps, m.ls_iterations);
+      alpha = ls.alpha, improvement = ls.improvement, noise_floor = ls.noise_floor;
+      ls_converged = ls.converged;
+#pragma unroll 1
       for (int i = lane; i < nv; i += 32) {
-        gq[0] = fmaf(search[i], Ma[i] - qfs[i], gq[0]);
-        gq[1] = fmaf(0.5f * search[i], mv[i], gq[1]);
-      }
-      for (int r = lane; r < ne; r += 32) {
-        const float jvD = jv[r] * Dsm[r];
-        gq[0] = fmaf(jvD, Jaref[r], gq[0]);
-        gq[1] = fmaf(0.5f * jv[r], jvD, gq[1]);
-      }
-      ls_sum(gq, bd);
-      const float q1 = gq[0], q2 = gq[1];
-      // the lane's first two rows stay in registers; further rows are re-read
-      const int ra = ne + lane, rb = ra + 32;
-      const Row rowa = ra < nefc ? make_row(true, ra < nef, floss[ra], Dsm[ra], Jaref[ra], jv[ra])
-                                 : make_row(false, false, 0.0f, 1.0f, 0.0f, 0.0f);
-      const Row rowb = rb < nefc ? make_row(true, rb < nef, floss[rb], Dsm[rb], Jaref[rb], jv[rb])
-                                 : make_row(false, false, 0.0f, 1.0f, 0.0f, 0.0f);
-      const bool more = ne + 64 < nefc;
-      float p[3];
-      {
-        Vec3 acc = v3(0.0f, 0.0f, 0.0f) + row_at_zero(rowa);  // running sums start at zero
-        acc = acc + row_at_zero(rowb);
-        if (more)
-          for (int r = rb + 32; r < nefc; r += 32)
-            acc = acc + row_at_zero(make_row(true, r < nef, floss[r], Dsm[r], Jaref[r], jv[r]));
-        p[0] = acc.c0, p[1] = acc.c1, p[2] = acc.c2;
-      }
-      ls_sum(p, bd);
-      const Vec3 rows = v3(p[0], p[1], p[2]);
-      const Vec3 p0 = v3(0.0f, q1, 2.0f * q2) + rows;
-      const Vec3 p0_delta = v3(0.0f, p0.c1, p0.c2);
-      const float q1_abs = sqrtf(2.0f * fmaxf(rows.c0, 0.0f) * fmaxf(rows.c2, 0.0f)) + fabsf(q1);
-      const float gtol_accept = fmaxf(gtol, eps * q1_abs);
-      noise_floor = eps * fmaxf(1.0f, safe_div(q1_abs, p0.c2));
-      alpha = 0.0f, improvement = 0.0f;
-      ls_converged = fabsf(p0.c1) < eps * q1_abs;
-      const float lo_alpha_in = -safe_div(p0.c1, p0.c2);
-      Vec3 lo_in = v3(0.0f, 0.0f, 0.0f);
-      if (!ls_converged) {
-        Vec3 acc = v3(0.0f, 0.0f, 0.0f) + row_at(rowa, lo_alpha_in);
-        acc = acc + row_at(rowb, lo_alpha_in);
-        if (more)
-          for (int r = rb + 32; r < nefc; r += 32)
-            acc = acc + row_at(make_row(true, r < nef, floss[r], Dsm[r], Jaref[r], jv[r]), lo_alpha_in);
-        p[0] = acc.c0, p[1] = acc.c1, p[2] = acc.c2;
-        ls_sum(p, bd);
-        lo_in = eval_quad(q1, q2, lo_alpha_in) + v3(p[0], p[1], p[2]);
-        if (fabsf(lo_in.c1) < gtol_accept && lo_in.c0 < 0.0f) {
-          ls_converged = true;
-          alpha = lo_alpha_in;
-          improvement = -lo_in.c0;
-        }
-      }
-      if (!ls_converged) {
-        const bool lo_less = lo_in.c1 < p0.c1;
-        Vec3 lo = lo_less ? lo_in : p0_delta;
-        float lo_alpha = lo_less ? lo_alpha_in : 0.0f;
-        Vec3 hi = lo_less ? p0_delta : lo_in;
-        float hi_alpha = lo_less ? 0.0f : lo_alpha_in;
-        for (int it = 0; it < m.ls_iterations; ++it) {
-          const float a_lo = lo_alpha - safe_div(lo.c1, lo.c2);
-          const float a_hi = hi_alpha - safe_div(hi.c1, hi.c2);
-          const float a_mid = 0.5f * (lo_alpha + hi_alpha);
-          const Vec3 z3 = v3(0.0f, 0.0f, 0.0f);
-          Vec3 s_lo = z3 + row_at(rowa, a_lo), s_hi = z3 + row_at(rowa, a_hi), s_mid = z3 + row_at(rowa, a_mid);
-          s_lo = s_lo + row_at(rowb, a_lo);
-          s_hi = s_hi + row_at(rowb, a_hi);
-          s_mid = s_mid + row_at(rowb, a_mid);
-          if (more)
-            for (int r = rb + 32; r < nefc; r += 32) {
-              const Row rr = make_row(true, r < nef, floss[r], Dsm[r], Jaref[r], jv[r]);
-              s_lo = s_lo + row_at(rr, a_lo);
-              s_hi = s_hi + row_at(rr, a_hi);
-              s_mid = s_mid + row_at(rr, a_mid);
-            }
-          float q[9] = {s_lo.c0, s_lo.c1, s_lo.c2, s_hi.c0, s_hi.c1, s_hi.c2, s_mid.c0, s_mid.c1, s_mid.c2};
-          ls_sum(q, bd);
-          const Vec3 lo_next = eval_quad(q1, q2, a_lo) + v3(q[0], q[1], q[2]);
-          const Vec3 hi_next = eval_quad(q1, q2, a_hi) + v3(q[3], q[4], q[5]);
-          const Vec3 mid = eval_quad(q1, q2, a_mid) + v3(q[6], q[7], q[8]);
-          const bool conv_lo = fabsf(lo_next.c1) < gtol_accept && lo_next.c0 < 0.0f;
-          const bool conv_hi = fabsf(hi_next.c1) < gtol_accept && hi_next.c0 < 0.0f;
-          const bool conv_mid = fabsf(mid.c1) < gtol_accept && mid.c0 < 0.0f;
-          const bool converged = conv_lo || conv_hi || conv_mid;
-          bool swap_lo = false, swap_hi = false;
-          if (converged) {
-            Vec3 best = v3(IMN_MJ_MAXVAL, 0.0f, 0.0f);
-            float best_alpha = 0.0f;
-            if (conv_lo && lo_next.c0 < best.c0) best = lo_next, best_alpha = a_lo;
-            if (conv_hi && hi_next.c0 < best.c0) best = hi_next, best_alpha = a_hi;
-            if (conv_mid && mid.c0 < best.c0) best = mid, best_alpha = a_mid;
-            lo = hi = best;
-            lo_alpha = hi_alpha = best_alpha;
-          } else {
-            bool s;
-            s = in_bracket(lo, lo_next);
-            if (s) lo = lo_next, lo_alpha = a_lo;
-            swap_lo |= s;
-            s = in_bracket(lo, mid);
-            if (s) lo = mid, lo_alpha = a_mid;
-            swap_lo |= s;
-            s = in_bracket(lo, hi_next);
-            if (s) lo = hi_next, lo_alpha = a_hi;
-            swap_lo |= s;
-            s = in_bracket(hi, hi_next) || (hi.c1 < 0.0f && hi_next.c1 > 0.0f);
-            if (s) hi = hi_next, hi_alpha = a_hi;
-            swap_hi |= s;
-            s = in_bracket(hi, mid);
-            if (s) hi = mid, hi_alpha = a_mid;
-            swap_hi |= s;
-            s = in_bracket(hi, lo_next);
-            if (s) hi = lo_next, hi_alpha = a_lo;
-            swap_hi |= s;
-          }
-          const bool ls_done = converged || (!swap_lo && !swap_hi) ||
-                               (lo.c0 < 0.0f && lo.c1 < 0.0f && lo.c1 > -gtol) ||
-                               (hi.c0 < 0.0f && hi.c1 > 0.0f && hi.c1 < gtol);
-          if (lo.c0 < 0.0f || hi.c0 < 0.0f) {
-            const bool lo_better = lo.c0 < hi.c0;
-            alpha = lo_better ? lo_alpha : hi_alpha;
-            improvement = -(lo_better ? lo.c0 : hi.c0);
-          }
-          if (ls_done) {
-            ls_converged = true;
-            break;
-          }
-        }
+        s.qacc[i] = fmaf(alpha, s.search[i], s.qacc[i]);
+        s.Ma[i] = fmaf(alpha, s.mv[i], s.Ma[i]);
       }
     }
     PROF(6);
-    // ---- move, re-evaluate rows, list QUADRATIC flips (newton_stages.py:373-426)
-    for (int i = lane; i < nv; i += 32) {
-      qacc[i] = fmaf(alpha, search[i], qacc[i]);
-      Ma[i] = fmaf(alpha, mv[i], Ma[i]);
-    }
+    // ---- move along the search direction, re-evaluate rows, list QUADRATIC flips
+    // (newton_stages.py:373-426); on pass 0 this is upstream's constraint update
     quad_count = 0;
     state_count = 0;
-    nfr = 0;
+    int nfr = 0;
+#pragma unroll 1
     for (int base = 0; base < nefc; base += 32) {
       const int r = base + lane;
       bool flip = false, changed = false;
       float f = 0.0f;
       if (r < nefc) {
-        const float nj = rounded_step(Jaref[r], alpha, jv[r]);
-        Jaref[r] = nj;
+        const float nj = first ? s.Jaref[r] : rounded_step(s.Jaref[r], alpha, s.jv[r]);
+        s.Jaref[r] = nj;
         const bool is_eq = r < ne, is_fr = !is_eq && r < nef;
         int ns;
-        eval_constraint(is_eq, is_fr, nj, Dsm[r], is_fr ? floss[r] : 0.0f, f, ns);
-        const int old = state[r];
-        force[r] = f;
-        state[r] = ns;
-        flip = (old == IMN_STATE_QUADRATIC) != (ns == IMN_STATE_QUADRATIC);
+        eval_constraint(is_eq, is_fr, nj, s.Dsm[r], is_fr ? s.floss[r] : 0.0f, f, ns);
+        const int old = first ? -1 : s.state[r];
+        s.force[r] = f;
+        s.state[r] = ns;
+        if (first) s.jv[r] = 0.0f;  // aref no longer needed
+        flip = !first && (old == IMN_STATE_QUADRATIC) != (ns == IMN_STATE_QUADRATIC);
         changed = old != ns;
       }
       const unsigned below = (1u << lane) - 1u;
       const unsigned fm = __ballot_sync(IMN_FULL_MASK, flip);
-      if (flip) ids[quad_count + __popc(fm & below)] = r;
+      if (flip) s.ids[quad_count + __popc(fm & below)] = r;
       quad_count += __popc(fm);
       state_count += __popc(__ballot_sync(IMN_FULL_MASK, changed));
       const unsigned nz = __ballot_sync(IMN_FULL_MASK, f != 0.0f);
-      if (f != 0.0f) frows[nfr + __popc(nz & below)] = r;
+      if (f != 0.0f) s.frows[nfr + __popc(nz & below)] = r;
       nfr += __popc(nz);
     }
-    ls_exhausted = fabsf(alpha) < noise_floor;
-    if (ls_exhausted) state_count += 1;
-    if (!ls_converged) {
-      if ((m.warn_overflow & m.overflow_ls_iterations) && lane == 0)
-        printf("linesearch iterations limit reached - please increase ls_iterations to %u\n",
-               (unsigned)m.ls_iterations);
-      overflow |= m.overflow_ls_iterations;
+    if (!first) {
+      ls_exhausted = fabsf(alpha) < noise_floor;
+      if (ls_exhausted) state_count += 1;
+      if (!ls_converged) {
+        if ((m.warn_overflow & m.overflow_ls_iterations) && lane == 0)
+          printf("linesearch iterations limit reached - please increase ls_iterations to %u\n",
+                 (unsigned)m.ls_iterations);
+        overflow |= m.overflow_ls_iterations;
+      }
     }
     __syncwarp();
     PROF(7);
-    // ---- gradient (newton_stages.py:745-798) and factor (newton_stages.py:629-740)
-    const bool changed = state_count != 0;
+    // ---- gradient (newton_stages.py:745-798), Hessian, factor (newton_stages.py:629-740)
+    const bool changed = first || state_count != 0;
     search_unchanged = !changed;
     if (!changed) {
       const float sigma = grad_scale, ns = sigma - alpha;
@@ -851,45 +267,21 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
       decrement *= rsq;
       grad_scale = ns;
     } else {
-      grad_dot = full_gradient(nfr);
+      grad_dot = full_gradient<JRES>(s, nfr);
       PROF(8);
       decrement = 0.0f;
       grad_scale = 1.0f;
-      if (quad_count > 0) {
-        // dofs the changed rows touch, ascending (newton_stages.py:657-680)
-        int n = 0;
-        for (int base = 0; base < nv; base += 32) {
-          const int dof = base + lane;
-          bool hit = false;
-          if (dof < nv)
-            for (int t = 0; t < quad_count && !hit; ++t) hit = Jat(ids[t], dof) != 0.0f;
-          const unsigned hm = __ballot_sync(IMN_FULL_MASK, hit);
-          if (hit) uni[n + __popc(hm & ((1u << lane) - 1u))] = dof;
-          n += __popc(hm);
-        }
-        if (lane == 0) uni[nv] = n;
-        __syncwarp();
-        const int npu = n * (n + 1) / 2;
-        int pi = lane, pj = 0;
-        pair_advance(pi, pj, 0);
-        for (int e = lane; e < npu; e += 32) {
-          const int row = uni[pi], col = uni[pj];
-          float delta = 0.0f;
-          for (int t = 0; t < quad_count; ++t) {
-            const int r = ids[t];
-            const float a = Jat(r, row), b = Jat(r, col);
-            float da = Dsm[r] * a;
-            if (state[r] != IMN_STATE_QUADRATIC) da = -da;
-            if (a != 0.0f && b != 0.0f) delta = fmaf(da, b, delta);
-          }
-          if (delta != 0.0f) A[(col + 1) * ldu + row] = A[(col + 1) * ldu + row] + delta;
-          pair_advance(pi, pj, 32);
-        }
-        __syncwarp();
-      }
+      if (first)
+        assemble_hessian<JRES>(s, nfr);
+      else if (quad_count > 0)
+        update_hessian<JRES>(s, quad_count);
       PROF(9);
-      factor_solve(quad_count > 0, search_dot, decrement);
+      factor_solve(s, first || quad_count > 0, search_dot, decrement);
       PROF(10);
+    }
+    if (first) {
+      quad_count = 0, state_count = 0;
+      continue;
     }
     // ---- convergence (newton_fusion.py:267-295) -------------------------------
     ++niter;
@@ -903,37 +295,44 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
                  (unsigned)m.iterations);
         overflow |= m.overflow_iterations;
       }
-      done = true;
       if (lane == 0 && cx.nsolving) atomicAdd(cx.nsolving, -1);
+      break;
     }
   }
 
   // ---- results (once) ---------------------------------------------------------
+#pragma unroll 1
   for (int i = lane; i < nv; i += 32) {
-    d.qacc[dofo + i] = qacc[i];
-    d.efc_Ma[dofo + i] = Ma[i];
-    d.qfrc_constraint[dofo + i] = rowless ? 0.0f : fmaf(-grad_scale, grad[i], Ma[i] - qfs[i]);
-    if (cx.search) cx.search[dofo + i] = search[i];
-    if (cx.mv) cx.mv[dofo + i] = mv[i];
-    if (cx.grad) cx.grad[(size_t)w * cx.grad_ld + i] = grad[i];
+    d.qacc[dofo + i] = s.qacc[i];
+    d.efc_Ma[dofo + i] = s.Ma[i];
+    d.qfrc_constraint[dofo + i] = rowless ? 0.0f : fmaf(-grad_scale, s.grad[i], s.Ma[i] - s.qfs[i]);
+    if (cx.search) cx.search[dofo + i] = s.search[i];
+    if (cx.mv) cx.mv[dofo + i] = s.mv[i];
+    if (cx.grad) cx.grad[(size_t)w * cx.grad_ld + i] = s.grad[i];
   }
+#pragma unroll 1
   for (int r = lane; r < nefc; r += 32) {
-    d.efc_force[efco + r] = force[r];
-    d.efc_state[efco + r] = state[r];
-    if (cx.Jaref) cx.Jaref[efco + r] = Jaref[r];
-    if (cx.jv) cx.jv[efco + r] = jv[r];
-    if (cx.quad_changed_ids && r < quad_count) cx.quad_changed_ids[efco + r] = ids[r];
+    d.efc_force[efco + r] = s.force[r];
+    d.efc_state[efco + r] = s.state[r];
+    if (cx.Jaref) cx.Jaref[efco + r] = s.Jaref[r];
+    if (cx.jv) cx.jv[efco + r] = s.jv[r];
+    if (cx.quad_changed_ids && r < quad_count) cx.quad_changed_ids[efco + r] = s.ids[r];
   }
   if (cx.dof_union && !rowless)
-    for (int i = lane; i <= nv; i += 32) cx.dof_union[(size_t)w * (nv + 1) + i] = uni[i];
+#pragma unroll 1
+    for (int i = lane; i <= nv; i += 32) cx.dof_union[(size_t)w * (nv + 1) + i] = s.uni[i];
   if (!rowless) {
     const size_t ho = (size_t)w * m.nv_pad * m.nv_pad;
     if (cx.h)
+#pragma unroll 1
       for (int r = 0; r < nv; ++r)
-        for (int c = r + lane; c < nv; c += 32) cx.h[ho + (size_t)r * m.nv_pad + c] = A[(c + 1) * ldu + r];
+#pragma unroll 1
+        for (int c = r + lane; c < nv; c += 32) cx.h[ho + (size_t)r * m.nv_pad + c] = s.A[(c + 1) * s.ldu + r];
     if (cx.hfactor && !cx.sparse_plan)
+#pragma unroll 1
       for (int r = 0; r < nv; ++r)
-        for (int c = r + lane; c < nv; c += 32) cx.hfactor[ho + (size_t)r * m.nv_pad + c] = A[r * ldu + c];
+#pragma unroll 1
+        for (int c = r + lane; c < nv; c += 32) cx.hfactor[ho + (size_t)r * m.nv_pad + c] = s.A[r * s.ldu + c];
   }
   PROF(11);
   PROF_FLUSH;
@@ -994,7 +393,12 @@ static int validate(const ImnModel* m, const ImnData* d, const ImnCtx* cx) {
 
 static int plan_launch(const ImnModel* m, const ImnData* d, Geom* g, bool* resident) {
   Geom gr = make_geom(*m, *d, true);
-  if (gr.total * 4 <= kResidentBudget) {
+#ifdef IMN_FORCE_STREAM
+  const int budget = 0;
+#else
+  const int budget = kResidentBudget;
+#endif
+  if (gr.total * 4 <= budget) {
     *g = gr, *resident = true;
     return IMN_OK;
   }

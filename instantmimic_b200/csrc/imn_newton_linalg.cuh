@@ -1,0 +1,228 @@
+// imn_newton_linalg.cuh -- per-world linear algebra of the fused Newton kernel,
+// executed by one warp on shared-memory operands.  Every function is called from
+// exactly one place in the kernel so that the machine code stays small (the
+// kernel is bound by instruction fetch and latency, not by arithmetic).
+#pragma once
+
+#include "imn_newton_dev.cuh"
+
+namespace imn {
+
+// Shared-memory view of one world plus the per-world constants.
+struct World {
+  int nv, ldj, ldu, bd, nefc, ne, nef, lane, nM;
+  float *Jsm, *A, *qacc, *Ma, *search, *mv, *grad, *qfs, *xsm, *dinv, *Msm;
+  float *Jaref, *jv, *Dsm, *floss, *force;
+  int *state, *ids, *frows, *uni;
+  const float* Jg;  // this world's J in global memory
+  const int* mulm_rowadr;
+  const uint32_t* mulm_pack;
+#ifdef IMN_PROFILE
+  long long* prof_acc;
+  long long* prof_t;
+#endif
+};
+
+#ifdef IMN_PROFILE
+#define IMN_MARK(s, k) do { const long long t_ = clock64(); (s).prof_acc[k] += t_ - *(s).prof_t; *(s).prof_t = t_; } while (0)
+#else
+#define IMN_MARK(s, k)
+#endif
+
+// Rows [base, base+32) of J: resident rows are addressed in place, otherwise they
+// are staged through the 32-row tile.
+template <bool JRES>
+__device__ __forceinline__ const float* j_tile(const World& s, int base) {
+  if (JRES) return s.Jsm + base * s.ldj;
+  __syncwarp();
+  const int n = min(32, s.nefc - base) * s.ldj;
+  const float* src = s.Jg + (size_t)base * s.ldj;
+#pragma unroll 4
+  for (int i = s.lane; i < n; i += 32) s.Jsm[i] = src[i];
+  __syncwarp();
+  return s.Jsm;
+}
+template <bool JRES>
+__device__ __forceinline__ float j_at(const World& s, int r, int i) {
+  return JRES ? s.Jsm[r * s.ldj + i] : s.Jg[(size_t)r * s.ldj + i];
+}
+
+// outM = M v over the symmetric rows (newton_fusion.py:171-176) and
+// outJ[r] = J[r,:] v (- minus[r]): one running sum per row; above 50 dofs in
+// 20-dof partials joined by plain adds (newton_stages.py:157-174).
+template <bool JRES>
+__device__ __forceinline__ void products(const World& s, const float* v, float* outM, float* outJ,
+                                         const float* minus) {
+  const int lane = s.lane, nv = s.nv;
+#pragma unroll 1
+  for (int i = lane; i < nv; i += 32) {
+    float acc = 0.0f;
+    const int k1 = __ldg(s.mulm_rowadr + i + 1);
+#pragma unroll 4
+    for (int k = __ldg(s.mulm_rowadr + i); k < k1; ++k) {
+      const uint32_t p = __ldg(s.mulm_pack + k);
+      acc = fmaf(s.Msm[p >> 16], v[p & 0xFFFF], acc);
+    }
+    outM[i] = acc;
+  }
+  const int chunk = nv > 50 ? 20 : nv;
+#pragma unroll 1
+  for (int base = 0; base < s.nefc; base += 32) {
+    const float* Jt = j_tile<JRES>(s, base);
+    const int r = base + lane;
+    if (r < s.nefc) {
+      const float* Jr = Jt + lane * s.ldj;
+      const float sub = minus ? minus[r] : 0.0f;
+      float total = 0.0f;
+#pragma unroll 1
+      for (int s0 = 0; s0 < nv; s0 += chunk) {
+        float p = 0.0f;
+        const int e = min(s0 + chunk, nv);
+#pragma unroll 4
+        for (int i = s0; i < e; ++i) p = fmaf(Jr[i], v[i], p);
+        if (s0 == 0)
+          total = minus ? p - sub : (nv > 50 ? 0.0f + p : p);
+        else
+          total = total + p;
+      }
+      outJ[r] = total;
+    }
+    if (!JRES) __syncwarp();
+  }
+}
+
+// grad = Ma - qfrc_smooth - J^T force over the rows with a nonzero force (a zero
+// force leaves the running sums unchanged), then grad_dot
+// (newton_stages.py:785-795).
+template <bool JRES>
+__device__ __forceinline__ float full_gradient(const World& s, int nfr) {
+  const int lane = s.lane, nv = s.nv;
+  float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f;
+  const int i0 = lane, i1 = lane + 32, i2 = lane + 64;
+  const bool h0 = i0 < nv, h1 = i1 < nv, h2 = i2 < nv;
+  int a = 0;
+#pragma unroll 1
+  for (int base = 0; base < s.nefc; base += 32) {
+    const float* Jt = j_tile<JRES>(s, base);
+    const int hi = JRES ? s.nefc : base + 32;
+#pragma unroll 2
+    for (; a < nfr; ++a) {
+      const int r = s.frows[a];
+      if (r >= hi) break;
+      const float f = s.force[r];
+      const float* Jr = Jt + (r - base) * s.ldj;
+      if (h0) s0 = fmaf(Jr[i0], f, s0);
+      if (h1) s1 = fmaf(Jr[i1], f, s1);
+      if (h2) s2 = fmaf(Jr[i2], f, s2);
+    }
+    if (JRES) break;
+    __syncwarp();
+  }
+  if (h0) s.grad[i0] = (s.Ma[i0] - s.qfs[i0]) - s0;
+  if (h1) s.grad[i1] = (s.Ma[i1] - s.qfs[i1]) - s1;
+  if (h2) s.grad[i2] = (s.Ma[i2] - s.qfs[i2]) - s2;
+  __syncwarp();
+  return logical_block_sum(nv, s.bd, lane, [&](int i, float acc) { return fmaf(s.grad[i], s.grad[i], acc); });
+}
+
+// H = M + J^T diag(D, QUADRATIC rows) J on the upper triangle, every entry summing
+// its rows in ascending order.  H[r][c] (r <= c) lives at A[(c+1)*ldu + r].
+template <bool JRES>
+__device__ __forceinline__ void assemble_hessian(const World& s, int nfr) {
+  const int lane = s.lane, nv = s.nv, ldu = s.ldu;
+  float* A = s.A;
+#pragma unroll 4
+  for (int e = lane; e < (nv + 1) * ldu; e += 32) A[e] = 0.0f;
+  __syncwarp();
+#pragma unroll 1
+  for (int i = lane; i < nv; i += 32) {
+    // the symmetric row of dof i lists every stored entry (i, c); keep c >= i
+    const int k1 = __ldg(s.mulm_rowadr + i + 1);
+#pragma unroll 1
+    for (int k = __ldg(s.mulm_rowadr + i); k < k1; ++k) {
+      const uint32_t p = __ldg(s.mulm_pack + k);
+      const int c = p & 0xFFFF;
+      if (c >= i) A[(c + 1) * ldu + i] = s.Msm[p >> 16];
+    }
+  }
+  __syncwarp();
+  const int npair = nv * (nv + 1) / 2;
+  int a_lo = 0;
+#pragma unroll 1
+  for (int base = 0; base < s.nefc; base += 32) {
+    const float* Jt = j_tile<JRES>(s, base);
+    const int row_hi = JRES ? s.nefc : min(base + 32, s.nefc);
+    int a_hi = a_lo;
+    while (a_hi < nfr && s.frows[a_hi] < row_hi) ++a_hi;
+    // two entries per lane per pass so that their running sums overlap
+    int i0 = lane, j0 = 0, i1 = lane + 32, j1 = 0;
+    pair_advance(i0, j0, 0);
+    pair_advance(i1, j1, 0);
+#pragma unroll 1
+    for (int e = lane; e < npair; e += 64) {
+      const bool two = e + 32 < npair;
+      const int i1c = two ? i1 : i0, j1c = two ? j1 : j0;
+      float v0 = A[(j0 + 1) * ldu + i0];
+      float v1 = A[(j1c + 1) * ldu + i1c];
+#pragma unroll 2
+      for (int a = a_lo; a < a_hi; ++a) {
+        const int r = s.frows[a];
+        if (s.state[r] != IMN_STATE_QUADRATIC) continue;
+        const float Dr = s.Dsm[r];
+        const float* Jr = Jt + (r - base) * s.ldj;
+        v0 = fmaf(Jr[i0] * Dr, Jr[j0], v0);
+        v1 = fmaf(Jr[i1c] * Dr, Jr[j1c], v1);
+      }
+      A[(j0 + 1) * ldu + i0] = v0;
+      if (two) A[(j1 + 1) * ldu + i1] = v1;
+      pair_advance(i0, j0, 64);
+      pair_advance(i1, j1, 64);
+    }
+    a_lo = a_hi;
+    if (JRES) break;
+    __syncwarp();
+  }
+  __syncwarp();
+}
+
+// Rows whose QUADRATIC membership flipped -> dofs they touch (ascending), then
+// the pair update of H in the listed row order (newton_stages.py:651-701).
+template <bool JRES>
+__device__ __forceinline__ void update_hessian(const World& s, int count) {
+  const int lane = s.lane, nv = s.nv, ldu = s.ldu;
+  int n = 0;
+#pragma unroll 1
+  for (int base = 0; base < nv; base += 32) {
+    const int dof = base + lane;
+    bool hit = false;
+    if (dof < nv)
+#pragma unroll 1
+      for (int t = 0; t < count && !hit; ++t) hit = j_at<JRES>(s, s.ids[t], dof) != 0.0f;
+    const unsigned hm = __ballot_sync(IMN_FULL_MASK, hit);
+    if (hit) s.uni[n + __popc(hm & ((1u << lane) - 1u))] = dof;
+    n += __popc(hm);
+  }
+  if (lane == 0) s.uni[nv] = n;
+  __syncwarp();
+  const int npu = n * (n + 1) / 2;
+  int pi = lane, pj = 0;
+  pair_advance(pi, pj, 0);
+#pragma unroll 1
+  for (int e = lane; e < npu; e += 32) {
+    const int row = s.uni[pi], col = s.uni[pj];
+    float delta = 0.0f;
+#pragma unroll 2
+    for (int t = 0; t < count; ++t) {
+      const int r = s.ids[t];
+      const float a = j_at<JRES>(s, r, row), b = j_at<JRES>(s, r, col);
+      float da = s.Dsm[r] * a;
+      if (s.state[r] != IMN_STATE_QUADRATIC) da = -da;
+      if (a != 0.0f && b != 0.0f) delta = fmaf(da, b, delta);
+    }
+    if (delta != 0.0f) s.A[(col + 1) * ldu + row] = s.A[(col + 1) * ldu + row] + delta;
+    pair_advance(pi, pj, 32);
+  }
+  __syncwarp();
+}
+
+}  // namespace imn
