@@ -1,14 +1,5 @@
 // Entry points whose kernels are not written yet: they refuse the call.
 #include "imn_common.cuh"
-extern "C" int imn_tree_ldl_solve(const ImnTreePlan*, const float*, int64_t, const float*, int64_t, float*,
-                                  int64_t, int32_t, void*) {
-  return imn::set_error("imn_tree_ldl_solve: not implemented"), IMN_ERR_UNSUPPORTED;
-}
-extern "C" int imn_blocked_dense_factor_solve(const ImnBlockedPlan*, const float*, int64_t, const float*,
-                                              float*, float*, const int32_t*, int32_t, int32_t, int32_t,
-                                              void*) {
-  return imn::set_error("imn_blocked_dense_factor_solve: not implemented"), IMN_ERR_UNSUPPORTED;
-}
 extern "C" int imn_sparse_factor_nonfused(const ImnSparsePlan*, const uint8_t*, const float*, int64_t,
                                           const float*, const int32_t*, const int32_t*, float*, float*,
                                           int64_t, float*, float*, int32_t, int32_t, int32_t, void*) {

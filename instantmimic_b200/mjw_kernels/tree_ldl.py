@@ -1,3 +1,347 @@
-"""placeholder"""
-def create_tree_factor_solve_scratch(m, device=None):
-    return None
+"""Tree-structured L'DL factor + solve of inertia-like matrices.
+
+MuJoCo stores M (and the implicit-integration matrix M - h qDeriv, which has M's
+sparsity) in CSR over each dof's ancestors: a row lists the dof's ancestors root
+first and ends with the diagonal, and every ancestor's row is a prefix of it.
+Eliminating dofs from the leaves towards the roots therefore creates no fill-in.
+
+Interface and planning rules follow the reference's
+``src/instantmimic/utils/mjw_kernels/tree_ldl.py`` (TreeLdlPlan :47-57, structure
+check :66-91, planner :105-185, profitability gate :188-193, entry point :419-433).
+The reference turns a plan into generated straight-line CUDA source per model;
+here the plan is compiled into a small instruction list that one generic sm_100a
+kernel interprets (``csrc/imn_msolve.cu``): 32 worlds per warp, one warp per
+group, all operands of a world in one shared-memory column, so lanes never
+conflict on a bank and nothing diverges.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Any
+
+import numpy as np
+
+from .. import _lib, abi
+from ..arrays import addr, elem_strides
+
+MAX_GROUPS = 4
+# Static shared memory the reference allows one block for the trunk exchange.
+MAX_SHARED_BYTES = 48 * 1024
+# The tree solve replaces the dense Cholesky when its critical path is short, or
+# short relative to the dense flops per world (tree_ldl.py:33-44).
+MAX_SHORT_SPAN = 4096
+MIN_DENSE_TO_SPAN_RATIO = 8.0
+
+# instruction opcodes of the interpreter (four int32 per instruction: op, dst, a | b << 16, c)
+OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X = range(10)
+
+
+@dataclass(frozen=True)
+class TreeLdlPlan:
+    groups: tuple[tuple[int, ...], ...]
+    """Dofs of each group's parts, leaves first (descending)."""
+    trunk: tuple[int, ...]
+    """Trunk dofs, ascending; ancestor-closed."""
+    span: int
+    """Critical path in update units: the trunk plus the heaviest group."""
+    dense_cost: int
+    """Dense Cholesky flops per world over all trees."""
+
+
+@dataclass
+class TreeFactorSolveScratch:
+    plan: TreeLdlPlan
+    groups: int
+    cuda: bool
+    struct: abi.ImnTreePlan
+    tables: tuple  # device tensors the struct points into (kept alive)
+    nv: int
+
+
+def tree_ldl_structure(rowadr, rownnz, colind):
+    """The CSR as tuples when it has the nested-ancestor form; else ``None``."""
+    rowadr = np.asarray(rowadr, dtype=np.int64)
+    rownnz = np.asarray(rownnz, dtype=np.int64)
+    colind = np.asarray(colind, dtype=np.int64)
+    nv = rowadr.size
+    if nv == 0 or rownnz.size != nv or (rownnz < 1).any():
+        return None
+    if (rowadr + rownnz > colind.size).any():
+        return None
+    for k in range(nv):
+        row = colind[rowadr[k] : rowadr[k] + rownnz[k]]
+        if row[-1] != k or (row[:-1] >= k).any():
+            return None
+        for depth, anc in enumerate(row[:-1]):
+            # the ancestor's row must be exactly this row's first depth+1 entries
+            if rownnz[anc] != depth + 1:
+                return None
+            if not np.array_equal(colind[rowadr[anc] : rowadr[anc] + depth + 1], row[: depth + 1]):
+                return None
+    as_tuple = lambda a: tuple(int(v) for v in a)  # noqa: E731
+    return as_tuple(rowadr), as_tuple(rownnz), as_tuple(colind)
+
+
+def _tree(rowadr, rownnz, colind):
+    nv = len(rowadr)
+    parent = [colind[rowadr[k] + rownnz[k] - 2] if rownnz[k] > 1 else -1 for k in range(nv)]
+    children: list[list[int]] = [[] for _ in range(nv)]
+    for k, p in enumerate(parent):
+        if p >= 0:
+            children[p].append(k)
+    return parent, children
+
+
+def _trunk_entry_count(rowadr, rownnz, trunk) -> int:
+    return sum(rownnz[i] for i in trunk)
+
+
+def _shared_bytes(rowadr, rownnz, groups: int, trunk) -> int:
+    """Bytes of the reference's trunk exchange arrays for one block of 32 worlds."""
+    if not trunk:
+        return 0
+    entries = _trunk_entry_count(rowadr, rownnz, trunk)
+    return 4 * 32 * (groups * (entries + len(trunk)) + len(trunk))
+
+
+def plan_tree_ldl(rowadr, rownnz, colind, groups: int) -> TreeLdlPlan:
+    """Shortest-critical-path plan with exactly ``groups`` groups.
+
+    Start with whole trees as parts.  Repeatedly take the heaviest part that still
+    has children, move its root dof to the trunk and let its children become
+    parts; after each move pack the parts onto the groups (heaviest first, always
+    onto the lightest group) and remember the cut with the shortest critical path.
+    """
+    nv = len(rowadr)
+    parent, children = _tree(rowadr, rownnz, colind)
+    # eliminating a dof with n row entries: n (n - 1) / 2 updates + scaling + solve
+    cost = [n * (n - 1) // 2 + 2 * n for n in rownnz]
+    weight, size = list(cost), [1] * nv
+    for k in range(nv - 1, -1, -1):
+        if parent[k] >= 0:
+            weight[parent[k]] += weight[k]
+            size[parent[k]] += size[k]
+    roots = [k for k in range(nv) if parent[k] < 0]
+    dense_cost = sum(size[r] ** 3 // 3 for r in roots)
+
+    def pack(parts):
+        load = [0] * groups
+        bins: list[list[int]] = [[] for _ in range(groups)]
+        for r in sorted(parts, key=lambda r: (-weight[r], r)):
+            g = load.index(min(load))
+            load[g] += weight[r]
+            bins[g].append(r)
+        return max(load), bins
+
+    parts, trunk = list(roots), []
+    best = None
+    while True:
+        heaviest, bins = pack(parts)
+        span = heaviest + sum(cost[k] + 2 * rownnz[k] for k in trunk)
+        if best is None or span < best[0]:
+            best = (span, sorted(trunk), bins)
+        candidates = [r for r in parts if children[r]]
+        if not candidates:
+            break
+        r = max(candidates, key=lambda r: (weight[r], -r))
+        parts.remove(r)
+        trunk.append(r)
+        parts.extend(children[r])
+    span, trunk, bins = best
+    out = []
+    for part_roots in bins:
+        nodes, stack = [], list(part_roots)
+        while stack:
+            k = stack.pop()
+            nodes.append(k)
+            stack.extend(children[k])
+        out.append(tuple(sorted(nodes, reverse=True)))
+    return TreeLdlPlan(groups=tuple(out), trunk=tuple(trunk), span=span, dense_cost=dense_cost)
+
+
+def best_tree_ldl_plan(rowadr, rownnz, colind) -> TreeLdlPlan:
+    """Fastest plan whose trunk exchange fits the shared-memory limit; fewest groups on ties."""
+    best = None
+    for groups in range(1, MAX_GROUPS + 1):
+        plan = plan_tree_ldl(rowadr, rownnz, colind, groups)
+        if _shared_bytes(rowadr, rownnz, groups, plan.trunk) > MAX_SHARED_BYTES:
+            continue
+        if best is None or plan.span < best.span:
+            best = plan
+    assert best is not None  # a single group has no trunk exchange
+    return best
+
+
+def tree_ldl_beats_dense(plan: TreeLdlPlan) -> bool:
+    return plan.span <= MAX_SHORT_SPAN or plan.dense_cost >= MIN_DENSE_TO_SPAN_RATIO * plan.span
+
+
+class _Program:
+    """Instruction streams of a plan: per group a forward and a backward stream, plus
+    the trunk stream run by the owner group between two block barriers."""
+
+    def __init__(self, rowadr, rownnz, colind, plan: TreeLdlPlan):
+        nv, nM, G = len(rowadr), len(colind), len(plan.groups)
+        trunk = set(plan.trunk)
+        entries = [e for i in plan.trunk for e in range(rowadr[i], rowadr[i] + rownnz[i])]
+        eslot = {e: n for n, e in enumerate(entries)}
+        dslot = {i: n for n, i in enumerate(plan.trunk)}
+        T, Tv = len(entries), len(plan.trunk)
+        # slot map of one world's shared-memory column
+        self.M0, self.S0, self.D0, self.X0 = 0, nM, nM + nv, nM + 2 * nv
+        acc0 = nM + 3 * nv
+        self.nslot = acc0 + G * (T + Tv)
+        am = lambda j, e: acc0 + j * (T + Tv) + eslot[e]  # noqa: E731
+        asol = lambda j, i: acc0 + j * (T + Tv) + T + dslot[i]  # noqa: E731
+        m, s, d, x = (lambda e: e), (lambda k: self.S0 + k), (lambda k: self.D0 + k), (lambda k: self.X0 + k)
+
+        def eliminate(k, out, target_m, target_s):
+            start, count = rowadr[k], rownnz[k] - 1
+            out.append((OP_INV, d(k), m(start + count), 0, 0))
+            for p in range(count):
+                anc = colind[start + p]
+                for q in range(p + 1):
+                    out.append((OP_UPD, target_m(anc, rowadr[anc] + q), m(start + p), m(start + q), d(k)))
+            for p in range(count):
+                out.append((OP_SCALE, m(start + p), d(k), 0, 0))
+            for p in range(count):
+                out.append((OP_SUBMUL, target_s(colind[start + p]), m(start + p), s(k), 0))
+
+        self.forward, self.backward = [], []
+        touched = []
+        for j, nodes in enumerate(plan.groups):
+            tm = sorted(
+                {
+                    rowadr[colind[rowadr[k] + p]] + q
+                    for k in nodes
+                    for p in range(rownnz[k] - 1)
+                    if colind[rowadr[k] + p] in trunk
+                    for q in range(p + 1)
+                }
+            )
+            ts = sorted({colind[rowadr[k] + p] for k in nodes for p in range(rownnz[k] - 1)} & trunk)
+            touched.append((set(tm), set(ts)))
+            f = []
+            for k in nodes:
+                for e in range(rowadr[k], rowadr[k] + rownnz[k]):
+                    f.append((OP_LOAD_M, m(e), e, 0, 0))
+            for k in nodes:
+                f.append((OP_LOAD_Y, s(k), k, 0, 0))
+            for e in tm:
+                f.append((OP_ZERO, am(j, e), 0, 0, 0))
+            for i in ts:
+                f.append((OP_ZERO, asol(j, i), 0, 0, 0))
+            tgt_m = lambda anc, index, j=j: index if anc not in trunk else am(j, index)  # noqa: E731
+            tgt_s = lambda anc, j=j: s(anc) if anc not in trunk else asol(j, anc)  # noqa: E731
+            for k in nodes:
+                eliminate(k, f, tgt_m, tgt_s)
+            self.forward.append(f)
+            b, own = [], set()
+            for i in reversed(nodes):
+                b.append((OP_MUL, x(i), s(i), d(i), 0))
+                for p in range(rownnz[i] - 1):
+                    b.append((OP_SUBMUL, x(i), m(rowadr[i] + p), x(colind[rowadr[i] + p]), 0))
+                own.add(i)
+                b.append((OP_STORE_X, i, x(i), 0, 0))
+            self.backward.append(b)
+        t = []
+        for e in entries:
+            t.append((OP_LOAD_M, m(e), e, 0, 0))
+            for j in range(G):
+                if e in touched[j][0]:
+                    t.append((OP_ADD, m(e), am(j, e), 0, 0))
+        for i in plan.trunk:
+            t.append((OP_LOAD_Y, s(i), i, 0, 0))
+            for j in range(G):
+                if i in touched[j][1]:
+                    t.append((OP_ADD, s(i), asol(j, i), 0, 0))
+        for k in reversed(plan.trunk):
+            eliminate(k, t, lambda anc, index: index, lambda anc: s(anc))
+        for i in plan.trunk:
+            # the trunk solution lands in x(i), where the groups' backward streams read it
+            t.append((OP_MUL, x(i), s(i), d(i), 0))
+            for p in range(rownnz[i] - 1):
+                t.append((OP_SUBMUL, x(i), m(rowadr[i] + p), x(colind[rowadr[i] + p]), 0))
+            t.append((OP_STORE_X, i, x(i), 0, 0))
+        self.trunk = t
+        self.owner = min(range(G), key=lambda j: sum(rownnz[k] ** 2 for k in plan.groups[j]))
+        self.ntrunk, self.ntrunk_entries = Tv, T
+
+    def encode(self):
+        """(prog int32 (n, 4), prog_ptr int32 (3 G + 2)): streams are stored as
+        forward_0..forward_{G-1}, trunk, backward_0..backward_{G-1}."""
+        streams = [*self.forward, self.trunk, *self.backward]
+        ptr, flat = [0], []
+        for st in streams:
+            for op, dst, a, b, c in st:
+                if max(dst, a, b, c) >= 1 << 16:
+                    raise ValueError("tree L'DL program exceeds 16-bit slots")
+                flat.append((op, dst, a | (b << 16), c))
+            ptr.append(len(flat))
+        prog = np.asarray(flat, dtype=np.int32).reshape(-1, 4)
+        return prog, np.asarray(ptr, dtype=np.int32)
+
+
+def compile_plan(structure, plan: TreeLdlPlan, device: Any) -> TreeFactorSolveScratch:
+    """Upload a plan's instruction streams and build its C-ABI struct."""
+    import torch
+
+    rowadr, rownnz, colind = structure
+    program = _Program(rowadr, rownnz, colind, plan)
+    prog, ptr = program.encode()
+    t_prog = torch.from_numpy(prog).to(device)
+    t_ptr = torch.from_numpy(ptr).to(device)
+    st = abi.ImnTreePlan()
+    st.nv, st.nM = len(rowadr), len(colind)
+    st.groups = len(plan.groups)
+    st.ntrunk, st.ntrunk_entries = program.ntrunk, program.ntrunk_entries
+    st.nslot = program.nslot
+    st.prog, st.prog_ptr = addr(t_prog), addr(t_ptr)
+    st.owner = program.owner
+    return TreeFactorSolveScratch(
+        plan=plan, groups=len(plan.groups), cuda=True, struct=st, tables=(t_prog, t_ptr), nv=len(rowadr)
+    )
+
+
+def scratch_for_plan(structure, plan: TreeLdlPlan, device: Any) -> TreeFactorSolveScratch:
+    return compile_plan(structure, plan, device)
+
+
+def _to_numpy(a):
+    if isinstance(a, np.ndarray):
+        return a
+    if hasattr(a, "cpu"):
+        return a.cpu().numpy()
+    return a.numpy()
+
+
+def create_tree_factor_solve_scratch(m: Any, device: Any = "cuda") -> TreeFactorSolveScratch | None:
+    """The compiled factor+solve for this model, or ``None`` when ineligible
+    (tree_ldl.py:403-416)."""
+    if getattr(m, "nv", 0) <= 0:
+        return None
+    arrays = [getattr(m, name, None) for name in ("M_rowadr", "M_rownnz", "M_colind")]
+    if any(a is None for a in arrays):
+        return None
+    structure = tree_ldl_structure(*(_to_numpy(a) for a in arrays))
+    if structure is None:
+        return None
+    plan = best_tree_ldl_plan(*structure)
+    if not tree_ldl_beats_dense(plan):
+        return None
+    return compile_plan(structure, plan, device)
+
+
+def tree_factor_solve(scratch: TreeFactorSolveScratch, M: Any, x: Any, y: Any, stream=None) -> None:
+    """x = M^-1 y for an M in the model's CSR layout (tree_ldl.py:419-433)."""
+    for array in (M, x, y):
+        if elem_strides(array)[1] != 1:
+            raise ValueError("tree_factor_solve needs rows of contiguous floats")
+    nworld = int(M.shape[0])
+    rc = _lib.lib().imn_tree_ldl_solve(
+        C.byref(scratch.struct), addr(M), elem_strides(M)[0], addr(y), elem_strides(y)[0], addr(x),
+        elem_strides(x)[0], nworld, _lib.current_stream_handle(stream),
+    )
+    _lib.check(rc, "imn_tree_ldl_solve")

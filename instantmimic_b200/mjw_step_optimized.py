@@ -148,3 +148,44 @@ def solve_with_scratch(
         )
     del use_optimized_kernel
     newton_fusion.solve_call(m, d, ctx, nsolving, cache_on=scratch)(stream)
+
+
+def _factor_solve_i_dense(
+    m: Any,
+    d: Any,
+    M: Any,
+    x: Any,
+    y: Any,
+    dense_factor_solve: Any = None,
+    *,
+    retain_factor: bool = False,
+    factor_workspace: Any = None,
+    tree_factor_solve: Any = None,
+    stream=None,
+) -> None:
+    """x = M^-1 y for M (or M - h qDeriv) in the model's CSR layout, choosing the
+    kernel as the reference does (mjw_step_optimized.py:1030-1070): the tree L'DL when
+    a plan exists and no factor has to be kept, else the blocked dense Cholesky.
+    Models with neither (nv < 32 without a tree plan) have no path here and raise."""
+    from .mjw_kernels import indexed_factor, tree_ldl
+
+    if factor_workspace is not None and dense_factor_solve is None:
+        raise RuntimeError("a retained factor workspace requires the blocked dense path")
+    if tree_factor_solve is not None and not retain_factor and factor_workspace is None:
+        tree_ldl.tree_factor_solve(tree_factor_solve, M, x, y, stream=stream)
+        return
+    if dense_factor_solve is not None:
+        indexed_factor.blocked_dense_factor_solve(
+            d, M, x, y, dense_factor_solve, factor_workspace=factor_workspace, stream=stream
+        )
+        return
+    raise RuntimeError("no factor/solve plan for this model (neither tree L'DL nor blocked dense)")
+
+
+def fwd_acceleration_solve(m: Any, d: Any, scratch: OptimizedFwdPositionScratch, stream=None) -> None:
+    """qacc_smooth = M^-1 qfrc_smooth, the factor/solve step of the reference's
+    ``fwd_acceleration_optimized`` (mjw_step_optimized.py:1274-1329)."""
+    _factor_solve_i_dense(
+        m, d, d.M, d.qacc_smooth, d.qfrc_smooth, scratch.dense_factor_solve,
+        tree_factor_solve=scratch.tree_factor_solve, stream=stream,
+    )

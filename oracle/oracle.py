@@ -69,3 +69,53 @@ def mul_m(m: Any, M, v, out) -> None:
     ms = binding.model_struct(m)
     lib().oracle_mul_m(C.byref(ms), M.ctypes.data, M.strides[0] // 4, v.ctypes.data,
                        v.strides[0] // 4, out.ctypes.data, out.strides[0] // 4, M.shape[0])
+
+
+def _i32(a):
+    import numpy as np
+
+    return np.ascontiguousarray(np.asarray(a, dtype=np.int32))
+
+
+def tree_ldl_solve(structure, plan, M, y):
+    """x = M^-1 y by the serial form of the tree L'DL plan; M (W, nM), y (W, nv) host."""
+    import numpy as np
+
+    rowadr, rownnz, colind = (_i32(a) for a in structure)
+    nodes = _i32([k for g in plan.groups for k in g])
+    ptr = _i32(np.cumsum([0] + [len(g) for g in plan.groups]))
+    trunk = _i32(plan.trunk)
+    M = np.ascontiguousarray(M, np.float32)
+    y = np.ascontiguousarray(y, np.float32)
+    x = np.zeros_like(y)
+    fn = lib().oracle_tree_ldl_solve
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_int, C.c_int, abi.P, abi.P, abi.P, C.c_int, abi.P, abi.P, C.c_int, abi.P,
+                   abi.P, abi.I64, abi.P, abi.I64, abi.P, abi.I64, C.c_int]
+    fn(rowadr.size, colind.size, rowadr.ctypes.data, rownnz.ctypes.data, colind.ctypes.data,
+       len(plan.groups), ptr.ctypes.data, nodes.ctypes.data, trunk.size, trunk.ctypes.data,
+       M.ctypes.data, M.shape[1], y.ctypes.data, y.shape[1], x.ctypes.data, x.shape[1], M.shape[0])
+    return x
+
+
+def blocked_dense_factor_solve(nv, pad, indices, identity, M, y, U=None, active=None, mode=0):
+    """Blocked dense Cholesky factor + solve; y (W, nv, rhs).  Returns (x, U)."""
+    import numpy as np
+
+    y = np.ascontiguousarray(y, np.float32)
+    W, _, rhs = y.shape
+    indices, identity = _i32(indices), np.ascontiguousarray(identity, np.float32)
+    U = np.zeros((W, pad, pad), np.float32) if U is None else np.ascontiguousarray(U, np.float32)
+    x = np.zeros_like(y)
+    fn = lib().oracle_blocked_dense_factor_solve
+    fn.restype = C.c_int
+    fn.argtypes = [C.c_int, C.c_int, C.c_int, abi.P, abi.P, abi.P, abi.I64, abi.P, abi.P, abi.P, abi.P,
+                   C.c_int, C.c_int, C.c_int]
+    Mp, nM, ld = (None, 0, 0)
+    if M is not None:
+        M = np.ascontiguousarray(M, np.float32)
+        Mp, nM, ld = M.ctypes.data, M.shape[1], M.shape[1]
+    act = _i32(active) if active is not None else None
+    fn(nv, pad, nM, indices.ctypes.data, identity.ctypes.data, Mp, ld, y.ctypes.data, U.ctypes.data,
+       x.ctypes.data, act.ctypes.data if act is not None else None, W, rhs, mode)
+    return x, U

@@ -1,0 +1,262 @@
+"""M-side factor + solve: tree L'DL plans, the blocked dense Cholesky and their
+kernels.  CPU tests pin the oracle against numpy.linalg.solve of the dense matrix
+(the pin the reference's own tests use, tests/test_tree_ldl.py:99-120,
+tests/test_blocked_dense_factor_solve.py:616-626); GPU tests compare the CUDA
+kernels with the oracle bit for bit."""
+
+import numpy as np
+import pytest
+
+from instantmimic_b200 import synthetic
+from instantmimic_b200.mjw_kernels import indexed_factor, tree_ldl
+from instantmimic_b200.mjw_model import put_model
+
+
+def _branched_tree():
+    """Free root with two branches (one with a ball joint) and a second free body:
+    nested ancestor rows, a 3-dof joint and two separate trees
+    (tests/test_tree_ldl.py:22-37)."""
+    joints = [(6, -1), (1, 0), (1, 1), (3, 0), (1, 3), (6, -1)]
+    return synthetic._tree_from_joints(joints)
+
+
+def _limbs_tree(limbs=4, links=6):
+    return synthetic.limb_tree(6 + limbs * links, limbs)
+
+
+TREES = {"branched": _branched_tree, "limbs": _limbs_tree, "humanoid": synthetic.humanoid_tree}
+
+
+def _model_and_matrices(tree, worlds, seed=0):
+    parent, body = tree()
+    m = put_model(parent, body_of_dof=body)
+    rng = np.random.default_rng(seed)
+    Mv, Md = synthetic.random_mass_matrices(m, worlds, rng)
+    return m, Mv, Md.astype(np.float64)
+
+
+def _structure(m):
+    return tree_ldl.tree_ldl_structure(m.M_rowadr, m.M_rownnz, m.M_colind)
+
+
+@pytest.mark.parametrize("tree", ["branched", "limbs", "humanoid"])
+@pytest.mark.parametrize("groups", [1, 2, 4])
+def test_tree_oracle_matches_a_dense_solve(oracle, tree, groups):
+    worlds = 37
+    m, Mv, Md = _model_and_matrices(TREES[tree], worlds)
+    structure = _structure(m)
+    assert structure is not None
+    plan = tree_ldl.plan_tree_ldl(*structure, groups)
+    y = np.random.default_rng(1).normal(size=(worlds, m.nv)).astype(np.float32)
+    x = oracle.tree_ldl_solve(structure, plan, Mv, y)
+    want = np.stack([np.linalg.solve(a, b) for a, b in zip(Md, y)])
+    np.testing.assert_allclose(x, want, rtol=2e-4, atol=2e-5)
+
+
+def test_plans_cover_every_dof_once_and_split_limbs_off_a_trunk():
+    """tests/test_tree_ldl.py:123-138."""
+    m, _, _ = _model_and_matrices(_limbs_tree, 1)
+    structure = _structure(m)
+    for groups in (1, 2, 4):
+        plan = tree_ldl.plan_tree_ldl(*structure, groups)
+        dofs = sorted([*plan.trunk, *(k for nodes in plan.groups for k in nodes)])
+        assert dofs == list(range(m.nv))
+    single = tree_ldl.plan_tree_ldl(*structure, 1)
+    split = tree_ldl.plan_tree_ldl(*structure, 4)
+    assert not single.trunk
+    assert split.trunk == tuple(range(6))
+    assert sorted(len(nodes) for nodes in split.groups) == [6, 6, 6, 6]
+    assert split.span < single.span
+
+
+def test_tree_solve_is_used_only_where_it_beats_the_dense_cost():
+    limbs, _, _ = _model_and_matrices(_limbs_tree, 1)
+    assert tree_ldl.tree_ldl_beats_dense(tree_ldl.best_tree_ldl_plan(*_structure(limbs)))
+    parent, body = synthetic._tree_from_joints([(6, -1)] + [(1, i) for i in range(40)])
+    chain = put_model(parent, body_of_dof=body)
+    plan = tree_ldl.best_tree_ldl_plan(*_structure(chain))
+    assert plan.span > tree_ldl.MAX_SHORT_SPAN
+    assert not tree_ldl.tree_ldl_beats_dense(plan)
+
+
+def test_structure_check_rejects_rows_that_are_not_nested_ancestor_chains():
+    m, _, _ = _model_and_matrices(_branched_tree, 1)
+    rowadr, rownnz, colind = (np.array(a) for a in (m.M_rowadr, m.M_rownnz, m.M_colind))
+    assert tree_ldl.tree_ldl_structure(rowadr, rownnz, colind) is not None
+    bad = colind.copy()
+    bad[rowadr[7]] = 1  # row 7 no longer starts with its root ancestor
+    assert tree_ldl.tree_ldl_structure(rowadr, rownnz, bad) is None
+    assert tree_ldl.tree_ldl_structure(rowadr, rownnz[:-1], colind) is None
+    assert tree_ldl.tree_ldl_structure(np.zeros(0), np.zeros(0), np.zeros(0)) is None
+
+
+def test_compiled_program_matches_the_plan_interpreter(oracle):
+    """The instruction list the CUDA kernel runs, interpreted in numpy float64,
+    solves M x = y (checks compilation independently of any kernel)."""
+    worlds = 5
+    m, Mv, Md = _model_and_matrices(synthetic.humanoid_tree, worlds)
+    structure = _structure(m)
+    y = np.random.default_rng(2).normal(size=(worlds, m.nv))
+    for groups in (1, 3, 4):
+        plan = tree_ldl.plan_tree_ldl(*structure, groups)
+        program = tree_ldl._Program(*structure, plan)
+        prog, ptr = program.encode()
+        G = len(plan.groups)
+        col = np.zeros((program.nslot, worlds))
+        x = np.zeros((worlds, m.nv))
+
+        def run(lo, hi):
+            for op, dst, ab, c in prog[lo:hi]:
+                a, b = ab & 0xFFFF, (ab >> 16) & 0xFFFF
+                if op == tree_ldl.OP_LOAD_M:
+                    col[dst] = Mv[:, a]
+                elif op == tree_ldl.OP_LOAD_Y:
+                    col[dst] = y[:, a]
+                elif op == tree_ldl.OP_ZERO:
+                    col[dst] = 0
+                elif op == tree_ldl.OP_INV:
+                    col[dst] = 1.0 / col[a]
+                elif op == tree_ldl.OP_UPD:
+                    col[dst] = col[dst] - col[a] * col[b] * col[c]
+                elif op == tree_ldl.OP_SCALE:
+                    col[dst] = col[dst] * col[a]
+                elif op == tree_ldl.OP_SUBMUL:
+                    col[dst] = col[dst] - col[a] * col[b]
+                elif op == tree_ldl.OP_MUL:
+                    col[dst] = col[a] * col[b]
+                elif op == tree_ldl.OP_ADD:
+                    col[dst] = col[dst] + col[a]
+                elif op == tree_ldl.OP_STORE_X:
+                    x[:, dst] = col[a]
+
+        for j in range(G):
+            run(ptr[j], ptr[j + 1])
+        run(ptr[G], ptr[G + 1])
+        for j in range(G):
+            run(ptr[G + 1 + j], ptr[G + 2 + j])
+        want = np.stack([np.linalg.solve(a, b) for a, b in zip(Md, y)])
+        np.testing.assert_allclose(x, want, rtol=1e-5, atol=1e-6)
+
+
+def _blocked_case(nv, worlds, rhs, seed=0):
+    parent, body = synthetic.limb_tree(nv)
+    m = put_model(parent, body_of_dof=body)
+    rng = np.random.default_rng(seed)
+    Mv, Md = synthetic.random_mass_matrices(m, worlds, rng)
+    pad = indexed_factor._round_up(nv, 16)
+    layout = indexed_factor.block_major_layout(indexed_factor.dense_index_table(m), pad, m.nM)
+    ident = indexed_factor.pad_identity(nv, pad)
+    y = rng.normal(size=(worlds, nv, rhs)).astype(np.float32)
+    return m, Mv, Md.astype(np.float64), pad, layout, ident, y
+
+
+@pytest.mark.parametrize("nv", [32, 35, 48, 56, 70])
+def test_blocked_oracle_matches_numpy_and_reuses_its_factor(oracle, nv):
+    worlds, rhs = 6, 3
+    m, Mv, Md, pad, layout, ident, y = _blocked_case(nv, worlds, rhs)
+    x, U = oracle.blocked_dense_factor_solve(nv, pad, layout, ident, Mv, y)
+    want = np.stack([np.linalg.solve(a, b) for a, b in zip(Md, y)])
+    np.testing.assert_allclose(x, want, rtol=2e-3, atol=2e-4)
+    # U^T U reproduces M; the padded block is the identity
+    for w in range(worlds):
+        np.testing.assert_allclose(U[w, :nv, :nv].T @ U[w, :nv, :nv], Md[w], rtol=1e-4, atol=1e-4)
+        np.testing.assert_array_equal(U[w, nv:, nv:], np.eye(pad - nv, dtype=np.float32))
+    # a second solve from the stored factor is bit-identical to the fresh one
+    x2, _ = oracle.blocked_dense_factor_solve(nv, pad, layout, ident, None, y, U=U, mode=1)
+    np.testing.assert_array_equal(x, x2)
+
+
+# ---------------------------------------------------------------------------- GPU
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tree", ["branched", "limbs", "humanoid"])
+@pytest.mark.parametrize("groups", [1, 2, 4])
+def test_tree_kernel_matches_oracle_bitwise(oracle, cuda_device, tree, groups):
+    import torch
+
+    worlds = 37  # not a multiple of the 32 worlds a block serves
+    m, Mv, Md = _model_and_matrices(TREES[tree], worlds)
+    structure = _structure(m)
+    plan = tree_ldl.plan_tree_ldl(*structure, groups)
+    scratch = tree_ldl.scratch_for_plan(structure, plan, cuda_device)
+    y = np.random.default_rng(1).normal(size=(worlds, m.nv)).astype(np.float32)
+    x = torch.zeros((worlds, m.nv), dtype=torch.float32, device=cuda_device)
+    tree_ldl.tree_factor_solve(scratch, torch.from_numpy(Mv).to(cuda_device), x, torch.from_numpy(y).to(cuda_device))
+    torch.cuda.synchronize()
+    want = oracle.tree_ldl_solve(structure, plan, Mv, y)
+    np.testing.assert_array_equal(x.cpu().numpy(), want)
+    dense = np.stack([np.linalg.solve(a, b) for a, b in zip(Md, y)])
+    np.testing.assert_allclose(x.cpu().numpy(), dense, rtol=2e-4, atol=2e-5)
+
+
+@pytest.mark.gpu
+def test_model_scratch_selects_tree_solve_and_solves_qacc_smooth(oracle, cuda_device):
+    import torch
+
+    from instantmimic_b200 import mjw_model
+    from instantmimic_b200 import mjw_step_optimized as runtime
+
+    m, d, Md = synthetic.make_workload("humanoid", 100, seed=4)
+    md, dd = mjw_model.to_device(m, cuda_device), mjw_model.to_device(d, cuda_device)
+    scratch = runtime.make_optimized_fwd_position_scratch(md, dd, cuda_device)
+    assert scratch.tree_factor_solve is not None and scratch.dense_factor_solve is not None
+    dd.qacc_smooth.zero_()
+    runtime.fwd_acceleration_solve(md, dd, scratch)
+    torch.cuda.synchronize()
+    want = np.stack([np.linalg.solve(a.astype(np.float64), b) for a, b in zip(Md, d.qfrc_smooth)])
+    np.testing.assert_allclose(dd.qacc_smooth.cpu().numpy(), want, rtol=2e-4, atol=2e-4)
+    # the blocked dense path gives the same answer within its own tolerance
+    out = torch.zeros_like(dd.qacc_smooth)
+    runtime._factor_solve_i_dense(md, dd, dd.M, out, dd.qfrc_smooth, scratch.dense_factor_solve, retain_factor=True)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(out.cpu().numpy(), want, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nv", [32, 35, 48, 56, 70])
+def test_blocked_kernel_matches_oracle_bitwise(oracle, cuda_device, nv):
+    import torch
+
+    from instantmimic_b200 import mjw_model
+
+    worlds, rhs = 9, 3
+    m, Mv, Md, pad, layout, ident, y = _blocked_case(nv, worlds, rhs)
+    md = mjw_model.to_device(m, cuda_device)
+    dd = mjw_model.to_device(mjw_model.make_data(m, worlds, 4), cuda_device)
+    scratch = indexed_factor.create_blocked_dense_factor_solve_scratch(md, dd, cuda_device)
+    assert scratch is not None and scratch.pad == pad
+    Mt = torch.from_numpy(Mv).to(cuda_device)
+    yt = torch.from_numpy(y).to(cuda_device)
+    active = torch.ones(worlds, dtype=torch.int32, device=cuda_device)
+    active[3] = 0
+    xt = torch.full_like(yt, 7.0)
+    U = torch.zeros((worlds, pad, pad), dtype=torch.float32, device=cuda_device)
+    indexed_factor.factor_multi_solve(scratch, Mt, yt, active, U, xt, rhs)
+    torch.cuda.synchronize()
+    want_x, want_U = oracle.blocked_dense_factor_solve(nv, pad, layout, ident, Mv, y)
+    got = xt.cpu().numpy()
+    live = np.arange(worlds) != 3
+    np.testing.assert_array_equal(got[live], want_x[live])
+    np.testing.assert_array_equal(got[3], 7.0)  # inactive world untouched
+    np.testing.assert_array_equal(U.cpu().numpy()[live], want_U[live])
+    # reuse of the stored factor == fresh solve, bit for bit
+    x2 = torch.zeros_like(yt)
+    active.fill_(1)
+    active[3] = 0
+    indexed_factor.multi_solve(scratch, U, yt, active, x2, rhs)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(x2.cpu().numpy()[live], got[live])
+    dense = np.stack([np.linalg.solve(a, b) for a, b in zip(Md, y)])
+    np.testing.assert_allclose(got[live], dense[live], rtol=2e-3, atol=2e-4)
+
+
+@pytest.mark.gpu
+def test_small_models_have_no_blocked_scratch(cuda_device):
+    from instantmimic_b200 import mjw_model
+
+    parent, body = synthetic.chain_tree(16)
+    m = put_model(parent, body_of_dof=body)
+    md = mjw_model.to_device(m, cuda_device)
+    dd = mjw_model.to_device(mjw_model.make_data(m, 4, 4), cuda_device)
+    assert indexed_factor.create_blocked_dense_factor_solve_scratch(md, dd, cuda_device) is None
