@@ -249,6 +249,31 @@ int imn_blocked_dense_factor_solve(const ImnBlockedPlan* plan, const float* M,
                                    const int32_t* active, int32_t nworld,
                                    int32_t rhs_count, int32_t mode, void* stream);
 
+/* Floats of the factor workspace built into the library (32 MiB per GPU). */
+#define IMN_STATIC_FACTOR_FLOATS (8 * 1024 * 1024)
+
+/* No counterpart in the reference.  Factor + solve (mode 0 of
+ * imn_blocked_dense_factor_solve) for callers that cannot provide the
+ * (W, pad, pad) factor workspace because they may not allocate device memory
+ * where they call: a step being recorded into a CUDA graph, a process whose
+ * device memory belongs to another framework's pool, a host that forbids
+ * cudaMalloc after start-up.  The workspace is a fixed array inside the library;
+ * every GPU that loads the library holds its 32 MiB until the process exits.
+ *   - nworld * pad * pad must not exceed IMN_STATIC_FACTOR_FLOATS, else
+ *     IMN_ERR_LIMIT is returned and nothing runs;
+ *   - the first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress with that device current); make that first call
+ *     outside any stream capture;
+ *   - all calls share the one array and it keeps the last call's factor: two
+ *     calls whose kernels overlap on the GPU (different streams) race, and the
+ *     stored factor cannot be reused by a later solve-only call;
+ *   - inputs, outputs, `active` and results are as for
+ *     imn_blocked_dense_factor_solve; no allocation happens in any call. */
+int imn_blocked_dense_factor_solve_static(const ImnBlockedPlan* plan, const float* M,
+                                          int64_t M_ld, const float* y, float* x,
+                                          const int32_t* active, int32_t nworld,
+                                          int32_t rhs_count, void* stream);
+
 /* Replaces sparse_hessian_upstream_factor, the sparse factor of the
  * non-fused iteration (sparse_hessian.py:849-894): mode 4 gathers the dense H
  * and factors, mode 5 solves with the stored factor.  hfactor layout:

@@ -197,6 +197,10 @@ SYMBOLS = {
         C.c_int,
         [C.POINTER(ImnBlockedPlan), P, I64, P, P, P, P, I32, I32, I32, P],
     ),
+    "imn_blocked_dense_factor_solve_static": (
+        C.c_int,
+        [C.POINTER(ImnBlockedPlan), P, I64, P, P, P, I32, I32, P],
+    ),
     "imn_sparse_factor_nonfused": (
         C.c_int,
         [C.POINTER(ImnSparsePlan), P, P, I64, P, P, P, P, P, I64, P, P, I32, I32, I32, P],

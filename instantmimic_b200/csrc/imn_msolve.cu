@@ -230,3 +230,60 @@ extern "C" int imn_blocked_dense_factor_solve(const ImnBlockedPlan* plan, const 
            IMN_ERR_LAUNCH;
   return IMN_OK;
 }
+
+// ---- factor + solve without any caller- or library-side allocation ---------------
+//
+// Some hosts of this library may not allocate device memory at the point where they
+// need a factor + solve: a simulation step that is being recorded into a CUDA graph,
+// a control loop that has handed all device memory to another framework's pool at
+// start-up, or a plug-in whose host forbids cudaMalloc after initialisation (the call
+// synchronises the device).  imn_blocked_dense_factor_solve needs a (W, pad, pad)
+// workspace for the factor; this variant keeps that workspace inside the library, in
+// a fixed-size array in device memory that every GPU loading the library holds until
+// the process exits.
+namespace imn {
+
+static __device__ __align__(256) float g_static_factor[IMN_STATIC_FACTOR_FLOATS];
+
+// Device address of g_static_factor per CUDA device.  In host code the array's name is
+// only a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+static float* g_static_factor_ptr[64] = {nullptr};
+
+static int static_factor_workspace(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return set_error("static workspace: cudaGetDevice: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  if (dev < 0 || dev >= 64) return set_error("static workspace: device index %d out of range", dev), IMN_ERR_LIMIT;
+  if (!g_static_factor_ptr[dev]) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_factor);
+    if (e != cudaSuccess || !ptr)
+      return set_error("static workspace: cudaGetSymbolAddress: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+    g_static_factor_ptr[dev] = ptr;
+  }
+  *out = g_static_factor_ptr[dev];
+  return IMN_OK;
+}
+
+}  // namespace imn
+
+extern "C" int imn_blocked_dense_factor_solve_static(const ImnBlockedPlan* plan, const float* M, int64_t M_ld,
+                                                     const float* y, float* x, const int32_t* active,
+                                                     int32_t nworld, int32_t rhs_count, void* stream) {
+  if (!plan) return imn::set_error("imn_blocked_dense_factor_solve_static: NULL plan"), IMN_ERR_NULL;
+  if (nworld < 0 || plan->pad <= 0)
+    return imn::set_error("imn_blocked_dense_factor_solve_static: bad extent"), IMN_ERR_SHAPE;
+  const int64_t need = (int64_t)nworld * plan->pad * plan->pad;
+  if (need > (int64_t)IMN_STATIC_FACTOR_FLOATS)
+    return imn::set_error("imn_blocked_dense_factor_solve_static: %d worlds x pad %d^2 = %lld floats exceed the "
+                          "built-in workspace of %lld floats; use imn_blocked_dense_factor_solve with your own",
+                          nworld, plan->pad, (long long)need, (long long)IMN_STATIC_FACTOR_FLOATS),
+           IMN_ERR_LIMIT;
+  float* U = nullptr;
+  const int rc = imn::static_factor_workspace(&U);
+  if (rc) return rc;
+  // The factor kernel writes every entry of an active world's U before the solve
+  // reads it, so nothing in the shared workspace has to start at zero.
+  return imn_blocked_dense_factor_solve(plan, M, M_ld, y, U, x, active, nworld, rhs_count, 0, stream);
+}
