@@ -1,0 +1,136 @@
+"""Host-side gates and error behaviour of the solver entry points (no GPU).  The
+tables are the reference's (tests/test_mjw_newton_fusion.py:30-96, 418-447)."""
+
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+
+from instantmimic_b200 import mjw_model, synthetic, types
+from instantmimic_b200 import mjw_step_optimized as runtime
+from instantmimic_b200.mjw_kernels import newton_fusion as fusion
+
+
+def _model(**updates):
+    model = SimpleNamespace(
+        nv=34,
+        nv_pad=48,
+        is_sparse=False,
+        opt=SimpleNamespace(
+            solver=types.SolverType.NEWTON,
+            cone=types.ConeType.PYRAMIDAL,
+            iterations=4,
+            integrator=types.IntegratorType.IMPLICITFAST,
+        ),
+        block_dim=SimpleNamespace(linesearch_iterative=32),
+        body_parentid=SimpleNamespace(device=SimpleNamespace(is_cuda=True)),
+    )
+    for key, value in updates.items():
+        setattr(model, key, value)
+    return model
+
+
+@pytest.mark.parametrize(
+    "nv,pad,expected",
+    [
+        (0, 0, False), (12, 12, False), (13, 16, True), (16, 16, True), (17, 32, True),
+        (31, 32, True), (32, 32, True), (32, 48, True), (33, 48, True), (35, 48, True),
+        (56, 64, True), (60, 64, True), (61, 64, True), (64, 80, True), (70, 80, True),
+        (79, 80, True), (80, 96, False), (34, 40, False),
+    ],
+)
+def test_eligibility_uses_dof_layout(nv, pad, expected):
+    assert fusion.eligible(_model(nv=nv, nv_pad=pad), object()) is expected
+
+
+@pytest.mark.parametrize("pad,expected", [(32, 32), (48, 32), (64, 64), (80, 64)])
+def test_block_width_uses_padded_dof_layout(pad, expected):
+    assert fusion.newton_block_dim(_model(nv_pad=pad)) == expected
+
+
+@pytest.mark.parametrize(
+    "reason",
+    ["compact", "sparse", "sparse_compact", "cg", "discrete", "elliptic", "zero_iterations",
+     "reduction_layout", "cpu_device"],
+)
+def test_unsupported_solver_modes_are_not_eligible(reason):
+    model = _model()
+    ctx = SimpleNamespace(sparse_compact=reason == "sparse_compact")
+    if reason == "sparse":
+        model.is_sparse = True
+    if reason == "discrete":
+        model.opt.integrator = types.IntegratorType.DISCRETE
+    if reason == "cg":
+        model.opt.solver = types.SolverType.CG
+    if reason == "elliptic":
+        model.opt.cone = types.ConeType.ELLIPTIC
+    if reason == "zero_iterations":
+        model.opt.iterations = 0
+    if reason == "reduction_layout":
+        model.block_dim.linesearch_iterative = 64
+    if reason == "cpu_device":
+        model.body_parentid.device.is_cuda = False
+    assert not fusion.eligible(model, ctx, compact=reason == "compact")
+
+
+@pytest.mark.parametrize(
+    "nworld,sm_count,expected",
+    [(1024, 170, 6), (2048, 170, 12), (4096, 170, 12), (8192, 170, 12), (512, 170, 3), (100, 170, 1),
+     (1024, 108, 9), (1024, 132, 7), (0, 170, 0), (1024, 0, 0), (-1, 170, 0), (8192, 148, 12)],
+)
+def test_min_blocks_tracks_grid_and_device(nworld, sm_count, expected):
+    assert fusion.newton_min_blocks_per_sm(nworld, sm_count) == expected
+
+
+def test_nv_pad_rule_and_dense_cap():
+    assert [mjw_model.newton_nv_pad(nv) for nv in (13, 15, 16, 31, 32, 34, 63, 64, 79)] == [
+        16, 16, 32, 32, 48, 48, 64, 80, 80]
+    assert mjw_model.DENSE_NV_MAX == 79
+
+
+def test_solve_with_scratch_error_behaviour():
+    """mjw_step_optimized.py:2701-2707: missing scratch and layout mismatch raise."""
+    m, d, _ = synthetic.make_workload("humanoid", 2, seed=0)
+    empty = runtime.OptimizedFwdPositionScratch()
+    with pytest.raises(RuntimeError, match="not initialized"):
+        runtime.solve_with_scratch(m, d, empty)
+    scratch = runtime.OptimizedFwdPositionScratch(solver_context=object(), solver_nsolving=object(),
+                                                  solver_uses_compact=True)
+    with pytest.raises(RuntimeError, match="no longer matches"):
+        runtime.solve_with_scratch(m, d, scratch)
+    # host arrays are not CUDA buffers: the model is outside the fused path and there
+    # is no other path
+    scratch.solver_uses_compact = False
+    with pytest.raises(RuntimeError, match="outside the fused Newton path"):
+        runtime.solve_with_scratch(m, d, scratch)
+    with pytest.raises(RuntimeError, match="factor workspace requires"):
+        runtime._factor_solve_i_dense(m, d, d.M, d.qacc, d.qfrc_smooth, None, factor_workspace=d.M)
+    with pytest.raises(RuntimeError, match="no factor/solve plan"):
+        runtime._factor_solve_i_dense(m, d, d.M, d.qacc, d.qfrc_smooth, None)
+
+
+def test_struct_builder_checks_strides():
+    from instantmimic_b200 import binding
+
+    m, d, _ = synthetic.make_workload("humanoid", 4, seed=0)
+    d.qacc = np.zeros((4, m.nv + 2), np.float32)[:, : m.nv]  # different world stride
+    with pytest.raises(ValueError, match="share one world stride"):
+        binding.data_struct(m, d)
+    m2, d2, _ = synthetic.make_workload("humanoid", 4, seed=0)
+    d2.efc.J = np.zeros((4, d2.njmax, 2 * m2.nv), np.float32)[:, :, ::2]
+    with pytest.raises(ValueError, match="unit innermost stride"):
+        binding.data_struct(m2, d2)
+    # a J with padded rows is accepted and described by its strides
+    m3, d3, _ = synthetic.make_workload("humanoid", 4, seed=0)
+    d3.efc.J = np.zeros((4, d3.njmax, 48), np.float32)[:, :, : m3.nv]
+    s = binding.data_struct(m3, d3)
+    assert (s.J_ld_row, s.J_ld_world) == (48, 48 * d3.njmax)
+
+
+def test_shard_bounds_cover_the_batch():
+    for n, g in ((8192, 8), (1000, 3), (5, 8)):
+        b = mjw_model.shard_bounds(n, g)
+        assert b[0][0] == 0 and b[-1][1] == n
+        assert all(lo2 == hi1 for (_, hi1), (lo2, _) in zip(b, b[1:]))
+        sizes = [hi - lo for lo, hi in b]
+        assert max(sizes) - min(sizes) <= 1
