@@ -56,7 +56,7 @@ struct Geom {
 
 static inline int up4(int n) { return (n + 3) & ~3; }
 
-static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident) {
+static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident, const ImnSparsePlan* sp = nullptr) {
   Geom g;
   g.nv = m.nv;
   g.njmax = d.njmax;
@@ -70,7 +70,8 @@ static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident) {
   int o = 0;
   g.oBar = o, o += 4;
   g.oJ = o, o += up4(g.jrows * g.ldj);
-  g.oA = o, o += (m.nv + 1) * g.ldu;
+  // dense: H and its factor share one (nv+1) x ldu array; sparse plan: packed H | N | 1/D
+  g.oA = o, o += sp ? up4(sp->nfac) + up4(sp->nslots) + up4(m.nv) : (m.nv + 1) * g.ldu;
   g.oVec = o, o += 8 * g.nv4;
   g.oM = o, o += up4(m.nM);
   g.oRowF = o, o += 5 * g.r4;
@@ -80,9 +81,9 @@ static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident) {
   return g;
 }
 
-template <bool JRES>
+template <bool JRES, bool SPARSE>
 __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnData d, const ImnCtx cx,
-                                                    const Geom g) {
+                                                    const Geom g, const ImnSparsePlan sp) {
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x;
   const int w = blockIdx.x;
@@ -113,6 +114,11 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   s.uni = reinterpret_cast<int*>(smem + g.oUni);
   s.mulm_rowadr = m.M_mulm_rowadr;
   s.mulm_pack = m.M_mulm_pack;
+  s.world = w;
+  s.Hp = s.A;
+  s.N = s.A + (SPARSE ? ((sp.nfac + 3) & ~3) : 0);
+  s.iD = s.N + (SPARSE ? ((sp.nslots + 3) & ~3) : 0);
+  s.viol = (SPARSE && cx.hfactor) ? cx.hfactor + ((size_t)w + 1) * m.nv_pad * m.nv_pad - 1 : nullptr;
 
   PROF_DECL;
   const int nefc_in = d.nefc[w];
@@ -271,12 +277,32 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
       PROF(8);
       decrement = 0.0f;
       grad_scale = 1.0f;
-      if (first)
-        assemble_hessian<JRES>(s, nfr);
-      else if (quad_count > 0)
-        update_hessian<JRES>(s, quad_count);
+      if (first) {
+        if (SPARSE)
+          assemble_hessian_sparse(s, nfr, sp);
+        else
+          assemble_hessian<JRES>(s, nfr);
+      } else if (quad_count > 0) {
+        update_hessian<JRES, SPARSE>(s, quad_count, sp);
+      }
       PROF(9);
-      factor_solve(s, first || quad_count > 0, search_dot, decrement);
+      if (SPARSE) {
+        // refactor the packed H, or solve with the resident factor
+        // (sparse_hessian.py:490-547)
+        if (first || quad_count > 0) {
+          if (!first) {
+#pragma unroll 1
+            for (int q = lane; q < sp.nfac; q += 32) s.N[q] = s.Hp[q];
+          }
+          sp_load_rhs(sp, s.N, s.grad, lane);
+          sp_factor_levels(sp, s.N, s.iD, lane);
+        } else {
+          sp_forward(sp, s.N, s.iD, s.grad, lane);
+        }
+        sp_backward(sp, s.N, s.iD, s.grad, s.search, s.bd, lane, search_dot, decrement);
+      } else {
+        factor_solve(s, first || quad_count > 0, search_dot, decrement);
+      }
       PROF(10);
     }
     if (first) {
@@ -321,14 +347,23 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   if (cx.dof_union && !rowless)
 #pragma unroll 1
     for (int i = lane; i <= nv; i += 32) cx.dof_union[(size_t)w * (nv + 1) + i] = s.uni[i];
-  if (!rowless) {
+  if (SPARSE && !rowless && cx.hfactor) {
+    // packed H | N | 1/D; the last element keeps counting violations
+    // (sparse_hessian.py:488-489)
+    float* Uf = cx.hfactor + (size_t)w * m.nv_pad * m.nv_pad;
+#pragma unroll 1
+    for (int q = lane; q < sp.nfac; q += 32) Uf[q] = s.Hp[q], Uf[sp.nfac + q] = s.N[q];
+#pragma unroll 1
+    for (int q = lane; q < nv; q += 32) Uf[2 * sp.nfac + q] = s.iD[q];
+  }
+  if (!SPARSE && !rowless) {
     const size_t ho = (size_t)w * m.nv_pad * m.nv_pad;
     if (cx.h)
 #pragma unroll 1
       for (int r = 0; r < nv; ++r)
 #pragma unroll 1
         for (int c = r + lane; c < nv; c += 32) cx.h[ho + (size_t)r * m.nv_pad + c] = s.A[(c + 1) * s.ldu + r];
-    if (cx.hfactor && !cx.sparse_plan)
+    if (cx.hfactor)
 #pragma unroll 1
       for (int r = 0; r < nv; ++r)
 #pragma unroll 1
@@ -387,12 +422,23 @@ static int validate(const ImnModel* m, const ImnData* d, const ImnCtx* cx) {
            IMN_ERR_SHAPE;
   if (m->nM >= (1 << 16)) return set_error("imn_solve: nM exceeds 16-bit indices"), IMN_ERR_LIMIT;
   if (cx->grad && cx->grad_ld < m->nv) return set_error("imn_solve: ctx.grad stride < nv"), IMN_ERR_SHAPE;
-  if (cx->sparse_plan) return set_error("imn_solve: sparse plan not supported by this kernel"), IMN_ERR_UNSUPPORTED;
+  if (cx->sparse_plan) {
+    const ImnSparsePlan* sp = cx->sparse_plan;
+    if (sp->nv != m->nv || sp->nv_pad != m->nv_pad || sp->nfac <= 0 || sp->nslots != sp->nfac + sp->nv ||
+        2 * sp->nfac + sp->nv >= sp->nv_pad * sp->nv_pad - 1 || sp->nlevels <= 0)
+      return set_error("imn_solve: sparse plan does not match the model"), IMN_ERR_SHAPE;
+    if (!cx->hfactor) return set_error("imn_solve: the sparse path needs ctx.hfactor (violation counter)"), IMN_ERR_NULL;
+    if (!sp->lvl_ptr || !sp->lvl_team || !sp->ent_slot || !sp->ent_col || !sp->run_ptr || !sp->run_ab ||
+        !sp->run_kl || !sp->orig || !sp->b_lvl || !sp->b_slot || !sp->b_src || !sp->b_dst || !sp->pair ||
+        !sp->f_lvl || !sp->f_row || !sp->row_start || !sp->rk_ptr || !sp->rk || !sp->pmask || !sp->s_a ||
+        !sp->s_b || !sp->s_m)
+      return set_error("imn_solve: a sparse plan table is NULL"), IMN_ERR_NULL;
+  }
   return IMN_OK;
 }
 
-static int plan_launch(const ImnModel* m, const ImnData* d, Geom* g, bool* resident) {
-  Geom gr = make_geom(*m, *d, true);
+static int plan_launch(const ImnModel* m, const ImnData* d, const ImnSparsePlan* sp, Geom* g, bool* resident) {
+  Geom gr = make_geom(*m, *d, true, sp);
 #ifdef IMN_FORCE_STREAM
   const int budget = 0;
 #else
@@ -402,6 +448,9 @@ static int plan_launch(const ImnModel* m, const ImnData* d, Geom* g, bool* resid
     *g = gr, *resident = true;
     return IMN_OK;
   }
+  if (sp)
+    return set_error("imn_solve: the sparse path keeps J in shared memory; njmax %d is too large", d->njmax),
+           IMN_ERR_LIMIT;
   Geom gs = make_geom(*m, *d, false);
   if (gs.total * 4 > kMaxSmem)
     return set_error("imn_solve: njmax %d needs %d bytes of shared memory per world (max %d)", d->njmax,
@@ -425,9 +474,9 @@ extern "C" int imn_debug_profile(unsigned long long* out, int reset) {
 extern "C" int imn_debug_occupancy(int bytes, int resident) {
   int n = 0;
   if (resident)
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel<true>, 32, bytes);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel<true, false>, 32, bytes);
   else
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel<false>, 32, bytes);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel<false, false>, 32, bytes);
   return n;
 }
 #endif
@@ -438,7 +487,7 @@ extern "C" int imn_launch_info(const ImnModel* m, const ImnData* d, const ImnCtx
   if (rc) return rc;
   imn::Geom g;
   bool res;
-  rc = imn::plan_launch(m, d, &g, &res);
+  rc = imn::plan_launch(m, d, cx->sparse_plan, &g, &res);
   if (rc) return rc;
   out->world_threads = g.bd;
   out->worlds_per_cta = 1;
@@ -455,10 +504,12 @@ extern "C" int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* cx, 
   if (d->nworld == 0) return IMN_OK;
   imn::Geom g;
   bool res;
-  rc = imn::plan_launch(m, d, &g, &res);
+  rc = imn::plan_launch(m, d, cx->sparse_plan, &g, &res);
   if (rc) return rc;
   const int bytes = g.total * 4;
-  auto kern = res ? imn::newton_kernel<true> : imn::newton_kernel<false>;
+  auto kern = cx->sparse_plan ? imn::newton_kernel<true, true>
+                              : (res ? imn::newton_kernel<true, false> : imn::newton_kernel<false, false>);
+  const ImnSparsePlan sp = cx->sparse_plan ? *cx->sparse_plan : ImnSparsePlan{};
   {
     // many one-warp CTAs share an SM: ask for the largest shared-memory carve-out,
     // otherwise the driver sizes it for a single CTA
@@ -470,7 +521,7 @@ extern "C" int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* cx, 
       return imn::set_error("imn_solve: cudaFuncSetAttribute: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
   }
   if (cx->nsolving) imn::fill_nsolving<<<1, 1, 0, stream>>>(cx->nsolving, d->nworld);
-  kern<<<d->nworld, 32, bytes, stream>>>(*m, *d, *cx, g);
+  kern<<<d->nworld, 32, bytes, stream>>>(*m, *d, *cx, g, sp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return imn::set_error("imn_solve: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
   return IMN_OK;

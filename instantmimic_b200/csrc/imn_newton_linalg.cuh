@@ -4,7 +4,10 @@
 // kernel is bound by instruction fetch and latency, not by arithmetic).
 #pragma once
 
+#include <stdio.h>
+
 #include "imn_newton_dev.cuh"
+#include "imn_sparse.cuh"
 
 namespace imn {
 
@@ -17,6 +20,10 @@ struct World {
   const float* Jg;  // this world's J in global memory
   const int* mulm_rowadr;
   const uint32_t* mulm_pack;
+  // sparse plan only: packed H, N = L D with the carried row, 1/D, the world's
+  // violation counter in global memory, the world index (for messages)
+  float *Hp, *N, *iD, *viol;
+  int world;
 #ifdef IMN_PROFILE
   long long* prof_acc;
   long long* prof_t;
@@ -187,8 +194,11 @@ __device__ __forceinline__ void assemble_hessian(const World& s, int nfr) {
 
 // Rows whose QUADRATIC membership flipped -> dofs they touch (ascending), then
 // the pair update of H in the listed row order (newton_stages.py:651-701).
-template <bool JRES>
-__device__ __forceinline__ void update_hessian(const World& s, int count) {
+// With a sparse plan (SP != nullptr) the entry lands in the packed H through the
+// plan's pair table; an entry outside the pattern is dropped and counted
+// (sparse_hessian.py:501-527).
+template <bool JRES, bool SPARSE>
+__device__ __forceinline__ void update_hessian(const World& s, int count, const ImnSparsePlan& SP) {
   const int lane = s.lane, nv = s.nv, ldu = s.ldu;
   int n = 0;
 #pragma unroll 1
@@ -219,8 +229,65 @@ __device__ __forceinline__ void update_hessian(const World& s, int count) {
       if (s.state[r] != IMN_STATE_QUADRATIC) da = -da;
       if (a != 0.0f && b != 0.0f) delta = fmaf(da, b, delta);
     }
-    if (delta != 0.0f) s.A[(col + 1) * ldu + row] = s.A[(col + 1) * ldu + row] + delta;
+    if (delta != 0.0f) {
+      if (SPARSE) {
+        const int sl = __ldg(SP.pair + row * nv + col);
+        if (sl >= 0)
+          s.Hp[sl] = s.Hp[sl] + delta;
+        else
+          sp_violation(s.viol, s.world, "updates an H entry");
+      } else {
+        s.A[(col + 1) * ldu + row] = s.A[(col + 1) * ldu + row] + delta;
+      }
+    }
     pair_advance(pi, pj, 32);
+  }
+  __syncwarp();
+}
+
+// Sparse plan: H = M + J^T diag(D, QUADRATIC rows) J on the pattern slots, each slot
+// summing its rows in ascending order; every active row's dof support must lie in
+// the pattern (sparse_hessian.py:571-637).  Leaves the packed H in both N and Hp.
+__device__ __forceinline__ void assemble_hessian_sparse(const World& s, int nfr, const ImnSparsePlan& SP) {
+  const int lane = s.lane, nv = s.nv, nfac = SP.nfac, words = (nv + 31) >> 5;
+#pragma unroll 1
+  for (int a = 0; a < nfr; ++a) {
+    const int r = s.frows[a];
+    if (s.state[r] != IMN_STATE_QUADRATIC || s.Dsm[r] == 0.0f) continue;
+    const float* Jr = s.Jsm + r * s.ldj;
+    unsigned rm[3] = {0u, 0u, 0u};
+#pragma unroll
+    for (int q = 0; q < 3; ++q)
+      if (q < words) {
+        const int d = q * 32 + lane;
+        rm[q] = __ballot_sync(IMN_FULL_MASK, d < nv && Jr[d] != 0.0f);
+      }
+    bool bad = false;
+#pragma unroll
+    for (int q = 0; q < 3; ++q) {
+      const int d = q * 32 + lane;
+      if (q < words && d < nv && ((rm[q] >> lane) & 1u)) {
+#pragma unroll
+        for (int p = 0; p < 3; ++p)
+          if (p < words) bad = bad || (rm[p] & ~__ldg(SP.pmask + d * words + p)) != 0u;
+      }
+    }
+    if (__any_sync(IMN_FULL_MASK, bad) && lane == 0) sp_violation(s.viol, s.world, "has a constraint row");
+  }
+#pragma unroll 1
+  for (int sl = lane; sl < nfac; sl += 32) {
+    const int e = __ldg(SP.s_m + sl);
+    const int a = __ldg(SP.s_a + sl), b = __ldg(SP.s_b + sl);
+    float v = e >= 0 ? s.Msm[e] : 0.0f;
+#pragma unroll 2
+    for (int k = 0; k < nfr; ++k) {
+      const int r = s.frows[k];
+      if (s.state[r] != IMN_STATE_QUADRATIC) continue;
+      const float* Jr = s.Jsm + r * s.ldj;
+      v = fmaf(Jr[a] * s.Dsm[r], Jr[b], v);
+    }
+    s.N[sl] = v;
+    s.Hp[sl] = v;
   }
   __syncwarp();
 }

@@ -182,6 +182,57 @@ def _factor_solve_i_dense(
     raise RuntimeError("no factor/solve plan for this model (neither tree L'DL nor blocked dense)")
 
 
+def refresh_sparse_hessian(m: Any, d: Any, scratch: OptimizedFwdPositionScratch, body_groups,
+                           device: Any = "cuda") -> str:
+    """Install (or remove) the sparse-Hessian plan on the solver context, as the
+    reference's ``_refresh_mjw_sparse_hessian`` does
+    (src/instantmimic/envs/direct_rl_env.py:2875-2925).  ``body_groups`` are the body
+    sets that custom contact producers declare; ``None`` disables the plan.  Returns
+    the reason string ("enabled" when a plan is installed)."""
+    import torch
+
+    from .mjw_kernels import sparse_hessian
+
+    ctx = scratch.solver_context
+    if ctx is None:
+        return "no solver context"
+    plan, reason = sparse_hessian.plan_for_model(m, ctx, body_groups, newton_fusion.newton_block_dim(m))
+    ctx.sparse_hessian_plan = None
+    if hasattr(scratch, "_imn_solve_call"):
+        del scratch._imn_solve_call
+    if plan is None:
+        return reason
+    sparse_hessian.upload(plan, device)
+    if getattr(ctx, "hfactor", None) is None:
+        ctx.hfactor = torch.zeros((d.nworld, m.nv_pad, m.nv_pad), dtype=torch.float32, device=device)
+    if plan.path == "fused":
+        sparse_hessian.violation_counter(ctx.hfactor, plan).zero_()
+    ctx.sparse_hessian_plan = plan
+    return reason
+
+
+def check_sparse_hessian_violations(scratch: OptimizedFwdPositionScratch) -> None:
+    """Raise when any world counted a constraint row or H update outside the declared
+    pattern since the last check, and reset the counters
+    (src/instantmimic/envs/direct_rl_env.py:2927-2951).  Reads device memory: call it
+    at metric cadence, not every step."""
+    from .mjw_kernels import sparse_hessian
+
+    ctx = scratch.solver_context
+    plan = getattr(ctx, "sparse_hessian_plan", None) if ctx is not None else None
+    if plan is None or plan.path != "fused":
+        return
+    counter = sparse_hessian.violation_counter(ctx.hfactor, plan)
+    total = float(counter.sum().item())
+    if total > 0:
+        worlds = int((counter > 0).sum().item())
+        counter.zero_()
+        raise RuntimeError(
+            f"sparse Hessian: {int(total)} constraint rows or updates in {worlds} worlds fell outside the "
+            "declared coupling pattern; a contact producer coupled bodies it did not declare"
+        )
+
+
 def fwd_acceleration_solve(m: Any, d: Any, scratch: OptimizedFwdPositionScratch, stream=None) -> None:
     """qacc_smooth = M^-1 qfrc_smooth, the factor/solve step of the reference's
     ``fwd_acceleration_optimized`` (mjw_step_optimized.py:1274-1329)."""

@@ -36,6 +36,7 @@
 
 #include "../include/imnewton.h"
 #include "oracle_common.h"
+#include "sparse_oracle.h"
 
 #define MJ_MAXVAL 1.0e10f
 
@@ -166,7 +167,25 @@ typedef struct World {
   int *state, *ids, *uni;
   float search_dot, grad_dot, grad_scale, decrement, improvement, alpha;
   int quad_count, state_count, search_unchanged, ls_exhausted, done, niter, overflow;
+  /* static-pattern sparse factor (NULL: dense): packed H, N = L D with the carried
+   * right-hand-side row, 1/D, and the count of pattern violations of this solve */
+  const ImnSparsePlan* sp;
+  float *Hp, *N, *iD;
+  int violations;
 } World;
+
+/* Sparse counterpart of factor_solve: mode 0 refactors the packed H, mode 1 solves
+ * with the resident factor (sparse_hessian.py:490-547). */
+static void factor_solve_sparse(World* w, int factor, float sums[2]) {
+  if (factor) {
+    memcpy(w->N, w->Hp, sizeof(float) * w->sp->nfac);
+    sparse_load_rhs(w->sp, w->N, w->grad);
+    sparse_factor_levels(w->sp, w->N, w->iD);
+  } else {
+    sparse_forward(w->sp, w->N, w->iD, w->grad);
+  }
+  sparse_backward(w->sp, w->N, w->iD, w->grad, w->search, w->sp->block, sums);
+}
 
 /* ctx.grad_dot: Warp tile_sum of one partial per thread of the logical block
  * (newton_stages.py:785-795). */
@@ -438,6 +457,11 @@ static void update_hessian(World* w) {
     if (hit) w->uni[n++] = dof;
   }
   w->uni[nv] = n;
+  if (w->sp) {
+    /* sparse plan: the same pair loop lands in the packed H (sparse_hessian.py:501-527) */
+    w->violations += sparse_update(w->sp, w->Hp, w->J, w->ldj, w->D, w->state, w->ids, count, w->uni, n);
+    return;
+  }
   for (int cj = 0; cj < n; ++cj)
     for (int ri = 0; ri <= cj; ++ri) {
       const int row = w->uni[ri], col = w->uni[cj];
@@ -494,6 +518,12 @@ static void solve_world(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, 
   w.state = ws->i;
   w.ids = ws->i + R;
   w.uni = ws->i + 2 * R;
+  w.sp = ctx ? ctx->sparse_plan : NULL;
+  if (w.sp) {
+    w.Hp = f, f += w.sp->nfac;
+    w.N = f, f += w.sp->nslots;
+    w.iD = f, f += nv;
+  }
   const float* qsm = d->qacc_smooth + (size_t)wid * d->dof_ld;
   const float* qws = d->qacc_warmstart + (size_t)wid * d->dof_ld;
   const int rowless = nefc_in == 0;
@@ -531,9 +561,17 @@ static void solve_world(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, 
                       (r >= w.ne && r < w.ne + w.nf) ? w.floss[r] : 0.0f, &w.force[r],
                       &w.state[r]);
     full_gradient(&w);
-    assemble_hessian(m, &w);
     float sums[2];
-    factor_solve(&w, 1, sums);
+    if (w.sp) {
+      /* H on the pattern slots, kept packed, then the level factor
+       * (sparse_hessian.py:571-637) */
+      w.violations += sparse_assemble(w.sp, w.N, w.M, w.J, w.ldj, w.D, w.state, w.nefc);
+      memcpy(w.Hp, w.N, sizeof(float) * w.sp->nfac);
+      factor_solve_sparse(&w, 1, sums);
+    } else {
+      assemble_hessian(m, &w);
+      factor_solve(&w, 1, sums);
+    }
     w.search_dot = sums[0];
     w.decrement = sums[1];
   }
@@ -583,7 +621,10 @@ static void solve_world(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, 
       /* factor */
       if (w.quad_count > 0) update_hessian(&w);
       float sums[2];
-      factor_solve(&w, w.quad_count > 0, sums);
+      if (w.sp)
+        factor_solve_sparse(&w, w.quad_count > 0, sums);
+      else
+        factor_solve(&w, w.quad_count > 0, sums);
       w.search_dot = sums[0];
       w.decrement = sums[1];
     }
@@ -637,10 +678,19 @@ static void solve_world(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, 
     if (ctx->ls_exhausted && !rowless) ctx->ls_exhausted[wid] = (uint8_t)w.ls_exhausted;
     if (ctx->quad_changed_count && !rowless) ctx->quad_changed_count[wid] = w.quad_count;
     if (ctx->state_changed_count && !rowless) ctx->state_changed_count[wid] = w.state_count;
-    if (ctx->h && !rowless)
+    if (ctx->h && !rowless && !w.sp)
       for (int r = 0; r < nv; ++r)
         for (int c = r; c < nv; ++c)
           ctx->h[((size_t)wid * m->nv_pad + r) * m->nv_pad + c] = w.H[r * nv + c];
+    if (ctx->hfactor && !rowless && w.sp) {
+      /* packed H | N | 1/D, and the violation counter in the last element
+       * (sparse_hessian.py:488-489, 795-796) */
+      float* Uf = ctx->hfactor + (size_t)wid * m->nv_pad * m->nv_pad;
+      const int nfac = w.sp->nfac;
+      for (int q = 0; q < nfac; ++q) Uf[q] = w.Hp[q], Uf[nfac + q] = w.N[q];
+      for (int q = 0; q < nv; ++q) Uf[2 * nfac + q] = w.iD[q];
+      Uf[m->nv_pad * m->nv_pad - 1] += (float)w.violations;
+    }
     if (ctx->hfactor && !rowless && !ctx->sparse_plan)
       for (int r = 0; r < nv; ++r)
         for (int c = r; c < nv; ++c)
@@ -651,7 +701,8 @@ static void solve_world(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, 
 /* Same contract as imn_solve, on host pointers.  threads <= 0: all cores. */
 int oracle_solve(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, int threads) {
   const int nv = m->nv, R = d->njmax;
-  const size_t nf = (size_t)7 * nv + (size_t)2 * nv * nv + (size_t)3 * R + 64;
+  size_t nf = (size_t)7 * nv + (size_t)2 * nv * nv + (size_t)3 * R + 64;
+  if (ctx && ctx->sparse_plan) nf += (size_t)ctx->sparse_plan->nfac + ctx->sparse_plan->nslots + nv;
   const size_t ni = (size_t)2 * R + nv + 8;
   int finished = 0;
 #ifdef _OPENMP
