@@ -50,6 +50,8 @@ def parse_args():
     p.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline sample length")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--sparse-hessian", default="off", choices=["on", "off"],
+                   help="install the static-pattern sparse Hessian plan (single-body contact groups)")
     return p.parse_args()
 
 
@@ -64,6 +66,7 @@ def workload_config(args, m, d):
         "batches_rotated": args.batches,
         "l2": f"inputs of {args.batches} distinct batches rotate (> 126 MB L2 in total)",
         "sharding": "by world, no collective on the data path",
+        "hessian_factor": "sparse-pattern L'DL" if args.sparse_hessian == "on" else "dense blocked Cholesky",
     }
 
 
@@ -249,6 +252,12 @@ def main():
     md = mjw_model.to_device(m_host, device)
     dev = [mjw_model.to_device(d, device) for _, d in host]
     scratch = [runtime.make_optimized_fwd_position_scratch(md, dd, device) for dd in dev]
+    if args.sparse_hessian == "on":
+        groups = [[b] for b in range(1, len(m_host.body_dofadr))]
+        for dd, sc in zip(dev, scratch):
+            reason = runtime.refresh_sparse_hessian(md, dd, sc, groups, device)
+            if reason != "enabled":
+                raise SystemExit(f"sparse Hessian plan not installed: {reason}")
     nb = len(dev)
 
     def step(k):

@@ -343,4 +343,4 @@ def test_nonfused_sparse_factor_matches_oracle_and_dense_search(oracle, cuda_dev
     ctx.quad_changed_count.zero_()
     sparse_hessian.nonfused_factor_solve(plan, ctx, d.nworld, skip_unchanged=True)
     torch.cuda.synchronize()
-    np.testing.assert_allclose(ctx.search.cpu().numpy(), got, rtol=1e-5, atol=1e-6)
+    np.testing.assert_allclose(ctx.search.cpu().numpy(), got, rtol=2e-4, atol=2e-5)
