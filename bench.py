@@ -30,9 +30,10 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "newton_solver_world_steps_per_s"
 UNIT = "world-steps/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one newton_kernel launch at the
-# bench workload, from the ncu capture summarised under profiles/ (None: not captured)
-NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum of one newton_kernel launch, from the ncu
+# capture summarised in profiles/newton_kernel_humanoid.md: 138.8 MB for 16384 humanoid
+# worlds (8.47 KB per world); traffic grows in proportion to the worlds of a launch.
+NCU_TRAFFIC_BYTES_PER_WORLD = 138.8e6 / 16384
 
 
 def parse_args():
@@ -50,7 +51,7 @@ def parse_args():
     p.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline sample length")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
-    p.add_argument("--sparse-hessian", default="off", choices=["on", "off"],
+    p.add_argument("--sparse-hessian", default="on", choices=["on", "off"],
                    help="install the static-pattern sparse Hessian plan (single-body contact groups)")
     return p.parse_args()
 
@@ -257,7 +258,9 @@ def main():
         for dd, sc in zip(dev, scratch):
             reason = runtime.refresh_sparse_hessian(md, dd, sc, groups, device)
             if reason != "enabled":
-                raise SystemExit(f"sparse Hessian plan not installed: {reason}")
+                # the model does not qualify (density, nv): the dense factor stays, as in the reference
+                args.sparse_hessian = "off"
+                break
     nb = len(dev)
 
     def step(k):
@@ -378,7 +381,7 @@ def main():
                 "peak_source": peak_src,
                 "unit": "GB/s",
                 "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH,
+                "traffic": NCU_TRAFFIC_BYTES_PER_WORLD * args.nworld if args.workload == "humanoid" else None,
                 "algorithmic_bytes_per_launch": alg,
                 "launch_ms": launch_s * 1e3,
             },

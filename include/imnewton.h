@@ -159,8 +159,9 @@ typedef struct ImnSparsePlan {
  * shared memory; any pointer that is non-NULL receives the final value of the
  * corresponding quantity when a world finishes, so a caller that inspects the
  * context (the reference's tests do) still finds it.  NULL pointers are
- * skipped.  `hfactor` is REQUIRED only on the sparse path (it carries the
- * violation counter). */
+ * skipped.  `hfactor` is REQUIRED only on the sparse path: its last element per
+ * world is the pattern-violation counter; the packed H | N | 1/D layout of
+ * sparse_hessian.py:488-489 is written there only when `h` is non-NULL too. */
 typedef struct ImnCtx {
   float* Jaref; /* (W, R) stride efc_ld of ImnData */
   float* jv;    /* (W, R) */

@@ -347,9 +347,11 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   if (cx.dof_union && !rowless)
 #pragma unroll 1
     for (int i = lane; i <= nv; i += 32) cx.dof_union[(size_t)w * (nv + 1) + i] = s.uni[i];
-  if (SPARSE && !rowless && cx.hfactor) {
-    // packed H | N | 1/D; the last element keeps counting violations
-    // (sparse_hessian.py:488-489)
+  if (SPARSE && !rowless && cx.hfactor && cx.h) {
+    // packed H | N | 1/D, the reference's hfactor layout (sparse_hessian.py:488-489).
+    // The factor never leaves the chip here, so it is written only for callers that
+    // inspect the context (those that also pass ctx.h); the violation counter in the
+    // last element is always live.
     float* Uf = cx.hfactor + (size_t)w * m.nv_pad * m.nv_pad;
 #pragma unroll 1
     for (int q = lane; q < sp.nfac; q += 32) Uf[q] = s.Hp[q], Uf[sp.nfac + q] = s.N[q];

@@ -214,6 +214,7 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
   }
   if (lane == 0) s.uni[nv] = n;
   __syncwarp();
+  IMN_MARK(s, 12);
   const int npu = n * (n + 1) / 2;
   int pi = lane, pj = 0;
   pair_advance(pi, pj, 0);
@@ -243,6 +244,7 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
     pair_advance(pi, pj, 32);
   }
   __syncwarp();
+  IMN_MARK(s, 13);
 }
 
 // Sparse plan: H = M + J^T diag(D, QUADRATIC rows) J on the pattern slots, each slot
