@@ -89,6 +89,27 @@ __device__ __forceinline__ Vec3 row_at(const Row& r, float alpha, bool absolute)
     o.c0 = r.f * (alpha * r.j);
   return o;
 }
+// The same for a plain inequality row (limit or pyramidal contact edge): cost
+// 0.5 D x^2 while x < 0, else nothing.  Branch-free; identical values to row_at.
+__device__ __forceinline__ Row make_row_ineq(bool valid, float D, float ja, float j) {
+  Row r;
+  r.f = 0.0f, r.D = D, r.ja = ja, r.j = j, r.rf = -1.0f;
+  r.z0 = valid ? (ja >= 0.0f ? IMN_STATE_SATISFIED : IMN_STATE_QUADRATIC) : -1;
+  r.jvD = j * D;
+  r.h = j * r.jvD;
+  r.q1r = r.jvD * ja;
+  r.cost0 = r.z0 == IMN_STATE_QUADRATIC ? ((0.5f * D) * ja) * ja : 0.0f;
+  return r;
+}
+__device__ __forceinline__ Vec3 row_at_ineq(const Row& r, float alpha, bool absolute) {
+  const float x = fmaf(alpha, r.j, r.ja);
+  const bool valid = r.z0 >= 0, on = valid && x < 0.0f, on0 = r.z0 == IMN_STATE_QUADRATIC;
+  const float cx = on ? ((0.5f * r.D) * x) * x : 0.0f;
+  float c0 = on == on0 ? (on ? alpha * fmaf(0.5f * alpha, r.h, r.q1r) : 0.0f) : cx - r.cost0;
+  if (absolute) c0 = r.cost0;
+  if (!valid) c0 = 0.0f;
+  return v3(c0, on ? r.jvD * x : 0.0f, on ? r.h : 0.0f);
+}
 __device__ __forceinline__ Vec3 eval_quad(float q1, float q2, float alpha) {
   return v3(fmaf(alpha, q1, (alpha * alpha) * q2) + 0.0f, fmaf(2.0f * alpha, q2, q1), 2.0f * q2);
 }

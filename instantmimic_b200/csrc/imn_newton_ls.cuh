@@ -41,10 +41,19 @@ __device__ __forceinline__ LineSearchResult line_search(const World& s, float se
   const float q1 = gq[0], q2 = gq[1];
   const int ra = ne + lane, rb = ra + 32;
   const bool va = ra < nefc, vb = rb < nefc;
-  const Row rowa = make_row(va, ra < nef, va ? s.floss[ra] : 0.0f, va ? s.Dsm[ra] : 1.0f,
-                            va ? s.Jaref[ra] : 0.0f, va ? s.jv[ra] : 0.0f);
-  const Row rowb = make_row(vb, rb < nef, vb ? s.floss[rb] : 0.0f, vb ? s.Dsm[rb] : 1.0f,
-                            vb ? s.Jaref[rb] : 0.0f, vb ? s.jv[rb] : 0.0f);
+  // friction-loss rows are rare: without any (warp-uniform test) the rows are plain
+  // inequalities and the short branch-free evaluation is used
+  const bool fric = nef > ne;
+  Row rowa, rowb;
+  if (fric) {
+    rowa = make_row(va, ra < nef, va ? s.floss[ra] : 0.0f, va ? s.Dsm[ra] : 1.0f, va ? s.Jaref[ra] : 0.0f,
+                    va ? s.jv[ra] : 0.0f);
+    rowb = make_row(vb, rb < nef, vb ? s.floss[rb] : 0.0f, vb ? s.Dsm[rb] : 1.0f, vb ? s.Jaref[rb] : 0.0f,
+                    vb ? s.jv[rb] : 0.0f);
+  } else {
+    rowa = make_row_ineq(va, va ? s.Dsm[ra] : 1.0f, va ? s.Jaref[ra] : 0.0f, va ? s.jv[ra] : 0.0f);
+    rowb = make_row_ineq(vb, vb ? s.Dsm[rb] : 1.0f, vb ? s.Jaref[rb] : 0.0f, vb ? s.jv[rb] : 0.0f);
+  }
   const bool more = ne + 64 < nefc;
 
   LineSearchResult out;
@@ -57,21 +66,38 @@ __device__ __forceinline__ LineSearchResult line_search(const World& s, float se
   for (int pass = 0; pass < ls_iterations + 2; ++pass) {
     const bool absolute = pass == 0;
     const Vec3 z3 = v3(0.0f, 0.0f, 0.0f);  // running sums start at zero
-    Vec3 s0 = z3 + row_at(rowa, a0, absolute), s1 = z3 + row_at(rowa, a1, absolute),
-         s2 = z3 + row_at(rowa, a2, absolute);
-    s0 = s0 + row_at(rowb, a0, absolute);
-    s1 = s1 + row_at(rowb, a1, absolute);
-    s2 = s2 + row_at(rowb, a2, absolute);
-    if (more)
-#pragma unroll 1
-      for (int r = rb + 32; r < nefc; r += 32) {
-        const Row rr = make_row(true, r < nef, s.floss[r], s.Dsm[r], s.Jaref[r], s.jv[r]);
-        s0 = s0 + row_at(rr, a0, absolute);
-        s1 = s1 + row_at(rr, a1, absolute);
-        s2 = s2 + row_at(rr, a2, absolute);
+    Vec3 s0 = z3, s1 = z3, s2 = z3;
+    if (!fric && !more) {
+      s0 = (z3 + row_at_ineq(rowa, a0, absolute)) + row_at_ineq(rowb, a0, absolute);
+      if (pass >= 2) {
+        s1 = (z3 + row_at_ineq(rowa, a1, absolute)) + row_at_ineq(rowb, a1, absolute);
+        s2 = (z3 + row_at_ineq(rowa, a2, absolute)) + row_at_ineq(rowb, a2, absolute);
       }
+    } else {
+      // general form (friction rows, or more than two rows per lane), one step size
+      // at a time to keep this rarely used code small
+      const int nalpha = pass >= 2 ? 3 : 1;
+#pragma unroll 1
+      for (int k = 0; k < nalpha; ++k) {
+        const float al = k == 0 ? a0 : (k == 1 ? a1 : a2);
+        Vec3 acc = (z3 + row_at(rowa, al, absolute)) + row_at(rowb, al, absolute);
+        if (more)
+#pragma unroll 1
+          for (int r = rb + 32; r < nefc; r += 32)
+            acc = acc + row_at(make_row(true, r < nef, s.floss[r], s.Dsm[r], s.Jaref[r], s.jv[r]), al, absolute);
+        if (k == 0) s0 = acc;
+        if (k == 1) s1 = acc;
+        if (k == 2) s2 = acc;
+      }
+    }
     float q[9] = {s0.c0, s0.c1, s0.c2, s1.c0, s1.c1, s1.c2, s2.c0, s2.c1, s2.c2};
-    ls_sum(q, bd);
+    if (pass >= 2) {
+      ls_sum(q, bd);
+    } else {
+      float q3[3] = {q[0], q[1], q[2]};
+      ls_sum(q3, bd);
+      q[0] = q3[0], q[1] = q3[1], q[2] = q3[2];
+    }
     if (pass == 0) {
       const Vec3 rows = v3(q[0], q[1], q[2]);
       p0 = v3(0.0f, q1, 2.0f * q2) + rows;
