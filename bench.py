@@ -306,32 +306,59 @@ def main():
             ({n: pin(getattr(d, n)) for n in in_names}, {n: pin(getattr(d.efc, n)) for n in efc_in})
             for _, d in host
         ]
-        hout = ({n: pin(getattr(host[0][1], n)) for n in out_names},
-                {n: pin(getattr(host[0][1].efc, n)) for n in efc_out})
-        dd, sc = dev[0], scratch[0]
+        # two slots (device buffers, stream, pinned result buffers): while slot A solves,
+        # slot B's inputs are already crossing PCIe; the host consumes the results of
+        # step k-1 while step k is in flight.  Every step's H2D and D2H is inside the
+        # timed region.
+        nslot = 2 if nb >= 2 else 1
+        slots = []
+        for i in range(nslot):
+            slots.append({
+                "dd": dev[i], "sc": scratch[i], "stream": torch.cuda.Stream(device=device),
+                "done": torch.cuda.Event(),
+                "out": ({n: pin(getattr(host[0][1], n)) for n in out_names},
+                        {n: pin(getattr(host[0][1].efc, n)) for n in efc_out}),
+            })
         h2d = sum(t.numel() * t.element_size() for part in hin[0] for t in part.values())
-        d2h = sum(t.numel() * t.element_size() for part in hout for t in part.values())
+        d2h = sum(t.numel() * t.element_size() for part in slots[0]["out"] for t in part.values())
+        checksum = 0.0
 
-        def e2e_step(k):
+        def e2e_issue(k):
+            sl = slots[k % nslot]
             a, b = hin[k % nb]
-            for n, t in a.items():
-                getattr(dd, n).copy_(t, non_blocking=True)
-            for n, t in b.items():
-                getattr(dd.efc, n).copy_(t, non_blocking=True)
-            runtime.solve_with_scratch(md, dd, sc, use_optimized_kernel=True)
-            for n, t in hout[0].items():
-                t.copy_(getattr(dd, n), non_blocking=True)
-            for n, t in hout[1].items():
-                t.copy_(getattr(dd.efc, n), non_blocking=True)
-            torch.cuda.synchronize()  # the caller reads the results
+            with torch.cuda.stream(sl["stream"]):
+                for n, t in a.items():
+                    getattr(sl["dd"], n).copy_(t, non_blocking=True)
+                for n, t in b.items():
+                    getattr(sl["dd"].efc, n).copy_(t, non_blocking=True)
+                runtime.solve_with_scratch(md, sl["dd"], sl["sc"], use_optimized_kernel=True, stream=sl["stream"])
+                for n, t in sl["out"][0].items():
+                    t.copy_(getattr(sl["dd"], n), non_blocking=True)
+                for n, t in sl["out"][1].items():
+                    t.copy_(getattr(sl["dd"].efc, n), non_blocking=True)
+                sl["done"].record(sl["stream"])
 
+        def e2e_consume(k):
+            sl = slots[k % nslot]
+            sl["done"].synchronize()  # the caller reads this step's results on the host
+            return float(sl["out"][0]["solver_niter"][0])
+
+        def e2e_run(n):
+            total = 0.0
+            for k in range(n):
+                if k >= nslot:
+                    total += e2e_consume(k - nslot)  # frees the slot step k is about to reuse
+                e2e_issue(k)
+            for k in range(max(n - nslot, 0), n):
+                total += e2e_consume(k)
+            return total
+
+        torch.cuda.synchronize()
         e2e_steps = min(args.steps, 50)
-        for k in range(3):
-            e2e_step(k)
+        e2e_run(4)
         barrier()
         t0 = time.perf_counter()
-        for k in range(e2e_steps):
-            e2e_step(k)
+        checksum = e2e_run(e2e_steps)
         barrier()
         dt = max_over_ranks(time.perf_counter() - t0)
         e2e = {
@@ -341,7 +368,47 @@ def main():
             "d2h_bytes_per_step": int(d2h),
             "steps": e2e_steps,
             "ms_per_step": 1e3 * dt / e2e_steps,
+            "pipeline": f"{nslot} slots (copy of step k+1 overlaps the solve of step k)",
+            "checksum": checksum,
         }
+
+    # ---- the M-side kernels of the same path, timed alone on the same batches --------
+    aux = None
+    if world == 1:
+        from instantmimic_b200.mjw_kernels import indexed_factor
+
+        def timed(fn, reps=20):
+            for k in range(3):
+                fn(k)
+            torch.cuda.synchronize()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for k in range(reps):
+                fn(k)
+            b.record()
+            torch.cuda.synchronize()
+            return a.elapsed_time(b) * 1e-3 / reps
+
+        W, nv, nM = args.nworld, m_host.nv, m_host.nM
+        aux = {}
+        sc0 = scratch[0]
+        if sc0.tree_factor_solve is not None:
+            t = timed(lambda k: runtime._factor_solve_i_dense(
+                md, dev[k % nb], dev[k % nb].M, dev[k % nb].qacc_smooth, dev[k % nb].qfrc_smooth, None,
+                tree_factor_solve=sc0.tree_factor_solve))
+            alg = 4.0 * W * (nM + 2 * nv)
+            aux["tree_ldl_kernel"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg,
+                                      "groups": sc0.tree_factor_solve.groups}
+        if sc0.dense_factor_solve is not None:
+            bs = sc0.dense_factor_solve
+            t = timed(lambda k: indexed_factor.blocked_dense_factor_solve(
+                dev[k % nb], dev[k % nb].M, dev[k % nb].qacc_smooth, dev[k % nb].qfrc_smooth, bs))
+            alg = 4.0 * W * (nM + 2 * nv + bs.pad * bs.pad)
+            aux["blocked_dense_kernel"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg}
+        t = timed(lambda k: runtime._rowless_handoff(md, dev[k % nb]))
+        alg = 4.0 * W * (nM + 4 * nv + 1)
+        aux["mul_m_kernel(rowless hand-off)"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9,
+                                                 "algorithmic_bytes": alg}
 
     if rank == 0:
         from instantmimic_b200.mjw_kernels import newton_fusion
@@ -391,6 +458,10 @@ def main():
                 "smem_bytes_per_world": int(info.smem_bytes),
             },
         }
+        if aux is not None:
+            for v in aux.values():
+                v["frac_of_hbm_peak"] = v["achieved_gbs"] / peak
+            line["aux_kernels"] = aux
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args, host)
         print(json.dumps(line))
