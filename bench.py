@@ -378,13 +378,21 @@ def main():
         from instantmimic_b200.mjw_kernels import indexed_factor
 
         def timed(fn, reps=20):
+            """Seconds per call on the device: the calls are recorded into a CUDA graph
+            (they allocate nothing) and the replay is timed, so that host time per call
+            (struct building, ctypes) does not hide the kernel's."""
             for k in range(3):
                 fn(k)
             torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for k in range(reps):
+                    fn(k)
+            graph.replay()
+            torch.cuda.synchronize()
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
-            for k in range(reps):
-                fn(k)
+            graph.replay()
             b.record()
             torch.cuda.synchronize()
             return a.elapsed_time(b) * 1e-3 / reps
@@ -397,8 +405,20 @@ def main():
                 md, dev[k % nb], dev[k % nb].M, dev[k % nb].qacc_smooth, dev[k % nb].qfrc_smooth, None,
                 tree_factor_solve=sc0.tree_factor_solve))
             alg = 4.0 * W * (nM + 2 * nv)
-            aux["tree_ldl_kernel"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg,
-                                      "groups": sc0.tree_factor_solve.groups}
+            generated = sc0.tree_factor_solve.kernel is not None
+            aux["tree_ldl_generated" if generated else "tree_ldl_kernel"] = {
+                "ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg,
+                "groups": sc0.tree_factor_solve.groups}
+            if generated:
+                # the same plan through the instruction-list interpreter (what runs without NVRTC)
+                import dataclasses
+
+                interp = dataclasses.replace(sc0.tree_factor_solve, kernel=None)
+                t = timed(lambda k: runtime._factor_solve_i_dense(
+                    md, dev[k % nb], dev[k % nb].M, dev[k % nb].qacc_smooth, dev[k % nb].qfrc_smooth, None,
+                    tree_factor_solve=interp))
+                aux["tree_ldl_kernel(interpreted)"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9,
+                                                       "algorithmic_bytes": alg}
         if sc0.dense_factor_solve is not None:
             bs = sc0.dense_factor_solve
             t = timed(lambda k: indexed_factor.blocked_dense_factor_solve(

@@ -198,7 +198,7 @@ typedef struct ImnTreePlan {
   int32_t ntrunk_entries;
   int32_t nslot;        /* per-world scratch slots in shared memory            */
   const int32_t* prog;      /* device: concatenated instruction streams        */
-  const int32_t* prog_ptr;  /* device: [3*groups + 2] stream offsets           */
+  const int32_t* prog_ptr;  /* device: [2*groups + 2] stream offsets           */
   int32_t owner;        /* group that finishes the trunk                       */
 } ImnTreePlan;
 
@@ -237,6 +237,30 @@ int imn_mul_m(const ImnModel* m, const float* M, int64_t M_ld, const float* v,
 int imn_tree_ldl_solve(const ImnTreePlan* plan, const float* M, int64_t M_ld,
                        const float* y, int64_t y_ld, float* x, int64_t x_ld,
                        int32_t nworld, void* stream);
+
+/* Replaces make_tree_ldl_factor_solve_kernel (tree_ldl.py:362-390, source text
+ * from _generate_source, tree_ldl.py:196-359): turns the plan's instruction list
+ * into straight-line CUDA C and compiles it for sm_100a at run time (NVRTC,
+ * looked up with dlopen; IMN_ERR_UNSUPPORTED when it is not installed -- callers
+ * then keep imn_tree_ldl_solve).  `prog` (n x 4 int32) and `prog_ptr`
+ * (2*groups + 2 offsets) are HOST copies of the arrays of ImnTreePlan.  Needs no
+ * GPU; the machine code is handed to the CUDA runtime on the first
+ * imn_tree_ldl_compiled_solve (make that call outside stream capture). */
+typedef struct ImnTreeKernel ImnTreeKernel;
+int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr, int32_t nv,
+                         int32_t nM, int32_t groups, int32_t owner, int32_t nslot,
+                         ImnTreeKernel** out);
+/* Shared-memory slots per world, bytes of machine code, and the generated source
+ * (owned by the kernel object); any pointer may be NULL. */
+int imn_tree_ldl_kernel_info(const ImnTreeKernel* kernel, int32_t* shared_slots,
+                             int64_t* code_bytes, const char** source);
+void imn_tree_ldl_kernel_destroy(ImnTreeKernel* kernel);
+
+/* tree_ldl.tree_factor_solve (tree_ldl.py:419-433) through the generated kernel;
+ * arguments and results as imn_tree_ldl_solve, bit for bit. */
+int imn_tree_ldl_compiled_solve(ImnTreeKernel* kernel, const float* M, int64_t M_ld,
+                                const float* y, int64_t y_ld, float* x, int64_t x_ld,
+                                int32_t nworld, void* stream);
 
 /* Replaces factor_solve_indexed_cholesky_kernel and its multi-RHS variants
  * (indexed_factor.py:176-214, 217-391, 394-493;

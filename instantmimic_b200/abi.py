@@ -193,6 +193,13 @@ SYMBOLS = {
     "imn_rowless_handoff": (C.c_int, [C.POINTER(ImnModel), C.POINTER(ImnData), P]),
     "imn_mul_m": (C.c_int, [C.POINTER(ImnModel), P, I64, P, I64, P, I64, I32, P]),
     "imn_tree_ldl_solve": (C.c_int, [C.POINTER(ImnTreePlan), P, I64, P, I64, P, I64, I32, P]),
+    "imn_tree_ldl_compile": (C.c_int, [P, P, I32, I32, I32, I32, I32, C.POINTER(C.c_void_p)]),
+    "imn_tree_ldl_kernel_info": (
+        C.c_int,
+        [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int64), C.POINTER(C.c_char_p)],
+    ),
+    "imn_tree_ldl_kernel_destroy": (None, [C.c_void_p]),
+    "imn_tree_ldl_compiled_solve": (C.c_int, [C.c_void_p, P, I64, P, I64, P, I64, I32, P]),
     "imn_blocked_dense_factor_solve": (
         C.c_int,
         [C.POINTER(ImnBlockedPlan), P, I64, P, P, P, P, I32, I32, I32, P],

@@ -26,6 +26,7 @@ NVCC_FLAGS = [
     "-Xcompiler",
     "-fPIC",
     "-shared",
+    "-ldl",
 ]
 
 

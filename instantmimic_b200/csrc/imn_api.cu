@@ -16,34 +16,42 @@ void set_error(const char* fmt, ...) {
   va_end(ap);
 }
 
-// One warp per world; M's row is read once into shared memory, then every lane
-// forms the running sums of its dofs over the symmetric row tables.
-__global__ void __launch_bounds__(128) mul_m_kernel(const int nv, const int nM, const int* __restrict__ rowadr,
+// M v over the symmetric row tables, a bandwidth-bound pass: every CTA stages the
+// (model-wide) tables in shared memory once and its eight warps then walk worlds
+// with a grid stride.  A lane owns dofs lane, lane+32, ...; its loads of M and v
+// are independent of one another, so many cache lines are in flight per warp; each
+// line of a world's M row and v is fetched from HBM once and reused out of L1.
+// Running sums are formed in table order (ascending stored entries), as the oracle.
+__global__ void __launch_bounds__(256) mul_m_kernel(const int nv, const int* __restrict__ rowadr,
                                                     const int* __restrict__ col, const int* __restrict__ madr,
                                                     const float* __restrict__ M, const int64_t M_ld,
                                                     const float* __restrict__ v, const int64_t v_ld,
                                                     float* __restrict__ out, const int64_t out_ld,
                                                     float* __restrict__ copy_to, int* __restrict__ niter,
                                                     float* __restrict__ zero, const int nworld) {
-  extern __shared__ float sm[];
-  const int lane = threadIdx.x & 31, slot = threadIdx.x >> 5;
-  const int w = blockIdx.x * (blockDim.x >> 5) + slot;
-  if (w >= nworld) return;
-  float* Ms = sm + slot * (nM + nv);
-  float* vs = Ms + nM;
-  for (int e = lane; e < nM; e += 32) Ms[e] = M[(size_t)w * M_ld + e];
-  for (int i = lane; i < nv; i += 32) {
-    const float x = v[(size_t)w * v_ld + i];
-    vs[i] = x;
-    if (copy_to) copy_to[(size_t)w * v_ld + i] = x;
-    if (zero) zero[(size_t)w * v_ld + i] = 0.0f;
-  }
-  if (niter && lane == 0) niter[w] = 0;
-  __syncwarp();
-  for (int i = lane; i < nv; i += 32) {
-    float s = 0.0f;
-    for (int k = rowadr[i]; k < rowadr[i + 1]; ++k) s = fmaf(Ms[madr[k]], vs[col[k]], s);
-    out[(size_t)w * out_ld + i] = s;
+  extern __shared__ uint32_t tab[];  // packed (col | madr << 16) entries, then nv + 1 row starts
+  const int nnz = rowadr[nv];
+  int* radr = reinterpret_cast<int*>(tab + nnz);
+  for (int e = threadIdx.x; e < nnz; e += blockDim.x) tab[e] = (uint32_t)col[e] | ((uint32_t)madr[e] << 16);
+  for (int i = threadIdx.x; i <= nv; i += blockDim.x) radr[i] = rowadr[i];
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  for (int w = blockIdx.x * warps + (threadIdx.x >> 5); w < nworld; w += gridDim.x * warps) {
+    const float* Mw = M + (size_t)w * M_ld;
+    const float* vw = v + (size_t)w * v_ld;
+    for (int i = lane; i < nv; i += 32) {
+      float s = 0.0f;
+      const int k1 = radr[i + 1];
+#pragma unroll 8
+      for (int k = radr[i]; k < k1; ++k) {
+        const uint32_t p = tab[k];
+        s = fmaf(__ldg(Mw + (p >> 16)), __ldg(vw + (p & 0xFFFF)), s);
+      }
+      out[(size_t)w * out_ld + i] = s;
+      if (copy_to) copy_to[(size_t)w * v_ld + i] = __ldg(vw + i);
+      if (zero) zero[(size_t)w * v_ld + i] = 0.0f;
+    }
+    if (niter && lane == 0) niter[w] = 0;
   }
 }
 
@@ -51,12 +59,19 @@ static int launch_mul_m(const ImnModel* m, const float* M, int64_t M_ld, const f
                         float* out, int64_t out_ld, float* copy_to, int* niter, float* zero, int nworld,
                         cudaStream_t stream) {
   if (nworld == 0) return IMN_OK;
-  const int wpc = 4;
-  const size_t bytes = (size_t)wpc * (m->nM + m->nv) * sizeof(float);
+  if (m->nM >= (1 << 16)) return set_error("mul_m: nM %d exceeds 16-bit indices", m->nM), IMN_ERR_LIMIT;
+  // the symmetric tables list every stored entry at most twice
+  const size_t bytes = ((size_t)2 * m->nM + m->nv + 1) * sizeof(uint32_t);
   if (bytes > 48 * 1024) return set_error("mul_m: nM %d too large", m->nM), IMN_ERR_LIMIT;
-  mul_m_kernel<<<(nworld + wpc - 1) / wpc, wpc * 32, bytes, stream>>>(
-      m->nv, m->nM, m->M_mulm_rowadr, m->M_mulm_col, m->M_mulm_madr, M, M_ld, v, v_ld, out, out_ld, copy_to,
-      niter, zero, nworld);
+  const int warps = 8;
+  int sms = 148;
+  {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  }
+  const int grid = min((nworld + warps - 1) / warps, sms * 8);
+  mul_m_kernel<<<grid, warps * 32, bytes, stream>>>(m->nv, m->M_mulm_rowadr, m->M_mulm_col, m->M_mulm_madr, M, M_ld,
+                                                    v, v_ld, out, out_ld, copy_to, niter, zero, nworld);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error("mul_m: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
   return IMN_OK;

@@ -67,102 +67,201 @@ __global__ void tree_ldl_kernel(const int4* __restrict__ prog, const int* __rest
 }
 
 // ---- blocked dense Cholesky ------------------------------------------------------
-__global__ void __launch_bounds__(32) blocked_dense_kernel(const int nv, const int pad, const int nM,
-                                                           const int* __restrict__ indices,
-                                                           const float* __restrict__ identity,
-                                                           const float* __restrict__ M, const int64_t M_ld,
-                                                           const float* __restrict__ y, float* __restrict__ Ug,
-                                                           float* __restrict__ x,
-                                                           const int* __restrict__ active, const int rhs,
-                                                           const int mode) {
-  extern __shared__ float sm[];
-  const int lane = threadIdx.x, w = blockIdx.x;
+// One warp per world, kWorldsPerCta worlds per CTA.  Shared memory of a world:
+//   A    (n + carry + 1) x ldu.  U[r][c] (r <= c) at A[r*ldu + c]; the value column c
+//        starts from (M's column c above the diagonal, or right-hand side c - n) is
+//        kept transposed at A[(c+1)*ldu + r], so a lane reads the 16 rows of its
+//        column with four 128-bit loads.
+//   dinv n, X n x rhs (right-hand sides, then solutions).
+// The factorisation works on the nv x nv part only: with zero padding and a unit
+// diagonal the padded rows of U are exactly the identity, which is what is stored.
+// Up to `carry` right-hand sides ride through the factorisation as extra columns
+// (that is the forward substitution); further ones, and mode 1, take the
+// substitution with the stored factor.  Every value receives its terms in the same
+// order as the plain row-by-row statement of the algorithm (ascending t).
+static const int kWorldsPerCta = 4;
+
+__device__ __forceinline__ void dense_factor_carry(float* A, float* dinv, const int n, const int nc, const int ldu,
+                                                   const int lane) {
+#pragma unroll 1
+  for (int b0 = 0; b0 < n; b0 += 16) {
+    const int nr = min(16, n - b0);
+    const int ng = (nr + 3) >> 2;
+    float acc[3][16];
+    int cc[3];
+    bool act[3], valid[3];
+#pragma unroll
+    for (int k = 0; k < 3; ++k) {
+      const int c = b0 + lane + 32 * k;
+      act[k] = b0 + 32 * k < nc;  // warp-uniform
+      valid[k] = c < nc;
+      cc[k] = valid[k] ? c : nc - 1;
+      if (act[k]) {
+        const float* src = A + (cc[k] + 1) * ldu + b0;
+#pragma unroll
+        for (int gi = 0; gi < 4; ++gi) {
+          float4 h = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+          if (gi < ng) h = *reinterpret_cast<const float4*>(src + 4 * gi);
+          acc[k][4 * gi] = h.x, acc[k][4 * gi + 1] = h.y, acc[k][4 * gi + 2] = h.z, acc[k][4 * gi + 3] = h.w;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) acc[k][i] = 0.0f;
+      }
+    }
+    // terms of the rows above the block
+#pragma unroll 2
+    for (int t = 0; t < b0; ++t) {
+      const float* Ut = A + t * ldu;
+      float ur[16];
+#pragma unroll
+      for (int gi = 0; gi < 4; ++gi) {
+        float4 u = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (gi < ng) u = *reinterpret_cast<const float4*>(Ut + b0 + 4 * gi);
+        ur[4 * gi] = u.x, ur[4 * gi + 1] = u.y, ur[4 * gi + 2] = u.z, ur[4 * gi + 3] = u.w;
+      }
+#pragma unroll
+      for (int k = 0; k < 3; ++k)
+        if (act[k]) {
+          const float uc = Ut[cc[k]];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[k][i] = fmaf(-ur[i], uc, acc[k][i]);
+        }
+    }
+    // the block's own rows, one by one; acc[k][0] is always the current row
+#pragma unroll 1
+    for (int r = 0; r < nr; ++r) {
+      const float pv = __shfl_sync(IMN_FULL_MASK, acc[0][0], r);
+      const float dg = sqrtf(pv);
+      const float rinv = 1.0f / dg;
+      float u[3];
+      float* Ur = A + (b0 + r) * ldu;
+#pragma unroll
+      for (int k = 0; k < 3; ++k)
+        if (act[k]) {
+          u[k] = acc[k][0] * rinv;
+          if (k == 0 && lane == r) u[k] = dg;
+          if (valid[k] && cc[k] >= b0 + r) Ur[cc[k]] = u[k];
+        }
+      if (lane == 0) dinv[b0 + r] = rinv;
+      float um[16];
+#pragma unroll
+      for (int j = 1; j < 16; ++j) um[j] = __shfl_sync(IMN_FULL_MASK, u[0], (r + j) & 31);
+#pragma unroll
+      for (int k = 0; k < 3; ++k)
+        if (act[k]) {
+#pragma unroll
+          for (int j = 1; j < 16; ++j) acc[k][j - 1] = fmaf(-um[j], u[k], acc[k][j]);
+          acc[k][15] = 0.0f;
+        }
+    }
+    __syncwarp();
+  }
+}
+
+__global__ void __launch_bounds__(32 * kWorldsPerCta)
+    blocked_dense_kernel(const int nv, const int pad, const int nM, const int* __restrict__ indices,
+                         const float* __restrict__ identity, const float* __restrict__ M, const int64_t M_ld,
+                         const float* __restrict__ y, float* __restrict__ Ug, float* __restrict__ x,
+                         const int* __restrict__ active, const int rhs, const int mode, const int carry,
+                         const int ldu, const int per_world, const int nworld) {
+  extern __shared__ __align__(16) float sm[];
+  const int lane = threadIdx.x & 31, w = blockIdx.x * kWorldsPerCta + (threadIdx.x >> 5);
+  if (w >= nworld) return;
   if (active && active[w] == 0) return;
-  const int ld = pad | 1;
-  float* U = sm;                 // pad x ld, upper triangle
-  float* dinv = U + pad * ld;    // pad
-  float* B = dinv + pad;         // pad x rhs right-hand sides / solutions
+  const int n = nv, nc = n + carry;
+  float* A = sm + (threadIdx.x >> 5) * per_world;
+  float* dinv = A + (nc + 1) * ldu;
+  float* X = dinv + ((n + 3) & ~3);
   float* Uw = Ug + (size_t)w * pad * pad;
   const int nblk = pad >> 4;
+  const float* yw = y + (size_t)w * n * rhs;
+  for (int q = lane; q < n * rhs; q += 32) X[q] = yw[q];
   if (mode == 0) {
-    // gather: table entry ((kb*nblk + ib)*16 + r)*16 + c addresses M's value of
-    // (16 kb + r, 16 ib + c); index nM is the extra zero slot; the padded diagonal
-    // of the last block gets the identity
+    // gather the blocks on and above the diagonal: table entry
+    // ((kb*nblk + ib)*16 + r)*16 + c addresses M's value of (16 kb + r, 16 ib + c);
+    // index nM is the extra zero slot
     const float* Mw = M + (size_t)w * M_ld;
-    for (int q = lane; q < pad * pad; q += 32) {
-      const int c = q & 15, r = (q >> 4) & 15, blk = q >> 8;
-      const int ib = blk % nblk, kb = blk / nblk;
-      const int idx = indices[q];
-      float v = idx < nM ? Mw[idx] : 0.0f;
-      if (kb == ib && 16 * (kb + 1) > nv) v += identity[(r << 4) | c];
-      U[(16 * kb + r) * ld + 16 * ib + c] = v;
+    for (int kb = 0; kb < nblk; ++kb)
+      for (int ib = kb; ib < nblk; ++ib) {
+        const int* tab = indices + ((kb * nblk + ib) << 8);
+#pragma unroll 4
+        for (int q = lane; q < 256; q += 32) {
+          const int row = 16 * kb + (q >> 4), colm = 16 * ib + (q & 15);
+          const int idx = __ldg(tab + q);
+          if (row <= colm && colm < n) A[(colm + 1) * ldu + row] = idx < nM ? __ldg(Mw + idx) : 0.0f;
+        }
+      }
+    __syncwarp();
+    for (int e = lane; e < n * carry; e += 32) {
+      const int r = e / carry, q = e - r * carry;
+      A[(n + q + 1) * ldu + r] = X[r * rhs + q];
     }
     __syncwarp();
+    dense_factor_carry(A, dinv, n, nc, ldu, lane);
+    // the factor, padded: zeros below the diagonal, the padded diagonal's own root
     for (int r = 0; r < pad; ++r) {
-      float dg = 0.0f;
-      for (int c = r + lane; c < pad; c += 32) {
-        float a = U[r * ld + c];
-        for (int t = 0; t < r; ++t) a = fmaf(-U[t * ld + r], U[t * ld + c], a);
-        U[r * ld + c] = a;
-        if (c == r) dg = sqrtf(a);
+      for (int c = lane; c < pad; c += 32) {
+        float v = 0.0f;
+        if (r < n && c >= r && c < n) v = A[r * ldu + c];
+        if (r >= n && c == r) v = sqrtf(identity[((r & 15) << 4) | (r & 15)]);
+        Uw[r * pad + c] = v;
       }
-      dg = __shfl_sync(IMN_FULL_MASK, dg, 0);
-      const float rinv = 1.0f / dg;
-      for (int c = r + lane; c < pad; c += 32) U[r * ld + c] = (c == r) ? dg : U[r * ld + c] * rinv;
-      if (lane == 0) dinv[r] = rinv;
-      __syncwarp();
     }
-    for (int q = lane; q < pad * pad; q += 32) {
-      const int r = q / pad, c = q - r * pad;
-      Uw[q] = c >= r ? U[r * ld + c] : 0.0f;
+    for (int e = lane; e < n * carry; e += 32) {
+      const int r = e / carry, q = e - r * carry;
+      X[r * rhs + q] = A[r * ldu + n + q];
     }
   } else {
-    for (int q = lane; q < pad * pad; q += 32) {
-      const int r = q / pad, c = q - r * pad;
-      U[r * ld + c] = Uw[q];
-    }
+    for (int r = 0; r < n; ++r)
+      for (int c = r + lane; c < n; c += 32) A[r * ldu + c] = Uw[r * pad + c];
     __syncwarp();
-    for (int r = lane; r < pad; r += 32) dinv[r] = 1.0f / U[r * ld + r];
+    for (int r = lane; r < n; r += 32) dinv[r] = 1.0f / A[r * ldu + r];
   }
-  // right-hand sides: rows nv..pad-1 are zero
-  const float* yw = y + (size_t)w * nv * rhs;
-  for (int q = lane; q < pad * rhs; q += 32) B[q] = q < nv * rhs ? yw[q] : 0.0f;
   __syncwarp();
-  // forward substitution: unknown r receives its terms in ascending order
-  for (int t = 0; t < pad; ++t) {
-    const float di = dinv[t];
-    for (int q = lane; q < rhs; q += 32) B[t * rhs + q] = B[t * rhs + q] * di;
-    __syncwarp();
-    for (int e = lane; e < (pad - t - 1) * rhs; e += 32) {
-      const int r = t + 1 + e / rhs, q = e % rhs;
-      B[r * rhs + q] = fmaf(-U[t * ld + r], B[t * rhs + q], B[r * rhs + q]);
-    }
-    __syncwarp();
-  }
-  // back substitution in 16-row blocks from the last: later blocks' columns first
-  // (ascending), then the block's own columns from its last inwards
-  for (int b0 = pad - 16; b0 >= 0; b0 -= 16) {
-    const int b1 = b0 + 16;
-    for (int e = lane; e < 16 * rhs; e += 32) {
-      const int r = b0 + e / rhs, q = e % rhs;
-      float acc = B[r * rhs + q];
-      for (int c = b1; c < pad; ++c) acc = fmaf(-U[r * ld + c], B[c * rhs + q], acc);
-      B[r * rhs + q] = acc;
-    }
-    __syncwarp();
-    for (int c = b1 - 1; c >= b0; --c) {
-      const float di = dinv[c];
-      for (int q = lane; q < rhs; q += 32) B[c * rhs + q] = B[c * rhs + q] * di;
+  // forward substitution with the stored factor for the right-hand sides that did
+  // not ride along: unknown r receives its terms in ascending order
+  const int q0 = mode == 0 ? carry : 0;
+  if (q0 < rhs) {
+    const int nq = rhs - q0;
+    for (int t = 0; t < n; ++t) {
+      const float di = dinv[t];
+      for (int q = lane; q < nq; q += 32) X[t * rhs + q0 + q] = X[t * rhs + q0 + q] * di;
       __syncwarp();
-      for (int e = lane; e < (c - b0) * rhs; e += 32) {
-        const int r = b0 + e / rhs, q = e % rhs;
-        B[r * rhs + q] = fmaf(-U[r * ld + c], B[c * rhs + q], B[r * rhs + q]);
+      for (int e = lane; e < (n - t - 1) * nq; e += 32) {
+        const int r = t + 1 + e / nq, q = q0 + e % nq;
+        X[r * rhs + q] = fmaf(-A[t * ldu + r], X[t * rhs + q], X[r * rhs + q]);
       }
       __syncwarp();
     }
   }
-  float* xw = x + (size_t)w * nv * rhs;
-  for (int q = lane; q < nv * rhs; q += 32) xw[q] = B[q];
+  // back substitution in 16-row blocks from the last: later blocks' columns first
+  // (ascending), then the block's own columns from its last inwards; two right-hand
+  // sides at a time on the two half-warps
+  for (int qb = 0; qb < rhs; qb += 2) {
+    const int q = qb + (lane >> 4), l = lane & 15;
+    const bool hasq = q < rhs;
+    for (int b0 = ((n - 1) / 16) * 16; b0 >= 0; b0 -= 16) {
+      const int b1 = min(b0 + 16, n);
+      const int r = b0 + l;
+      const float* Ur = A + r * ldu;
+      float acc = 0.0f, di = 0.0f;
+      if (r < b1 && hasq) {
+        acc = X[r * rhs + q];
+        di = dinv[r];
+#pragma unroll 2
+        for (int c = b1; c < n; ++c) acc = fmaf(-Ur[c], X[c * rhs + q], acc);
+      }
+      for (int c = b1 - 1; c >= b0; --c) {
+        const float xc = __shfl_sync(IMN_FULL_MASK, acc * di, (lane & 16) | (c - b0));
+        if (r < c && hasq) acc = fmaf(-Ur[c], xc, acc);
+        if (l == 0 && hasq) X[c * rhs + q] = xc;
+      }
+      __syncwarp();
+    }
+  }
+  float* xw = x + (size_t)w * n * rhs;
+  for (int q = lane; q < n * rhs; q += 32) xw[q] = X[q];
 }
 
 }  // namespace imn
@@ -209,21 +308,30 @@ extern "C" int imn_blocked_dense_factor_solve(const ImnBlockedPlan* plan, const 
   if (nworld < 0 || rhs_count < 1 || (mode == 0 && M_ld < plan->nM))
     return imn::set_error("imn_blocked_dense_factor_solve: bad extent or stride"), IMN_ERR_SHAPE;
   if (nworld == 0) return IMN_OK;
-  const int ld = plan->pad | 1;
-  const size_t bytes = sizeof(float) * ((size_t)plan->pad * ld + plan->pad + (size_t)plan->pad * rhs_count);
+  const int n = plan->nv;
+  if (n > 80) return imn::set_error("imn_blocked_dense_factor_solve: nv %d above 80", n), IMN_ERR_UNSUPPORTED;
+  // right-hand sides that ride through the factorisation as extra columns
+  const int carry = mode == 0 ? (rhs_count < 96 - n ? rhs_count : 96 - n) : 0;
+  const int ldu = (n + carry + 3) & ~3;
+  const int per_world = (n + carry + 1) * ldu + ((n + 3) & ~3) + ((n * rhs_count + 3) & ~3);
+  const size_t bytes = sizeof(float) * (size_t)per_world * imn::kWorldsPerCta;
   if (bytes > 227 * 1024)
     return imn::set_error("imn_blocked_dense_factor_solve: %zu bytes of shared memory needed (max %d)", bytes,
                           227 * 1024),
            IMN_ERR_LIMIT;
-  if (bytes > 48 * 1024) {
-    cudaError_t e =
-        cudaFuncSetAttribute(imn::blocked_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  {
+    cudaError_t e = cudaFuncSetAttribute(imn::blocked_dense_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                         cudaSharedmemCarveoutMaxShared);
+    if (e == cudaSuccess && bytes > 48 * 1024)
+      e = cudaFuncSetAttribute(imn::blocked_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess)
       return imn::set_error("imn_blocked_dense_factor_solve: cudaFuncSetAttribute: %s", cudaGetErrorString(e)),
              IMN_ERR_LAUNCH;
   }
-  imn::blocked_dense_kernel<<<nworld, 32, bytes, (cudaStream_t)stream>>>(
-      plan->nv, plan->pad, plan->nM, plan->indices, plan->identity, M, M_ld, y, U, x, active, rhs_count, mode);
+  imn::blocked_dense_kernel<<<(nworld + imn::kWorldsPerCta - 1) / imn::kWorldsPerCta, 32 * imn::kWorldsPerCta, bytes,
+                              (cudaStream_t)stream>>>(plan->nv, plan->pad, plan->nM, plan->indices, plan->identity, M,
+                                                      M_ld, y, U, x, active, rhs_count, mode, carry, ldu, per_world,
+                                                      nworld);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess)
     return imn::set_error("imn_blocked_dense_factor_solve: launch failed: %s", cudaGetErrorString(e)),

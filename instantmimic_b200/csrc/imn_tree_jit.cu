@@ -1,0 +1,293 @@
+// imn_tree_jit.cu -- the tree L'DL plan as generated straight-line code.
+//
+// The reference turns a TreeLdlPlan into source text and compiles it at run time
+// (tree_ldl.py:196-359 _generate_source, tree_ldl.py:362-390
+// make_tree_ldl_factor_solve_kernel).  This file does the same for sm_100a: it writes
+// CUDA C from the plan's instruction list, compiles it with NVRTC (loaded with dlopen,
+// so the library itself does not depend on it) and launches the result through the
+// runtime's library API.  The mapping is the plan's: a block serves 32 worlds with one
+// warp per group, lane l works on world 32*block + l, the trunk runs on the owner
+// warp between two block barriers.
+//
+// What the generator adds over interpreting the list (imn_tree_ldl_solve): a slot
+// that only one warp ever touches becomes a register variable of that warp's
+// straight-line code, so the elimination runs from registers with no instruction
+// decode; only the values that cross warps (the groups' contributions to the trunk and
+// the trunk's solution) go through shared memory, column = lane.  Every statement is
+// the instruction's own float32 operation (explicit fmaf, IEEE division, contraction
+// off), in list order, so the results are bit-identical to the interpreter's.
+#include <dlfcn.h>
+
+#include <string>
+#include <vector>
+
+#include "imn_common.cuh"
+
+namespace {
+
+enum { OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X };
+
+// ---- NVRTC through dlopen ---------------------------------------------------------
+typedef void* nvrtcProgram_t;
+struct Nvrtc {
+  void* handle = nullptr;
+  int (*create)(nvrtcProgram_t*, const char*, const char*, int, const char* const*, const char* const*) = nullptr;
+  int (*compile)(nvrtcProgram_t, int, const char* const*) = nullptr;
+  int (*log_size)(nvrtcProgram_t, size_t*) = nullptr;
+  int (*log)(nvrtcProgram_t, char*) = nullptr;
+  int (*cubin_size)(nvrtcProgram_t, size_t*) = nullptr;
+  int (*cubin)(nvrtcProgram_t, char*) = nullptr;
+  int (*destroy)(nvrtcProgram_t*) = nullptr;
+  const char* (*error_string)(int) = nullptr;
+};
+
+Nvrtc* nvrtc() {
+  static Nvrtc api;
+  static bool tried = false;
+  if (tried) return api.handle ? &api : nullptr;
+  tried = true;
+  const char* names[] = {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12",
+                         "/usr/local/cuda/lib64/libnvrtc.so"};
+  void* h = nullptr;
+  for (const char* n : names)
+    if ((h = dlopen(n, RTLD_NOW | RTLD_LOCAL))) break;
+  if (!h) return nullptr;
+#define IMN_SYM(field, name)                                        \
+  api.field = reinterpret_cast<decltype(api.field)>(dlsym(h, name)); \
+  if (!api.field) return nullptr
+  IMN_SYM(create, "nvrtcCreateProgram");
+  IMN_SYM(compile, "nvrtcCompileProgram");
+  IMN_SYM(log_size, "nvrtcGetProgramLogSize");
+  IMN_SYM(log, "nvrtcGetProgramLog");
+  IMN_SYM(cubin_size, "nvrtcGetCUBINSize");
+  IMN_SYM(cubin, "nvrtcGetCUBIN");
+  IMN_SYM(destroy, "nvrtcDestroyProgram");
+  IMN_SYM(error_string, "nvrtcGetErrorString");
+#undef IMN_SYM
+  api.handle = h;
+  return &api;
+}
+
+struct Ins {
+  int op, dst, a, b, c;
+};
+
+// operands an instruction reads / the slot it writes (-1: none)
+void operands(const Ins& i, int reads[4], int& nread, int& write) {
+  nread = 0, write = -1;
+  switch (i.op) {
+    case OP_LOAD_M:
+    case OP_LOAD_Y:
+    case OP_ZERO: write = i.dst; break;
+    case OP_INV: reads[nread++] = i.a, write = i.dst; break;
+    case OP_UPD: reads[nread++] = i.a, reads[nread++] = i.b, reads[nread++] = i.c, reads[nread++] = i.dst, write = i.dst; break;
+    case OP_SCALE: reads[nread++] = i.a, reads[nread++] = i.dst, write = i.dst; break;
+    case OP_SUBMUL: reads[nread++] = i.a, reads[nread++] = i.b, reads[nread++] = i.dst, write = i.dst; break;
+    case OP_MUL: reads[nread++] = i.a, reads[nread++] = i.b, write = i.dst; break;
+    case OP_ADD: reads[nread++] = i.a, reads[nread++] = i.dst, write = i.dst; break;
+    case OP_STORE_X: reads[nread++] = i.a; break;
+    default: break;
+  }
+}
+
+}  // namespace
+
+struct ImnTreeKernel {
+  int nv = 0, nM = 0, groups = 0, nshared = 0;
+  std::string source;
+  std::vector<char> cubin;
+  cudaLibrary_t library = nullptr;
+  cudaKernel_t kernel = nullptr;
+};
+
+namespace {
+
+std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int owner, int nslot, int* nshared_out) {
+  const int nstream = 2 * groups + 1;
+  auto warp_of = [&](int st) { return st < groups ? st : (st == groups ? owner : st - groups - 1); };
+  std::vector<std::vector<Ins>> streams(nstream);
+  std::vector<unsigned> users(nslot, 0u);
+  for (int st = 0; st < nstream; ++st)
+    for (int pc = ptr[st]; pc < ptr[st + 1]; ++pc) {
+      const int32_t* w = prog + 4 * pc;
+      Ins i{w[0], w[1], w[2] & 0xFFFF, (w[2] >> 16) & 0xFFFF, w[3]};
+      streams[st].push_back(i);
+      int reads[4], nread, write;
+      operands(i, reads, nread, write);
+      for (int k = 0; k < nread; ++k) users[reads[k]] |= 1u << warp_of(st);
+      if (write >= 0) users[write] |= 1u << warp_of(st);
+    }
+  // slots that more than one warp touches live in shared memory
+  std::vector<int> shared_index(nslot, -1);
+  int nshared = 0;
+  for (int sl = 0; sl < nslot; ++sl)
+    if (users[sl] & (users[sl] - 1u)) shared_index[sl] = nshared++;
+  *nshared_out = nshared;
+  auto ref = [&](int sl) {
+    return shared_index[sl] >= 0 ? "S[" + std::to_string(shared_index[sl] * 32) + "]" : "r" + std::to_string(sl);
+  };
+  auto emit = [&](std::string& out, const std::vector<Ins>& code) {
+    for (const Ins& i : code) {
+      const std::string d = i.op == OP_STORE_X ? "" : ref(i.dst);
+      switch (i.op) {
+        case OP_LOAD_M: out += d + " = Mr[" + std::to_string(i.a) + "];\n"; break;
+        case OP_LOAD_Y: out += d + " = yr[" + std::to_string(i.a) + "];\n"; break;
+        case OP_ZERO: out += d + " = 0.0f;\n"; break;
+        case OP_INV: out += d + " = 1.0f / " + ref(i.a) + ";\n"; break;
+        case OP_UPD:
+          out += d + " = fmaf(-(" + ref(i.a) + " * " + ref(i.b) + "), " + ref(i.c) + ", " + d + ");\n";
+          break;
+        case OP_SCALE: out += d + " = " + d + " * " + ref(i.a) + ";\n"; break;
+        case OP_SUBMUL: out += d + " = fmaf(-" + ref(i.a) + ", " + ref(i.b) + ", " + d + ");\n"; break;
+        case OP_MUL: out += d + " = " + ref(i.a) + " * " + ref(i.b) + ";\n"; break;
+        case OP_ADD: out += d + " = " + d + " + " + ref(i.a) + ";\n"; break;
+        case OP_STORE_X: out += "if (live) xr[" + std::to_string(i.dst) + "] = " + ref(i.a) + ";\n"; break;
+        default: break;
+      }
+    }
+  };
+  std::string src;
+  src +=
+      "extern \"C\" __global__ void __launch_bounds__(" + std::to_string(32 * groups) +
+      ") tree_ldl_generated(const float* __restrict__ M, long long M_ld, const float* __restrict__ y,\n"
+      "    long long y_ld, float* __restrict__ x, long long x_ld, int nworld) {\n"
+      "  extern __shared__ float slots[];\n"
+      "  const int lw = threadIdx.x & 31, part = threadIdx.x >> 5;\n"
+      "  const int world = blockIdx.x * 32 + lw;\n"
+      "  const bool live = world < nworld;\n"
+      "  const int src = live ? world : nworld - 1;\n"
+      "  const float* Mr = M + (long long)src * M_ld;\n"
+      "  const float* yr = y + (long long)src * y_ld;\n"
+      "  float* xr = x + (long long)src * x_ld;\n"
+      "  float* S = slots + lw;\n"
+      "  switch (part) {\n";
+  for (int j = 0; j < groups; ++j) {
+    src += "  case " + std::to_string(j) + ": {\n";
+    // register variables of this warp
+    int n = 0;
+    for (int sl = 0; sl < nslot; ++sl)
+      if (shared_index[sl] < 0 && users[sl] == (1u << j)) {
+        src += (n % 8 == 0 ? std::string(n ? ";\nfloat " : "float ") : std::string(", ")) + "r" + std::to_string(sl) +
+               " = 0.0f";
+        ++n;
+      }
+    if (n) src += ";\n";
+    emit(src, streams[j]);
+    src += "asm volatile(\"bar.sync 0;\" ::: \"memory\");\n";
+    if (j == owner) emit(src, streams[groups]);
+    src += "asm volatile(\"bar.sync 0;\" ::: \"memory\");\n";
+    emit(src, streams[groups + 1 + j]);
+    src += "  } break;\n";
+  }
+  src += "  default: break;\n  }\n}\n";
+  return src;
+}
+
+}  // namespace
+
+extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr, int32_t nv, int32_t nM,
+                                    int32_t groups, int32_t owner, int32_t nslot, ImnTreeKernel** out) {
+  if (!prog || !prog_ptr || !out) return imn::set_error("imn_tree_ldl_compile: NULL argument"), IMN_ERR_NULL;
+  *out = nullptr;
+  if (nv <= 0 || groups < 1 || groups > 4 || owner < 0 || owner >= groups || nslot <= 0 || nslot > (1 << 16))
+    return imn::set_error("imn_tree_ldl_compile: malformed plan"), IMN_ERR_SHAPE;
+  const int nstream = 2 * groups + 1;
+  for (int st = 0; st < nstream; ++st)
+    if (prog_ptr[st] > prog_ptr[st + 1] || prog_ptr[st] < 0)
+      return imn::set_error("imn_tree_ldl_compile: stream offsets are not ascending"), IMN_ERR_SHAPE;
+  for (int pc = 0; pc < prog_ptr[nstream]; ++pc) {
+    const int32_t* w = prog + 4 * pc;
+    const int dst = w[1], a = w[2] & 0xFFFF, b = (w[2] >> 16) & 0xFFFF, c = w[3];
+    const bool index_a = w[0] == OP_LOAD_M || w[0] == OP_LOAD_Y;  // a addresses M or y
+    const bool index_d = w[0] == OP_STORE_X;                      // dst addresses x
+    if (w[0] < 0 || w[0] > OP_STORE_X || dst < 0 || (!index_d && dst >= nslot) || (index_d && dst >= nv) ||
+        (!index_a && a >= nslot) || (w[0] == OP_LOAD_M && a >= nM) || (w[0] == OP_LOAD_Y && a >= nv) || b >= nslot ||
+        c < 0 || c >= nslot)
+      return imn::set_error("imn_tree_ldl_compile: instruction %d is out of range", pc), IMN_ERR_SHAPE;
+  }
+  Nvrtc* rt = nvrtc();
+  if (!rt) return imn::set_error("imn_tree_ldl_compile: NVRTC (libnvrtc.so.12) could not be loaded"), IMN_ERR_UNSUPPORTED;
+  ImnTreeKernel* k = new ImnTreeKernel;
+  k->nv = nv, k->nM = nM, k->groups = groups;
+  k->source = generate(prog, prog_ptr, groups, owner, nslot, &k->nshared);
+  nvrtcProgram_t p = nullptr;
+  int rc = rt->create(&p, k->source.c_str(), "tree_ldl_generated.cu", 0, nullptr, nullptr);
+  if (rc) {
+    imn::set_error("imn_tree_ldl_compile: nvrtcCreateProgram: %s", rt->error_string(rc));
+    delete k;
+    return IMN_ERR_LAUNCH;
+  }
+  const char* opts[] = {"--gpu-architecture=sm_100a", "--fmad=false", "--std=c++17", "-lineinfo"};
+  rc = rt->compile(p, 4, opts);
+  if (rc) {
+    size_t n = 0;
+    rt->log_size(p, &n);
+    std::string log(n, '\0');
+    if (n) rt->log(p, &log[0]);
+    imn::set_error("imn_tree_ldl_compile: %s: %.380s", rt->error_string(rc), log.c_str());
+    rt->destroy(&p);
+    delete k;
+    return IMN_ERR_LAUNCH;
+  }
+  size_t n = 0;
+  rt->cubin_size(p, &n);
+  k->cubin.resize(n);
+  if (n) rt->cubin(p, k->cubin.data());
+  rt->destroy(&p);
+  if (!n) {
+    imn::set_error("imn_tree_ldl_compile: NVRTC produced no machine code");
+    delete k;
+    return IMN_ERR_LAUNCH;
+  }
+  *out = k;
+  return IMN_OK;
+}
+
+extern "C" int imn_tree_ldl_kernel_info(const ImnTreeKernel* k, int32_t* shared_slots, int64_t* code_bytes,
+                                        const char** source) {
+  if (!k) return imn::set_error("imn_tree_ldl_kernel_info: NULL kernel"), IMN_ERR_NULL;
+  if (shared_slots) *shared_slots = k->nshared;
+  if (code_bytes) *code_bytes = (int64_t)k->cubin.size();
+  if (source) *source = k->source.c_str();
+  return IMN_OK;
+}
+
+extern "C" void imn_tree_ldl_kernel_destroy(ImnTreeKernel* k) {
+  if (!k) return;
+  if (k->library) cudaLibraryUnload(k->library);
+  delete k;
+}
+
+extern "C" int imn_tree_ldl_compiled_solve(ImnTreeKernel* k, const float* M, int64_t M_ld, const float* y,
+                                           int64_t y_ld, float* x, int64_t x_ld, int32_t nworld, void* stream) {
+  if (!k || !M || !y || !x) return imn::set_error("imn_tree_ldl_compiled_solve: NULL argument"), IMN_ERR_NULL;
+  if (nworld < 0 || M_ld < k->nM || y_ld < k->nv || x_ld < k->nv)
+    return imn::set_error("imn_tree_ldl_compiled_solve: a stride is smaller than its extent"), IMN_ERR_SHAPE;
+  if (nworld == 0) return IMN_OK;
+  const size_t bytes = (size_t)(k->nshared > 0 ? k->nshared : 1) * 32 * sizeof(float);
+  if (bytes > 227 * 1024)
+    return imn::set_error("imn_tree_ldl_compiled_solve: %zu bytes of shared memory per block (max %d)", bytes,
+                          227 * 1024),
+           IMN_ERR_LIMIT;
+  if (!k->kernel) {
+    // first use: hand the machine code to the runtime (do this outside stream capture)
+    cudaError_t e = cudaLibraryLoadData(&k->library, k->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
+    if (e == cudaSuccess) e = cudaLibraryGetKernel(&k->kernel, k->library, "tree_ldl_generated");
+    if (e == cudaSuccess && bytes > 48 * 1024)
+      e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k->kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)bytes);
+    if (e != cudaSuccess) {
+      k->kernel = nullptr;
+      return imn::set_error("imn_tree_ldl_compiled_solve: loading the generated kernel: %s", cudaGetErrorString(e)),
+             IMN_ERR_LAUNCH;
+    }
+  }
+  long long mld = M_ld, yld = y_ld, xld = x_ld;
+  int nw = nworld;
+  void* args[] = {&M, &mld, &y, &yld, &x, &xld, &nw};
+  cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(k->kernel), dim3((nworld + 31) / 32),
+                                   dim3(32 * k->groups), args, bytes, (cudaStream_t)stream);
+  if (e != cudaSuccess)
+    return imn::set_error("imn_tree_ldl_compiled_solve: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  return IMN_OK;
+}

@@ -58,6 +58,40 @@ class TreeFactorSolveScratch:
     struct: abi.ImnTreePlan
     tables: tuple  # device tensors the struct points into (kept alive)
     nv: int
+    # generated straight-line kernel (None: the instruction list is interpreted)
+    kernel: "GeneratedKernel | None" = None
+
+
+class GeneratedKernel:
+    """Owner of an ``ImnTreeKernel``: the plan's instruction list turned into CUDA C
+    and compiled for sm_100a at run time, as the reference does through Warp
+    (tree_ldl.py:362-390)."""
+
+    def __init__(self, prog: np.ndarray, ptr: np.ndarray, nv: int, nM: int, groups: int, owner: int, nslot: int):
+        prog = np.ascontiguousarray(prog, dtype=np.int32)
+        ptr = np.ascontiguousarray(ptr, dtype=np.int32)
+        handle = C.c_void_p()
+        rc = _lib.lib().imn_tree_ldl_compile(
+            prog.ctypes.data, ptr.ctypes.data, nv, nM, groups, owner, nslot, C.byref(handle)
+        )
+        _lib.check(rc, "imn_tree_ldl_compile")
+        self.handle = handle
+
+    def info(self) -> dict:
+        slots, size, src = C.c_int32(), C.c_int64(), C.c_char_p()
+        _lib.check(
+            _lib.lib().imn_tree_ldl_kernel_info(self.handle, C.byref(slots), C.byref(size), C.byref(src)),
+            "imn_tree_ldl_kernel_info",
+        )
+        return {"shared_slots": slots.value, "code_bytes": size.value, "source": src.value.decode()}
+
+    def __del__(self):
+        handle, self.handle = getattr(self, "handle", None), None
+        if handle:
+            try:
+                _lib.lib().imn_tree_ldl_kernel_destroy(handle)
+            except Exception:  # interpreter shutdown
+                pass
 
 
 def tree_ldl_structure(rowadr, rownnz, colind):
@@ -284,8 +318,10 @@ class _Program:
         return prog, np.asarray(ptr, dtype=np.int32)
 
 
-def compile_plan(structure, plan: TreeLdlPlan, device: Any) -> TreeFactorSolveScratch:
-    """Upload a plan's instruction streams and build its C-ABI struct."""
+def compile_plan(structure, plan: TreeLdlPlan, device: Any, generate: bool = True) -> TreeFactorSolveScratch:
+    """Upload a plan's instruction streams, build its C-ABI struct and (``generate``)
+    compile the streams into a straight-line kernel.  Without a run-time compiler on
+    the machine the instruction list is interpreted instead; same results."""
     import torch
 
     rowadr, rownnz, colind = structure
@@ -300,13 +336,21 @@ def compile_plan(structure, plan: TreeLdlPlan, device: Any) -> TreeFactorSolveSc
     st.nslot = program.nslot
     st.prog, st.prog_ptr = addr(t_prog), addr(t_ptr)
     st.owner = program.owner
+    kernel = None
+    if generate:
+        try:
+            kernel = GeneratedKernel(prog, ptr, st.nv, st.nM, st.groups, st.owner, st.nslot)
+        except _lib.ImnError as e:
+            if "NVRTC" not in str(e):
+                raise
     return TreeFactorSolveScratch(
-        plan=plan, groups=len(plan.groups), cuda=True, struct=st, tables=(t_prog, t_ptr), nv=len(rowadr)
+        plan=plan, groups=len(plan.groups), cuda=True, struct=st, tables=(t_prog, t_ptr), nv=len(rowadr),
+        kernel=kernel,
     )
 
 
-def scratch_for_plan(structure, plan: TreeLdlPlan, device: Any) -> TreeFactorSolveScratch:
-    return compile_plan(structure, plan, device)
+def scratch_for_plan(structure, plan: TreeLdlPlan, device: Any, generate: bool = True) -> TreeFactorSolveScratch:
+    return compile_plan(structure, plan, device, generate)
 
 
 def _to_numpy(a):
@@ -317,7 +361,7 @@ def _to_numpy(a):
     return a.numpy()
 
 
-def create_tree_factor_solve_scratch(m: Any, device: Any = "cuda") -> TreeFactorSolveScratch | None:
+def create_tree_factor_solve_scratch(m: Any, device: Any = "cuda", generate: bool = True) -> TreeFactorSolveScratch | None:
     """The compiled factor+solve for this model, or ``None`` when ineligible
     (tree_ldl.py:403-416)."""
     if getattr(m, "nv", 0) <= 0:
@@ -331,7 +375,7 @@ def create_tree_factor_solve_scratch(m: Any, device: Any = "cuda") -> TreeFactor
     plan = best_tree_ldl_plan(*structure)
     if not tree_ldl_beats_dense(plan):
         return None
-    return compile_plan(structure, plan, device)
+    return compile_plan(structure, plan, device, generate)
 
 
 def tree_factor_solve(scratch: TreeFactorSolveScratch, M: Any, x: Any, y: Any, stream=None) -> None:
@@ -340,6 +384,13 @@ def tree_factor_solve(scratch: TreeFactorSolveScratch, M: Any, x: Any, y: Any, s
         if elem_strides(array)[1] != 1:
             raise ValueError("tree_factor_solve needs rows of contiguous floats")
     nworld = int(M.shape[0])
+    if scratch.kernel is not None:
+        rc = _lib.lib().imn_tree_ldl_compiled_solve(
+            scratch.kernel.handle, addr(M), elem_strides(M)[0], addr(y), elem_strides(y)[0], addr(x),
+            elem_strides(x)[0], nworld, _lib.current_stream_handle(stream),
+        )
+        _lib.check(rc, "imn_tree_ldl_compiled_solve")
+        return
     rc = _lib.lib().imn_tree_ldl_solve(
         C.byref(scratch.struct), addr(M), elem_strides(M)[0], addr(y), elem_strides(y)[0], addr(x),
         elem_strides(x)[0], nworld, _lib.current_stream_handle(stream),

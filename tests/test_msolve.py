@@ -166,20 +166,49 @@ def test_blocked_oracle_matches_numpy_and_reuses_its_factor(oracle, nv):
     np.testing.assert_array_equal(x, x2)
 
 
+def test_plan_compiles_to_a_straight_line_kernel_without_a_gpu():
+    """tree_ldl.py:362-390 builds its kernel from generated source at run time; so does
+    imn_tree_ldl_compile (no GPU needed to compile).  Values that one warp keeps to
+    itself become registers: only the trunk exchange is left in shared memory."""
+    m, _, _ = _model_and_matrices(synthetic.humanoid_tree, 1)
+    structure = _structure(m)
+    plan = tree_ldl.plan_tree_ldl(*structure, 4)
+    program = tree_ldl._Program(*structure, plan)
+    prog, ptr = program.encode()
+    kernel = tree_ldl.GeneratedKernel(prog, ptr, m.nv, m.nM, len(plan.groups), program.owner, program.nslot)
+    info = kernel.info()
+    assert info["code_bytes"] > 0
+    assert 0 < info["shared_slots"] < program.nslot // 2
+    src = info["source"]
+    assert src.count("fmaf(") == int(((prog[:, 0] == tree_ldl.OP_UPD) | (prog[:, 0] == tree_ldl.OP_SUBMUL)).sum())
+    assert src.count("bar.sync") == 2 * len(plan.groups)
+    # malformed programs are rejected before any compilation
+    from instantmimic_b200 import _lib
+
+    bad = prog.copy()
+    bad[0, 1] = program.nslot  # destination slot out of range
+    with pytest.raises(_lib.ImnError, match="out of range"):
+        tree_ldl.GeneratedKernel(bad, ptr, m.nv, m.nM, len(plan.groups), program.owner, program.nslot)
+
+
 # ---------------------------------------------------------------------------- GPU
 
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("tree", ["branched", "limbs", "humanoid"])
 @pytest.mark.parametrize("groups", [1, 2, 4])
-def test_tree_kernel_matches_oracle_bitwise(oracle, cuda_device, tree, groups):
+@pytest.mark.parametrize("generate", [True, False])
+def test_tree_kernel_matches_oracle_bitwise(oracle, cuda_device, tree, groups, generate):
+    """Both forms of the plan -- the straight-line kernel generated and compiled at run
+    time, and the interpreted instruction list -- against the oracle, bit for bit."""
     import torch
 
     worlds = 37  # not a multiple of the 32 worlds a block serves
     m, Mv, Md = _model_and_matrices(TREES[tree], worlds)
     structure = _structure(m)
     plan = tree_ldl.plan_tree_ldl(*structure, groups)
-    scratch = tree_ldl.scratch_for_plan(structure, plan, cuda_device)
+    scratch = tree_ldl.scratch_for_plan(structure, plan, cuda_device, generate)
+    assert (scratch.kernel is not None) == generate
     y = np.random.default_rng(1).normal(size=(worlds, m.nv)).astype(np.float32)
     x = torch.zeros((worlds, m.nv), dtype=torch.float32, device=cuda_device)
     tree_ldl.tree_factor_solve(scratch, torch.from_numpy(Mv).to(cuda_device), x, torch.from_numpy(y).to(cuda_device))
@@ -214,13 +243,15 @@ def test_model_scratch_selects_tree_solve_and_solves_qacc_smooth(oracle, cuda_de
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("nv", [32, 35, 48, 56, 70])
-def test_blocked_kernel_matches_oracle_bitwise(oracle, cuda_device, nv):
+@pytest.mark.parametrize("nv,rhs", [(32, 3), (35, 1), (35, 3), (48, 2), (56, 3), (70, 1), (70, 30), (79, 5)])
+def test_blocked_kernel_matches_oracle_bitwise(oracle, cuda_device, nv, rhs):
+    """rhs 30 at nv 70 exceeds the columns that ride through the factorisation, so
+    part of them takes the substitution with the stored factor."""
     import torch
 
     from instantmimic_b200 import mjw_model
 
-    worlds, rhs = 9, 3
+    worlds = 9
     m, Mv, Md, pad, layout, ident, y = _blocked_case(nv, worlds, rhs)
     md = mjw_model.to_device(m, cuda_device)
     dd = mjw_model.to_device(mjw_model.make_data(m, worlds, 4), cuda_device)
