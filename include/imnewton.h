@@ -151,6 +151,20 @@ typedef struct ImnSparsePlan {
   const uint16_t* s_b;      /* SH_SB  [nfac]                                   */
   const int32_t* s_m;       /* SH_SM  [nfac]                                   */
   const uint32_t* gat;      /* SH_GAT [nfac] (non-fused path)                  */
+  /* The level tables once more, laid out for the fused kernel: one record per
+   * (sweep, lane), so that a lane fetches all it needs for a sweep with one load
+   * and can fetch the next sweep's record ahead of time.  A sweep is 32 / team
+   * entries of one level.
+   *   fsweep [nfsweep][32][4]: {slot | (col+1) << 16, run_ab, run_kl of the entry's
+   *     first run, flags}; flags bit 0 = the lane has an entry, bit 1 = last sweep
+   *     of its level, bits 2-4 = log2(team), bits 8-15 = further runs of the entry,
+   *     bits 16-31 = index of the first of those in run_ab / run_kl.
+   *   bsweep [nbsweep][32]: slot | src << 16 | dst << 23 | has-work << 30 |
+   *     last-of-level << 31 (backward solve).
+   * NULL / 0 when the plan is only used by the non-fused kernel. */
+  const uint32_t* fsweep;
+  const uint32_t* bsweep;
+  int32_t nfsweep, nbsweep;
 } ImnSparsePlan;
 
 /* Solver context: the arrays mujoco_warp's `_create_solver_context` allocates

@@ -108,6 +108,8 @@ SPARSE_TABLES = (
     ("s_b", "uint16"),
     ("s_m", "int32"),
     ("gat", "uint32"),
+    ("fsweep", "uint32"),
+    ("bsweep", "uint32"),
 )
 
 
@@ -122,7 +124,7 @@ class ImnSparsePlan(C.Structure):
         ("nentries", I32),
         ("nruns", I32),
         ("nback", I32),
-    ] + [(name, P) for name, _ in SPARSE_TABLES]
+    ] + [(name, P) for name, _ in SPARSE_TABLES] + [("nfsweep", I32), ("nbsweep", I32)]
 
 
 class ImnCtx(C.Structure):

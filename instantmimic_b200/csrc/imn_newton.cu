@@ -295,11 +295,15 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
             for (int q = lane; q < sp.nfac; q += 32) s.N[q] = s.Hp[q];
           }
           sp_load_rhs(sp, s.N, s.grad, lane);
-          sp_factor_levels(sp, s.N, s.iD, lane);
+          IMN_MARK(s, 1);
+          sp_factor_sweeps(sp, s.N, s.iD, lane);
+          IMN_MARK(s, 2);
         } else {
           sp_forward(sp, s.N, s.iD, s.grad, lane);
+          IMN_MARK(s, 3);
         }
-        sp_backward(sp, s.N, s.iD, s.grad, s.search, s.bd, lane, search_dot, decrement);
+        sp_backward_sweeps(sp, s.N, s.iD, s.grad, s.search, s.bd, lane, search_dot, decrement);
+        IMN_MARK(s, 4);
       } else {
         factor_solve(s, first || quad_count > 0, search_dot, decrement);
       }
@@ -433,7 +437,7 @@ static int validate(const ImnModel* m, const ImnData* d, const ImnCtx* cx) {
     if (!sp->lvl_ptr || !sp->lvl_team || !sp->ent_slot || !sp->ent_col || !sp->run_ptr || !sp->run_ab ||
         !sp->run_kl || !sp->orig || !sp->b_lvl || !sp->b_slot || !sp->b_src || !sp->b_dst || !sp->pair ||
         !sp->f_lvl || !sp->f_row || !sp->row_start || !sp->rk_ptr || !sp->rk || !sp->pmask || !sp->s_a ||
-        !sp->s_b || !sp->s_m)
+        !sp->s_b || !sp->s_m || !sp->fsweep || !sp->bsweep || sp->nfsweep <= 0 || sp->nbsweep < 0)
       return set_error("imn_solve: a sparse plan table is NULL"), IMN_ERR_NULL;
   }
   return IMN_OK;

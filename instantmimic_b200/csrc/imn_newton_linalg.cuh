@@ -221,6 +221,8 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
 #pragma unroll 1
   for (int e = lane; e < npu; e += 32) {
     const int row = s.uni[pi], col = s.uni[pj];
+    // looked up ahead of the sum so that the table's latency is hidden behind it
+    const int sl = SPARSE ? __ldg(SP.pair + row * nv + col) : 0;
     float delta = 0.0f;
 #pragma unroll 2
     for (int t = 0; t < count; ++t) {
@@ -232,7 +234,6 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
     }
     if (delta != 0.0f) {
       if (SPARSE) {
-        const int sl = __ldg(SP.pair + row * nv + col);
         if (sl >= 0)
           s.Hp[sl] = s.Hp[sl] + delta;
         else
@@ -250,12 +251,20 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
 // Sparse plan: H = M + J^T diag(D, QUADRATIC rows) J on the pattern slots, each slot
 // summing its rows in ascending order; every active row's dof support must lie in
 // the pattern (sparse_hessian.py:571-637).  Leaves the packed H in both N and Hp.
+// A lane keeps the running sums of ten slots in registers and walks the QUADRATIC
+// rows once per ten slots: the row's D is read once, and ten independent sums overlap
+// their latencies.  The row list is compacted into s.ids first (unused during the
+// initial pass).
 __device__ __forceinline__ void assemble_hessian_sparse(const World& s, int nfr, const ImnSparsePlan& SP) {
   const int lane = s.lane, nv = s.nv, nfac = SP.nfac, words = (nv + 31) >> 5;
+  int nq = 0;
 #pragma unroll 1
   for (int a = 0; a < nfr; ++a) {
     const int r = s.frows[a];
-    if (s.state[r] != IMN_STATE_QUADRATIC || s.Dsm[r] == 0.0f) continue;
+    if (s.state[r] != IMN_STATE_QUADRATIC) continue;
+    if (lane == 0) s.ids[nq] = r;
+    ++nq;
+    if (s.Dsm[r] == 0.0f) continue;
     const float* Jr = s.Jsm + r * s.ldj;
     unsigned rm[3] = {0u, 0u, 0u};
 #pragma unroll
@@ -276,20 +285,35 @@ __device__ __forceinline__ void assemble_hessian_sparse(const World& s, int nfr,
     }
     if (__any_sync(IMN_FULL_MASK, bad) && lane == 0) sp_violation(s.viol, s.world, "has a constraint row");
   }
+  __syncwarp();
+  constexpr int Q = 10;
 #pragma unroll 1
-  for (int sl = lane; sl < nfac; sl += 32) {
-    const int e = __ldg(SP.s_m + sl);
-    const int a = __ldg(SP.s_a + sl), b = __ldg(SP.s_b + sl);
-    float v = e >= 0 ? s.Msm[e] : 0.0f;
-#pragma unroll 2
-    for (int k = 0; k < nfr; ++k) {
-      const int r = s.frows[k];
-      if (s.state[r] != IMN_STATE_QUADRATIC) continue;
-      const float* Jr = s.Jsm + r * s.ldj;
-      v = fmaf(Jr[a] * s.Dsm[r], Jr[b], v);
+  for (int base = 0; base < nfac; base += 32 * Q) {
+    float acc[Q];
+    int ab[Q];
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      const int sl = base + 32 * q + lane;
+      acc[q] = 0.0f, ab[q] = 0;
+      if (sl < nfac) {
+        const int e = __ldg(SP.s_m + sl);
+        ab[q] = (int)__ldg(SP.s_a + sl) | ((int)__ldg(SP.s_b + sl) << 16);
+        acc[q] = e >= 0 ? s.Msm[e] : 0.0f;
+      }
     }
-    s.N[sl] = v;
-    s.Hp[sl] = v;
+#pragma unroll 1
+    for (int k = 0; k < nq; ++k) {
+      const int r = s.ids[k];
+      const float Dr = s.Dsm[r];
+      const float* Jr = s.Jsm + r * s.ldj;
+#pragma unroll
+      for (int q = 0; q < Q; ++q) acc[q] = fmaf(Jr[ab[q] & 0xFFFF] * Dr, Jr[ab[q] >> 16], acc[q]);
+    }
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      const int sl = base + 32 * q + lane;
+      if (sl < nfac) s.N[sl] = acc[q], s.Hp[sl] = acc[q];
+    }
   }
   __syncwarp();
 }

@@ -62,6 +62,65 @@ __device__ __forceinline__ void sp_factor_levels(const ImnSparsePlan& P, float* 
   }
 }
 
+// The same factorisation driven by the per-(sweep, lane) records (ImnSparsePlan::
+// fsweep): one 128-bit load gives a lane its entry, the entry's first run and the
+// sweep's team width, and the next sweep's record is fetched while the current one is
+// worked on, so no table load sits on the dependent path.  Terms are taken four at a
+// time (loads first, then the fused multiply-adds in order): the order in which an
+// entry receives its terms is unchanged.
+__device__ __forceinline__ float sp_run_terms(const float* N, const float* iD, uint32_t ab, uint32_t kl, int tl,
+                                              int T, float v) {
+  const float* pa = N + (ab & 0xFFFFu);
+  const float* pb = N + (ab >> 16);
+  const float* pd = iD + (kl & 0xFFFFu);
+  const int len = (int)(kl >> 16);
+  int t = tl;
+#pragma unroll 1
+  for (; t + 3 * T < len; t += 4 * T) {
+    const float a0 = pa[t], b0 = pb[t], d0 = pd[t];
+    const float a1 = pa[t + T], b1 = pb[t + T], d1 = pd[t + T];
+    const float a2 = pa[t + 2 * T], b2 = pb[t + 2 * T], d2 = pd[t + 2 * T];
+    const float a3 = pa[t + 3 * T], b3 = pb[t + 3 * T], d3 = pd[t + 3 * T];
+    v = fmaf(a0 * b0, d0, v);
+    v = fmaf(a1 * b1, d1, v);
+    v = fmaf(a2 * b2, d2, v);
+    v = fmaf(a3 * b3, d3, v);
+  }
+#pragma unroll 1
+  for (; t < len; t += T) v = fmaf(pa[t] * pb[t], pd[t], v);
+  return v;
+}
+
+__device__ __forceinline__ void sp_factor_sweeps(const ImnSparsePlan& P, float* N, float* iD, int lane) {
+  const uint4* tab = reinterpret_cast<const uint4*>(P.fsweep) + lane;
+  const int ns = P.nfsweep;
+  uint4 cur = __ldg(tab);
+#pragma unroll 1
+  for (int s = 0; s < ns; ++s) {
+    const uint4 nxt = __ldg(tab + 32 * min(s + 1, ns - 1));
+    const uint32_t fl = cur.w;
+    const int T = 1 << ((fl >> 2) & 7), tl = lane & (T - 1);
+    const bool has = (fl & 1u) != 0u;
+    float v = 0.0f;
+    if (has) {
+      v = sp_run_terms(N, iD, cur.y, cur.z, tl, T, v);
+      const int extra = (fl >> 8) & 0xFF, r0 = fl >> 16;
+#pragma unroll 1
+      for (int r = r0; r < r0 + extra; ++r) v = sp_run_terms(N, iD, __ldg(P.run_ab + r), __ldg(P.run_kl + r), tl, T, v);
+    }
+#pragma unroll 1
+    for (int off = T >> 1; off > 0; off >>= 1) v = v + __shfl_down_sync(IMN_FULL_MASK, v, off, T);
+    if (has && tl == 0) {
+      const int sl = cur.x & 0xFFFF, col = (int)(cur.x >> 16) - 1;
+      const float w = N[sl] - v;
+      N[sl] = w;
+      if (col >= 0) iD[col] = 1.0f / w;
+    }
+    if (fl & 2u) __syncwarp();
+    cur = nxt;
+  }
+}
+
 // Forward solve with a stored factor (rows by level).
 __device__ __forceinline__ void sp_forward(const ImnSparsePlan& P, float* N, const float* iD,
                                            const float* grad, int lane) {
@@ -102,6 +161,42 @@ __device__ __forceinline__ void sp_backward(const ImnSparsePlan& P, float* N, co
       N[rhs + j] = fmaf(-N[__ldg(P.b_slot + p)], N[rhs + i] * iD[i], N[rhs + j]);
     }
     __syncwarp();
+  }
+  float ra = 0.0f, rb = 0.0f;
+#pragma unroll 1
+  for (int w = 0; w < bd / 32; ++w) {
+    float s0 = 0.0f, s1 = 0.0f;
+#pragma unroll 1
+    for (int j = lane + 32 * w; j < n; j += bd) {
+      const int d = __ldg(P.orig + j);
+      const float v = N[rhs + j] * iD[j];
+      search[d] = -v;
+      s0 = fmaf(v, v, s0);
+      s1 = fmaf(grad[d], v, s1);
+    }
+    ra = ra + warp_tree_sum(s0);
+    rb = rb + warp_tree_sum(s1);
+  }
+  sum0 = ra, sum1 = rb;
+  __syncwarp();
+}
+
+// sp_backward driven by the per-(sweep, lane) records (ImnSparsePlan::bsweep).
+__device__ __forceinline__ void sp_backward_sweeps(const ImnSparsePlan& P, float* N, const float* iD,
+                                                   const float* grad, float* search, int bd, int lane,
+                                                   float& sum0, float& sum1) {
+  const int rhs = P.nfac, n = P.nv, ns = P.nbsweep;
+  const uint32_t* tab = P.bsweep + lane;
+  uint32_t cur = ns ? __ldg(tab) : 0u;
+#pragma unroll 1
+  for (int s = 0; s < ns; ++s) {
+    const uint32_t nxt = __ldg(tab + 32 * min(s + 1, ns - 1));
+    if (cur & (1u << 30)) {
+      const int i = (cur >> 16) & 0x7F, j = (cur >> 23) & 0x7F;
+      N[rhs + j] = fmaf(-N[cur & 0xFFFFu], N[rhs + i] * iD[i], N[rhs + j]);
+    }
+    if (cur >> 31) __syncwarp();
+    cur = nxt;
   }
   float ra = 0.0f, rb = 0.0f;
 #pragma unroll 1

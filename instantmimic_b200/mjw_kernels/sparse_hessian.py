@@ -272,14 +272,63 @@ def build_plan(m: Any, body_groups: Sequence[Sequence[int]], block: int, path: s
         pair=pair, f_lvl=f_lvl, f_row=f_row, row_start=row_start, rk_ptr=rk_ptr, rk=rk or [0],
         pmask=pmask, s_a=s_a, s_b=s_b, s_m=s_m, gat=gat,
     )
+    raw["fsweep"], raw["bsweep"] = _pack_sweeps(raw) if path == "fused" else ([], [])
     tables = {}
     for name, dtype in abi.SPARSE_TABLES:
         vals = raw[name] if len(raw[name]) else [0]
         tables[name] = np.asarray(vals, dtype=np.int64).astype(dtype)
+    if path != "fused":
+        tables["fsweep"], tables["bsweep"] = tables["fsweep"][:0], tables["bsweep"][:0]
     return SparseHessianPlan(
         nv=nv, nv_pad=nv_pad, block=block, nslots=nslots, nterms=nterms, levels=len(levels),
         density=nfac / (nv * (nv + 1) / 2), path=path, nfac=nfac, tables=tables, adjacency=adj,
     )
+
+
+def _pack_sweeps(raw: dict) -> tuple[list[int], list[int]]:
+    """The level tables as one record per (sweep, lane) for the fused kernel (layout in
+    include/imnewton.h).  A sweep is the 32 / team entries of a level that the warp
+    works on at once; lanes of a team carry the same record."""
+    lvl_ptr, lvl_team = raw["lvl_ptr"], raw["lvl_team"]
+    run_ptr, run_ab, run_kl = raw["run_ptr"], raw["run_ab"], raw["run_kl"]
+    fs: list[int] = []
+    for lvl, team in enumerate(lvl_team):
+        e0, e1, per = lvl_ptr[lvl], lvl_ptr[lvl + 1], 32 // team
+        starts = list(range(e0, e1, per))
+        for eb in starts:
+            base = (2 if eb == starts[-1] else 0) | ((team.bit_length() - 1) << 2)
+            for lane in range(32):
+                e = eb + lane // team
+                if e >= e1:
+                    fs += [0, 0, 0, base]
+                    continue
+                r0, r1 = run_ptr[e], run_ptr[e + 1]
+                extra = max(r1 - r0 - 1, 0)
+                if extra > 255 or r0 + 1 > 0xFFFF or raw["ent_col"][e] + 1 > 0xFFFF:
+                    raise ValueError("sparse plan exceeds the packed sweep record")
+                fs += [
+                    raw["ent_slot"][e] | ((raw["ent_col"][e] + 1) << 16),
+                    run_ab[r0] if r1 > r0 else 0,
+                    run_kl[r0] if r1 > r0 else 0,
+                    base | 1 | (extra << 8) | ((r0 + 1) << 16),
+                ]
+    bs: list[int] = []
+    b_lvl = raw["b_lvl"]
+    for lvl in range(len(b_lvl) - 1):
+        p0, p1 = b_lvl[lvl], b_lvl[lvl + 1]
+        starts = list(range(p0, p1, 32))
+        for pb in starts:
+            last = (1 << 31) if pb == starts[-1] else 0
+            for lane in range(32):
+                p = pb + lane
+                if p >= p1:
+                    bs.append(last)
+                    continue
+                src, dst = raw["b_src"][p], raw["b_dst"][p]
+                if src > 127 or dst > 127:
+                    raise ValueError("sparse plan exceeds the packed sweep record")
+                bs.append(raw["b_slot"][p] | (src << 16) | (dst << 23) | (1 << 30) | last)
+    return fs, bs
 
 
 def plan_struct(plan: SparseHessianPlan, arrays: dict) -> abi.ImnSparsePlan:
@@ -292,6 +341,10 @@ def plan_struct(plan: SparseHessianPlan, arrays: dict) -> abi.ImnSparsePlan:
     st.nback = int(plan.tables["b_slot"].shape[0])
     for name, _ in abi.SPARSE_TABLES:
         setattr(st, name, addr(arrays[name]))
+    st.nfsweep = int(plan.tables["fsweep"].shape[0]) // 128
+    st.nbsweep = int(plan.tables["bsweep"].shape[0]) // 32
+    if not st.nfsweep:
+        st.fsweep = st.bsweep = None
     return st
 
 
