@@ -72,10 +72,11 @@ static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident, const 
   g.oJ = o, o += up4(g.jrows * g.ldj);
   // dense: H and its factor share one (nv+1) x ldu array; sparse plan: packed H | N | 1/D
   g.oA = o, o += sp ? up4(sp->nfac) + up4(sp->nslots) + up4(m.nv) : (m.nv + 1) * g.ldu;
-  g.oVec = o, o += 8 * g.nv4;
+  // dof vectors; the dense factor needs two more (forward-solve scratch, 1 / pivot)
+  g.oVec = o, o += (sp ? 6 : 8) * g.nv4;
   g.oM = o, o += up4(m.nM);
   g.oRowF = o, o += 5 * g.r4;
-  g.oRowI = o, o += 3 * g.r4;
+  g.oRowI = o, o += up4(3 * g.r4 / 2);  // three 16-bit row lists
   g.oUni = o, o += up4(m.nv + 1);
   g.total = o;
   return g;
@@ -100,15 +101,15 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   s.mv = s.search + nv4;
   s.grad = s.mv + nv4;
   s.qfs = s.grad + nv4;
-  s.xsm = s.qfs + nv4;
-  s.dinv = s.xsm + nv4;
+  s.xsm = SPARSE ? nullptr : s.qfs + nv4;
+  s.dinv = SPARSE ? nullptr : s.xsm + nv4;
   s.Msm = smem + g.oM;
   s.Jaref = smem + g.oRowF;
   s.jv = s.Jaref + r4;
   s.Dsm = s.jv + r4;
   s.floss = s.Dsm + r4;
   s.force = s.floss + r4;
-  s.state = reinterpret_cast<int*>(smem + g.oRowI);
+  s.state = reinterpret_cast<uint16_t*>(smem + g.oRowI);
   s.ids = s.state + r4;
   s.frows = s.ids + r4;  // rows with a nonzero force, ascending
   s.uni = reinterpret_cast<int*>(smem + g.oUni);
@@ -406,6 +407,7 @@ static const int kResidentBudget = kMaxSmem / 4;
 static int validate(const ImnModel* m, const ImnData* d, const ImnCtx* cx) {
   if (!m || !d || !cx) return set_error("imn_solve: NULL struct"), IMN_ERR_NULL;
   if (d->nworld < 0 || d->njmax < 0) return set_error("imn_solve: negative extent"), IMN_ERR_SHAPE;
+  if (d->njmax >= (1 << 16)) return set_error("imn_solve: njmax %d exceeds 16-bit row indices", d->njmax), IMN_ERR_LIMIT;
   if (m->nv <= 0 || m->nv > 79 || m->nv_pad % 16 != 0 || m->nv_pad > 80 || m->nv_pad <= m->nv)
     return set_error("imn_solve: nv %d / nv_pad %d outside the fused path (0 < nv <= 79, nv_pad %% 16 == 0, nv < nv_pad <= 80)",
                      m->nv, m->nv_pad),

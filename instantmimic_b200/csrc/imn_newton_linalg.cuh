@@ -16,7 +16,10 @@ struct World {
   int nv, ldj, ldu, bd, nefc, ne, nef, lane, nM;
   float *Jsm, *A, *qacc, *Ma, *search, *mv, *grad, *qfs, *xsm, *dinv, *Msm;
   float *Jaref, *jv, *Dsm, *floss, *force;
-  int *state, *ids, *frows, *uni;
+  // row states and the two row lists are 16-bit (njmax < 65536): shared memory per
+  // world decides how many worlds an SM holds
+  uint16_t *state, *ids, *frows;
+  int* uni;
   const float* Jg;  // this world's J in global memory
   const int* mulm_rowadr;
   const uint32_t* mulm_pack;
@@ -216,33 +219,47 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
   __syncwarp();
   IMN_MARK(s, 12);
   const int npu = n * (n + 1) / 2;
+  // four pairs per lane at a time: the listed rows are walked once per four pairs and
+  // the four sums overlap their latencies; each sum still takes its rows in list order
+  constexpr int Q = 4;
   int pi = lane, pj = 0;
   pair_advance(pi, pj, 0);
 #pragma unroll 1
-  for (int e = lane; e < npu; e += 32) {
-    const int row = s.uni[pi], col = s.uni[pj];
-    // looked up ahead of the sum so that the table's latency is hidden behind it
-    const int sl = SPARSE ? __ldg(SP.pair + row * nv + col) : 0;
-    float delta = 0.0f;
-#pragma unroll 2
+  for (int base = 0; base < npu; base += 32 * Q) {
+    int row[Q], col[Q], sl[Q];
+    float delta[Q];
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      const bool in = base + 32 * q + lane < npu;
+      row[q] = in ? s.uni[pi] : 0, col[q] = in ? s.uni[pj] : 0;
+      // looked up ahead of the sum so that the table's latency is hidden behind it
+      sl[q] = in ? (SPARSE ? __ldg(SP.pair + row[q] * nv + col[q]) : 0) : -2;
+      delta[q] = 0.0f;
+      pair_advance(pi, pj, 32);
+    }
+#pragma unroll 1
     for (int t = 0; t < count; ++t) {
       const int r = s.ids[t];
-      const float a = j_at<JRES>(s, r, row), b = j_at<JRES>(s, r, col);
-      float da = s.Dsm[r] * a;
-      if (s.state[r] != IMN_STATE_QUADRATIC) da = -da;
-      if (a != 0.0f && b != 0.0f) delta = fmaf(da, b, delta);
-    }
-    if (delta != 0.0f) {
-      if (SPARSE) {
-        if (sl >= 0)
-          s.Hp[sl] = s.Hp[sl] + delta;
-        else
-          sp_violation(s.viol, s.world, "updates an H entry");
-      } else {
-        s.A[(col + 1) * ldu + row] = s.A[(col + 1) * ldu + row] + delta;
+      const float Dr = s.state[r] == IMN_STATE_QUADRATIC ? s.Dsm[r] : -s.Dsm[r];
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        const float a = j_at<JRES>(s, r, row[q]), b = j_at<JRES>(s, r, col[q]);
+        if (a != 0.0f && b != 0.0f) delta[q] = fmaf(Dr * a, b, delta[q]);
       }
     }
-    pair_advance(pi, pj, 32);
+#pragma unroll
+    for (int q = 0; q < Q; ++q) {
+      if (sl[q] != -2 && delta[q] != 0.0f) {
+        if (SPARSE) {
+          if (sl[q] >= 0)
+            s.Hp[sl[q]] = s.Hp[sl[q]] + delta[q];
+          else
+            sp_violation(s.viol, s.world, "updates an H entry");
+        } else {
+          s.A[(col[q] + 1) * ldu + row[q]] = s.A[(col[q] + 1) * ldu + row[q]] + delta[q];
+        }
+      }
+    }
   }
   __syncwarp();
   IMN_MARK(s, 13);
