@@ -514,7 +514,11 @@ extern "C" int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* cx, 
   bool res;
   rc = imn::plan_launch(m, d, cx->sparse_plan, &g, &res);
   if (rc) return rc;
+#ifdef IMN_PAD_SMEM  // experiment: fewer resident worlds per SM
+  const int bytes = g.total * 4 + IMN_PAD_SMEM;
+#else
   const int bytes = g.total * 4;
+#endif
   auto kern = cx->sparse_plan ? imn::newton_kernel<true, true>
                               : (res ? imn::newton_kernel<true, false> : imn::newton_kernel<false, false>);
   const ImnSparsePlan sp = cx->sparse_plan ? *cx->sparse_plan : ImnSparsePlan{};
