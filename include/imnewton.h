@@ -200,6 +200,11 @@ typedef struct ImnCtx {
   int32_t* dof_union;          /* (W, nv + 1) */
   int32_t* nsolving;           /* (1): nworld minus the worlds that finished */
   const ImnSparsePlan* sparse_plan; /* HOST pointer or NULL (dense factor)    */
+  int32_t* world_order; /* optional scratch (W): when given, imn_solve fills it with
+                         * the worlds ordered by descending row count and hands the
+                         * worlds to the GPU in that order (long solves first, which
+                         * shortens the tail of the launch); results do not depend
+                         * on it                                                  */
 } ImnCtx;
 
 /* Tree-structured L'DL plan (tree_ldl.py:47-57, 105-170) as an instruction

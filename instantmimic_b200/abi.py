@@ -152,6 +152,7 @@ class ImnCtx(C.Structure):
         ("dof_union", P),
         ("nsolving", P),
         ("sparse_plan", C.POINTER(ImnSparsePlan)),
+        ("world_order", P),
     ]
 
 

@@ -182,4 +182,8 @@ def ctx_struct(d_struct: abi.ImnData, ctx: Any, nsolving: Any, sparse_plan_struc
     s.nsolving = addr(nsolving)
     if sparse_plan_struct is not None:
         s.sparse_plan = C.pointer(sparse_plan_struct)
+    order = get("world_order")
+    if order is not None and length(order) < d_struct.nworld:
+        raise ValueError("ctx.world_order must hold one int32 per world")
+    s.world_order = addr(order)
     return s

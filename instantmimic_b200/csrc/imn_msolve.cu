@@ -125,7 +125,11 @@ __device__ __forceinline__ void dense_factor_carry(float* A, float* dinv, const 
         if (act[k]) {
           const float uc = Ut[cc[k]];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) acc[k][i] = fmaf(-ur[i], uc, acc[k][i]);
+          for (int gi = 0; gi < 4; ++gi)
+            if (gi < ng) {  // warp-uniform: a short last block skips its absent rows
+#pragma unroll
+              for (int i = 4 * gi; i < 4 * gi + 4; ++i) acc[k][i] = fmaf(-ur[i], uc, acc[k][i]);
+            }
         }
     }
     // the block's own rows, one by one; acc[k][0] is always the current row
@@ -200,13 +204,15 @@ __global__ void __launch_bounds__(32 * kWorldsPerCta)
     __syncwarp();
     dense_factor_carry(A, dinv, n, nc, ldu, lane);
     // the factor, padded: zeros below the diagonal, the padded diagonal's own root
-    for (int r = 0; r < pad; ++r) {
-      for (int c = lane; c < pad; c += 32) {
-        float v = 0.0f;
-        if (r < n && c >= r && c < n) v = A[r * ldu + c];
-        if (r >= n && c == r) v = sqrtf(identity[((r & 15) << 4) | (r & 15)]);
-        Uw[r * pad + c] = v;
-      }
+    for (int r = 0; r < n; ++r) {
+      const float* Ar = A + r * ldu;
+      float* Ur = Uw + r * pad;
+#pragma unroll 3
+      for (int c = lane; c < pad; c += 32) Ur[c] = (c >= r && c < n) ? Ar[c] : 0.0f;
+    }
+    for (int r = n; r < pad; ++r) {
+      const float dg = sqrtf(identity[((r & 15) << 4) | (r & 15)]);
+      for (int c = lane; c < pad; c += 32) Uw[r * pad + c] = c == r ? dg : 0.0f;
     }
     for (int e = lane; e < n * carry; e += 32) {
       const int r = e / carry, q = e - r * carry;

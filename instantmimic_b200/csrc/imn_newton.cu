@@ -87,7 +87,7 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
                                                     const Geom g, const ImnSparsePlan sp) {
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x;
-  const int w = blockIdx.x;
+  const int w = cx.world_order ? cx.world_order[blockIdx.x] : (int)blockIdx.x;
   const int nv = g.nv, R = g.njmax, nv4 = g.nv4, r4 = g.r4;
 
   void* bar = smem + g.oBar;
@@ -399,6 +399,35 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
 
 __global__ void fill_nsolving(int* nsolving, int value) { *nsolving = value; }
 
+// The hardware hands CTAs to SMs in index order and a world's solve time grows with
+// its row count, so worlds are launched by descending row count: the long solves
+// start first and the launch ends with short ones instead of a few stragglers.  One
+// CTA sorts the worlds into 64 classes of row count (counting sort through shared
+// memory); the order inside a class depends on atomics and is irrelevant: every
+// world is solved independently of which CTA takes it.
+#define IMN_ORDER_CLASSES 64
+__global__ void __launch_bounds__(1024) order_worlds_kernel(const int* __restrict__ nefc, int njmax, int nworld,
+                                                            int* __restrict__ order, int* nsolving) {
+  __shared__ int count[IMN_ORDER_CLASSES], start[IMN_ORDER_CLASSES];
+  const int tid = threadIdx.x;
+  if (tid < IMN_ORDER_CLASSES) count[tid] = 0;
+  if (tid == 0 && nsolving) *nsolving = nworld;
+  __syncthreads();
+  // class 0 holds the largest row counts
+  auto cls = [&](int n) {
+    n = min(max(n, 0), njmax);
+    return (int)(((long long)(njmax - n) * IMN_ORDER_CLASSES) / (njmax + 1));
+  };
+  for (int w = tid; w < nworld; w += blockDim.x) atomicAdd(&count[cls(nefc[w])], 1);
+  __syncthreads();
+  if (tid == 0) {
+    int run = 0;
+    for (int c = 0; c < IMN_ORDER_CLASSES; ++c) start[c] = run, run += count[c];
+  }
+  __syncthreads();
+  for (int w = tid; w < nworld; w += blockDim.x) order[atomicAdd(&start[cls(nefc[w])], 1)] = w;
+}
+
 // Largest dynamic shared memory one CTA may opt into on sm_100 (227 KB).
 static const int kMaxSmem = 227 * 1024;
 // Resident-J budget per world: keep at least 4 worlds per SM.
@@ -532,7 +561,10 @@ extern "C" int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* cx, 
     if (e != cudaSuccess)
       return imn::set_error("imn_solve: cudaFuncSetAttribute: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
   }
-  if (cx->nsolving) imn::fill_nsolving<<<1, 1, 0, stream>>>(cx->nsolving, d->nworld);
+  if (cx->world_order)
+    imn::order_worlds_kernel<<<1, 1024, 0, stream>>>(d->nefc, d->njmax, d->nworld, cx->world_order, cx->nsolving);
+  else if (cx->nsolving)
+    imn::fill_nsolving<<<1, 1, 0, stream>>>(cx->nsolving, d->nworld);
   kern<<<d->nworld, 32, bytes, stream>>>(*m, *d, *cx, g, sp);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return imn::set_error("imn_solve: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;

@@ -40,6 +40,8 @@ class SolverContext:
         self.quad_changed_ids = i(W, R)
         self.quad_changed_count, self.state_changed_count = i(W), i(W)
         self.sparse_hessian_plan = None
+        # scratch of the fused kernel: worlds ordered by row count (no counterpart upstream)
+        self.world_order = i(W)
 
 
 @dataclass

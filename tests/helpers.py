@@ -35,8 +35,10 @@ def run_oracle(oracle, m, d, matrices=True, threads=0):
     return d2, ctx, nsolving
 
 
-def run_cuda(m, d, device, matrices=True, use_optimized_kernel=True):
-    """Solve a copy of host data on the GPU through solve_with_scratch; results on host."""
+def run_cuda(m, d, device, matrices=True, use_optimized_kernel=True, ordered=True):
+    """Solve a copy of host data on the GPU through solve_with_scratch; results on host.
+    ``ordered=False`` withholds the context's world-order scratch, so worlds are handed
+    to the GPU in index order instead of by descending row count."""
     import torch
 
     from instantmimic_b200 import mjw_step_optimized as runtime
@@ -44,6 +46,8 @@ def run_cuda(m, d, device, matrices=True, use_optimized_kernel=True):
     md = mjw_model.to_device(m, device)
     dd = mjw_model.to_device(copy.deepcopy(d), device)
     scratch = runtime.make_optimized_fwd_position_scratch(md, dd, device, with_matrices=matrices)
+    if not ordered and scratch.solver_context is not None:
+        scratch.solver_context.world_order = None
     runtime.solve_with_scratch(md, dd, scratch, use_optimized_kernel=use_optimized_kernel)
     torch.cuda.synchronize()
     ctx = scratch.solver_context

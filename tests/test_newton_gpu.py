@@ -117,6 +117,29 @@ def test_rowless_worlds_finish_at_the_smooth_acceleration(oracle, cuda_device):
     _check(got, want)
 
 
+def test_world_order_changes_nothing_but_the_schedule(oracle, cuda_device):
+    """With the context's world_order scratch the kernel takes worlds by descending row
+    count; the scratch then holds a permutation sorted that way, and every result
+    equals the index-order launch bit for bit."""
+    m, d, _ = synthetic.make_workload("humanoid", 700, seed=9, rowless_fraction=0.1)
+    a, actx, an, _ = run_cuda(m, d, cuda_device)
+    b, bctx, bn, _ = run_cuda(m, d, cuda_device, ordered=False)
+    order = actx.world_order
+    assert bctx.world_order is None
+    assert sorted(order.tolist()) == list(range(700))
+    cls = (64 * (d.njmax - np.minimum(d.nefc[order], d.njmax).astype(np.int64))) // (d.njmax + 1)
+    assert (np.diff(cls) >= 0).all() and d.nefc[order[0]] >= d.nefc.max() - 1 and d.nefc[order[-1]] == 0
+    assert an[0] == bn[0]
+    for name in ("qacc", "qfrc_constraint", "solver_niter", "overflow"):
+        assert np.array_equal(getattr(a, name), getattr(b, name)), name
+    assert np.array_equal(a.efc.Ma, b.efc.Ma)
+    live = np.arange(d.njmax)[None, :] < np.minimum(d.nefc, d.njmax)[:, None]
+    assert np.array_equal(a.efc.force[live], b.efc.force[live])
+    assert np.array_equal(a.efc.state[live], b.efc.state[live])
+    want, _, _ = run_oracle(oracle, m, d)
+    assert np.array_equal(a.qacc, want.qacc)
+
+
 def test_repeated_solves_are_bitwise_identical(cuda_device):
     """tests/test_mjw_newton_fusion.py:290-346: eight solves, identical qacc."""
     m, d, _ = synthetic.make_workload("snu", 64, seed=29, iterations=3, ls_iterations=50)
