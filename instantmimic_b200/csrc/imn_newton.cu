@@ -198,10 +198,11 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   // Every later pass is one Newton iteration (newton_fusion.py:170-296).
 #pragma unroll 1
   for (bool first = true;; first = false) {
-    if (first)
-      products<JRES>(s, s.qacc, s.Ma, s.Jaref, s.jv);
-    else if (!search_unchanged)
-      products<JRES>(s, s.search, s.mv, s.jv, nullptr);
+    // one call site: Ma = M qacc, Jaref = J qacc - aref on pass 0; mv = M search,
+    // jv = J search afterwards
+    if (first || !search_unchanged)
+      products<JRES>(s, first ? s.qacc : s.search, first ? s.Ma : s.mv, first ? s.Jaref : s.jv,
+                     first ? s.jv : nullptr);
     __syncwarp();
     PROF(5);
     if (rowless) break;

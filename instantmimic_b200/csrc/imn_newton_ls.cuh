@@ -14,6 +14,21 @@
 
 namespace imn {
 
+// Row sums of one lane at step size `al` in the general form (friction-loss rows,
+// or more than two rows per lane): rows ne+lane, ne+lane+32, ... in ascending order,
+// each prepared from shared memory.  Kept out of line: models without friction-loss
+// rows and with at most 64 inequality rows never run it, and the line search's
+// resident code stays small (the kernel is bound by instruction fetch).
+__device__ __noinline__ Vec3 ls_rows_general(const float* floss, const float* D, const float* Jaref,
+                                             const float* jv, int ne, int nef, int nefc, int lane, float al,
+                                             bool absolute) {
+  Vec3 acc = v3(0.0f, 0.0f, 0.0f);
+#pragma unroll 1
+  for (int r = ne + lane; r < nefc; r += 32)
+    acc = acc + row_at(make_row(true, r < nef, floss[r], D[r], Jaref[r], jv[r]), al, absolute);
+  return acc;
+}
+
 struct LineSearchResult {
   float alpha, improvement, noise_floor;
   bool converged;
@@ -44,17 +59,9 @@ __device__ __forceinline__ LineSearchResult line_search(const World& s, float se
   // friction-loss rows are rare: without any (warp-uniform test) the rows are plain
   // inequalities and the short branch-free evaluation is used
   const bool fric = nef > ne;
-  Row rowa, rowb;
-  if (fric) {
-    rowa = make_row(va, ra < nef, va ? s.floss[ra] : 0.0f, va ? s.Dsm[ra] : 1.0f, va ? s.Jaref[ra] : 0.0f,
-                    va ? s.jv[ra] : 0.0f);
-    rowb = make_row(vb, rb < nef, vb ? s.floss[rb] : 0.0f, vb ? s.Dsm[rb] : 1.0f, vb ? s.Jaref[rb] : 0.0f,
-                    vb ? s.jv[rb] : 0.0f);
-  } else {
-    rowa = make_row_ineq(va, va ? s.Dsm[ra] : 1.0f, va ? s.Jaref[ra] : 0.0f, va ? s.jv[ra] : 0.0f);
-    rowb = make_row_ineq(vb, vb ? s.Dsm[rb] : 1.0f, vb ? s.Jaref[rb] : 0.0f, vb ? s.jv[rb] : 0.0f);
-  }
   const bool more = ne + 64 < nefc;
+  const Row rowa = make_row_ineq(va, va ? s.Dsm[ra] : 1.0f, va ? s.Jaref[ra] : 0.0f, va ? s.jv[ra] : 0.0f);
+  const Row rowb = make_row_ineq(vb, vb ? s.Dsm[rb] : 1.0f, vb ? s.Jaref[rb] : 0.0f, vb ? s.jv[rb] : 0.0f);
 
   LineSearchResult out;
   out.alpha = 0.0f, out.improvement = 0.0f, out.noise_floor = 0.0f, out.converged = false;
@@ -74,20 +81,11 @@ __device__ __forceinline__ LineSearchResult line_search(const World& s, float se
         s2 = (z3 + row_at_ineq(rowa, a2, absolute)) + row_at_ineq(rowb, a2, absolute);
       }
     } else {
-      // general form (friction rows, or more than two rows per lane), one step size
-      // at a time to keep this rarely used code small
-      const int nalpha = pass >= 2 ? 3 : 1;
-#pragma unroll 1
-      for (int k = 0; k < nalpha; ++k) {
-        const float al = k == 0 ? a0 : (k == 1 ? a1 : a2);
-        Vec3 acc = (z3 + row_at(rowa, al, absolute)) + row_at(rowb, al, absolute);
-        if (more)
-#pragma unroll 1
-          for (int r = rb + 32; r < nefc; r += 32)
-            acc = acc + row_at(make_row(true, r < nef, s.floss[r], s.Dsm[r], s.Jaref[r], s.jv[r]), al, absolute);
-        if (k == 0) s0 = acc;
-        if (k == 1) s1 = acc;
-        if (k == 2) s2 = acc;
+      // general form, one step size at a time
+      s0 = ls_rows_general(s.floss, s.Dsm, s.Jaref, s.jv, ne, nef, nefc, lane, a0, absolute);
+      if (pass >= 2) {
+        s1 = ls_rows_general(s.floss, s.Dsm, s.Jaref, s.jv, ne, nef, nefc, lane, a1, absolute);
+        s2 = ls_rows_general(s.floss, s.Dsm, s.Jaref, s.jv, ne, nef, nefc, lane, a2, absolute);
       }
     }
     float q[9] = {s0.c0, s0.c1, s0.c2, s1.c0, s1.c1, s1.c2, s2.c0, s2.c1, s2.c2};
