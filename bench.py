@@ -1,7 +1,7 @@
 """Benchmark of the Newton constraint solve: world-steps/s on N B200s.
 
-A "step" is one ``solve_with_scratch`` over one batch of worlds (the humanoid of
-BASELINE.json's second config: nv 34, njmax 64, 8192 worlds per GPU).  Inputs are
+A "step" is one ``solve_with_scratch`` over one batch of worlds (the reference's
+humanoid benchmark configuration: nv 34, njmax 64, 8192 worlds per GPU).  Inputs are
 seeded synthetic solver states with that model's shapes; several distinct batches
 are rotated so that consecutive steps never find their inputs in L2.
 

@@ -267,7 +267,7 @@ def make_problem(
     return d, Mdense
 
 
-# Named workloads (BASELINE.json configs; see make_workload).
+# Named workloads: the shapes of the reference's benchmark models (see make_workload).
 WORKLOADS = {
     # name: (tree, njmax, nefc_range, iterations, ls_iterations)
     "humanoid": (humanoid_tree, 64, (16, 64)),
