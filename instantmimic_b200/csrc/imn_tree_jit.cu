@@ -18,6 +18,7 @@
 // off), in list order, so the results are bit-identical to the interpreter's.
 #include <dlfcn.h>
 
+#include <mutex>
 #include <string>
 #include <vector>
 
@@ -41,20 +42,25 @@ struct Nvrtc {
   const char* (*error_string)(int) = nullptr;
 };
 
+bool nvrtc_open(Nvrtc& api);
+
 Nvrtc* nvrtc() {
   static Nvrtc api;
-  static bool tried = false;
-  if (tried) return api.handle ? &api : nullptr;
-  tried = true;
+  static std::once_flag once;
+  std::call_once(once, [] { nvrtc_open(api); });
+  return api.handle ? &api : nullptr;
+}
+
+bool nvrtc_open(Nvrtc& api) {
   const char* names[] = {"libnvrtc.so.12", "libnvrtc.so", "/usr/local/cuda/lib64/libnvrtc.so.12",
                          "/usr/local/cuda/lib64/libnvrtc.so"};
   void* h = nullptr;
   for (const char* n : names)
     if ((h = dlopen(n, RTLD_NOW | RTLD_LOCAL))) break;
-  if (!h) return nullptr;
+  if (!h) return false;
 #define IMN_SYM(field, name)                                        \
   api.field = reinterpret_cast<decltype(api.field)>(dlsym(h, name)); \
-  if (!api.field) return nullptr
+  if (!api.field) return false
   IMN_SYM(create, "nvrtcCreateProgram");
   IMN_SYM(compile, "nvrtcCompileProgram");
   IMN_SYM(log_size, "nvrtcGetProgramLogSize");
@@ -65,7 +71,7 @@ Nvrtc* nvrtc() {
   IMN_SYM(error_string, "nvrtcGetErrorString");
 #undef IMN_SYM
   api.handle = h;
-  return &api;
+  return true;
 }
 
 struct Ins {
@@ -98,6 +104,7 @@ struct ImnTreeKernel {
   std::vector<char> cubin;
   cudaLibrary_t library = nullptr;
   cudaKernel_t kernel = nullptr;
+  std::mutex load_mutex;  // the first solve loads the machine code
 };
 
 namespace {
@@ -269,6 +276,7 @@ extern "C" int imn_tree_ldl_compiled_solve(ImnTreeKernel* k, const float* M, int
     return imn::set_error("imn_tree_ldl_compiled_solve: %zu bytes of shared memory per block (max %d)", bytes,
                           227 * 1024),
            IMN_ERR_LIMIT;
+  std::unique_lock<std::mutex> lock(k->load_mutex);
   if (!k->kernel) {
     // first use: hand the machine code to the runtime (do this outside stream capture)
     cudaError_t e = cudaLibraryLoadData(&k->library, k->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
@@ -282,6 +290,7 @@ extern "C" int imn_tree_ldl_compiled_solve(ImnTreeKernel* k, const float* M, int
              IMN_ERR_LAUNCH;
     }
   }
+  lock.unlock();
   long long mld = M_ld, yld = y_ld, xld = x_ld;
   int nw = nworld;
   void* args[] = {&M, &mld, &y, &yld, &x, &xld, &nw};
