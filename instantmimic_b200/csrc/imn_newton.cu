@@ -281,7 +281,7 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
       grad_scale = 1.0f;
       if (first) {
         if (SPARSE)
-          assemble_hessian_sparse(s, nfr, sp);
+          assemble_hessian_sparse<JRES>(s, nfr, sp);
         else
           assemble_hessian<JRES>(s, nfr);
       } else if (quad_count > 0) {
@@ -475,21 +475,31 @@ static int validate(const ImnModel* m, const ImnData* d, const ImnCtx* cx) {
   return IMN_OK;
 }
 
+// Worlds one SM holds at `bytes` of dynamic shared memory per one-warp CTA (1 KB is
+// reserved per CTA; 16 is the register limit of the kernels).
+static int worlds_per_sm(int bytes) {
+  const int n = (228 * 1024) / (bytes + 1024);
+  return n < 16 ? n : 16;
+}
+
+// J resident in shared memory or streamed through the 32-row tile.  Resident J is
+// read once from HBM; a streamed J is re-read from L2 in every stage but leaves room
+// for more worlds per SM.  Measured on B200 (dense factor): humanoid (njmax 64) 12
+// resident vs 16 streamed worlds per SM: resident 7 % faster; SNU-like (njmax 128) 4 vs
+// 7: streamed 1.22x faster; G1-like (njmax 250) 4 vs 11: streamed 1.6x faster.  Hence:
+// stream when it holds at least 1.6x the worlds.
 static int plan_launch(const ImnModel* m, const ImnData* d, const ImnSparsePlan* sp, Geom* g, bool* resident) {
-  Geom gr = make_geom(*m, *d, true, sp);
+  const Geom gr = make_geom(*m, *d, true, sp);
+  const Geom gs = make_geom(*m, *d, false, sp);
 #ifdef IMN_FORCE_STREAM
-  const int budget = 0;
+  const bool fits = false;
 #else
-  const int budget = kResidentBudget;
+  const bool fits = gr.total * 4 <= kResidentBudget;
 #endif
-  if (gr.total * 4 <= budget) {
+  if (fits && 10 * worlds_per_sm(gs.total * 4) < 16 * worlds_per_sm(gr.total * 4)) {
     *g = gr, *resident = true;
     return IMN_OK;
   }
-  if (sp)
-    return set_error("imn_solve: the sparse path keeps J in shared memory; njmax %d is too large", d->njmax),
-           IMN_ERR_LIMIT;
-  Geom gs = make_geom(*m, *d, false);
   if (gs.total * 4 > kMaxSmem)
     return set_error("imn_solve: njmax %d needs %d bytes of shared memory per world (max %d)", d->njmax,
                      gs.total * 4, kMaxSmem),
@@ -549,7 +559,7 @@ extern "C" int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* cx, 
 #else
   const int bytes = g.total * 4;
 #endif
-  auto kern = cx->sparse_plan ? imn::newton_kernel<true, true>
+  auto kern = cx->sparse_plan ? (res ? imn::newton_kernel<true, true> : imn::newton_kernel<false, true>)
                               : (res ? imn::newton_kernel<true, false> : imn::newton_kernel<false, false>);
   const ImnSparsePlan sp = cx->sparse_plan ? *cx->sparse_plan : ImnSparsePlan{};
   {

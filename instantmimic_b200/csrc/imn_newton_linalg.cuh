@@ -272,6 +272,7 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
 // rows once per ten slots: the row's D is read once, and ten independent sums overlap
 // their latencies.  The row list is compacted into s.ids first (unused during the
 // initial pass).
+template <bool JRES>
 __device__ __forceinline__ void assemble_hessian_sparse(const World& s, int nfr, const ImnSparsePlan& SP) {
   const int lane = s.lane, nv = s.nv, nfac = SP.nfac, words = (nv + 31) >> 5;
   int nq = 0;
@@ -282,13 +283,12 @@ __device__ __forceinline__ void assemble_hessian_sparse(const World& s, int nfr,
     if (lane == 0) s.ids[nq] = r;
     ++nq;
     if (s.Dsm[r] == 0.0f) continue;
-    const float* Jr = s.Jsm + r * s.ldj;
     unsigned rm[3] = {0u, 0u, 0u};
 #pragma unroll
     for (int q = 0; q < 3; ++q)
       if (q < words) {
         const int d = q * 32 + lane;
-        rm[q] = __ballot_sync(IMN_FULL_MASK, d < nv && Jr[d] != 0.0f);
+        rm[q] = __ballot_sync(IMN_FULL_MASK, d < nv && j_at<JRES>(s, r, d) != 0.0f);
       }
     bool bad = false;
 #pragma unroll
@@ -318,13 +318,23 @@ __device__ __forceinline__ void assemble_hessian_sparse(const World& s, int nfr,
         acc[q] = e >= 0 ? s.Msm[e] : 0.0f;
       }
     }
+    // rows in ascending order; a streamed J passes through its 32-row tile
+    int k = 0;
 #pragma unroll 1
-    for (int k = 0; k < nq; ++k) {
-      const int r = s.ids[k];
-      const float Dr = s.Dsm[r];
-      const float* Jr = s.Jsm + r * s.ldj;
+    for (int row0 = 0; row0 < s.nefc && k < nq; row0 += 32) {
+      const float* Jt = j_tile<JRES>(s, row0);
+      const int row1 = JRES ? s.nefc : row0 + 32;
+#pragma unroll 1
+      for (; k < nq; ++k) {
+        const int r = s.ids[k];
+        if (r >= row1) break;
+        const float Dr = s.Dsm[r];
+        const float* Jr = Jt + (r - row0) * s.ldj;
 #pragma unroll
-      for (int q = 0; q < Q; ++q) acc[q] = fmaf(Jr[ab[q] & 0xFFFF] * Dr, Jr[ab[q] >> 16], acc[q]);
+        for (int q = 0; q < Q; ++q) acc[q] = fmaf(Jr[ab[q] & 0xFFFF] * Dr, Jr[ab[q] >> 16], acc[q]);
+      }
+      if (JRES) break;
+      __syncwarp();
     }
 #pragma unroll
     for (int q = 0; q < Q; ++q) {
