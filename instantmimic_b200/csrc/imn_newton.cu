@@ -116,6 +116,9 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   s.mulm_rowadr = m.M_mulm_rowadr;
   s.mulm_pack = m.M_mulm_pack;
   s.world = w;
+  s.jbar = bar;
+  s.jphase = reinterpret_cast<int*>(smem + g.oBar) + 2;  // the barrier itself takes two words
+  s.jfail = s.jphase + 1;
   s.Hp = s.A;
   s.N = s.A + (SPARSE ? ((sp.nfac + 3) & ~3) : 0);
   s.iD = s.N + (SPARSE ? ((sp.nslots + 3) & ~3) : 0);
@@ -148,7 +151,11 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
         {s.qacc, q0 + dofo, nv},
         {s.qfs, d.qfrc_smooth + dofo, nv},
     };
-    if (lane == 0) mbar_init(bar, 1);
+    if (lane == 0) {
+      mbar_init(bar, 1);
+      *s.jphase = 1;  // phase 0 is the load below
+      *s.jfail = 0;
+    }
     __syncwarp();
     uint32_t tx = 0;
 #pragma unroll
@@ -198,6 +205,16 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   // Every later pass is one Newton iteration (newton_fusion.py:170-296).
 #pragma unroll 1
   for (bool first = true;; first = false) {
+    if (!JRES && *s.jfail) {
+      // a tile copy did not complete within its wait limit: give it one more bounded
+      // wait (it writes this CTA's shared memory), then leave the world unsolved
+      const uint32_t parity = (uint32_t)*s.jphase ^ 1u;
+      bool arrived = false;
+#pragma unroll 1
+      for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) arrived = mbar_try_wait(bar, parity);
+      if (lane == 0) d.overflow[w] |= IMN_OVERFLOW_COPY_TIMEOUT;
+      return;
+    }
     // one call site: Ma = M qacc, Jaref = J qacc - aref on pass 0; mv = M search,
     // jv = J search afterwards
     if (first || !search_unchanged)

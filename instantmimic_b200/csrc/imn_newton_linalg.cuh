@@ -21,6 +21,11 @@ struct World {
   uint16_t *state, *ids, *frows;
   int* uni;
   const float* Jg;  // this world's J in global memory
+  // streamed J: the copy barrier of the row tile, the parity of its next phase and the
+  // flag a timed-out copy raises (all in shared memory)
+  void* jbar;
+  int* jphase;
+  int* jfail;
   const int* mulm_rowadr;
   const uint32_t* mulm_pack;
   // sparse plan only: packed H, N = L D with the carried row, 1/D, the world's
@@ -44,11 +49,26 @@ struct World {
 template <bool JRES>
 __device__ __forceinline__ const float* j_tile(const World& s, int base) {
   if (JRES) return s.Jsm + base * s.ldj;
-  __syncwarp();
+  __syncwarp();  // every lane is done with the previous tile
   const int n = min(32, s.nefc - base) * s.ldj;
   const float* src = s.Jg + (size_t)base * s.ldj;
+  if ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (n & 3) == 0) {
+    // one TMA bulk copy on the world's mbarrier; the wait is bounded
+    const uint32_t parity = (uint32_t)*s.jphase;
+    __syncwarp();
+    if (s.lane == 0) {
+      mbar_expect_tx(s.jbar, (uint32_t)n * 4u);
+      bulk_g2s(s.Jsm, src, (uint32_t)n * 4u, s.jbar);
+      *s.jphase = (int)(parity ^ 1u);
+    }
+    bool arrived = false;
+#pragma unroll 1
+    for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) arrived = mbar_try_wait(s.jbar, parity);
+    if (!arrived && s.lane == 0) *s.jfail = 1;
+  } else {
 #pragma unroll 4
-  for (int i = s.lane; i < n; i += 32) s.Jsm[i] = src[i];
+    for (int i = s.lane; i < n; i += 32) s.Jsm[i] = src[i];
+  }
   __syncwarp();
   return s.Jsm;
 }
