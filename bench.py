@@ -461,7 +461,7 @@ def main():
             "e2e": e2e,
             "gpu_launches": 2 * args.steps,
             "roofline": {
-                "kernel": "newton_kernel<resident>" if info.j_resident else "newton_kernel<streamed>",
+                "kernel": "newton_kernel_resident" if info.j_resident else "newton_kernel_streamed",
                 "bound": "hbm",
                 "achieved": achieved,
                 "peak": peak,

@@ -69,7 +69,8 @@ static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident, const 
   g.r4 = up4(d.njmax);
   int o = 0;
   g.oBar = o, o += 4;
-  g.oJ = o, o += up4(g.jrows * g.ldj);
+  // a streamed tile may start up to three floats into its buffer and end on a 16-byte boundary
+  g.oJ = o, o += up4(g.jrows * g.ldj) + (resident ? 0 : 8);
   // dense: H and its factor share one (nv+1) x ldu array; sparse plan: packed H | N | 1/D
   g.oA = o, o += sp ? up4(sp->nfac) + up4(sp->nslots) + up4(m.nv) : (m.nv + 1) * g.ldu;
   // dof vectors; the dense factor needs two more (forward-solve scratch, 1 / pivot)
@@ -83,8 +84,8 @@ static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident, const 
 }
 
 template <bool JRES, bool SPARSE>
-__global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnData d, const ImnCtx cx,
-                                                    const Geom g, const ImnSparsePlan sp) {
+__device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d, const ImnCtx& cx, const Geom& g,
+                                             const ImnSparsePlan& sp) {
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x;
   const int w = cx.world_order ? cx.world_order[blockIdx.x] : (int)blockIdx.x;
@@ -132,6 +133,8 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   const bool rowless = nefc_in == 0;
   const size_t dofo = (size_t)w * d.dof_ld, efco = (size_t)w * d.efc_ld;
   s.Jg = d.efc_J + (size_t)w * d.J_ld_world;
+  s.Jbeg = d.efc_J;
+  s.Jend = d.efc_J + (size_t)(d.nworld - 1) * d.J_ld_world + (size_t)d.njmax * d.J_ld_row;
 
   // ---- load: TMA bulk copies for the 16-byte-aligned bulk of every array, plain
   // loads for the ragged ends -----------------------------------------------------
@@ -415,6 +418,20 @@ __global__ void __launch_bounds__(32) newton_kernel(const ImnModel m, const ImnD
   }
 }
 
+// Two entry points over the same body: with J resident the compiler is left its own
+// register choice; the streamed variants hold more worlds per SM in shared memory than
+// an uncapped register count would allow, so theirs is capped at 128 (16 warps per SM).
+template <bool SPARSE>
+__global__ void __launch_bounds__(32) newton_kernel_resident(const ImnModel m, const ImnData d, const ImnCtx cx,
+                                                             const Geom g, const ImnSparsePlan sp) {
+  newton_world<true, SPARSE>(m, d, cx, g, sp);
+}
+template <bool SPARSE>
+__global__ void __launch_bounds__(32, 16) newton_kernel_streamed(const ImnModel m, const ImnData d, const ImnCtx cx,
+                                                                 const Geom g, const ImnSparsePlan sp) {
+  newton_world<false, SPARSE>(m, d, cx, g, sp);
+}
+
 __global__ void fill_nsolving(int* nsolving, int value) { *nsolving = value; }
 
 // The hardware hands CTAs to SMs in index order and a world's solve time grows with
@@ -539,9 +556,9 @@ extern "C" int imn_debug_profile(unsigned long long* out, int reset) {
 extern "C" int imn_debug_occupancy(int bytes, int resident) {
   int n = 0;
   if (resident)
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel<true, false>, 32, bytes);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel_resident<false>, 32, bytes);
   else
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel<false, false>, 32, bytes);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel_streamed<false>, 32, bytes);
   return n;
 }
 #endif
@@ -576,8 +593,9 @@ extern "C" int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* cx, 
 #else
   const int bytes = g.total * 4;
 #endif
-  auto kern = cx->sparse_plan ? (res ? imn::newton_kernel<true, true> : imn::newton_kernel<false, true>)
-                              : (res ? imn::newton_kernel<true, false> : imn::newton_kernel<false, false>);
+  auto kern = cx->sparse_plan
+                  ? (res ? imn::newton_kernel_resident<true> : imn::newton_kernel_streamed<true>)
+                  : (res ? imn::newton_kernel_resident<false> : imn::newton_kernel_streamed<false>);
   const ImnSparsePlan sp = cx->sparse_plan ? *cx->sparse_plan : ImnSparsePlan{};
   {
     // many one-warp CTAs share an SM: ask for the largest shared-memory carve-out,

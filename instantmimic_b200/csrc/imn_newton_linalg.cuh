@@ -20,7 +20,8 @@ struct World {
   // world decides how many worlds an SM holds
   uint16_t *state, *ids, *frows;
   int* uni;
-  const float* Jg;  // this world's J in global memory
+  const float* Jg;    // this world's J in global memory
+  const float *Jbeg, *Jend;  // first element and one past the last row of the whole J array
   // streamed J: the copy barrier of the row tile, the parity of its next phase and the
   // flag a timed-out copy raises (all in shared memory)
   void* jbar;
@@ -52,23 +53,29 @@ __device__ __forceinline__ const float* j_tile(const World& s, int base) {
   __syncwarp();  // every lane is done with the previous tile
   const int n = min(32, s.nefc - base) * s.ldj;
   const float* src = s.Jg + (size_t)base * s.ldj;
-  if ((reinterpret_cast<uintptr_t>(src) & 15) == 0 && (n & 3) == 0) {
-    // one TMA bulk copy on the world's mbarrier; the wait is bounded
+  // One TMA bulk copy on the world's mbarrier; the wait is bounded.  A bulk copy wants
+  // 16-byte aligned ends, so the smallest aligned range around the rows is copied (up
+  // to three floats of the neighbouring rows on either side, still inside the J
+  // array) and the tile starts `head` floats into the buffer.
+  const int head = (int)((reinterpret_cast<uintptr_t>(src) & 15) >> 2);
+  const uint32_t bytes = (uint32_t)((head + n + 3) & ~3) * 4u;
+  if (src - head >= s.Jbeg && src - head + (bytes >> 2) <= s.Jend) {
     const uint32_t parity = (uint32_t)*s.jphase;
     __syncwarp();
     if (s.lane == 0) {
-      mbar_expect_tx(s.jbar, (uint32_t)n * 4u);
-      bulk_g2s(s.Jsm, src, (uint32_t)n * 4u, s.jbar);
+      mbar_expect_tx(s.jbar, bytes);
+      bulk_g2s(s.Jsm, src - head, bytes, s.jbar);
       *s.jphase = (int)(parity ^ 1u);
     }
     bool arrived = false;
 #pragma unroll 1
     for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) arrived = mbar_try_wait(s.jbar, parity);
     if (!arrived && s.lane == 0) *s.jfail = 1;
-  } else {
-#pragma unroll 4
-    for (int i = s.lane; i < n; i += 32) s.Jsm[i] = src[i];
+    __syncwarp();
+    return s.Jsm + head;
   }
+#pragma unroll 4
+  for (int i = s.lane; i < n; i += 32) s.Jsm[i] = src[i];
   __syncwarp();
   return s.Jsm;
 }
