@@ -2,8 +2,9 @@
 // the tree-structured L'DL and the blocked dense Cholesky.
 //
 // Tree L'DL (reference: tree_ldl.py:196-359, 419-433).  The reference generates
-// straight-line source per model; here one kernel interprets the plan's
-// instruction list.  A block serves 32 worlds with one warp per group; lane l of
+// straight-line source per model; imn_tree_jit.cu does the same with NVRTC.  The
+// kernel here interprets the plan's instruction list instead (the fallback when no
+// run-time compiler is installed, and the statement the generated code must match).  A block serves 32 worlds with one warp per group; lane l of
 // every warp works on world 32*block + l, all operands of a world live in column
 // l of a [slot][32] shared-memory array (bank = lane, so no conflicts), every
 // lane of a warp executes the same instruction on its own world, and the only

@@ -13,8 +13,9 @@
 // Cholesky factor and every vector stay on chip for all iterations, and the
 // results are written once.  A warp needs no block barrier (only __syncwarp),
 // lane reductions are shuffle trees, and the hardware CTA scheduler balances
-// worlds whose iteration counts differ.  Worlds with more rows than fit on chip
-// stream J through a 32-row staging tile.  The initialisation runs through the
+// worlds whose iteration counts differ; worlds are launched by descending row count
+// so that the long solves start first.  Models whose J would leave room for few
+// worlds per SM stream it through a 32-row tile (TMA bulk copies from L2) instead.  The initialisation runs through the
 // same code as an iteration (as "iteration 0" without a line search): the kernel
 // is bound by instruction fetch and latency, so every stage exists once.
 //

@@ -8,11 +8,13 @@ Eliminating dofs from the leaves towards the roots therefore creates no fill-in.
 Interface and planning rules follow the reference's
 ``src/instantmimic/utils/mjw_kernels/tree_ldl.py`` (TreeLdlPlan :47-57, structure
 check :66-91, planner :105-185, profitability gate :188-193, entry point :419-433).
-The reference turns a plan into generated straight-line CUDA source per model;
-here the plan is compiled into a small instruction list that one generic sm_100a
-kernel interprets (``csrc/imn_msolve.cu``): 32 worlds per warp, one warp per
-group, all operands of a world in one shared-memory column, so lanes never
-conflict on a bank and nothing diverges.
+The reference turns a plan into generated straight-line source per model and
+compiles it at run time.  Here the plan is first compiled into a small instruction
+list (``_Program``); ``csrc/imn_tree_jit.cu`` turns that list into straight-line CUDA C
+and compiles it for sm_100a with NVRTC (values only one warp touches live in
+registers), and ``csrc/imn_msolve.cu`` holds a generic kernel that interprets the same
+list for machines without NVRTC.  Both map 32 worlds to a warp, one warp per group,
+lane = world, and give the same bits.
 """
 
 from __future__ import annotations
