@@ -140,6 +140,52 @@ def test_world_order_changes_nothing_but_the_schedule(oracle, cuda_device):
     assert np.array_equal(a.qacc, want.qacc)
 
 
+@pytest.mark.parametrize("name,worlds,jpad", [("humanoid", 96, 48), ("humanoid", 96, 37), ("g1", 24, 37), ("snu", 24, 64)])
+def test_padded_strides_are_read_from_the_arrays(oracle, cuda_device, name, worlds, jpad):
+    """Upstream allocates efc.J with a third extent >= nv and may pad other arrays; the
+    library takes every stride from the live arrays.  Padding is poisoned with NaN.
+    jpad 37 makes the rows of J unaligned for the bulk copies (resident and streamed)."""
+    import torch
+
+    from instantmimic_b200 import mjw_model
+    from instantmimic_b200 import mjw_step_optimized as runtime
+
+    m, d, _ = synthetic.make_workload(name, worlds, seed=17, rowless_fraction=0.1)
+    want, _, _ = run_oracle(oracle, m, d)
+    md, dd = mjw_model.to_device(m, cuda_device), mjw_model.to_device(copy.deepcopy(d), cuda_device)
+    nan = float("nan")
+
+    def padded(t, extra):
+        full = torch.full((*t.shape[:-1], t.shape[-1] + extra), nan if t.is_floating_point() else -7,
+                          dtype=t.dtype, device=t.device)
+        view = full[..., : t.shape[-1]]
+        view.copy_(t)
+        return view
+
+    for field in ("qacc_smooth", "qacc_warmstart", "qfrc_smooth", "qacc", "qfrc_constraint"):
+        setattr(dd, field, padded(getattr(dd, field), 6))
+    dd.efc.Ma = padded(dd.efc.Ma, 6)
+    dd.M = padded(dd.M, 3)
+    for field in ("D", "aref", "frictionloss", "force", "state"):
+        setattr(dd.efc, field, padded(getattr(dd.efc, field), 8))
+    dd.efc.J = padded(dd.efc.J, jpad - m.nv)
+    assert not dd.efc.J.is_contiguous() and dd.efc.J.stride() == (d.njmax * jpad, jpad, 1)
+    scratch = runtime.make_optimized_fwd_position_scratch(md, dd, cuda_device)
+    ctx = scratch.solver_context  # its row / dof arrays share the strides of the data arrays
+    for field in ("Jaref", "jv", "quad_changed_ids"):
+        setattr(ctx, field, padded(getattr(ctx, field), 8))
+    for field in ("search", "mv"):
+        setattr(ctx, field, padded(getattr(ctx, field), 6))
+    runtime.solve_with_scratch(md, dd, scratch, use_optimized_kernel=True)
+    torch.cuda.synchronize()
+    assert np.array_equal(dd.solver_niter.cpu().numpy(), want.solver_niter)
+    assert np.array_equal(dd.qacc.cpu().numpy(), want.qacc)
+    assert np.array_equal(dd.qfrc_constraint.cpu().numpy(), want.qfrc_constraint)
+    live = np.arange(d.njmax)[None, :] < np.minimum(d.nefc, d.njmax)[:, None]
+    assert np.array_equal(dd.efc.state.cpu().numpy()[live], want.efc.state[live])
+    assert np.array_equal(dd.efc.force.cpu().numpy()[live], want.efc.force[live])
+
+
 def test_repeated_solves_are_bitwise_identical(cuda_device):
     """tests/test_mjw_newton_fusion.py:290-346: eight solves, identical qacc."""
     m, d, _ = synthetic.make_workload("snu", 64, seed=29, iterations=3, ls_iterations=50)
