@@ -87,3 +87,46 @@ def test_full_batch_properties(oracle, cuda_device, case):
     flipped = sel & (again.efc.state != got.efc.state)
     assert flipped.sum() <= 1e-4 * sel.sum()
     assert (np.abs(jar[flipped]) < 1e-3 * scale[flipped]).all()
+
+
+@pytest.mark.parametrize("name,worlds", [("humanoid", 8192), ("snu", 4096)])
+def test_full_batch_m_side_kernels(oracle, cuda_device, name, worlds):
+    """tree L'DL, blocked dense Cholesky and M v on a whole batch: M x = y holds to
+    rounding, both solvers agree, M v is linear, and a strided sample equals the oracle."""
+    import torch
+
+    from instantmimic_b200 import mjw_step_optimized as runtime
+    from instantmimic_b200.mjw_kernels import indexed_factor, tree_ldl
+
+    m, d, Mdense = synthetic.make_workload(name, worlds, seed=1)
+    md, dd = mjw_model.to_device(m, cuda_device), mjw_model.to_device(d, cuda_device)
+    scratch = runtime.make_optimized_fwd_position_scratch(md, dd, cuda_device)
+    assert scratch.tree_factor_solve is not None and scratch.dense_factor_solve is not None
+    y = dd.qfrc_smooth
+    x_tree, x_dense, back = torch.zeros_like(y), torch.zeros_like(y), torch.zeros_like(y)
+    tree_ldl.tree_factor_solve(scratch.tree_factor_solve, dd.M, x_tree, y)
+    indexed_factor.blocked_dense_factor_solve(dd, dd.M, x_dense, y, scratch.dense_factor_solve)
+    runtime.mul_m(md, dd, back, x_tree)
+    torch.cuda.synchronize()
+    yh, xt, xd = d.qfrc_smooth.astype(np.float64), x_tree.cpu().numpy(), x_dense.cpu().numpy()
+    scale = 1.0 + np.abs(yh).max(axis=1, keepdims=True)
+    assert (np.abs(back.cpu().numpy() - yh) / scale).max() < 2e-4          # M (M^-1 y) = y
+    assert (np.abs(xt - xd) / (1.0 + np.abs(xd).max(axis=1, keepdims=True))).max() < 2e-3
+    # linearity of M v: M (2 a + b) = 2 M a + M b up to rounding
+    a, b = dd.qacc_smooth, dd.qacc_warmstart
+    Ma, Mb, Mab = torch.zeros_like(a), torch.zeros_like(a), torch.zeros_like(a)
+    runtime.mul_m(md, dd, Ma, a)
+    runtime.mul_m(md, dd, Mb, b)
+    runtime.mul_m(md, dd, Mab, 2.0 * a + b)
+    torch.cuda.synchronize()
+    lin = (Mab - (2.0 * Ma + Mb)).abs().max().item() / (1.0 + Mab.abs().max().item())
+    assert lin < 1e-5, lin
+    # strided sample against the oracle, bit for bit
+    idx = np.arange(0, worlds, worlds // 64)
+    structure = tree_ldl.tree_ldl_structure(m.M_rowadr, m.M_rownnz, m.M_colind)
+    want = oracle.tree_ldl_solve(structure, scratch.tree_factor_solve.plan, np.ascontiguousarray(d.M[idx]),
+                                 np.ascontiguousarray(d.qfrc_smooth[idx]))
+    assert np.array_equal(xt[idx].view(np.uint32), want.view(np.uint32))
+    want_ma = np.zeros((len(idx), m.nv), np.float32)
+    oracle.mul_m(m, np.ascontiguousarray(d.M[idx]), np.ascontiguousarray(d.qacc_smooth[idx]), want_ma)
+    assert np.array_equal(Ma.cpu().numpy()[idx].view(np.uint32), want_ma.view(np.uint32))
