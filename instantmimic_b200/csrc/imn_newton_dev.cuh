@@ -173,4 +173,20 @@ __device__ __forceinline__ void pair_advance(int& i, int& j, int step) {
   while (i > j) i -= j + 1, ++j;
 }
 
+// The same enumeration as a table: entry e holds i | j << 8 of the e-th pair (i <= j),
+// for every pair of up to 80 indices.  One coalesced load replaces the stepping loop.
+struct PairTable {
+  uint16_t v[80 * 81 / 2];
+  constexpr PairTable() : v() {
+    int e = 0;
+    for (int j = 0; j < 80; ++j)
+      for (int i = 0; i <= j; ++i) v[e++] = (uint16_t)(i | (j << 8));
+  }
+};
+__device__ const PairTable g_pairs = PairTable();
+__device__ __forceinline__ void pair_lookup(int e, int& i, int& j) {
+  const int p = g_pairs.v[e];
+  i = p & 0xFF, j = p >> 8;
+}
+
 }  // namespace imn

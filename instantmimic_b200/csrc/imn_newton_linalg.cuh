@@ -249,8 +249,6 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
   // four pairs per lane at a time: the listed rows are walked once per four pairs and
   // the four sums overlap their latencies; each sum still takes its rows in list order
   constexpr int Q = 4;
-  int pi = lane, pj = 0;
-  pair_advance(pi, pj, 0);
 #pragma unroll 1
   for (int base = 0; base < npu; base += 32 * Q) {
     int row[Q], col[Q], sl[Q];
@@ -258,11 +256,12 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
 #pragma unroll
     for (int q = 0; q < Q; ++q) {
       const bool in = base + 32 * q + lane < npu;
+      int pi = 0, pj = 0;
+      if (in) pair_lookup(base + 32 * q + lane, pi, pj);
       row[q] = in ? s.uni[pi] : 0, col[q] = in ? s.uni[pj] : 0;
       // looked up ahead of the sum so that the table's latency is hidden behind it
       sl[q] = in ? (SPARSE ? __ldg(SP.pair + row[q] * nv + col[q]) : 0) : -2;
       delta[q] = 0.0f;
-      pair_advance(pi, pj, 32);
     }
 #pragma unroll 1
     for (int t = 0; t < count; ++t) {
