@@ -184,38 +184,55 @@ __device__ __forceinline__ void assemble_hessian(const World& s, int nfr) {
   }
   __syncwarp();
   const int npair = nv * (nv + 1) / 2;
-  int a_lo = 0;
+  // the QUADRATIC rows with a force, ascending, compacted into s.ids (unused during the
+  // initial pass)
+  int nq = 0;
 #pragma unroll 1
-  for (int base = 0; base < s.nefc; base += 32) {
+  for (int a = 0; a < nfr; ++a) {
+    const int r = s.frows[a];
+    if (s.state[r] != IMN_STATE_QUADRATIC) continue;
+    if (lane == 0) s.ids[nq] = r;
+    ++nq;
+  }
+  __syncwarp();
+  // six entries per lane at a time: a row's D is read once per six entries and the six
+  // running sums overlap; every entry still receives its rows in ascending order
+  constexpr int Q = 6;
+  int k_lo = 0;
+#pragma unroll 1
+  for (int base = 0; base < s.nefc && k_lo < nq; base += 32) {
     const float* Jt = j_tile<JRES>(s, base);
-    const int row_hi = JRES ? s.nefc : min(base + 32, s.nefc);
-    int a_hi = a_lo;
-    while (a_hi < nfr && s.frows[a_hi] < row_hi) ++a_hi;
-    // two entries per lane per pass so that their running sums overlap
-    int i0 = lane, j0 = 0, i1 = lane + 32, j1 = 0;
-    pair_advance(i0, j0, 0);
-    pair_advance(i1, j1, 0);
+    const int row_hi = JRES ? s.nefc : base + 32;
+    int k_hi = k_lo;
+    while (k_hi < nq && s.ids[k_hi] < row_hi) ++k_hi;
 #pragma unroll 1
-    for (int e = lane; e < npair; e += 64) {
-      const bool two = e + 32 < npair;
-      const int i1c = two ? i1 : i0, j1c = two ? j1 : j0;
-      float v0 = A[(j0 + 1) * ldu + i0];
-      float v1 = A[(j1c + 1) * ldu + i1c];
-#pragma unroll 2
-      for (int a = a_lo; a < a_hi; ++a) {
-        const int r = s.frows[a];
-        if (s.state[r] != IMN_STATE_QUADRATIC) continue;
+    for (int e0 = 0; e0 < npair && k_hi > k_lo; e0 += 32 * Q) {
+      float acc[Q];
+      int ij[Q];
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        const int e = e0 + 32 * q + lane;
+        int pi = 0, pj = 0;
+        if (e < npair) pair_lookup(e, pi, pj);
+        ij[q] = e < npair ? (pi | (pj << 16)) : -1;
+        acc[q] = e < npair ? A[(pj + 1) * ldu + pi] : 0.0f;
+      }
+#pragma unroll 1
+      for (int k = k_lo; k < k_hi; ++k) {
+        const int r = s.ids[k];
         const float Dr = s.Dsm[r];
         const float* Jr = Jt + (r - base) * s.ldj;
-        v0 = fmaf(Jr[i0] * Dr, Jr[j0], v0);
-        v1 = fmaf(Jr[i1c] * Dr, Jr[j1c], v1);
+#pragma unroll
+        for (int q = 0; q < Q; ++q) {
+          const int pi = ij[q] < 0 ? 0 : (ij[q] & 0xFFFF), pj = ij[q] < 0 ? 0 : (ij[q] >> 16);
+          acc[q] = fmaf(Jr[pi] * Dr, Jr[pj], acc[q]);
+        }
       }
-      A[(j0 + 1) * ldu + i0] = v0;
-      if (two) A[(j1 + 1) * ldu + i1] = v1;
-      pair_advance(i0, j0, 64);
-      pair_advance(i1, j1, 64);
+#pragma unroll
+      for (int q = 0; q < Q; ++q)
+        if (ij[q] >= 0) A[((ij[q] >> 16) + 1) * ldu + (ij[q] & 0xFFFF)] = acc[q];
     }
-    a_lo = a_hi;
+    k_lo = k_hi;
     if (JRES) break;
     __syncwarp();
   }
