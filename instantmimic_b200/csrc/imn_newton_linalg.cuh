@@ -263,9 +263,12 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
   __syncwarp();
   IMN_MARK(s, 12);
   const int npu = n * (n + 1) / 2;
-  // four pairs per lane at a time: the listed rows are walked once per four pairs and
-  // the four sums overlap their latencies; each sum still takes its rows in list order
-  constexpr int Q = 4;
+  // several pairs per lane at a time: the listed rows are walked once per group and the
+  // sums overlap their latencies; each sum still takes its rows in list order.  Four,
+  // except two in the resident-J kernel with the sparse plan, where the smaller code is
+  // worth more (measured: 2 % faster there; 1-3 % slower with the dense factor, 2-8 %
+  // slower with streamed J).
+  constexpr int Q = (JRES && SPARSE) ? 2 : 4;
 #pragma unroll 1
   for (int base = 0; base < npu; base += 32 * Q) {
     int row[Q], col[Q], sl[Q];
