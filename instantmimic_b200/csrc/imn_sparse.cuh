@@ -65,10 +65,9 @@ __device__ __forceinline__ void sp_factor_levels(const ImnSparsePlan& P, float* 
 // The same factorisation driven by the per-(sweep, lane) records (ImnSparsePlan::
 // fsweep): one 128-bit load gives a lane its entry, the entry's first run and the
 // sweep's team width, and the next sweep's record is fetched while the current one is
-// worked on, so no table load sits on the dependent path.  Terms are taken two at a
-// time (loads first, then the fused multiply-adds in order; groups of four were
-// measured 1-2 % slower: more code): the order in which an entry receives its terms is
-// unchanged.
+// worked on, so no table load sits on the dependent path.  The term loop is kept
+// rolled: taking terms in groups of four or two (loads first) was measured 2-4 % slower
+// on the whole kernel, which is bound by instruction fetch.
 __device__ __forceinline__ float sp_run_terms(const float* N, const float* iD, uint32_t ab, uint32_t kl, int tl,
                                               int T, float v) {
   const float* pa = N + (ab & 0xFFFFu);
@@ -76,13 +75,6 @@ __device__ __forceinline__ float sp_run_terms(const float* N, const float* iD, u
   const float* pd = iD + (kl & 0xFFFFu);
   const int len = (int)(kl >> 16);
   int t = tl;
-#pragma unroll 1
-  for (; t + T < len; t += 2 * T) {
-    const float a0 = pa[t], b0 = pb[t], d0 = pd[t];
-    const float a1 = pa[t + T], b1 = pb[t + T], d1 = pd[t + T];
-    v = fmaf(a0 * b0, d0, v);
-    v = fmaf(a1 * b1, d1, v);
-  }
 #pragma unroll 1
   for (; t < len; t += T) v = fmaf(pa[t] * pb[t], pd[t], v);
   return v;
