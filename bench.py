@@ -33,7 +33,7 @@ UNIT = "world-steps/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one newton_kernel launch, from the ncu
 # capture summarised in profiles/newton_kernel_humanoid.md: 138.8 MB for 16384 humanoid
 # worlds (8.47 KB per world); traffic grows in proportion to the worlds of a launch.
-NCU_TRAFFIC_BYTES_PER_WORLD = 139.75e6 / 16384
+NCU_TRAFFIC_BYTES_PER_WORLD = 140.06e6 / 16384
 
 
 def parse_args():
