@@ -344,3 +344,49 @@ def test_nonfused_sparse_factor_matches_oracle_and_dense_search(oracle, cuda_dev
     sparse_hessian.nonfused_factor_solve(plan, ctx, d.nworld, skip_unchanged=True)
     torch.cuda.synchronize()
     np.testing.assert_allclose(ctx.search.cpu().numpy(), got, rtol=2e-4, atol=2e-5)
+
+
+def test_sweep_records_restate_the_level_tables():
+    """The per-(sweep, lane) records the fused kernel reads (include/imnewton.h) carry the
+    same entries, runs and level boundaries as the level tables they are packed from."""
+    for name in ("humanoid", "snu"):
+        m, _, _ = synthetic.make_workload(name, 1, seed=0)
+        plan = sparse_hessian.build_plan(m, _single_body_groups(m), 32 if m.nv_pad < 64 else 64, "fused")
+        t = plan.tables
+        fs = t["fsweep"].reshape(-1, 32, 4).astype(np.int64)
+        seen, sweep = [], 0
+        for lvl, team in enumerate(int(v) for v in t["lvl_team"]):
+            e0, e1, per = int(t["lvl_ptr"][lvl]), int(t["lvl_ptr"][lvl + 1]), 32 // team
+            starts = list(range(e0, e1, per))
+            for eb in starts:
+                rec = fs[sweep]
+                sweep += 1
+                assert ((rec[:, 3] >> 1) & 1 == (eb == starts[-1])).all()        # last sweep of the level
+                assert ((rec[:, 3] >> 2) & 7 == team.bit_length() - 1).all()     # team width
+                for lane in range(32):
+                    e = eb + lane // team
+                    has = rec[lane, 3] & 1
+                    assert bool(has) == (e < e1)
+                    if not has:
+                        continue
+                    seen.append(e) if lane % team == 0 else None
+                    assert rec[lane, 0] & 0xFFFF == t["ent_slot"][e]
+                    assert (rec[lane, 0] >> 16) - 1 == t["ent_col"][e]
+                    r0, r1 = int(t["run_ptr"][e]), int(t["run_ptr"][e + 1])
+                    assert (rec[lane, 3] >> 8) & 0xFF == max(r1 - r0 - 1, 0)
+                    if r1 > r0:
+                        assert rec[lane, 1] == t["run_ab"][r0] and rec[lane, 2] == t["run_kl"][r0]
+                        assert rec[lane, 3] >> 16 == r0 + 1
+        assert sweep == fs.shape[0] and seen == list(range(len(t["ent_slot"])))
+        # backward records: every (slot, src, dst) once, levels closed by the last-of-level bit
+        bs = t["bsweep"].astype(np.int64)
+        live = bs[(bs >> 30) & 1 == 1]
+        assert len(live) == len(t["b_slot"])
+        assert sorted(zip(live & 0xFFFF, (live >> 16) & 0x7F, (live >> 23) & 0x7F)) == sorted(
+            zip(t["b_slot"].astype(int), t["b_src"].astype(int), t["b_dst"].astype(int)))
+        nonempty = int((np.diff(t["b_lvl"].astype(int)) > 0).sum())
+        assert int(((bs.reshape(-1, 32)[:, 0] >> 31) & 1).sum()) == nonempty
+    # the non-fused plan carries no records
+    big, _, _ = synthetic.make_workload("humanoid", 1, seed=0)
+    nf = sparse_hessian.build_plan(big, _single_body_groups(big), 64, "nonfused")
+    assert nf.tables["fsweep"].size == 0 and sparse_hessian.host_struct(nf).nfsweep == 0
