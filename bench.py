@@ -369,6 +369,7 @@ def main():
             "steps": e2e_steps,
             "ms_per_step": 1e3 * dt / e2e_steps,
             "pipeline": f"{nslot} slots (copy of step k+1 overlaps the solve of step k)",
+            "h2d_gbs_per_gpu": float(h2d) * e2e_steps / dt / 1e9,  # the copy is the limit of this path
             "checksum": checksum,
         }
 
