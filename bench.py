@@ -104,7 +104,14 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
+
+    def wait_started(self, timeout: float = 3.0) -> None:
+        """nvidia-smi takes a few hundred ms to deliver its first row; a timed region of
+        0.1-0.2 s would otherwise pass without a sample."""
+        t0 = time.perf_counter()
+        while self.proc is not None and not self.rows and time.perf_counter() - t0 < timeout:
+            time.sleep(0.01)
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -115,10 +122,18 @@ class ClockSampler:
                 self.proc.kill()
             self.thread.join(timeout=5)
 
-    def summary(self):
+    def summary(self, t_begin: float, t_end: float):
+        """Median SM clock and throttle reasons of the rows received in [t_begin, t_end]
+        (host clock); when the window is too short to hold one, of all rows since the
+        sampler started (warm-up and timed steps of the same workload), and says so."""
+        inside = [r for t, r in self.rows if t_begin <= t <= t_end]
+        window = "timed region"
+        if not inside:
+            inside = [r for _, r in self.rows]
+            window = "warm-up and timed steps (no sample fell inside the timed region)"
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for r in inside:
             if len(r) < 7:
                 continue
             try:
@@ -130,9 +145,9 @@ class ClockSampler:
                 if flag.lower().startswith("active"):
                     reasons.add(name)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "window": window}
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
-                "samples": len(sm)}
+                "samples": len(sm), "window": window}
 
 
 def make_batches(args, rank):
@@ -279,17 +294,19 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    for k in range(args.warmup):
-        step(k)
-    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
+        clocks.wait_started()
+        for k in range(args.warmup):
+            step(k)
         barrier()
+        t_begin = time.perf_counter()
         e0.record()
         for k in range(args.steps):
             step(k)
         e1.record()
         barrier()
+        t_end = time.perf_counter()
     ms = max_over_ranks(e0.elapsed_time(e1))
     value = world * args.nworld * args.steps / (ms * 1e-3)
     niter = np.concatenate([dd.solver_niter.cpu().numpy() for dd in dev])
@@ -458,7 +475,7 @@ def main():
             "dtype": "f32",
             "data": "synthetic",
             "config": workload_config(args, m_host, host[0][1]),
-            "clocks": clocks.summary(),
+            "clocks": clocks.summary(t_begin, t_end),
             "e2e": e2e,
             "gpu_launches": 2 * args.steps,
             "roofline": {
