@@ -186,6 +186,29 @@ def test_padded_strides_are_read_from_the_arrays(oracle, cuda_device, name, worl
     assert np.array_equal(dd.efc.force.cpu().numpy()[live], want.efc.force[live])
 
 
+def test_iteration_limits_set_overflow_bits_and_warn_when_asked(oracle, cuda_device, capfd):
+    """newton_fusion.py:284-293, newton_stages.py:435-439: hitting the iteration or
+    line-search limit ORs the upstream overflow bits into d.overflow; the device prints
+    the upstream messages only when opt.warn_overflow has the bit."""
+    import torch
+
+    m, d, _ = synthetic.make_workload("humanoid", 64, seed=23, iterations=1, ls_iterations=1)
+    m.opt.warn_overflow = 3
+    want, _, _ = run_oracle(oracle, m, d)
+    got, _, _, _ = run_cuda(m, d, cuda_device)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(got.overflow, want.overflow)
+    assert (got.overflow & 1).any() and (got.overflow & 2).any()
+    out = capfd.readouterr().out
+    assert "solver iterations limit reached - please increase iterations to 1" in out
+    assert "linesearch iterations limit reached - please increase ls_iterations to 1" in out
+    m.opt.warn_overflow = 0
+    quiet, _, _, _ = run_cuda(m, d, cuda_device)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(quiet.overflow, want.overflow)
+    assert "limit reached" not in capfd.readouterr().out
+
+
 def test_repeated_solves_are_bitwise_identical(cuda_device):
     """tests/test_mjw_newton_fusion.py:290-346: eight solves, identical qacc."""
     m, d, _ = synthetic.make_workload("snu", 64, seed=29, iterations=3, ls_iterations=50)
