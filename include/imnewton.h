@@ -344,6 +344,17 @@ typedef struct ImnLaunchInfo {
 int imn_launch_info(const ImnModel* m, const ImnData* d, const ImnCtx* ctx,
                     ImnLaunchInfo* out);
 
+/* Failure detection of the input copies (no counterpart in the reference, whose
+ * Warp kernels use plain loads).  A world's inputs arrive by TMA bulk copies on an
+ * mbarrier; a world waits at most `polls` polls for them (default 1 << 22), then
+ * ORs bit 30 into its `overflow` word, waits once more with the same limit for the
+ * copies in flight and returns with no result written.  `withhold_copies` is the
+ * host-side fault injection of that path: bit 0 makes the initial load, bit 1 the
+ * streamed row tiles, bring their data with plain loads while the barrier is still
+ * told to expect bytes, so that the wait runs out although nothing is in flight.
+ * Process-wide; read when a launch is planned.  Pass (1 << 22, 0) to restore. */
+int imn_set_copy_wait_limit(int32_t polls, int32_t withhold_copies);
+
 /* Text of the last validation failure on the calling thread. */
 const char* imn_last_error(void);
 int imn_abi_version(void);

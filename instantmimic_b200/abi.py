@@ -219,6 +219,7 @@ SYMBOLS = {
         C.c_int,
         [C.POINTER(ImnModel), C.POINTER(ImnData), C.POINTER(ImnCtx), C.POINTER(ImnLaunchInfo)],
     ),
+    "imn_set_copy_wait_limit": (C.c_int, [I32, I32]),
     "imn_last_error": (C.c_char_p, []),
     "imn_abi_version": (C.c_int, []),
 }

@@ -53,7 +53,16 @@ struct Geom {
   int jrows;  // rows of J held in shared memory (njmax when resident, else 32)
   // offsets in 4-byte words; every region starts on a 16-byte boundary
   int oBar, oJ, oA, oVec, nv4, oM, oRowF, oRowI, r4, oUni, total;
+  // polls a copy wait may take before the world gives up, and the failure-path test
+  // switch: when set no bulk copy is issued (plain loads bring the data) while the
+  // barrier is told to expect bytes, so the wait runs out with nothing in flight
+  int wait_polls, withhold_copies;
 };
+
+// Set by imn_set_copy_wait_limit; read when a launch is planned.
+static int g_wait_polls = 1 << 22;
+static int g_withhold_copies = 0;
+
 
 static inline int up4(int n) { return (n + 3) & ~3; }
 
@@ -81,6 +90,8 @@ static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident, const 
   g.oRowI = o, o += up4(3 * g.r4 / 2);  // three 16-bit row lists
   g.oUni = o, o += up4(m.nv + 1);
   g.total = o;
+  g.wait_polls = g_wait_polls;
+  g.withhold_copies = g_withhold_copies;
   return g;
 }
 
@@ -121,6 +132,7 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
   s.jbar = bar;
   s.jphase = reinterpret_cast<int*>(smem + g.oBar) + 2;  // the barrier itself takes two words
   s.jfail = s.jphase + 1;
+  s.wait_polls = g.wait_polls, s.withhold_copies = g.withhold_copies;
   s.Hp = s.A;
   s.N = s.A + (SPARSE ? ((sp.nfac + 3) & ~3) : 0);
   s.iD = s.N + (SPARSE ? ((sp.nslots + 3) & ~3) : 0);
@@ -161,22 +173,23 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
       *s.jfail = 0;
     }
     __syncwarp();
+    const bool bulk = !(g.withhold_copies & 1);
     uint32_t tx = 0;
 #pragma unroll
     for (int k = 0; k < 7; ++k)
-      if ((reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0) tx += (uint32_t)(srcs[k].n & ~3) * 4u;
+      if (bulk && (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0) tx += (uint32_t)(srcs[k].n & ~3) * 4u;
     if (lane == 0) {
-      mbar_expect_tx(bar, tx);
+      mbar_expect_tx(bar, bulk ? tx : 16u);
 #pragma unroll
       for (int k = 0; k < 7; ++k) {
         const uint32_t bytes =
-            (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0 ? (uint32_t)(srcs[k].n & ~3) * 4u : 0u;
+            bulk && (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0 ? (uint32_t)(srcs[k].n & ~3) * 4u : 0u;
         if (bytes) bulk_g2s(srcs[k].dst, srcs[k].src, bytes, bar);
       }
     }
 #pragma unroll
     for (int k = 0; k < 7; ++k) {
-      const int done_n = (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0 ? (srcs[k].n & ~3) : 0;
+      const int done_n = bulk && (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0 ? (srcs[k].n & ~3) : 0;
 #pragma unroll 1
       for (int i = done_n + lane; i < srcs[k].n; i += 32) srcs[k].dst[i] = srcs[k].src[i];
     }
@@ -184,11 +197,15 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
     for (int i = lane; i < nv; i += 32) s.search[i] = 0.0f, s.mv[i] = 0.0f, s.grad[i] = 0.0f;
 #pragma unroll 1
     for (int i = lane; i <= nv; i += 32) s.uni[i] = 0;
-    // bounded wait for the copies
+    // bounded wait for the copies; when it runs out the copies get one more bounded wait
+    // (they write this CTA's shared memory, which the SM hands to the next CTA once
+    // this one is gone), then the world is left unsolved with the time-out bit set
     bool arrived = false;
 #pragma unroll 1
-    for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) arrived = mbar_try_wait(bar, 0);
+    for (int tries = 0; tries < g.wait_polls && !arrived; ++tries) arrived = mbar_try_wait(bar, 0);
     if (!arrived) {
+#pragma unroll 1
+      for (int tries = 0; tries < g.wait_polls && !arrived; ++tries) arrived = mbar_try_wait(bar, 0);
       if (lane == 0) d.overflow[w] |= IMN_OVERFLOW_COPY_TIMEOUT;
       return;
     }
@@ -209,16 +226,6 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
   // Every later pass is one Newton iteration (newton_fusion.py:170-296).
 #pragma unroll 1
   for (bool first = true;; first = false) {
-    if (!JRES && *s.jfail) {
-      // a tile copy did not complete within its wait limit: give it one more bounded
-      // wait (it writes this CTA's shared memory), then leave the world unsolved
-      const uint32_t parity = (uint32_t)*s.jphase ^ 1u;
-      bool arrived = false;
-#pragma unroll 1
-      for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) arrived = mbar_try_wait(bar, parity);
-      if (lane == 0) d.overflow[w] |= IMN_OVERFLOW_COPY_TIMEOUT;
-      return;
-    }
     // one call site: Ma = M qacc, Jaref = J qacc - aref on pass 0; mv = M search,
     // jv = J search afterwards
     if (first || !search_unchanged)
@@ -261,7 +268,11 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
         s.force[r] = f;
         s.state[r] = ns;
         if (first) s.jv[r] = 0.0f;  // aref no longer needed
-        flip = !first && (old == IMN_STATE_QUADRATIC) != (ns == IMN_STATE_QUADRATIC);
+        // pass 0 lists every QUADRATIC row (the rows of the full Hessian, whatever their
+        // force: a row at Jaref == 0 has no force but still carries D J^T J); later
+        // passes list the rows whose QUADRATIC membership flipped
+        flip = first ? ns == IMN_STATE_QUADRATIC
+                     : (old == IMN_STATE_QUADRATIC) != (ns == IMN_STATE_QUADRATIC);
         changed = old != ns;
       }
       const unsigned below = (1u << lane) - 1u;
@@ -302,9 +313,9 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
       grad_scale = 1.0f;
       if (first) {
         if (SPARSE)
-          assemble_hessian_sparse<JRES>(s, nfr, sp);
+          assemble_hessian_sparse<JRES>(s, quad_count, sp);
         else
-          assemble_hessian<JRES>(s, nfr);
+          assemble_hessian<JRES>(s, quad_count);
       } else if (quad_count > 0) {
         update_hessian<JRES, SPARSE>(s, quad_count, sp);
       }
@@ -331,6 +342,17 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
         factor_solve(s, first || quad_count > 0, search_dot, decrement);
       }
       PROF(10);
+    }
+    if (!JRES && *s.jfail) {
+      // a tile copy of this pass did not complete within its wait limit, so the pass
+      // worked on stale rows: give the copy one more bounded wait (it writes this
+      // CTA's shared memory), then leave the world unsolved, results unwritten
+      const uint32_t parity = (uint32_t)*s.jphase ^ 1u;
+      bool arrived = false;
+#pragma unroll 1
+      for (int tries = 0; tries < g.wait_polls && !arrived; ++tries) arrived = mbar_try_wait(bar, parity);
+      if (lane == 0) d.overflow[w] |= IMN_OVERFLOW_COPY_TIMEOUT;
+      return;
     }
     if (first) {
       quad_count = 0, state_count = 0;
@@ -526,11 +548,7 @@ static int worlds_per_sm(int bytes) {
 static int plan_launch(const ImnModel* m, const ImnData* d, const ImnSparsePlan* sp, Geom* g, bool* resident) {
   const Geom gr = make_geom(*m, *d, true, sp);
   const Geom gs = make_geom(*m, *d, false, sp);
-#ifdef IMN_FORCE_STREAM
-  const bool fits = false;
-#else
   const bool fits = gr.total * 4 <= kResidentBudget;
-#endif
   if (fits && 10 * worlds_per_sm(gs.total * 4) < 16 * worlds_per_sm(gr.total * 4)) {
     *g = gr, *resident = true;
     return IMN_OK;
@@ -554,15 +572,14 @@ extern "C" int imn_debug_profile(unsigned long long* out, int reset) {
   }
   return 0;
 }
-extern "C" int imn_debug_occupancy(int bytes, int resident) {
-  int n = 0;
-  if (resident)
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel_resident<false>, 32, bytes);
-  else
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, imn::newton_kernel_streamed<false>, 32, bytes);
-  return n;
-}
 #endif
+
+extern "C" int imn_set_copy_wait_limit(int32_t polls, int32_t withhold_copies) {
+  if (polls <= 0) return imn::set_error("imn_set_copy_wait_limit: polls must be positive"), IMN_ERR_SHAPE;
+  imn::g_wait_polls = polls;
+  imn::g_withhold_copies = withhold_copies & 3;
+  return IMN_OK;
+}
 
 extern "C" int imn_launch_info(const ImnModel* m, const ImnData* d, const ImnCtx* cx, ImnLaunchInfo* out) {
   if (!out) return imn::set_error("imn_launch_info: NULL out"), IMN_ERR_NULL;
@@ -589,11 +606,7 @@ extern "C" int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* cx, 
   bool res;
   rc = imn::plan_launch(m, d, cx->sparse_plan, &g, &res);
   if (rc) return rc;
-#ifdef IMN_PAD_SMEM  // experiment: fewer resident worlds per SM
-  const int bytes = g.total * 4 + IMN_PAD_SMEM;
-#else
   const int bytes = g.total * 4;
-#endif
   auto kern = cx->sparse_plan
                   ? (res ? imn::newton_kernel_resident<true> : imn::newton_kernel_streamed<true>)
                   : (res ? imn::newton_kernel_resident<false> : imn::newton_kernel_streamed<false>);

@@ -23,10 +23,12 @@ struct World {
   const float* Jg;    // this world's J in global memory
   const float *Jbeg, *Jend;  // first element and one past the last row of the whole J array
   // streamed J: the copy barrier of the row tile, the parity of its next phase and the
-  // flag a timed-out copy raises (all in shared memory)
+  // flag a timed-out copy raises (all in shared memory); wait limit in polls and the
+  // failure-path test switch that withholds the copies
   void* jbar;
   int* jphase;
   int* jfail;
+  int wait_polls, withhold_copies;
   const int* mulm_rowadr;
   const uint32_t* mulm_pack;
   // sparse plan only: packed H, N = L D with the carried row, 1/D, the world's
@@ -59,23 +61,27 @@ __device__ __forceinline__ const float* j_tile(const World& s, int base) {
   // array) and the tile starts `head` floats into the buffer.
   const int head = (int)((reinterpret_cast<uintptr_t>(src) & 15) >> 2);
   const uint32_t bytes = (uint32_t)((head + n + 3) & ~3) * 4u;
-  if (src - head >= s.Jbeg && src - head + (bytes >> 2) <= s.Jend) {
+  // after a copy that timed out the barrier's phase is unknown: the world is lost (the
+  // caller checks jfail at the end of the pass) and the rest of the pass uses plain loads
+  if (src - head >= s.Jbeg && src - head + (bytes >> 2) <= s.Jend && !*s.jfail) {
     const uint32_t parity = (uint32_t)*s.jphase;
     __syncwarp();
     if (s.lane == 0) {
       mbar_expect_tx(s.jbar, bytes);
-      bulk_g2s(s.Jsm, src - head, bytes, s.jbar);
+      if (!(s.withhold_copies & 2)) bulk_g2s(s.Jsm, src - head, bytes, s.jbar);
       *s.jphase = (int)(parity ^ 1u);
     }
     bool arrived = false;
 #pragma unroll 1
-    for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) arrived = mbar_try_wait(s.jbar, parity);
+    for (int tries = 0; tries < s.wait_polls && !arrived; ++tries) arrived = mbar_try_wait(s.jbar, parity);
     if (!arrived && s.lane == 0) *s.jfail = 1;
     __syncwarp();
     return s.Jsm + head;
   }
 #pragma unroll 4
   for (int i = s.lane; i < n; i += 32) s.Jsm[i] = src[i];
+  // the next tile may arrive through the async proxy into the same buffer
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   __syncwarp();
   return s.Jsm;
 }
@@ -164,8 +170,10 @@ __device__ __forceinline__ float full_gradient(const World& s, int nfr) {
 
 // H = M + J^T diag(D, QUADRATIC rows) J on the upper triangle, every entry summing
 // its rows in ascending order.  H[r][c] (r <= c) lives at A[(c+1)*ldu + r].
+// The QUADRATIC rows arrive as the ascending list s.ids[0, nq) (built by the row
+// update of the initial pass).
 template <bool JRES>
-__device__ __forceinline__ void assemble_hessian(const World& s, int nfr) {
+__device__ __forceinline__ void assemble_hessian(const World& s, int nq) {
   const int lane = s.lane, nv = s.nv, ldu = s.ldu;
   float* A = s.A;
 #pragma unroll 4
@@ -184,17 +192,6 @@ __device__ __forceinline__ void assemble_hessian(const World& s, int nfr) {
   }
   __syncwarp();
   const int npair = nv * (nv + 1) / 2;
-  // the QUADRATIC rows with a force, ascending, compacted into s.ids (unused during the
-  // initial pass)
-  int nq = 0;
-#pragma unroll 1
-  for (int a = 0; a < nfr; ++a) {
-    const int r = s.frows[a];
-    if (s.state[r] != IMN_STATE_QUADRATIC) continue;
-    if (lane == 0) s.ids[nq] = r;
-    ++nq;
-  }
-  __syncwarp();
   // six entries per lane at a time: a row's D is read once per six entries and the six
   // running sums overlap; every entry still receives its rows in ascending order
   constexpr int Q = 6;
@@ -316,18 +313,13 @@ __device__ __forceinline__ void update_hessian(const World& s, int count, const 
 // the pattern (sparse_hessian.py:571-637).  Leaves the packed H in both N and Hp.
 // A lane keeps the running sums of ten slots in registers and walks the QUADRATIC
 // rows once per ten slots: the row's D is read once, and ten independent sums overlap
-// their latencies.  The row list is compacted into s.ids first (unused during the
-// initial pass).
+// their latencies.  The QUADRATIC rows arrive as the ascending list s.ids[0, nq).
 template <bool JRES>
-__device__ __forceinline__ void assemble_hessian_sparse(const World& s, int nfr, const ImnSparsePlan& SP) {
+__device__ __forceinline__ void assemble_hessian_sparse(const World& s, int nq, const ImnSparsePlan& SP) {
   const int lane = s.lane, nv = s.nv, nfac = SP.nfac, words = (nv + 31) >> 5;
-  int nq = 0;
 #pragma unroll 1
-  for (int a = 0; a < nfr; ++a) {
-    const int r = s.frows[a];
-    if (s.state[r] != IMN_STATE_QUADRATIC) continue;
-    if (lane == 0) s.ids[nq] = r;
-    ++nq;
+  for (int a = 0; a < nq; ++a) {
+    const int r = s.ids[a];
     if (s.Dsm[r] == 0.0f) continue;
     unsigned rm[3] = {0u, 0u, 0u};
 #pragma unroll

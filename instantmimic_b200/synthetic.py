@@ -50,22 +50,35 @@ def humanoid_tree():
     return _tree_from_joints(joints)
 
 
-def snu_like_tree():
-    """Shape stand-in for the SNU muscle humanoid (nv 56: free root, 14 ball joints,
-    8 hinges; data/snu_humanoid/mjcf/include/body.xml:52-897)."""
-    joints = [(6, -1)]
-    # spine: 3 balls, then neck and head balls
-    joints += [(3, 0), (3, 1), (3, 2), (3, 3), (3, 4)]
-    # arms off the upper spine: clavicle ball, shoulder ball, elbow hinge, wrist hinge
-    for _ in range(2):
-        base = len(joints)
-        joints += [(3, 3), (3, base), (1, base + 1), (1, base + 2)]
-    # legs off the pelvis: hip ball, knee hinge, ankle ball, toe hinge
-    for _ in range(2):
-        base = len(joints)
-        joints += [(3, 0), (1, base), (3, base + 1), (1, base + 2)]
-    # 5 + 2*2 + 2*2 = 13 balls so far; one more ball (jaw) and 0 more hinges: 8 hinges
-    joints += [(3, 5)]
+def snu_tree():
+    """The SNU muscle humanoid's joint tree, transcribed from
+    data/snu_humanoid/mjcf/include/body.xml:50-897 (bodies in document order, which
+    is MuJoCo's body order): free root, 14 ball joints, 8 hinges, nv 56."""
+    joints = [
+        (6, -1),  # 0 Pelvis (free)
+        (3, 0),  # 1 FemurR
+        (1, 1),  # 2 TibiaR
+        (3, 2),  # 3 TalusR
+        (1, 3),  # 4 FootThumbR
+        (1, 3),  # 5 FootPinkyR
+        (3, 0),  # 6 FemurL
+        (1, 6),  # 7 TibiaL
+        (3, 7),  # 8 TalusL
+        (1, 8),  # 9 FootThumbL
+        (1, 8),  # 10 FootPinkyL
+        (3, 0),  # 11 Spine
+        (3, 11),  # 12 Torso
+        (3, 12),  # 13 Neck
+        (3, 13),  # 14 Head
+        (3, 12),  # 15 ShoulderR
+        (3, 15),  # 16 ArmR
+        (1, 16),  # 17 ForeArmR
+        (3, 17),  # 18 HandR
+        (3, 12),  # 19 ShoulderL
+        (3, 19),  # 20 ArmL
+        (1, 20),  # 21 ForeArmL
+        (3, 21),  # 22 HandL
+    ]
     parent, body = _tree_from_joints(joints)
     assert parent.size == 56, parent.size
     return parent, body
@@ -271,7 +284,7 @@ def make_problem(
 WORKLOADS = {
     # name: (tree, njmax, nefc_range, iterations, ls_iterations)
     "humanoid": (humanoid_tree, 64, (16, 64)),
-    "snu": (snu_like_tree, 128, (24, 128)),
+    "snu": (snu_tree, 128, (24, 128)),
     "g1": (g1_like_tree, 250, (16, 200)),
 }
 

@@ -59,6 +59,12 @@ def main():
     m = put_model(parent, body_of_dof=body, iterations=100, ls_iterations=50)
     d, _ = synthetic.make_problem(m, 6, 48, seed=13, ne=3, nf=5, nefc_range=(8, 48))
     newton_case("eq_friction", m, d)
+    # worlds at rest: aref = 0 and a zero warm start make Jaref exactly 0, so equality and
+    # friction-loss rows are QUADRATIC with a force of exactly 0 and still enter the Hessian
+    d, _ = synthetic.make_problem(m, 6, 48, seed=15, ne=4, nf=5, nefc_range=(12, 48))
+    d.efc.aref[:] = 0.0
+    d.qacc_warmstart[:] = 0.0
+    newton_case("at_rest", m, d)
 
     # M-side: tree L'DL (1 and 4 groups) and blocked dense (3 right-hand sides)
     parent, body = synthetic.humanoid_tree()

@@ -67,6 +67,13 @@ def test_validation_rejects_bad_calls_before_any_launch():
     assert lib.imn_blocked_dense_factor_solve(C.byref(bp), p, 0, p, p, p, None, 1, 1, 1, None) == abi.IMN_ERR_SHAPE
 
 
+def test_copy_wait_limit_is_validated():
+    lib = _lib.lib()
+    assert lib.imn_set_copy_wait_limit(0, 0) == abi.IMN_ERR_SHAPE
+    assert b"positive" in lib.imn_last_error()
+    assert lib.imn_set_copy_wait_limit(1 << 22, 0) == 0
+
+
 def test_launch_info_reports_geometry_without_a_gpu():
     """Host-only: which kernel variant and how much shared memory a model gets."""
     import numpy as np

@@ -34,7 +34,7 @@ def _check_solution(d, out, what):
 
 
 def test_fixture_folder_is_complete():
-    assert NEWTON == ["newton_eq_friction.npz", "newton_humanoid.npz", "newton_snu.npz"]
+    assert NEWTON == ["newton_at_rest.npz", "newton_eq_friction.npz", "newton_humanoid.npz", "newton_snu.npz"]
     assert (GOLDEN / "msolve_humanoid.npz").exists() and (GOLDEN / "make_golden.py").exists()
 
 
