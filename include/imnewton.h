@@ -307,7 +307,9 @@ int imn_blocked_dense_factor_solve(const ImnBlockedPlan* plan, const float* M,
  *     IMN_ERR_LIMIT is returned and nothing runs;
  *   - the first call on each device looks up the array's device address
  *     (cudaGetSymbolAddress with that device current); make that first call
- *     outside any stream capture;
+ *     outside any stream capture; the address is cached per device (first calls
+ *     from several host threads are safe) and belongs to the device's primary
+ *     context: it does not survive cudaDeviceReset;
  *   - all calls share the one array and it keeps the last call's factor: two
  *     calls whose kernels overlap on the GPU (different streams) race, and the
  *     stored factor cannot be reused by a later solve-only call;

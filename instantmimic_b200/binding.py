@@ -41,18 +41,18 @@ def _mulm_pack(m: Any):
     if pack is None:
         import numpy as np
 
+        from .arrays import device_of, to_host
         from .mjw_model import pack_mulm
 
         col, madr = m.M_mulm_col, m.M_mulm_madr
-        to_np = lambda a: a.numpy() if hasattr(a, "numpy") and not hasattr(a, "data_ptr") else (  # noqa: E731
-            a.cpu().numpy() if hasattr(a, "cpu") else np.asarray(a))
-        host = pack_mulm(to_np(col), to_np(madr))
+        host = pack_mulm(to_host(col), to_host(madr))
         if isinstance(col, np.ndarray):
             pack = host
         else:
             import torch
 
-            pack = torch.from_numpy(host).to("cuda")
+            # on the device that holds the model's tables, not torch's current one
+            pack = torch.from_numpy(host).to(device_of(col))
         try:
             m._imn_mulm_pack = pack
         except AttributeError:
@@ -116,16 +116,21 @@ def data_struct(m: Any, d: Any) -> abi.ImnData:
         [d.qacc_smooth, d.qacc_warmstart, d.qfrc_smooth, d.qacc, d.qfrc_constraint, d.efc.Ma],
     )
     s.efc_J = addr(d.efc.J)
-    js = elem_strides(d.efc.J)
-    if js[2] != 1:
-        raise ValueError("efc.J needs a unit innermost stride")
-    s.J_ld_world, s.J_ld_row = js[0], js[1]
+    if s.njmax > 0:
+        js = elem_strides(d.efc.J)
+        if js[2] != 1:
+            raise ValueError("efc.J needs a unit innermost stride")
+        s.J_ld_world, s.J_ld_row = js[0], js[1]
+        s.efc_ld = _same_ld(
+            "efc", [d.efc.D, d.efc.aref, d.efc.frictionloss, d.efc.force, d.efc.state]
+        )
+    else:
+        # a model without constraint storage: the row arrays are empty, their strides
+        # carry no information, and only the rowless hand-off may be called
+        s.J_ld_world = s.J_ld_row = s.efc_ld = 0
     s.efc_D = addr(d.efc.D)
     s.efc_aref = addr(d.efc.aref)
     s.efc_frictionloss = addr(d.efc.frictionloss)
-    s.efc_ld = _same_ld(
-        "efc", [d.efc.D, d.efc.aref, d.efc.frictionloss, d.efc.force, d.efc.state]
-    )
     s.M = addr(d.M)
     s.M_ld = _row_ld(d.M)
     s.qacc = addr(d.qacc)

@@ -15,6 +15,8 @@
 // memory, factors it (same entry formula as the Newton Hessian factor), carries
 // `rhs_count` right-hand sides through the forward and backward substitution and
 // stores U (pad x pad, upper) in the caller's workspace.
+#include <atomic>
+
 #include "imn_common.cuh"
 
 namespace imn {
@@ -362,22 +364,25 @@ static __device__ __align__(256) float g_static_factor[IMN_STATIC_FACTOR_FLOATS]
 
 // Device address of g_static_factor per CUDA device.  In host code the array's name is
 // only a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked
-// once per device with that device current.
-static float* g_static_factor_ptr[64] = {nullptr};
+// once per device with that device current.  The slots are atomics: two host threads
+// that make the first call on a device at the same time both look the address up and
+// store the same value.  A cached address belongs to the device's primary context; it
+// does not survive cudaDeviceReset (after a reset, reload the library).
+static std::atomic<float*> g_static_factor_ptr[64];
 
 static int static_factor_workspace(float** out) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return set_error("static workspace: cudaGetDevice: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
   if (dev < 0 || dev >= 64) return set_error("static workspace: device index %d out of range", dev), IMN_ERR_LIMIT;
-  if (!g_static_factor_ptr[dev]) {
-    float* ptr = nullptr;
+  float* ptr = g_static_factor_ptr[dev].load(std::memory_order_acquire);
+  if (!ptr) {
     e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_factor);
     if (e != cudaSuccess || !ptr)
       return set_error("static workspace: cudaGetSymbolAddress: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
-    g_static_factor_ptr[dev] = ptr;
+    g_static_factor_ptr[dev].store(ptr, std::memory_order_release);
   }
-  *out = g_static_factor_ptr[dev];
+  *out = ptr;
   return IMN_OK;
 }
 

@@ -18,7 +18,7 @@ from typing import Any
 import numpy as np
 
 from .. import _lib, abi
-from ..arrays import addr, elem_strides
+from ..arrays import addr, elem_strides, is_contiguous, to_host
 
 # Small blocked tiles avoid the long dependency chain of a full-matrix tile
 # (mjw_step_optimized.py:868-872).
@@ -47,8 +47,7 @@ def dense_index_table(m: Any) -> np.ndarray:
     """(nv, nv) table of M's CSR entry for every dense position (nM where the
     matrix is structurally zero): upstream's ``M_tiles[0].elemid`` for a model whose
     inertia matrix is one dense tile."""
-    to_np = lambda a: a if isinstance(a, np.ndarray) else a.cpu().numpy()  # noqa: E731
-    rowadr, rownnz, colind = (to_np(getattr(m, n)) for n in ("M_rowadr", "M_rownnz", "M_colind"))
+    rowadr, rownnz, colind = (to_host(getattr(m, n)) for n in ("M_rowadr", "M_rownnz", "M_colind"))
     nv, nM = int(m.nv), int(colind.shape[0])
     table = np.full((nv, nv), nM, np.int32)
     for k in range(nv):
@@ -108,7 +107,7 @@ def create_blocked_dense_factor_solve_scratch(
 
 def _launch(scratch, M, y, U, x, active, nworld, rhs_count, mode, stream):
     for name, a in (("y", y), ("x", x), ("U", U)):
-        if not a.is_contiguous():
+        if not is_contiguous(a):
             raise ValueError(f"blocked dense factor/solve needs a contiguous {name}")
     rc = _lib.lib().imn_blocked_dense_factor_solve(
         C.byref(scratch.struct),

@@ -66,6 +66,24 @@ def eligible(m: Any, ctx: Any, *, compact: bool = False) -> bool:
     )
 
 
+def ineligible_reasons(m: Any, ctx: Any, *, compact: bool = False) -> list[str]:
+    """The gates of ``eligible`` that this model fails, in words."""
+    checks = [
+        (not compact, "compact (sleeping-island) solve"),
+        (_on_cuda(m), "model buffers are not on a CUDA device"),
+        (0 < m.nv <= 79, f"nv {m.nv} outside 1..79"),
+        (m.nv_pad % 16 == 0 and m.nv_pad <= 80, f"nv_pad {m.nv_pad} is not a multiple of 16 up to 80"),
+        (_use_incremental(m), "solver is not Newton"),
+        (int(m.opt.integrator) != int(types.IntegratorType.DISCRETE), "DISCRETE integrator"),
+        (int(m.opt.cone) == int(types.ConeType.PYRAMIDAL), "elliptic friction cones"),
+        (not m.is_sparse, "sparse constraint Jacobian"),
+        (not _sparse_compact(ctx), "sparse-compact solver context"),
+        (m.opt.iterations > 0, "opt.iterations is 0"),
+        (m.block_dim.linesearch_iterative == 32, "line-search block width is not 32"),
+    ]
+    return [why for ok, why in checks if not ok]
+
+
 def newton_block_dim(m: Any) -> int:
     """Logical block width of one world (newton_fusion.py:325-327).  It fixes the
     order of the per-thread partial sums; the CUDA kernel reproduces that order
@@ -111,23 +129,28 @@ class SolveCall:
         _lib.check(rc, "imn_solve")
 
 
+_KEY_DATA = ("nefc", "ne", "nf", "qacc_smooth", "qacc_warmstart", "qfrc_smooth", "M", "qacc",
+             "qfrc_constraint", "solver_niter", "overflow")
+_KEY_EFC = ("J", "D", "aref", "frictionloss", "force", "state", "Ma")
+_KEY_CTX = ("Jaref", "jv", "search", "mv", "grad", "h", "hfactor", "quad_changed_ids", "newton_dof_union",
+            "world_order") + binding._CTX_WORLD_ARRAYS
+
+
 def _key(m, d, ctx, nsolving):
+    """Everything the cached structs were built from: the address of every buffer the
+    kernel is handed and the scalar options.  A caller that rebinds any of them gets
+    fresh structs instead of stale pointers."""
     from ..arrays import addr
 
     plan = getattr(ctx, "sparse_hessian_plan", None)
     return (
-        id(m),
-        id(d),
-        id(ctx),
-        addr(d.efc.J),
-        addr(d.qacc),
-        addr(d.M),
-        addr(nsolving),
-        int(m.opt.iterations),
-        int(m.opt.ls_iterations),
-        int(m.opt.disableflags),
-        int(d.nworld),
-        id(plan),
+        id(m), id(d), id(ctx), id(plan), addr(nsolving),
+        tuple(addr(getattr(d, n)) for n in _KEY_DATA),
+        tuple(addr(getattr(d.efc, n)) for n in _KEY_EFC),
+        tuple(addr(getattr(ctx, n, None)) for n in _KEY_CTX),
+        addr(m.opt.tolerance), addr(m.opt.ls_tolerance), addr(m.stat.meaninertia),
+        int(m.opt.iterations), int(m.opt.ls_iterations), int(m.opt.disableflags),
+        int(getattr(m.opt, "warn_overflow", 0) or 0), int(d.nworld), int(d.njmax),
     )
 
 

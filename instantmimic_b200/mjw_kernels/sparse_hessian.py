@@ -57,11 +57,9 @@ class SparseHessianPlan:
 def _np(a):
     if a is None:
         return None
-    if isinstance(a, np.ndarray):
-        return a
-    if hasattr(a, "cpu"):
-        return a.cpu().numpy()
-    return a.numpy()
+    from ..arrays import to_host
+
+    return to_host(a)
 
 
 def _chain(body: int, body_parentid, body_dofadr, body_dofnum) -> list[int]:
@@ -414,8 +412,10 @@ def violation_counter(hfactor: Any, plan: SparseHessianPlan):
     (sparse_hessian.py:786-801)."""
     if plan.path != "fused":
         raise ValueError("the violation counter exists on the fused path only")
+    from ..arrays import as_torch
+
     last = plan.nv_pad - 1
-    return hfactor[:, last, last]
+    return as_torch(hfactor)[:, last, last]
 
 
 def violations(hfactor: Any, plan: SparseHessianPlan) -> np.ndarray:

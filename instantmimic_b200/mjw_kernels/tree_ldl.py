@@ -356,11 +356,9 @@ def scratch_for_plan(structure, plan: TreeLdlPlan, device: Any, generate: bool =
 
 
 def _to_numpy(a):
-    if isinstance(a, np.ndarray):
-        return a
-    if hasattr(a, "cpu"):
-        return a.cpu().numpy()
-    return a.numpy()
+    from ..arrays import to_host
+
+    return to_host(a)
 
 
 def create_tree_factor_solve_scratch(m: Any, device: Any = "cuda", generate: bool = True) -> TreeFactorSolveScratch | None:

@@ -10,11 +10,17 @@ a launch of hand-written CUDA through the C ABI; there is no other code path.
 from __future__ import annotations
 
 import ctypes as C
+import logging
 from dataclasses import dataclass
-from typing import Any
+from typing import Any, Sequence
+
+import numpy as np
 
 from . import _lib, binding
+from .arrays import to_host
 from .mjw_kernels import newton_fusion
+
+logger = logging.getLogger(__name__)
 
 
 class SolverContext:
@@ -57,6 +63,89 @@ class OptimizedFwdPositionScratch:
     dense_factor_solve: Any = None
     tree_factor_solve: Any = None
     unroll_solver_iterations: bool = False
+    # single-tile factor/solve of M for models below the blocked kernel's dof count
+    # that have no tree plan (the reference's per-tile kernels, :672-750, 793-838)
+    tile_factor_solve: Any = None
+
+
+def _constraint_rows_impossible(m: Any, ball_joint_limits: Sequence[Any] = ()) -> bool:
+    """True when the constraint producer can never emit a row for this model, so that
+    MuJoCo's ``nefc == 0`` result holds on every step (mjw_step_optimized.py:116-147).
+
+    Rows can come from equalities, friction loss (dofs, tendons), joint and tendon
+    limits, contacts of any candidate geom pair, flexes, collision sensors and the
+    caller's ball-joint limit rows.  The answer is True only when the model states the
+    absence of each of them; a model that lacks one of the fields (this package's
+    stand-in ``Model`` carries none) keeps the general path."""
+    opt = getattr(m, "opt", None)
+    if opt is None or not getattr(opt, "run_collision_detection", False):
+        return False
+    if ball_joint_limits or _solver_compact_enabled(m):
+        return False
+    for count in ("neq", "nflex", "nsensorcollision"):
+        if int(getattr(m, count, 1)):
+            return False
+    for name in ("jnt_limited_slide_hinge_adr", "jnt_limited_ball_adr", "tendon_limited_adr"):
+        rows = getattr(m, name, None)
+        if rows is None or int(np.size(to_host(rows))):
+            return False
+    for name in ("dof_frictionloss", "tendon_frictionloss"):
+        loss = getattr(m, name, None)
+        if loss is None:
+            return False
+        loss = to_host(loss)
+        if loss.size and bool((loss > 0.0).any()):
+            return False
+    pairs = getattr(m, "nxn_pairid_filtered", None)
+    if pairs is None:
+        return False
+    # a pair id of -2 in the first column marks a geom pair that is filtered out
+    return not bool((to_host(pairs).reshape(-1, 2)[:, 0] > -2).any())
+
+
+def optimized_kernel_capabilities(m: Any, scratch: "OptimizedFwdPositionScratch", *, enabled: bool = True) -> dict:
+    """Which kernel variants this model gets, without changing any state
+    (mjw_step_optimized.py:2862-2875), extended by the choices this library makes
+    below the reference's granularity."""
+    ctx = getattr(scratch, "solver_context", None)
+    fused = bool(enabled and ctx is not None and newton_fusion.eligible(m, ctx, compact=scratch.solver_uses_compact))
+    plan = getattr(ctx, "sparse_hessian_plan", None) if ctx is not None else None
+    tree = getattr(scratch, "tree_factor_solve", None)
+    return {
+        "tree": False,  # body-tree reductions are not part of this library
+        "indexed_factor": bool(enabled and getattr(scratch, "dense_factor_solve", None) is not None),
+        "persistent_newton": fused,
+        "constraint_free": bool(getattr(scratch, "constraint_free", False)),
+        "hessian_factor": (f"sparse pattern ({plan.path})" if plan is not None else "dense blocked Cholesky") if fused else None,
+        "m_factor_solve": (
+            f"tree L'DL, {tree.groups} group(s), {'generated' if tree.kernel is not None else 'interpreted'} kernel"
+            if tree is not None
+            else "blocked dense Cholesky" if scratch.dense_factor_solve is not None
+            else "single-tile dense Cholesky" if scratch.tile_factor_solve is not None else None
+        ),
+    }
+
+
+def log_kernel_selection(m: Any, d: Any, scratch: "OptimizedFwdPositionScratch") -> str:
+    """One INFO line per model naming the kernel variants chosen (the counterpart of
+    the reference's MJW_KERNEL_PATH / MJW_SPARSE_HESSIAN records,
+    src/instantmimic/envs/direct_rl_env.py:873-884, 2909-2925)."""
+    caps = optimized_kernel_capabilities(m, scratch)
+    parts = [f"nv {int(m.nv)}", f"njmax {int(d.njmax)}", f"nworld {int(d.nworld)}"]
+    if caps["constraint_free"] or d.njmax == 0:
+        parts.append("solve: rowless hand-off (no constraint rows possible)")
+    elif caps["persistent_newton"]:
+        info = newton_fusion.solve_call(m, d, scratch.solver_context, scratch.solver_nsolving,
+                                        cache_on=scratch).launch_info()
+        parts.append(
+            f"solve: fused Newton kernel, J {'resident in shared memory' if info.j_resident else 'streamed in 32-row tiles'}, "
+            f"{info.smem_bytes} B shared memory per world, {caps['hessian_factor']}")
+    else:
+        parts.append("solve: outside the fused path")
+    parts.append(f"M factor/solve: {caps['m_factor_solve']}")
+    line = "IMN_KERNEL_PATH " + "; ".join(parts)
+    logger.info(line)
+    return line
 
 
 def mul_m(m: Any, d: Any, res: Any, vec: Any, stream=None) -> None:
@@ -79,8 +168,10 @@ def make_optimized_fwd_position_scratch(
     *,
     include_optimized_kernel_scratch: bool = True,
     with_matrices: bool = False,
+    ball_joint_limits: Sequence[Any] = (),
 ) -> OptimizedFwdPositionScratch:
-    """Solver context, nsolving counter and the M-side factor/solve plans."""
+    """Solver context, nsolving counter, the M-side factor/solve plans and the
+    ``constraint_free`` decision (mjw_step_optimized.py:2237-2255, 2510-2585)."""
     import torch
 
     from .mjw_kernels import indexed_factor, tree_ldl
@@ -90,17 +181,29 @@ def make_optimized_fwd_position_scratch(
         ctx = SolverContext(m, d, device, with_matrices=with_matrices)
         newton_fusion.attach_scratch(m, d, ctx, device)
         nsolving = torch.zeros((1,), dtype=torch.int32, device=device)
-    return OptimizedFwdPositionScratch(
+    dense = indexed_factor.create_blocked_dense_factor_solve_scratch(m, d, device)
+    tree = tree_ldl.create_tree_factor_solve_scratch(m, device) if include_optimized_kernel_scratch else None
+    tile = None
+    if dense is None and m.nv > 0 and getattr(d, "M", None) is not None:
+        # below the blocked kernel's dof count the reference factors M tile by tile; the
+        # same kernel does it here with one 16- or 32-wide tile per world
+        tile = indexed_factor.create_blocked_dense_factor_solve_scratch(m, d, device, minimum_nv=1)
+    scratch = OptimizedFwdPositionScratch(
         solver_context=ctx,
         solver_nsolving=nsolving,
+        constraint_free=_constraint_rows_impossible(m, ball_joint_limits),
         mul_m_call=mul_m,
-        dense_factor_solve=indexed_factor.create_blocked_dense_factor_solve_scratch(m, d, device),
-        tree_factor_solve=(
-            tree_ldl.create_tree_factor_solve_scratch(m, device)
-            if include_optimized_kernel_scratch
-            else None
-        ),
+        dense_factor_solve=dense,
+        tree_factor_solve=tree,
+        tile_factor_solve=tile,
     )
+    try:
+        m._imn_tile_factor_solve = tile
+    except AttributeError:
+        pass
+    if logger.isEnabledFor(logging.INFO) and newton_fusion._on_cuda(m):
+        log_kernel_selection(m, d, scratch)
+    return scratch
 
 
 def _solver_compact_enabled(m: Any) -> bool:
@@ -145,8 +248,8 @@ def solve_with_scratch(
         raise RuntimeError("compact (sleeping-island) solves are outside this solver's path")
     if not newton_fusion.eligible(m, ctx, compact=False):
         raise RuntimeError(
-            "model is outside the fused Newton path (dense pyramidal Newton, 0 < nv <= 79, "
-            "nv_pad % 16 == 0, CUDA buffers); no other solver path exists here"
+            "model is outside the fused Newton path: " + "; ".join(newton_fusion.ineligible_reasons(m, ctx))
+            + ".  This library has no other solver path: route such models to the upstream solve"
         )
     del use_optimized_kernel
     newton_fusion.solve_call(m, d, ctx, nsolving, cache_on=scratch)(stream)
@@ -167,8 +270,12 @@ def _factor_solve_i_dense(
 ) -> None:
     """x = M^-1 y for M (or M - h qDeriv) in the model's CSR layout, choosing the
     kernel as the reference does (mjw_step_optimized.py:1030-1070): the tree L'DL when
-    a plan exists and no factor has to be kept, else the blocked dense Cholesky.
-    Models with neither (nv < 32 without a tree plan) have no path here and raise."""
+    a plan exists and no factor has to be kept, else the blocked dense Cholesky, else
+    (nv < 32 without a tree plan, e.g. a short hinge chain) the single-tile dense
+    Cholesky that stands in for the reference's per-tile kernels (:793-838).  The tile
+    plan is made by ``make_optimized_fwd_position_scratch`` and remembered on the
+    model; without it the first call builds it, which allocates (call once outside
+    graph capture)."""
     from .mjw_kernels import indexed_factor, tree_ldl
 
     if factor_workspace is not None and dense_factor_solve is None:
@@ -181,7 +288,24 @@ def _factor_solve_i_dense(
             d, M, x, y, dense_factor_solve, factor_workspace=factor_workspace, stream=stream
         )
         return
-    raise RuntimeError("no factor/solve plan for this model (neither tree L'DL nor blocked dense)")
+    if retain_factor:
+        raise RuntimeError("a retained factor requires the blocked dense path (nv >= 32)")
+    from .arrays import is_device
+
+    if not is_device(M):
+        raise RuntimeError("no factor/solve path for host buffers: the M-side kernels need CUDA arrays")
+    tile = getattr(m, "_imn_tile_factor_solve", None)
+    if tile is None or tile.U.shape[0] < d.nworld:
+        from .arrays import device_of
+
+        tile = indexed_factor.create_blocked_dense_factor_solve_scratch(m, d, device_of(M), minimum_nv=1)
+        if tile is None:
+            raise RuntimeError("no factor/solve plan for this model (nv == 0 or no inertia matrix)")
+        try:
+            m._imn_tile_factor_solve = tile
+        except AttributeError:
+            pass
+    indexed_factor.blocked_dense_factor_solve(d, M, x, y, tile, stream=stream)
 
 
 def refresh_sparse_hessian(m: Any, d: Any, scratch: OptimizedFwdPositionScratch, body_groups,

@@ -198,13 +198,15 @@ def make_problem(
     warmstart_scale: float = 0.1,
     poison: bool = False,
     d_range: tuple[float, float] = (0.1, 10.0),
+    couple: bool = True,
 ) -> tuple[Data, np.ndarray]:
     """Seeded solver inputs for ``nworld`` worlds; returns (Data, dense M).
 
     rows = "contacts": inequality rows come in groups of four pyramid edges
     (Jn +- mu Jt1, Jn +- mu Jt2) on the ancestor chain of one random dof, followed by
     single-dof joint-limit rows.  rows = "generic": every row is N(0,1) on the union
-    of the ancestor chains of one or two random dofs.  Rows [0, ne) are equality rows,
+    of the ancestor chains of one or two random dofs (of one only with ``couple=False``, so that every row stays
+    inside the tree-ancestry pattern).  Rows [0, ne) are equality rows,
     [ne, ne+nf) friction-loss rows on single dofs.  ``poison`` fills rows at and
     beyond nefc with NaN so that a kernel that reads them is caught.
     """
@@ -230,7 +232,7 @@ def make_problem(
     if rows == "generic":
         a = rng.integers(0, nv, (nworld, R))
         b = rng.integers(0, nv, (nworld, R))
-        two = rng.random((nworld, R)) < 0.5
+        two = (rng.random((nworld, R)) < 0.5) & couple
         mask = masks[a]
         mask = np.maximum(mask, masks[b] * two[..., None])
         J[:] = rng.normal(0.0, 1.0, (nworld, R, nv)).astype(np.float32) * mask
@@ -315,9 +317,9 @@ def make_workload(
     return m, d, Mdense
 
 
-def make_sweep_point(nv: int, nefc: int, nworld: int, seed: int = 0, **opts):
+def make_sweep_point(nv: int, nefc: int, nworld: int, seed: int = 0, *, couple: bool = True, **opts):
     """One point of the isolated sweep: generic rows, ne = nf = 0, R = nefc."""
     parent, body = limb_tree(nv)
     m = put_model(parent, body_of_dof=body, **opts)
-    d, Mdense = make_problem(m, nworld, nefc, seed, nefc_range=(nefc, nefc), rows="generic")
+    d, Mdense = make_problem(m, nworld, nefc, seed, nefc_range=(nefc, nefc), rows="generic", couple=couple)
     return m, d, Mdense

@@ -105,7 +105,9 @@ def test_solve_with_scratch_error_behaviour():
         runtime.solve_with_scratch(m, d, scratch)
     with pytest.raises(RuntimeError, match="factor workspace requires"):
         runtime._factor_solve_i_dense(m, d, d.M, d.qacc, d.qfrc_smooth, None, factor_workspace=d.M)
-    with pytest.raises(RuntimeError, match="no factor/solve plan"):
+    with pytest.raises(RuntimeError, match="retained factor requires"):
+        runtime._factor_solve_i_dense(m, d, d.M, d.qacc, d.qfrc_smooth, None, retain_factor=True)
+    with pytest.raises(RuntimeError, match="need CUDA arrays"):
         runtime._factor_solve_i_dense(m, d, d.M, d.qacc, d.qfrc_smooth, None)
 
 

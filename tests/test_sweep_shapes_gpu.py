@@ -31,16 +31,13 @@ def test_sweep_shape_dense_factor(oracle, cuda_device, nv, nefc):
 
 @pytest.mark.parametrize("nv,nefc", [s for s in SHAPES if s[0] >= sparse_hessian.MIN_NV])
 def test_sweep_shape_sparse_factor(oracle, cuda_device, nv, nefc):
-    from test_sparse_hessian import _cuda_sparse, _oracle_sparse
+    """Rows on one ancestor chain each stay inside the tree-ancestry pattern, which is
+    what the sparse plan's density gate admits (rows that couple two arbitrary chains
+    need a dense pattern, for which the reference keeps the dense factor too)."""
+    from test_sparse_hessian import _cuda_sparse, _oracle_sparse, _single_body_groups
 
-    m, d, _ = synthetic.make_sweep_point(nv, nefc, 64, seed=0, iterations=50, ls_iterations=50)
-    # generic rows couple the ancestor chains of two arbitrary dofs: declare every body
-    # as one group so that the pattern covers them (dense pattern, same kernels)
-    groups = [list(range(1, len(m.body_dofadr)))]
-    plan, reason = sparse_hessian.plan_for_model(m, None, groups, 32 if m.nv_pad < 64 else 64)
-    if plan is None:
-        pytest.skip(f"no sparse plan for this shape: {reason}")
-    got, scratch, _ = _cuda_sparse(m, copy.deepcopy(d), cuda_device, groups)
+    m, d, _ = synthetic.make_sweep_point(nv, nefc, 64, seed=0, couple=False, iterations=50, ls_iterations=50)
+    got, scratch, _ = _cuda_sparse(m, copy.deepcopy(d), cuda_device, _single_body_groups(m))
     plan = scratch.solver_context.sparse_hessian_plan
     want, _ = _oracle_sparse(oracle, m, d, plan)
     np.testing.assert_array_equal(got.solver_niter, want.solver_niter)
