@@ -12,24 +12,65 @@ from . import abi, types
 from .arrays import addr, elem_strides, length, shape
 
 
-def _upstream_constants() -> tuple[float, int, int]:
-    """(_ALPHA_NOISE_EPS, OverflowType.ITERATIONS, OverflowType.LS_ITERATIONS) from a
-    live mujoco-warp when importable, else this package's defaults."""
-    try:  # pragma: no cover - mujoco_warp is not installed in the build image
-        from mujoco_warp._src import solver as up_solver
-        from mujoco_warp._src import types as up_types
+_UPSTREAM: dict | None = None
 
-        return (
-            float(up_solver._ALPHA_NOISE_EPS),
-            int(up_types.OverflowType.ITERATIONS),
-            int(up_types.OverflowType.LS_ITERATIONS),
-        )
-    except Exception:
-        return (
-            float(types.ALPHA_NOISE_EPS),
-            int(types.OverflowType.ITERATIONS),
-            int(types.OverflowType.LS_ITERATIONS),
-        )
+
+def upstream_constants(module_types: Any = None, module_solver: Any = None) -> dict:
+    """Every constant this package shares with mujoco-warp, from the live upstream
+    modules when they import (``mujoco_warp._src.types`` / ``.solver``; the arguments
+    let a test pass stand-ins), else this package's defaults (``types``).
+
+    MuJoCo has moved ``mjDSBL_*`` bits and enum members between releases, so nothing
+    that is compared with a value stored in a caller's ``Model`` / ``Data`` is taken
+    from this package when the real definition is at hand.  ``MJ_MINVAL`` /
+    ``MJ_MAXVAL`` are compiled into the kernels: a live module that disagrees with
+    them is an error, not an override."""
+    global _UPSTREAM
+    injected = module_types is not None or module_solver is not None
+    if _UPSTREAM is not None and not injected:
+        return _UPSTREAM
+    if not injected:
+        try:  # pragma: no cover - mujoco_warp is not installed in the build image
+            from mujoco_warp._src import solver as module_solver
+            from mujoco_warp._src import types as module_types
+        except Exception:
+            module_solver = module_types = None
+
+    def member(enum_name: str, name: str, default: int) -> int:
+        enum_cls = getattr(module_types, enum_name, None) if module_types is not None else None
+        value = getattr(enum_cls, name, None)
+        return int(default if value is None else value)
+
+    out = {
+        "source": "mujoco_warp" if module_types is not None else "package defaults",
+        "alpha_noise_eps": float(getattr(module_solver, "_ALPHA_NOISE_EPS", types.ALPHA_NOISE_EPS)),
+        "overflow_iterations": member("OverflowType", "ITERATIONS", types.OverflowType.ITERATIONS),
+        "overflow_ls_iterations": member("OverflowType", "LS_ITERATIONS", types.OverflowType.LS_ITERATIONS),
+        "disable_warmstart": member("DisableBit", "WARMSTART", types.DisableBit.WARMSTART),
+        "solver_newton": member("SolverType", "NEWTON", types.SolverType.NEWTON),
+        "cone_pyramidal": member("ConeType", "PYRAMIDAL", types.ConeType.PYRAMIDAL),
+        "integrator_discrete": member("IntegratorType", "DISCRETE", types.IntegratorType.DISCRETE),
+    }
+    for name in ("SATISFIED", "QUADRATIC", "LINEARNEG", "LINEARPOS"):
+        live = member("ConstraintState", name, getattr(types.ConstraintState, name))
+        if live != int(getattr(types.ConstraintState, name)):
+            raise RuntimeError(
+                f"mujoco_warp ConstraintState.{name} = {live} differs from the value compiled into the kernels "
+                f"({int(getattr(types.ConstraintState, name))})")
+    for name in ("MJ_MINVAL", "MJ_MAXVAL"):
+        live = getattr(module_types, name, None) if module_types is not None else None
+        if live is not None and float(live) != float(getattr(types, name)):
+            raise RuntimeError(
+                f"mujoco_warp {name} = {live} differs from the value compiled into the kernels "
+                f"({getattr(types, name)})")
+    if not injected:
+        _UPSTREAM = out
+    return out
+
+
+def _upstream_constants() -> tuple[float, int, int]:
+    c = upstream_constants()
+    return c["alpha_noise_eps"], c["overflow_iterations"], c["overflow_ls_iterations"]
 
 
 def _mulm_pack(m: Any):
@@ -68,7 +109,7 @@ def model_struct(m: Any) -> abi.ImnModel:
     s.nM = int(shape(m.M_colind)[0])
     s.iterations = int(m.opt.iterations)
     s.ls_iterations = int(m.opt.ls_iterations)
-    s.warmstart = 0 if (int(m.opt.disableflags) & int(types.DisableBit.WARMSTART)) else 1
+    s.warmstart = 0 if (int(m.opt.disableflags) & upstream_constants()["disable_warmstart"]) else 1
     s.n_tolerance = length(m.opt.tolerance)
     s.n_ls_tolerance = length(m.opt.ls_tolerance)
     s.n_meaninertia = length(m.stat.meaninertia)

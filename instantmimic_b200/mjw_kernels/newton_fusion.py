@@ -31,7 +31,7 @@ def newton_min_blocks_per_sm(nworld: int, sm_count: int) -> int:
 def _use_incremental(m: Any) -> bool:
     """Upstream ``solver._use_incremental``: the Newton solver keeps H between
     iterations."""
-    return int(m.opt.solver) == int(types.SolverType.NEWTON)
+    return int(m.opt.solver) == binding.upstream_constants()["solver_newton"]
 
 
 def _sparse_compact(ctx: Any) -> bool:
@@ -57,8 +57,8 @@ def eligible(m: Any, ctx: Any, *, compact: bool = False) -> bool:
         and m.nv_pad % 16 == 0
         and m.nv_pad <= 80
         and _use_incremental(m)
-        and int(m.opt.integrator) != int(types.IntegratorType.DISCRETE)
-        and int(m.opt.cone) == int(types.ConeType.PYRAMIDAL)
+        and int(m.opt.integrator) != binding.upstream_constants()["integrator_discrete"]
+        and int(m.opt.cone) == binding.upstream_constants()["cone_pyramidal"]
         and not m.is_sparse
         and not _sparse_compact(ctx)
         and m.opt.iterations > 0
@@ -74,8 +74,8 @@ def ineligible_reasons(m: Any, ctx: Any, *, compact: bool = False) -> list[str]:
         (0 < m.nv <= 79, f"nv {m.nv} outside 1..79"),
         (m.nv_pad % 16 == 0 and m.nv_pad <= 80, f"nv_pad {m.nv_pad} is not a multiple of 16 up to 80"),
         (_use_incremental(m), "solver is not Newton"),
-        (int(m.opt.integrator) != int(types.IntegratorType.DISCRETE), "DISCRETE integrator"),
-        (int(m.opt.cone) == int(types.ConeType.PYRAMIDAL), "elliptic friction cones"),
+        (int(m.opt.integrator) != binding.upstream_constants()["integrator_discrete"], "DISCRETE integrator"),
+        (int(m.opt.cone) == binding.upstream_constants()["cone_pyramidal"], "elliptic friction cones"),
         (not m.is_sparse, "sparse constraint Jacobian"),
         (not _sparse_compact(ctx), "sparse-compact solver context"),
         (m.opt.iterations > 0, "opt.iterations is 0"),

@@ -136,3 +136,58 @@ def test_shard_bounds_cover_the_batch():
         assert all(lo2 == hi1 for (_, hi1), (lo2, _) in zip(b, b[1:]))
         sizes = [hi - lo for lo, hi in b]
         assert max(sizes) - min(sizes) <= 1
+
+
+def test_constants_follow_a_live_upstream_module():
+    """Bits and enum members that are compared with values stored in a caller's Model
+    come from the upstream module when there is one; constants compiled into the
+    kernels must agree with it."""
+    import enum
+    from types import SimpleNamespace
+
+    from instantmimic_b200 import binding, types
+
+    class DisableBit(enum.IntFlag):
+        WARMSTART = 1 << 9  # moved by one bit, as MuJoCo releases have done
+
+    class OverflowType(enum.IntFlag):
+        ITERATIONS = 8
+        LS_ITERATIONS = 16
+
+    live = SimpleNamespace(DisableBit=DisableBit, OverflowType=OverflowType, MJ_MINVAL=1e-15, MJ_MAXVAL=1e10)
+    c = binding.upstream_constants(live, SimpleNamespace(_ALPHA_NOISE_EPS=2e-6))
+    assert c["disable_warmstart"] == 512 and c["overflow_iterations"] == 8 and c["overflow_ls_iterations"] == 16
+    assert c["alpha_noise_eps"] == 2e-6 and c["solver_newton"] == int(types.SolverType.NEWTON)
+    with pytest.raises(RuntimeError, match="MJ_MINVAL"):
+        binding.upstream_constants(SimpleNamespace(MJ_MINVAL=1e-12), None)
+
+    class ConstraintState(enum.IntEnum):
+        SATISFIED = 0
+        QUADRATIC = 2
+
+    with pytest.raises(RuntimeError, match="ConstraintState.QUADRATIC"):
+        binding.upstream_constants(SimpleNamespace(ConstraintState=ConstraintState), None)
+    assert binding.upstream_constants()["source"] == "package defaults"
+
+
+def test_constraint_rows_impossible_gate():
+    """mjw_step_optimized.py:116-147: True only when the model rules out every row
+    source; a model without the fields keeps the general path."""
+    from types import SimpleNamespace
+
+    m, _, _ = synthetic.make_workload("humanoid", 1, seed=0)
+    assert runtime._constraint_rows_impossible(m, ()) is False  # the stand-in carries none of the fields
+    e = np.zeros(0, np.int32)
+    free = SimpleNamespace(
+        opt=SimpleNamespace(run_collision_detection=True), neq=0, nflex=0, nsensorcollision=0,
+        jnt_limited_slide_hinge_adr=e, jnt_limited_ball_adr=e, tendon_limited_adr=e,
+        dof_frictionloss=np.zeros(5, np.float32), tendon_frictionloss=np.zeros(0, np.float32),
+        nxn_pairid_filtered=np.full((3, 2), -2, np.int32))
+    assert runtime._constraint_rows_impossible(free, ()) is True
+    assert runtime._constraint_rows_impossible(free, [object()]) is False  # ball-limit rows declared
+    for change in (dict(neq=1), dict(nflex=2), dict(nsensorcollision=1),
+                   dict(jnt_limited_slide_hinge_adr=np.array([3], np.int32)),
+                   dict(dof_frictionloss=np.array([0, 0.2], np.float32)),
+                   dict(nxn_pairid_filtered=np.array([[-2, -2], [-1, 4]], np.int32)),
+                   dict(solver_compact=True), dict(opt=SimpleNamespace(run_collision_detection=False))):
+        assert runtime._constraint_rows_impossible(SimpleNamespace(**{**vars(free), **change}), ()) is False, change
