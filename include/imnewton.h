@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define IMN_ABI_VERSION 1
+#define IMN_ABI_VERSION 2
 
 typedef enum ImnStatus {
   IMN_OK = 0,
@@ -205,6 +205,13 @@ typedef struct ImnCtx {
                          * worlds to the GPU in that order (long solves first, which
                          * shortens the tail of the launch); results do not depend
                          * on it                                                  */
+  int32_t* stats;       /* optional (W, 4), no counterpart in the reference: work
+                         * counters of each world's solve, from which the flop count
+                         * of a batch is computed -- [0] row-evaluation passes of the
+                         * line searches, [1] rows whose QUADRATIC membership flipped
+                         * (summed over iterations), [2] factorisations (the initial
+                         * one included), [3] full gradient evaluations (the initial
+                         * one included)                                          */
 } ImnCtx;
 
 /* Tree-structured L'DL plan (tree_ldl.py:47-57, 105-170) as an instruction

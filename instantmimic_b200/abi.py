@@ -15,7 +15,7 @@ I32 = C.c_int32
 I64 = C.c_int64
 F32 = C.c_float
 
-IMN_ABI_VERSION = 1
+IMN_ABI_VERSION = 2
 
 IMN_OK = 0
 IMN_ERR_NULL = -1
@@ -153,6 +153,7 @@ class ImnCtx(C.Structure):
         ("nsolving", P),
         ("sparse_plan", C.POINTER(ImnSparsePlan)),
         ("world_order", P),
+        ("stats", P),
     ]
 
 

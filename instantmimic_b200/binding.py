@@ -232,4 +232,8 @@ def ctx_struct(d_struct: abi.ImnData, ctx: Any, nsolving: Any, sparse_plan_struc
     if order is not None and length(order) < d_struct.nworld:
         raise ValueError("ctx.world_order must hold one int32 per world")
     s.world_order = addr(order)
+    stats = get("stats")
+    if stats is not None and (tuple(shape(stats)) != (d_struct.nworld, 4) or elem_strides(stats) != (4, 1)):
+        raise ValueError("ctx.stats must be a contiguous (nworld, 4) int32 array")
+    s.stats = addr(stats)
     return s

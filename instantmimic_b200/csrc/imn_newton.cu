@@ -217,6 +217,7 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
   float improvement = 0.0f, alpha = 0.0f;
   int quad_count = 0, state_count = 0, niter = 0, overflow = 0;
   bool search_unchanged = false, ls_exhausted = false;
+  int st_passes = 0, st_flips = 0, st_factor = 0, st_grad = 0;  // work counters (ctx.stats)
   const float tolerance = m.opt_tolerance[w % m.n_tolerance];
   const float ls_tolerance = m.opt_ls_tolerance[w % m.n_ls_tolerance];
   const float scale = m.stat_meaninertia[w % m.n_meaninertia] * (float)nv;
@@ -241,6 +242,7 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
           line_search(s, search_dot, tolerance, ls_tolerance, scale, m.alpha_noise_eps, m.ls_iterations);
       alpha = ls.alpha, improvement = ls.improvement, noise_floor = ls.noise_floor;
       ls_converged = ls.converged;
+      st_passes += ls.passes;
 #pragma unroll 1
       for (int i = lane; i < nv; i += 32) {
         s.qacc[i] = fmaf(alpha, s.search[i], s.qacc[i]);
@@ -308,6 +310,9 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
       grad_scale = ns;
     } else {
       grad_dot = full_gradient<JRES>(s, nfr);
+      ++st_grad;
+      if (!first) st_flips += quad_count;
+      if (first || quad_count > 0) ++st_factor;
       PROF(8);
       decrement = 0.0f;
       grad_scale = 1.0f;
@@ -427,6 +432,10 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
     if (overflow) d.overflow[w] |= overflow;
     if (cx.search_dot) cx.search_dot[w] = search_dot;
     if (cx.done) cx.done[w] = 1;
+    if (cx.stats) {
+      int4 st = make_int4(st_passes, st_flips, st_factor, st_grad);
+      *reinterpret_cast<int4*>(cx.stats + 4 * (size_t)w) = st;
+    }
     if (!rowless) {
       if (cx.grad_dot) cx.grad_dot[w] = grad_dot;
       if (cx.grad_scale) cx.grad_scale[w] = grad_scale;

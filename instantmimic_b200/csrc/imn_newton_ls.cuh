@@ -32,6 +32,7 @@ __device__ __noinline__ Vec3 ls_rows_general(const float* floss, const float* D,
 struct LineSearchResult {
   float alpha, improvement, noise_floor;
   bool converged;
+  int passes;  // row-evaluation passes made
 };
 
 __device__ __forceinline__ LineSearchResult line_search(const World& s, float search_dot, float tolerance,
@@ -64,7 +65,7 @@ __device__ __forceinline__ LineSearchResult line_search(const World& s, float se
   const Row rowb = make_row_ineq(vb, vb ? s.Dsm[rb] : 1.0f, vb ? s.Jaref[rb] : 0.0f, vb ? s.jv[rb] : 0.0f);
 
   LineSearchResult out;
-  out.alpha = 0.0f, out.improvement = 0.0f, out.noise_floor = 0.0f, out.converged = false;
+  out.alpha = 0.0f, out.improvement = 0.0f, out.noise_floor = 0.0f, out.converged = false, out.passes = 0;
   Vec3 p0 = v3(0.0f, 0.0f, 0.0f), lo = p0, hi = p0;
   float gtol_accept = 0.0f, lo_alpha = 0.0f, hi_alpha = 0.0f;
   float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f;  // step sizes of the coming pass
@@ -72,6 +73,7 @@ __device__ __forceinline__ LineSearchResult line_search(const World& s, float se
 #pragma unroll 1
   for (int pass = 0; pass < ls_iterations + 2; ++pass) {
     const bool absolute = pass == 0;
+    out.passes = pass + 1;
     const Vec3 z3 = v3(0.0f, 0.0f, 0.0f);  // running sums start at zero
     Vec3 s0 = z3, s1 = z3, s2 = z3;
     if (!fric && !more) {

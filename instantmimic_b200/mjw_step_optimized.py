@@ -48,6 +48,8 @@ class SolverContext:
         self.sparse_hessian_plan = None
         # scratch of the fused kernel: worlds ordered by row count (no counterpart upstream)
         self.world_order = i(W)
+        # work counters of each world's solve (passes, flips, factorisations, gradients)
+        self.stats = i(W, 4)
 
 
 @dataclass

@@ -167,6 +167,8 @@ typedef struct World {
   int *state, *ids, *uni;
   float search_dot, grad_dot, grad_scale, decrement, improvement, alpha;
   int quad_count, state_count, search_unchanged, ls_exhausted, done, niter, overflow;
+  /* work counters reported through ctx->stats */
+  int st_passes, st_flips, st_factor, st_grad;
   /* static-pattern sparse factor (NULL: dense): packed H, N = L D with the carried
    * right-hand-side row, 1/D, and the count of pattern violations of this solve */
   const ImnSparsePlan* sp;
@@ -349,6 +351,7 @@ static void line_search(const ImnModel* m, World* w, int worldid, float* noise_f
   } while (0)
 
   Vec3 rows;
+  w->st_passes += 1;
   ROW_SUM(rows, eval_row_zero(r, nef, w->D[r], w->floss, w->Jaref[r], w->jv[r]));
   const Vec3 p0 = v3add(v3(qg[0], qg[1], 2.0f * qg[2]), rows);
   const Vec3 p0_delta = v3(0.0f, p0.c[1], p0.c[2]);
@@ -362,6 +365,7 @@ static void line_search(const ImnModel* m, World* w, int worldid, float* noise_f
   Vec3 lo_in = v3(0.0f, 0.0f, 0.0f);
   if (!ls_converged) {
     Vec3 s;
+    w->st_passes += 1;
     ROW_SUM(s, eval_row(r, lo_alpha_in, nef, w->D[r], w->floss, w->Jaref[r], w->jv[r]));
     lo_in = v3add(eval_quad(qg, lo_alpha_in), s);
     if (fabsf(lo_in.c[1]) < gtol_accept && lo_in.c[0] < 0.0f) {
@@ -381,6 +385,7 @@ static void line_search(const ImnModel* m, World* w, int worldid, float* noise_f
       const float a_hi = hi_alpha - safe_div(hi.c[1], hi.c[2]);
       const float a_mid = 0.5f * (lo_alpha + hi_alpha);
       Vec3 s_lo, s_hi, s_mid;
+      w->st_passes += 1;
       ROW_SUM(s_lo, eval_row(r, a_lo, nef, w->D[r], w->floss, w->Jaref[r], w->jv[r]));
       ROW_SUM(s_hi, eval_row(r, a_hi, nef, w->D[r], w->floss, w->Jaref[r], w->jv[r]));
       ROW_SUM(s_mid, eval_row(r, a_mid, nef, w->D[r], w->floss, w->Jaref[r], w->jv[r]));
@@ -561,6 +566,7 @@ static void solve_world(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, 
                       (r >= w.ne && r < w.ne + w.nf) ? w.floss[r] : 0.0f, &w.force[r],
                       &w.state[r]);
     full_gradient(&w);
+    w.st_grad = 1, w.st_factor = 1;
     float sums[2];
     if (w.sp) {
       /* H on the pattern slots, kept packed, then the level factor
@@ -616,6 +622,7 @@ static void solve_world(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, 
       w.grad_scale = ns;
     } else {
       full_gradient(&w);
+      w.st_grad++, w.st_flips += w.quad_count, w.st_factor += w.quad_count > 0;
       w.decrement = 0.0f;
       w.grad_scale = 1.0f;
       /* factor */
@@ -674,6 +681,10 @@ static void solve_world(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, 
     if (ctx->improvement && !rowless) ctx->improvement[wid] = w.improvement;
     if (ctx->alpha && !rowless) ctx->alpha[wid] = w.alpha;
     if (ctx->done) ctx->done[wid] = 1;
+    if (ctx->stats) {
+      int32_t* st = ctx->stats + 4 * (size_t)wid;
+      st[0] = w.st_passes, st[1] = w.st_flips, st[2] = w.st_factor, st[3] = w.st_grad;
+    }
     if (ctx->search_unchanged && !rowless) ctx->search_unchanged[wid] = (uint8_t)w.search_unchanged;
     if (ctx->ls_exhausted && !rowless) ctx->ls_exhausted[wid] = (uint8_t)w.ls_exhausted;
     if (ctx->quad_changed_count && !rowless) ctx->quad_changed_count[wid] = w.quad_count;

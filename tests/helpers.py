@@ -22,7 +22,7 @@ def host_ctx(m, d, matrices=True):
         done=np.zeros(W, np.uint8), search_unchanged=np.zeros(W, np.uint8),
         ls_exhausted=np.zeros(W, np.uint8),
         quad_changed_ids=i(W, R), quad_changed_count=i(W), state_changed_count=i(W),
-        newton_dof_union=i(W, nv + 1),
+        newton_dof_union=i(W, nv + 1), stats=i(W, 4),
     )
 
 

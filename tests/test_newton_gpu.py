@@ -39,6 +39,7 @@ def _check(got, want, gctx=None, wctx=None):
         np.testing.assert_array_equal(gctx.quad_changed_count, wctx.quad_changed_count)
         np.testing.assert_array_equal(gctx.state_changed_count, wctx.state_changed_count)
         np.testing.assert_array_equal(gctx.search_unchanged, wctx.search_unchanged)
+        np.testing.assert_array_equal(gctx.stats, wctx.stats)  # passes, flips, factorisations, gradients
         for w in range(want.nworld):
             k = wctx.quad_changed_count[w]
             np.testing.assert_array_equal(gctx.quad_changed_ids[w, :k], wctx.quad_changed_ids[w, :k])

@@ -79,3 +79,18 @@ def test_oracle_is_deterministic_across_thread_counts(oracle):
     b, _, _ = run_oracle(oracle, m, copy.deepcopy(d), threads=4)
     for x, y in ((a.qacc, b.qacc), (a.efc.force, b.efc.force), (a.efc.state, b.efc.state)):
         np.testing.assert_array_equal(x, y)
+
+
+def test_work_counters_are_consistent(oracle):
+    """ctx.stats: line-search passes, flipped rows, factorisations, gradient evaluations."""
+    from helpers import run_oracle
+
+    m, d, _ = synthetic.make_workload("humanoid", 64, seed=2, rowless_fraction=0.1)
+    got, ctx, _ = run_oracle(oracle, m, d)
+    st, niter = ctx.stats, got.solver_niter
+    rows = d.nefc > 0
+    assert (st[~rows] == 0).all()
+    assert (st[rows, 3] >= 1).all() and (st[rows, 3] <= niter[rows] + 1).all()  # one gradient at init, at most one per iteration
+    assert (st[rows, 2] >= 1).all() and (st[rows, 2] <= st[rows, 3]).all()      # a factorisation needs a gradient
+    assert (st[rows, 0] >= niter[rows]).all() and (st[rows, 0] <= niter[rows] * (m.opt.ls_iterations + 2)).all()
+    assert (st[rows, 1] >= st[rows, 2] - 1).all()                                # every refactorisation had a flip
