@@ -6,9 +6,14 @@ seeded synthetic solver states with that model's shapes; several distinct batche
 are rotated so that consecutive steps never find their inputs in L2.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+                    [--workload humanoid|snu|g1|sweep]
 
-One JSON line is printed by rank 0.  ``--impl reference`` times the CPU
-restatement of the reference's solver (the oracle) on all host cores.
+One JSON line is printed by rank 0.  The timed unit is a round of exactly K steps
+between two CUDA events; rounds are repeated (at least nine, and until about a second
+of device time has passed, so that the clock sampler sees the region) and
+``ms_per_step`` is the median round, with p10 / p90 beside it.  ``--impl reference``
+times the reference's CPU path: MuJoCo C ``mj_step`` when the ``mujoco`` package is
+installed, else the CPU restatement of the solver (the oracle), on all host cores.
 """
 
 from __future__ import annotations
@@ -30,10 +35,12 @@ sys.path.insert(0, str(ROOT))
 
 METRIC = "newton_solver_world_steps_per_s"
 UNIT = "world-steps/s"
-# dram__bytes_read.sum + dram__bytes_write.sum of one newton_kernel launch, from the ncu
-# capture summarised in profiles/newton_kernel_humanoid.md: 138.8 MB for 16384 humanoid
-# worlds (8.47 KB per world); traffic grows in proportion to the worlds of a launch.
-NCU_TRAFFIC_BYTES_PER_WORLD = 140.06e6 / 16384
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the humanoid solve kernel
+# in an ncu capture of a 16384-world batch: 140.0 MB, 8.55 KB per world.  DRAM traffic of
+# this kernel grows in proportion to the worlds of a launch (every world's inputs are
+# read once), so the figure is scaled by the worlds of the bench's launch.
+NCU_TRAFFIC_BYTES_PER_WORLD_HUMANOID = 140.0e6 / 16384
+STRONG_TOTAL_WORLDS = 8192
 
 
 def parse_args():
@@ -42,15 +49,18 @@ def parse_args():
     p.add_argument("--steps", type=int, default=200)
     p.add_argument("--warmup", type=int, default=10)
     p.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    p.add_argument("--workload", default="humanoid", choices=["humanoid", "snu", "g1"])
+    p.add_argument("--workload", default="humanoid", choices=["humanoid", "snu", "g1", "sweep"])
     p.add_argument("--nworld", type=int, default=8192, help="worlds per GPU")
     p.add_argument("--batches", type=int, default=4, help="distinct input batches rotated per GPU")
     p.add_argument("--iterations", type=int, default=50)
     p.add_argument("--ls-iterations", type=int, default=50)
     p.add_argument("--tolerance", type=float, default=1e-8)
+    p.add_argument("--rounds", type=int, default=0, help="timed rounds of --steps steps (0: at least 9, ~1 s)")
     p.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU baseline sample length")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--no-aux", action="store_true")
+    p.add_argument("--aux-nworld", type=int, default=65536, help="worlds of the M-side kernel timings")
     p.add_argument("--sparse-hessian", default="on", choices=["on", "off"],
                    help="install the static-pattern sparse Hessian plan (single-body contact groups)")
     return p.parse_args()
@@ -81,6 +91,42 @@ def algorithmic_bytes(m, d) -> int:
     return int(4 * (read + write).sum())
 
 
+def algorithmic_flops(m, d_host, niter, stats, state, plan) -> float:
+    """Floating-point operations one solve of the batch needs, from the per-world work
+    counters the kernel records (line-search passes, flipped rows, factorisations,
+    gradient evaluations), the iteration counts and the final row states.  Per world:
+    J qacc, M qacc, the initial Hessian over its QUADRATIC rows, per iteration M v, J v
+    and ~20 operations per row and line-search step size, per gradient J^T f, per
+    flipped row a rank-one update over the dofs the row touches, per factorisation the
+    factor's multiply-adds (the plan's term count for the sparse factor, nv^3 / 3
+    dense) and per gradient one forward + backward substitution."""
+    nv, nM = m.nv, m.nM
+    nefc = np.minimum(d_host.nefc, d_host.njmax).astype(np.float64)
+    nM2 = 2 * nM - nv
+    live = np.arange(d_host.njmax)[None, :] < nefc[:, None]
+    J = d_host.efc.J[..., :nv]
+    support = ((J != 0).sum(axis=2) * live).sum() / max(live.sum(), 1)  # dofs a row touches, mean
+    nquad = ((state == 1) & live).sum(axis=1).astype(np.float64)
+    if plan is not None:
+        terms = float((plan.tables["run_kl"].astype(np.int64) >> 16).sum())
+        f_factor = 3.0 * terms + 2.0 * plan.nfac
+        f_solve = 4.0 * plan.nfac
+    else:
+        f_factor = nv**3 / 3.0
+        f_solve = 2.0 * nv * nv
+    passes, flips, nfactor, ngrad = (stats[:, k].astype(np.float64) for k in range(4))
+    it = niter.astype(np.float64)
+    # step sizes evaluated: one per pass for the first two passes of a search, three afterwards
+    evals = np.maximum(passes, 0) + 2.0 * np.maximum(passes - 2.0 * it, 0)
+    f = (2 * nefc * nv + 2 * nM2 + nquad * support * (support + 1)
+         + it * (2 * nM2 + 2 * nefc * nv + 4 * nv)
+         + 20.0 * nefc * evals
+         + ngrad * (2 * nefc * nv + 3 * nv)
+         + flips * support * (support + 1)
+         + nfactor * f_factor + ngrad * f_solve)
+    return float(f.sum())
+
+
 class ClockSampler:
     """nvidia-smi clocks and throttle reasons of one GPU while a region runs."""
 
@@ -107,8 +153,7 @@ class ClockSampler:
             self.rows.append((time.perf_counter(), [c.strip() for c in line.split(",")]))
 
     def wait_started(self, timeout: float = 3.0) -> None:
-        """nvidia-smi takes a few hundred ms to deliver its first row; a timed region of
-        0.1-0.2 s would otherwise pass without a sample."""
+        """nvidia-smi takes a few hundred ms to deliver its first row."""
         t0 = time.perf_counter()
         while self.proc is not None and not self.rows and time.perf_counter() - t0 < timeout:
             time.sleep(0.01)
@@ -124,14 +169,13 @@ class ClockSampler:
 
     def summary(self, t_begin: float, t_end: float):
         """Median SM clock and throttle reasons of the rows received in [t_begin, t_end]
-        (host clock); when the window is too short to hold one, of all rows since the
-        sampler started (warm-up and timed steps of the same workload), and says so."""
+        (host clock); when the window holds none, of all rows, and says so."""
         inside = [r for t, r in self.rows if t_begin <= t <= t_end]
         window = "timed region"
         if not inside:
             inside = [r for _, r in self.rows]
             window = "warm-up and timed steps (no sample fell inside the timed region)"
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for r in inside:
             if len(r) < 7:
@@ -139,6 +183,7 @@ class ClockSampler:
             try:
                 sm.append(float(r[0]))
                 mx.append(float(r[1]))
+                power.append(float(r[2]))
             except ValueError:
                 continue
             for name, flag in zip(names, r[3:7]):
@@ -147,72 +192,126 @@ class ClockSampler:
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "window": window}
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons),
-                "samples": len(sm), "window": window}
+                "samples": len(sm), "window": window, "power_w_median": float(np.median(power))}
 
 
-def make_batches(args, rank):
+def make_batches(args, rank, nworld=None, count=None):
     from instantmimic_b200 import synthetic
 
     out = []
-    for b in range(args.batches):
+    for b in range(count or args.batches):
         m, d, _ = synthetic.make_workload(
-            args.workload, args.nworld, seed=1000 * rank + b, iterations=args.iterations,
+            args.workload, nworld or args.nworld, seed=1000 * rank + b, iterations=args.iterations,
             ls_iterations=args.ls_iterations, tolerance=args.tolerance)
         out.append((m, d))
     return out
 
 
+# ------------------------------------------------------------------ reference arm
+
+
+def mujoco_reference(args):
+    """The reference's own CPU path: MuJoCo C ``mj_step`` (Newton, pyramidal, dense,
+    same iteration limits and tolerance) over a thread pool, one MjData per thread.
+    Returns None when the ``mujoco`` package is not installed."""
+    try:
+        import mujoco  # noqa: F401
+    except Exception as e:  # not installed on this pool's boxes
+        return None, f"{type(e).__name__}: {e}"
+    # A humanoid with the workload's joint tree is generated as MJCF text: the model files
+    # of the reference are not shipped with this repository.
+    from concurrent.futures import ThreadPoolExecutor
+
+    from instantmimic_b200 import synthetic
+
+    xml = synthetic.humanoid_mjcf(iterations=args.iterations, ls_iterations=args.ls_iterations,
+                                  tolerance=args.tolerance)
+    model = mujoco.MjModel.from_xml_string(xml)
+    cores = os.cpu_count() or 1
+    datas = [mujoco.MjData(model) for _ in range(cores)]
+    rng = np.random.default_rng(0)
+
+    def work(i):
+        d = datas[i]
+        per = args.nworld // cores + (1 if i < args.nworld % cores else 0)
+        for _ in range(per):
+            mujoco.mj_resetData(model, d)
+            d.qpos[2] = 0.9 + 0.1 * rng.random()
+            d.qvel[:] = 0.5 * rng.standard_normal(model.nv)
+            mujoco.mj_step(model, d)
+        return per
+
+    with ThreadPoolExecutor(cores) as pool:
+        for _ in range(args.warmup):
+            list(pool.map(work, range(cores)))
+        t0 = time.perf_counter()
+        done = 0
+        for _ in range(args.steps):
+            done += sum(pool.map(work, range(cores)))
+            if time.perf_counter() - t0 > 150.0:
+                break
+        dt = time.perf_counter() - t0
+    return {"value": done / dt, "cores": cores, "kind": "reference",
+            "sample": f"{done} mj_step calls (generated humanoid MJCF), thread pool of {cores}", "dt": dt,
+            "steps": done // max(args.nworld, 1)}, None
+
+
 def run_reference(args):
-    """The reference's CPU path for this solve, restated (oracle), on all host cores."""
+    """The reference's CPU path for this solve on all host cores (rank 0 only)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import oracle
-
-    oracle.build()
     cores = os.cpu_count() or 1
     batches = make_batches(args, 0)
     m = batches[0][0]
-    work = [copy.deepcopy(d) for _, d in batches]
-    for k in range(min(args.warmup, 2)):
-        oracle.solve(m, work[k % len(work)], threads=cores)
-    steps = args.steps
-    # bounded: stop once a few minutes are used; the steps actually timed are reported
-    elapsed, done = 0.0, 0
-    for k in range(steps):
-        dd = copy.deepcopy(batches[k % len(batches)][1])
-        t1 = time.perf_counter()
-        oracle.solve(m, dd, threads=cores)
-        elapsed += time.perf_counter() - t1
-        done += 1
-        if elapsed > 150.0:
-            break
-    value = args.nworld * done / elapsed
+    result, why_not = None, "workload has no generated MJCF"
+    if args.workload == "humanoid":
+        try:
+            result, why_not = mujoco_reference(args)
+        except Exception as e:  # a MuJoCo that rejects the generated model: keep the restated solver
+            result, why_not = None, f"mj_step arm failed: {type(e).__name__}: {e}"
+    if result is None:
+        from oracle import oracle
+
+        oracle.build()
+        work = [copy.deepcopy(d) for _, d in batches]
+        for k in range(args.warmup):
+            oracle.solve(m, work[k % len(work)], threads=cores)
+        elapsed, done = 0.0, 0
+        for k in range(args.steps):
+            dd = copy.deepcopy(batches[k % len(batches)][1])
+            t1 = time.perf_counter()
+            oracle.solve(m, dd, threads=cores)
+            elapsed += time.perf_counter() - t1
+            done += 1
+            if elapsed > 150.0:  # bounded: the steps actually timed are reported
+                break
+        result = {"value": args.nworld * done / elapsed, "cores": cores, "kind": "port", "dt": elapsed,
+                  "steps": done,
+                  "sample": f"{done} steps of {args.nworld} worlds, OpenMP over worlds, {cores} threads"}
+    value = result["value"]
     line = {
         "impl": "reference",
         "metric": METRIC,
         "value": value,
         "unit": UNIT,
         "n_gpus": args.gpus,
-        "steps": done,
-        "warmup": min(args.warmup, 2),
-        "ms_per_step": 1e3 * elapsed / done,
+        "steps": result["steps"],
+        "warmup": args.warmup,
+        "ms_per_step": 1e3 * result["dt"] / max(result["steps"], 1),
         "higher_is_better": True,
         "scaling": "weak",
         "vs_baseline": None,
-        "dtype": "f32",
+        "dtype": "f32" if result["kind"] == "port" else "f64",
         "data": "synthetic",
         "config": workload_config(args, m, batches[0][1]),
-        "cpu_baseline": {
-            "value": value,
-            "unit": UNIT,
-            "cores": cores,
-            "kind": "port",
-            "sample": f"{done} steps of {args.nworld} worlds, OpenMP over worlds",
-        },
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": result["cores"], "kind": result["kind"],
+                         "sample": result["sample"]},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
-        "note": "CPU restatement of the reference solver (MuJoCo / mujoco-warp are not installed)",
+        "note": ("MuJoCo C mj_step" if result["kind"] == "reference" else
+                 f"CPU restatement of the reference solver; MuJoCo C unavailable ({why_not}); "
+                 "reference Warp solver: unavailable on this box (not installed)"),
     }
     print(json.dumps(line))
 
@@ -229,27 +328,172 @@ def cpu_baseline(args, batches):
         t = time.perf_counter()
         oracle.solve(m, dd, threads=cores)
         elapsed += time.perf_counter() - t
-        solved += args.nworld
+        solved += dd.nworld
         k += 1
     return {
         "value": solved / elapsed,
         "unit": UNIT,
         "cores": cores,
         "kind": "port",
-        "sample": f"{k} solves of {args.nworld} worlds ({elapsed:.1f} s), OpenMP over worlds, {cores} threads",
+        "sample": f"{k} solves of {batches[0][1].nworld} worlds ({elapsed:.1f} s), OpenMP over worlds, {cores} threads",
     }
+
+
+# ------------------------------------------------------------------ timing helpers
+
+
+def percentiles(xs):
+    xs = np.asarray(xs, dtype=np.float64)
+    return float(np.median(xs)), float(np.percentile(xs, 10)), float(np.percentile(xs, 90))
+
+
+class Timer:
+    """Rounds of K calls between CUDA events on torch's current stream, bracketed by a
+    device synchronisation and (multi-GPU) a barrier; per round the max over ranks."""
+
+    def __init__(self, torch, dist, world, device):
+        self.torch, self.dist, self.world, self.device = torch, dist, world, device
+
+    def barrier(self):
+        self.torch.cuda.synchronize()
+        if self.world > 1:
+            self.dist.barrier()
+            self.torch.cuda.synchronize()
+
+    def max_over_ranks(self, xs):
+        if self.world == 1:
+            return list(xs)
+        t = self.torch.tensor(list(xs), dtype=self.torch.float64, device=self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return [float(v) for v in t.tolist()]
+
+    def rounds(self, step, steps, rounds, min_seconds=0.0, max_rounds=400):
+        """ms of each round of `steps` calls.  With rounds == 0: at least nine, then until
+        `min_seconds` of device time (decided on rank 0's first round, same count on all)."""
+        ev = self.torch.cuda.Event
+        out = []
+        k0 = 0
+
+        def one():
+            nonlocal k0
+            e0, e1 = ev(enable_timing=True), ev(enable_timing=True)
+            self.barrier()
+            e0.record()
+            for k in range(steps):
+                step(k0 + k)
+            e1.record()
+            self.barrier()
+            k0 += steps
+            return e0.elapsed_time(e1)
+
+        first = one()
+        out.append(first)
+        if rounds <= 0:
+            first_max = self.max_over_ranks([first])[0]
+            rounds = int(min(max_rounds, max(9, np.ceil(min_seconds * 1e3 / max(first_max, 1e-3)))))
+        for _ in range(rounds - 1):
+            out.append(one())
+        return self.max_over_ranks(out)
+
+
+def graph_of(torch, fn, reps):
+    """`reps` calls recorded into one CUDA graph (they allocate nothing)."""
+    for k in range(3):
+        fn(k)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for k in range(reps):
+            fn(k)
+    graph.replay()
+    torch.cuda.synchronize()
+    return graph
+
+
+def time_graph(torch, graph, reps, replays=5):
+    """Median ms per call over `replays` replays of a graph of `reps` calls."""
+    ms = []
+    for _ in range(replays):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ms.append(a.elapsed_time(b) / reps)
+    return float(np.median(ms))
+
+
+# ------------------------------------------------------------------ sweep workload
+
+
+SWEEP_NV = (27, 35, 64)
+SWEEP_NEFC = (32, 128, 512)
+SWEEP_WORLDS = (4096, 16384, 65536)
+
+
+def run_sweep(args, torch, timer, world, rank, device, peak):
+    """The isolated sweep: nv x nefc x batch, generic rows on tree-ancestor patterns,
+    dense factor; worlds sharded over the ranks.  Inputs of 2048 generated worlds are
+    repeated to the batch size on the device (generation on the host is what costs
+    time; every world is still solved)."""
+    from instantmimic_b200 import mjw_model, synthetic
+    from instantmimic_b200 import mjw_step_optimized as runtime
+
+    points = []
+    base_worlds = 2048
+    for nv in SWEEP_NV:
+        for nefc in SWEEP_NEFC:
+            m, d, _ = synthetic.make_sweep_point(nv, nefc, base_worlds, seed=rank, iterations=args.iterations,
+                                                 ls_iterations=args.ls_iterations, tolerance=args.tolerance)
+            md = mjw_model.to_device(m, device)
+            bytes_per_world = algorithmic_bytes(m, d) / base_worlds
+            for total in SWEEP_WORLDS:
+                W = total // world
+                reps = max(1, W // base_worlds)
+
+                dev_arrays = mjw_model.to_device(d, device)  # one base copy on the device
+                dd = copy.copy(dev_arrays)
+                dd.nworld = W
+                rep = lambda t: t.repeat((reps,) + (1,) * (t.dim() - 1))[:W].contiguous()  # noqa: E731
+                for name in ("nefc", "ne", "nf", "qacc_smooth", "qacc_warmstart", "qfrc_smooth", "M", "qacc",
+                             "qfrc_constraint", "solver_niter", "overflow"):
+                    setattr(dd, name, rep(getattr(dev_arrays, name)))
+                dd.efc = copy.copy(dev_arrays.efc)
+                for name in ("J", "D", "aref", "frictionloss", "force", "state", "Ma"):
+                    setattr(dd.efc, name, rep(getattr(dev_arrays.efc, name)))
+                scratch = runtime.make_optimized_fwd_position_scratch(md, dd, device)
+                step = lambda k: runtime.solve_with_scratch(md, dd, scratch, use_optimized_kernel=True)  # noqa: E731
+                for _ in range(3):
+                    step(0)
+                ms = timer.rounds(step, 1, 5)
+                med, p10, p90 = percentiles(ms)
+                niter = float(dd.solver_niter.float().mean().item())
+                points.append({
+                    "nv": nv, "nefc": nefc, "worlds_total": total, "worlds_per_gpu": W, "ms": med, "ms_p10": p10,
+                    "ms_p90": p90, "value": total / (med * 1e-3), "niter_mean": niter,
+                    "achieved_gbs_per_gpu": bytes_per_world * W / (med * 1e-3) / 1e9,
+                    "frac_of_hbm_peak": bytes_per_world * W / (med * 1e-3) / 1e9 / peak,
+                })
+                del dd, scratch, dev_arrays
+                torch.cuda.empty_cache()
+    return points
+
+
+# ------------------------------------------------------------------ main
 
 
 def main():
     args = parse_args()
     if args.impl == "reference":
+        if args.workload == "sweep":
+            args.workload = "humanoid"
         run_reference(args)
         return
 
     import torch
     import torch.distributed as dist
 
-    from instantmimic_b200 import _lib, mjw_model
+    from instantmimic_b200 import _lib, host_batch, mjw_model
     from instantmimic_b200 import mjw_step_optimized as runtime
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -262,122 +506,113 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     _lib.lib()
+    timer = Timer(torch, dist, world, device)
+    peaks_file = ROOT / "MEASURED_PEAKS.json"
+    if peaks_file.exists():
+        peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
+    else:
+        peak, peak_src = 6650.0, "fallback"
+    props = torch.cuda.get_device_properties(device)
+
+    sweep_mode = args.workload == "sweep"
+    if sweep_mode:
+        args.workload = "humanoid"  # the headline line still carries the humanoid step
 
     host = make_batches(args, rank)
     m_host = host[0][0]
     md = mjw_model.to_device(m_host, device)
     dev = [mjw_model.to_device(d, device) for _, d in host]
     scratch = [runtime.make_optimized_fwd_position_scratch(md, dd, device) for dd in dev]
+    groups = None
     if args.sparse_hessian == "on":
         groups = [[b] for b in range(1, len(m_host.body_dofadr))]
         for dd, sc in zip(dev, scratch):
             reason = runtime.refresh_sparse_hessian(md, dd, sc, groups, device)
             if reason != "enabled":
                 # the model does not qualify (density, nv): the dense factor stays, as in the reference
-                args.sparse_hessian = "off"
+                args.sparse_hessian, groups = "off", None
                 break
     nb = len(dev)
 
     def step(k):
         runtime.solve_with_scratch(md, dev[k % nb], scratch[k % nb], use_optimized_kernel=True)
 
-    def barrier():
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-            torch.cuda.synchronize()
-
-    def max_over_ranks(x: float) -> float:
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device=device)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local) as clocks:
         clocks.wait_started()
         for k in range(args.warmup):
             step(k)
-        barrier()
+        timer.barrier()
         t_begin = time.perf_counter()
-        e0.record()
-        for k in range(args.steps):
-            step(k)
-        e1.record()
-        barrier()
+        round_ms = timer.rounds(step, args.steps, args.rounds, min_seconds=1.2)
         t_end = time.perf_counter()
-    ms = max_over_ranks(e0.elapsed_time(e1))
+    ms, ms_p10, ms_p90 = percentiles(round_ms)
     value = world * args.nworld * args.steps / (ms * 1e-3)
     niter = np.concatenate([dd.solver_niter.cpu().numpy() for dd in dev])
 
-    # ---- end to end: host buffers in, host results out, every step -----------
+    # the same steps as one CUDA-graph replay (the reference's step runs inside a graph)
+    graph_steps = min(args.steps, 4 * nb)
+    graph = graph_of(torch, step, graph_steps)
+    graph_ms = timer.max_over_ranks([time_graph(torch, graph, graph_steps)])[0]
+
+    # ---- strong scaling: a fixed total of worlds divided over the GPUs --------------
+    strong = None
+    if args.nworld >= STRONG_TOTAL_WORLDS // world and STRONG_TOTAL_WORLDS % world == 0:
+        Ws = STRONG_TOTAL_WORLDS // world
+        sdev = [mjw_model.slice_worlds(dd, 0, Ws) for dd in dev]
+        ssc = [runtime.make_optimized_fwd_position_scratch(md, dd, device) for dd in sdev]
+        if groups is not None:
+            for dd, sc in zip(sdev, ssc):
+                runtime.refresh_sparse_hessian(md, dd, sc, groups, device)
+        sstep = lambda k: runtime.solve_with_scratch(md, sdev[k % nb], ssc[k % nb], use_optimized_kernel=True)  # noqa: E731
+        for k in range(args.warmup):
+            sstep(k)
+        sms, sp10, sp90 = percentiles(timer.rounds(sstep, args.steps, 9))
+        strong = {
+            "total_worlds": STRONG_TOTAL_WORLDS, "worlds_per_gpu": Ws, "ms_per_step": sms / args.steps,
+            "ms_per_step_p10": sp10 / args.steps, "ms_per_step_p90": sp90 / args.steps,
+            "value": STRONG_TOTAL_WORLDS * args.steps / (sms * 1e-3),
+            # one GPU solving all of them = this run's own step when it holds that many worlds per GPU
+            "speedup_vs_one_gpu": (ms / sms) if args.nworld == STRONG_TOTAL_WORLDS else None,
+            "note": "eager launches; a world is solved by one warp, so with few worlds per GPU the step "
+                    "lasts as long as its slowest world's solve",
+        }
+        del sdev, ssc
+
+    # ---- end to end: pinned host batches in, host results out, every step -----------
     e2e = None
     if not args.no_e2e:
-        in_names = ["nefc", "ne", "nf", "qacc_smooth", "qacc_warmstart", "qfrc_smooth", "M"]
-        efc_in = ["J", "D", "aref", "frictionloss"]
-        out_names = ["qacc", "qfrc_constraint", "solver_niter"]
-        efc_out = ["force", "state", "Ma"]
-        pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()  # noqa: E731
-        hin = [
-            ({n: pin(getattr(d, n)) for n in in_names}, {n: pin(getattr(d.efc, n)) for n in efc_in})
-            for _, d in host
-        ]
-        # two slots (device buffers, stream, pinned result buffers): while slot A solves,
-        # slot B's inputs are already crossing PCIe; the host consumes the results of
-        # step k-1 while step k is in flight.  Every step's H2D and D2H is inside the
-        # timed region.
-        nslot = 2 if nb >= 2 else 1
-        slots = []
-        for i in range(nslot):
-            slots.append({
-                "dd": dev[i], "sc": scratch[i], "stream": torch.cuda.Stream(device=device),
-                "done": torch.cuda.Event(),
-                "out": ({n: pin(getattr(host[0][1], n)) for n in out_names},
-                        {n: pin(getattr(host[0][1].efc, n)) for n in efc_out}),
-            })
-        h2d = sum(t.numel() * t.element_size() for part in hin[0] for t in part.values())
-        d2h = sum(t.numel() * t.element_size() for part in slots[0]["out"] for t in part.values())
-        checksum = 0.0
-
-        def e2e_issue(k):
-            sl = slots[k % nslot]
-            a, b = hin[k % nb]
-            with torch.cuda.stream(sl["stream"]):
-                for n, t in a.items():
-                    getattr(sl["dd"], n).copy_(t, non_blocking=True)
-                for n, t in b.items():
-                    getattr(sl["dd"].efc, n).copy_(t, non_blocking=True)
-                runtime.solve_with_scratch(md, sl["dd"], sl["sc"], use_optimized_kernel=True, stream=sl["stream"])
-                for n, t in sl["out"][0].items():
-                    t.copy_(getattr(sl["dd"], n), non_blocking=True)
-                for n, t in sl["out"][1].items():
-                    t.copy_(getattr(sl["dd"].efc, n), non_blocking=True)
-                sl["done"].record(sl["stream"])
-
-        def e2e_consume(k):
-            sl = slots[k % nslot]
-            sl["done"].synchronize()  # the caller reads this step's results on the host
-            return float(sl["out"][0]["solver_niter"][0])
+        grouped = [host_batch.group_by_row_count(d)[0] for _, d in host]
+        pinned = [host_batch.pin_batch(d) for d in grouped]
+        pipe = host_batch.HostBatchPipeline(md, grouped[0], device, slots=2 if nb >= 2 else 1, sparse_groups=groups)
+        nslot = len(pipe.slots)
+        ldj = int(dev[0].efc.J.stride(1))
+        h2d = float(np.mean([b.h2d_bytes(m_host.nv, ldj, m_host.nM) for b in pinned]))
+        d2h = float(np.mean([b.d2h_bytes(m_host.nv) for b in pinned]))
+        full_h2d = sum(t.numel() * t.element_size() for t in pinned[0].tensors.values())
 
         def e2e_run(n):
             total = 0.0
             for k in range(n):
                 if k >= nslot:
-                    total += e2e_consume(k - nslot)  # frees the slot step k is about to reuse
-                e2e_issue(k)
+                    total += float(pipe.result(k - nslot)["solver_niter"][0])  # frees the slot step k reuses
+                pipe.submit(k, pinned[k % nb])
             for k in range(max(n - nslot, 0), n):
-                total += e2e_consume(k)
+                total += float(pipe.result(k)["solver_niter"][0])
             return total
 
         torch.cuda.synchronize()
         e2e_steps = min(args.steps, 50)
         e2e_run(4)
-        barrier()
-        t0 = time.perf_counter()
-        checksum = e2e_run(e2e_steps)
-        barrier()
-        dt = max_over_ranks(time.perf_counter() - t0)
+        dts = []
+        for _ in range(5):
+            timer.barrier()
+            t0 = time.perf_counter()
+            checksum = e2e_run(e2e_steps)
+            torch.cuda.synchronize()
+            dts.append(time.perf_counter() - t0)
+            timer.barrier()
+        dts = timer.max_over_ranks(dts)
+        dt, dt10, dt90 = percentiles(dts)
         e2e = {
             "value": world * args.nworld * e2e_steps / dt,
             "unit": UNIT,
@@ -385,68 +620,71 @@ def main():
             "d2h_bytes_per_step": int(d2h),
             "steps": e2e_steps,
             "ms_per_step": 1e3 * dt / e2e_steps,
-            "pipeline": f"{nslot} slots (copy of step k+1 overlaps the solve of step k)",
-            "h2d_gbs_per_gpu": float(h2d) * e2e_steps / dt / 1e9,  # the copy is the limit of this path
+            "ms_per_step_p10": 1e3 * dt10 / e2e_steps,
+            "ms_per_step_p90": 1e3 * dt90 / e2e_steps,
+            "api": "instantmimic_b200.host_batch.HostBatchPipeline.submit / result",
+            "pipeline": f"{nslot} slots (copies of step k+1 overlap the solve of step k)",
+            "host_layout": "worlds grouped by descending row count; each chunk of 256 worlds copies rows "
+                           "[0, its largest nefc) of efc.J / D / aref / frictionloss in and of force / state out",
+            "h2d_bytes_full_arrays": int(full_h2d),
+            "h2d_gbs_per_gpu": h2d * e2e_steps / dt / 1e9,  # the copy is the limit of this path
             "checksum": checksum,
         }
+        del pipe, pinned
 
-    # ---- the M-side kernels of the same path, timed alone on the same batches --------
+    # ---- work counters -> flop count of one batch -------------------------------------
+    runtime.solve_with_scratch(md, dev[0], scratch[0], use_optimized_kernel=True)
+    torch.cuda.synchronize()
+    stats = scratch[0].solver_context.stats.cpu().numpy()
+    state0 = dev[0].efc.state.cpu().numpy()
+    plan0 = getattr(scratch[0].solver_context, "sparse_hessian_plan", None)
+    flops = algorithmic_flops(m_host, host[0][1], dev[0].solver_niter.cpu().numpy(), stats, state0, plan0)
+
+    # ---- the M-side kernels of the same path at a batch that exceeds L2 --------------
     aux = None
-    if world == 1:
+    if world == 1 and not args.no_aux:
         from instantmimic_b200.mjw_kernels import indexed_factor
 
-        def timed(fn, reps=20):
-            """Seconds per call on the device: the calls are recorded into a CUDA graph
-            (they allocate nothing) and the replay is timed, so that host time per call
-            (struct building, ctypes) does not hide the kernel's."""
-            for k in range(3):
-                fn(k)
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                for k in range(reps):
-                    fn(k)
-            graph.replay()
-            torch.cuda.synchronize()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            graph.replay()
-            b.record()
-            torch.cuda.synchronize()
-            return a.elapsed_time(b) * 1e-3 / reps
+        W, nv, nM = args.aux_nworld, m_host.nv, m_host.nM
+        reps = max(1, W // args.nworld)
+        rep = lambda t: t.repeat((reps,) + (1,) * (t.dim() - 1))[:W].contiguous()  # noqa: E731
+        from types import SimpleNamespace
 
-        W, nv, nM = args.nworld, m_host.nv, m_host.nM
-        aux = {}
+        big = [SimpleNamespace(nworld=W, M=rep(dev[i].M), y=rep(dev[i].qfrc_smooth), x=rep(dev[i].qacc_smooth))
+               for i in range(2)]
         sc0 = scratch[0]
+        aux = {"worlds": W, "batches_rotated": 2,
+               "note": "timed as CUDA-graph replays of 8 calls over two rotating batches (M alone is "
+                       f"{4 * W * nM / 1e6:.0f} MB per batch, so every call reads DRAM)"}
+
+        def timed(fn):
+            g = graph_of(torch, fn, 8)
+            return time_graph(torch, g, 8) * 1e-3
+
         if sc0.tree_factor_solve is not None:
             t = timed(lambda k: runtime._factor_solve_i_dense(
-                md, dev[k % nb], dev[k % nb].M, dev[k % nb].qacc_smooth, dev[k % nb].qfrc_smooth, None,
+                md, big[k % 2], big[k % 2].M, big[k % 2].x, big[k % 2].y, None,
                 tree_factor_solve=sc0.tree_factor_solve))
             alg = 4.0 * W * (nM + 2 * nv)
             generated = sc0.tree_factor_solve.kernel is not None
             aux["tree_ldl_generated" if generated else "tree_ldl_kernel"] = {
                 "ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg,
                 "groups": sc0.tree_factor_solve.groups}
-            if generated:
-                # the same plan through the instruction-list interpreter (what runs without NVRTC)
-                import dataclasses
-
-                interp = dataclasses.replace(sc0.tree_factor_solve, kernel=None)
-                t = timed(lambda k: runtime._factor_solve_i_dense(
-                    md, dev[k % nb], dev[k % nb].M, dev[k % nb].qacc_smooth, dev[k % nb].qfrc_smooth, None,
-                    tree_factor_solve=interp))
-                aux["tree_ldl_kernel(interpreted)"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9,
-                                                       "algorithmic_bytes": alg}
         if sc0.dense_factor_solve is not None:
-            bs = sc0.dense_factor_solve
+            bs = indexed_factor.create_blocked_dense_factor_solve_scratch(md, big[0], device)
             t = timed(lambda k: indexed_factor.blocked_dense_factor_solve(
-                dev[k % nb], dev[k % nb].M, dev[k % nb].qacc_smooth, dev[k % nb].qfrc_smooth, bs))
+                big[k % 2], big[k % 2].M, big[k % 2].x, big[k % 2].y, bs))
             alg = 4.0 * W * (nM + 2 * nv + bs.pad * bs.pad)
             aux["blocked_dense_kernel"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg}
-        t = timed(lambda k: runtime._rowless_handoff(md, dev[k % nb]))
-        alg = 4.0 * W * (nM + 4 * nv + 1)
-        aux["mul_m_kernel(rowless hand-off)"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9,
-                                                 "algorithmic_bytes": alg}
+            del bs
+        outv = torch.empty_like(big[0].x)
+        t = timed(lambda k: runtime.mul_m(md, big[k % 2], outv, big[k % 2].y))
+        alg = 4.0 * W * (nM + 2 * nv)
+        aux["mul_m_kernel"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg}
+        del big, outv
+        torch.cuda.empty_cache()
+
+    sweep = run_sweep(args, torch, timer, world, rank, device, peak) if sweep_mode else None
 
     if rank == 0:
         from instantmimic_b200.mjw_kernels import newton_fusion
@@ -454,13 +692,9 @@ def main():
         info = newton_fusion.solve_call(md, dev[0], scratch[0].solver_context, scratch[0].solver_nsolving,
                                         cache_on=scratch[0]).launch_info()
         alg = float(np.mean([algorithmic_bytes(m_host, d) for _, d in host]))
-        peaks_file = ROOT / "MEASURED_PEAKS.json"
-        if peaks_file.exists():
-            peak, peak_src = float(json.loads(peaks_file.read_text())["hbm_gbs"]), "measured"
-        else:
-            peak, peak_src = 6650.0, "fallback"
         launch_s = (ms * 1e-3) / args.steps
         achieved = alg / launch_s / 1e9
+        fp32_peak = 2.0 * 128 * props.multi_processor_count * 1.965e9 / 1e12  # TFLOP/s at the max SM clock
         line = {
             "metric": METRIC,
             "value": value,
@@ -469,6 +703,12 @@ def main():
             "steps": args.steps,
             "warmup": args.warmup,
             "ms_per_step": ms / args.steps,
+            "ms_per_step_p10": ms_p10 / args.steps,
+            "ms_per_step_p90": ms_p90 / args.steps,
+            "rounds": len(round_ms),
+            "timing": "median over rounds of exactly --steps eager steps between two CUDA events "
+                      "(device synchronised and ranks joined on both sides; per round the max over ranks)",
+            "graph_replay_ms_per_step": graph_ms,
             "higher_is_better": True,
             "scaling": "weak",
             "vs_baseline": None,
@@ -486,20 +726,38 @@ def main():
                 "peak_source": peak_src,
                 "unit": "GB/s",
                 "frac": achieved / peak,
-                "traffic": NCU_TRAFFIC_BYTES_PER_WORLD * args.nworld if args.workload == "humanoid" else None,
+                "traffic": NCU_TRAFFIC_BYTES_PER_WORLD_HUMANOID * args.nworld if args.workload == "humanoid" else None,
+                "traffic_source": ("ncu capture of a 16384-world launch of the same kernel and workload, scaled by worlds"
+                                   if args.workload == "humanoid" else None),
                 "algorithmic_bytes_per_launch": alg,
                 "launch_ms": launch_s * 1e3,
+                "fp32": {
+                    "algorithmic_flops_per_launch": flops,
+                    "achieved_tflops": flops / launch_s / 1e12,
+                    "peak_tflops": fp32_peak,
+                    "peak_source": f"2 x 128 lanes x {props.multi_processor_count} SMs x 1.965 GHz",
+                    "frac": flops / launch_s / 1e12 / fp32_peak,
+                },
+                "binding": "neither: the solve is a chain of dependent small-matrix steps per world, bound by "
+                           "instruction issue and latency",
             },
             "solver": {
                 "niter_mean": float(niter.mean()),
                 "niter_max": int(niter.max()),
                 "smem_bytes_per_world": int(info.smem_bytes),
+                "line_search_passes_mean": float(stats[:, 0].mean()),
+                "factorisations_mean": float(stats[:, 2].mean()),
             },
         }
+        if strong is not None:
+            line["strong"] = strong
         if aux is not None:
             for v in aux.values():
-                v["frac_of_hbm_peak"] = v["achieved_gbs"] / peak
+                if isinstance(v, dict):
+                    v["frac_of_hbm_peak"] = v["achieved_gbs"] / peak
             line["aux_kernels"] = aux
+        if sweep is not None:
+            line["sweep"] = sweep
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline(args, host)
         print(json.dumps(line))

@@ -353,6 +353,16 @@ typedef struct ImnLaunchInfo {
 int imn_launch_info(const ImnModel* m, const ImnData* d, const ImnCtx* ctx,
                     ImnLaunchInfo* out);
 
+/* No counterpart in the reference, whose solver buffers never leave the GPU.  For
+ * callers that keep a batch in pinned host memory: copies the leading `width` bytes
+ * of each of `nworld` per-world blocks (block strides `dst_pitch` / `src_pitch`
+ * bytes) between host and device with ONE cudaMemcpy2DAsync on `stream`.  Used to
+ * move only rows [0, max nefc) of efc.J / D / aref / frictionloss in and of
+ * efc.force / state out: the solver never reads or writes rows at or beyond nefc.
+ * to_host 0: host -> device, 1: device -> host. */
+int imn_copy_rows(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width,
+                  int32_t nworld, int32_t to_host, void* stream);
+
 /* Failure detection of the input copies (no counterpart in the reference, whose
  * Warp kernels use plain loads).  A world's inputs arrive by TMA bulk copies on an
  * mbarrier; a world waits at most `polls` polls for them (default 1 << 22), then

@@ -221,6 +221,7 @@ SYMBOLS = {
         [C.POINTER(ImnModel), C.POINTER(ImnData), C.POINTER(ImnCtx), C.POINTER(ImnLaunchInfo)],
     ),
     "imn_set_copy_wait_limit": (C.c_int, [I32, I32]),
+    "imn_copy_rows": (C.c_int, [P, I64, P, I64, I64, I32, I32, P]),
     "imn_last_error": (C.c_char_p, []),
     "imn_abi_version": (C.c_int, []),
 }

@@ -103,3 +103,18 @@ extern "C" int imn_rowless_handoff(const ImnModel* m, const ImnData* d, void* st
   return imn::launch_mul_m(m, d->M, d->M_ld, d->qacc_smooth, d->dof_ld, d->efc_Ma, d->dof_ld, d->qacc,
                            d->solver_niter, d->qfrc_constraint, d->nworld, (cudaStream_t)stream);
 }
+
+extern "C" int imn_copy_rows(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width,
+                             int32_t nworld, int32_t to_host, void* stream) {
+  if (!dst || !src) return imn::set_error("imn_copy_rows: NULL buffer"), IMN_ERR_NULL;
+  if (width < 0 || nworld < 0 || width > dst_pitch || width > src_pitch)
+    return imn::set_error("imn_copy_rows: width %lld exceeds a pitch (%lld, %lld)", (long long)width,
+                          (long long)dst_pitch, (long long)src_pitch),
+           IMN_ERR_SHAPE;
+  if (width == 0 || nworld == 0) return IMN_OK;
+  const cudaError_t e = cudaMemcpy2DAsync(dst, (size_t)dst_pitch, src, (size_t)src_pitch, (size_t)width, (size_t)nworld,
+                                          to_host ? cudaMemcpyDeviceToHost : cudaMemcpyHostToDevice,
+                                          (cudaStream_t)stream);
+  if (e != cudaSuccess) return imn::set_error("imn_copy_rows: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  return IMN_OK;
+}

@@ -50,6 +50,61 @@ def humanoid_tree():
     return _tree_from_joints(joints)
 
 
+def humanoid_mjcf(iterations: int = 50, ls_iterations: int = 50, tolerance: float = 1e-8) -> str:
+    """MJCF text of a humanoid with the joint tree of ``humanoid_tree`` (free root, 8 ball
+    joints, 4 hinges, nv 34), capsule links, box feet and a floor plane, with the
+    benchmark's solver options (Newton, pyramidal cones, dense Jacobian).  Geometry is
+    generated, not taken from the reference's model file: it serves the CPU baseline
+    that steps MuJoCo C on a model of the same structure."""
+    names = ["pelvis", "abdomen", "neck", "r_shoulder", "r_elbow", "l_shoulder", "l_elbow", "r_hip", "r_knee",
+             "r_ankle", "l_hip", "l_knee", "l_ankle"]
+    joints = [(6, -1), (3, 0), (3, 1), (3, 1), (1, 3), (3, 1), (1, 5), (3, 0), (1, 7), (3, 8), (3, 0), (1, 10),
+              (3, 11)]
+    # offset of each body in its parent's frame, and the link capsule's end point
+    pos = {"pelvis": (0, 0, 0.98), "abdomen": (0, 0, 0.12), "neck": (0, 0, 0.32), "r_shoulder": (0, -0.18, 0.26),
+           "r_elbow": (0, 0, -0.28), "l_shoulder": (0, 0.18, 0.26), "l_elbow": (0, 0, -0.28),
+           "r_hip": (0, -0.09, -0.06), "r_knee": (0, 0, -0.42), "r_ankle": (0, 0, -0.41),
+           "l_hip": (0, 0.09, -0.06), "l_knee": (0, 0, -0.42), "l_ankle": (0, 0, -0.41)}
+    tip = {"pelvis": (0, 0, 0.08), "abdomen": (0, 0, 0.28), "neck": (0, 0, 0.14), "r_shoulder": (0, 0, -0.26),
+           "r_elbow": (0, 0, -0.24), "l_shoulder": (0, 0, -0.26), "l_elbow": (0, 0, -0.24), "r_hip": (0, 0, -0.40),
+           "r_knee": (0, 0, -0.39), "l_hip": (0, 0, -0.40), "l_knee": (0, 0, -0.39)}
+    children: dict[int, list[int]] = {}
+    for j, (_, pj) in enumerate(joints):
+        children.setdefault(pj, []).append(j)
+    vec = lambda v: " ".join(f"{x:g}" for x in v)  # noqa: E731
+
+    def body(j: int, indent: str) -> str:
+        name, ndof = names[j], joints[j][0]
+        out = [f'{indent}<body name="{name}" pos="{vec(pos[name])}">']
+        if ndof == 6:
+            out.append(f'{indent}  <freejoint name="{name}"/>')
+        elif ndof == 3:
+            out.append(f'{indent}  <joint name="{name}" type="ball" damping="1"/>')
+        else:
+            out.append(f'{indent}  <joint name="{name}" type="hinge" axis="0 1 0" range="-140 5" damping="1"/>')
+        if name.endswith("ankle"):
+            out.append(f'{indent}  <geom name="{name}_foot" type="box" size="0.09 0.045 0.03" pos="0.045 0 -0.03"/>')
+        else:
+            out.append(f'{indent}  <geom name="{name}_link" type="capsule" size="0.05" '
+                       f'fromto="0 0 0 {vec(tip[name])}" contype="0" conaffinity="0"/>')
+        for c in children.get(j, []):
+            out.append(body(c, indent + "  "))
+        out.append(f"{indent}</body>")
+        return "\n".join(out)
+
+    return f"""<mujoco model="generated_humanoid">
+  <compiler angle="degree"/>
+  <option timestep="{1 / 120:.8f}" integrator="implicitfast" solver="Newton" cone="pyramidal" jacobian="dense"
+          iterations="{iterations}" ls_iterations="{ls_iterations}" tolerance="{tolerance:g}"/>
+  <default><geom density="1000" friction="1 0.005 0.0001"/></default>
+  <worldbody>
+    <geom name="floor" type="plane" size="0 0 0.05" conaffinity="1"/>
+{body(0, "    ")}
+  </worldbody>
+</mujoco>
+"""
+
+
 def snu_tree():
     """The SNU muscle humanoid's joint tree, transcribed from
     data/snu_humanoid/mjcf/include/body.xml:50-897 (bodies in document order, which

@@ -85,7 +85,8 @@ def test_solve_with_scratch_on_warp_style_buffers(oracle, cuda_device):
     got = mjw_model.to_host(dd)
     np.testing.assert_array_equal(got.qacc.view(np.uint32), want.qacc.view(np.uint32))
     np.testing.assert_array_equal(got.solver_niter, want.solver_niter)
-    assert int(scratch.solver_nsolving.item()) == 0
+    # worlds without rows are finished before the loop and never count down (as in the reference)
+    assert int(scratch.solver_nsolving.item()) == int((d.nefc == 0).sum())
     # the sparse plan is installed on, and its counter read from, a Warp-style context
     groups = [[b] for b in range(1, len(m.body_dofadr))]
     assert runtime.refresh_sparse_hessian(mw, dw, sw, groups, cuda_device) == "enabled"
