@@ -62,213 +62,297 @@ def _np(a):
     return to_host(a)
 
 
-def _chain(body: int, body_parentid, body_dofadr, body_dofnum) -> list[int]:
-    """Dofs of a body and of all its ancestors."""
-    out = []
-    b = int(body)
-    while b > 0:
+def _strict_ancestors(dof_parentid: np.ndarray) -> np.ndarray:
+    """(nv, nv) bool: entry [d, a] says dof a is a strict tree ancestor of dof d.  A
+    dof's parent precedes it, so one pass in dof order inherits the parent's row."""
+    nv = int(dof_parentid.size)
+    anc = np.zeros((nv, nv), bool)
+    for d in range(nv):
+        p = int(dof_parentid[d])
+        if p >= 0:
+            anc[d] = anc[p]
+            anc[d, p] = True
+    return anc
+
+
+def _chain_masks(body_parentid, body_dofadr, body_dofnum, nv: int) -> np.ndarray:
+    """(nbody, nv) bool: the dofs that move body b, i.e. its own and those of every
+    body between it and the world.  Bodies follow their parents, so a body's mask is
+    its parent's plus its own dofs."""
+    nbody = int(body_parentid.size)
+    masks = np.zeros((nbody, nv), bool)
+    for b in range(1, nbody):
+        masks[b] = masks[int(body_parentid[b])]
         first = int(body_dofadr[b])
         if first >= 0:
-            out.extend(range(first, first + int(body_dofnum[b])))
-        b = int(body_parentid[b])
-    return out
+            masks[b, first : first + int(body_dofnum[b])] = True
+    return masks
+
+
+class _Coupling:
+    """Symmetric dof-coupling matrix under construction."""
+
+    def __init__(self, m: Any):
+        self.nv = int(m.nv)
+        anc = _strict_ancestors(_np(m.dof_parentid).astype(np.int64))
+        self.P = anc | anc.T
+        self.masks = _chain_masks(_np(m.body_parentid), _np(m.body_dofadr), _np(m.body_dofnum), self.nv)
+
+    def bodies(self, ids) -> None:
+        """One constraint row may touch all these bodies at once: every dof that moves
+        one of them couples with every other."""
+        ids = [int(b) for b in ids if int(b) > 0]
+        if ids:
+            self.dofs(np.flatnonzero(self.masks[ids].any(axis=0)))
+
+    def dofs(self, ids) -> None:
+        ids = np.asarray(ids, dtype=np.int64)
+        self.P[np.ix_(ids, ids)] = True
+
+    def adjacency(self) -> list[set[int]]:
+        P = self.P.copy()
+        np.fill_diagonal(P, False)
+        return [set(int(b) for b in np.flatnonzero(P[a])) for a in range(self.nv)]
+
+
+def _couple_equalities(m: Any, cp: _Coupling) -> None:
+    """connect / weld rows couple two bodies (given directly or through two sites),
+    joint rows couple the first dof of one or two joints; flex equalities live inside
+    the flex couplings."""
+    eq_type, obj1, obj2, objtype = (_np(getattr(m, n)) for n in ("eq_type", "eq_obj1id", "eq_obj2id", "eq_objtype"))
+    for t, a, b, kind in zip(eq_type, obj1, obj2, objtype):
+        t, a, b = int(t), int(a), int(b)
+        if t in (EQ_FLEX, EQ_FLEXVERT, EQ_FLEXSTRAIN):
+            continue
+        if t in (EQ_CONNECT, EQ_WELD):
+            if int(kind) == OBJ_SITE:
+                site_bodyid = _np(m.site_bodyid)
+                a, b = int(site_bodyid[a]), int(site_bodyid[b])
+            cp.bodies([a, b])
+        elif t == EQ_JOINT:
+            jnt_dofadr = _np(m.jnt_dofadr)
+            cp.dofs([int(jnt_dofadr[a])] + ([int(jnt_dofadr[b])] if b >= 0 else []))
+        else:
+            raise ValueError(f"equality constraint of type {t} has no coupling rule")
+
+
+def _couple_flexes(m: Any, cp: _Coupling) -> None:
+    """Bodies one flex row can touch (sparse_hessian.py:121-170).  A flex with
+    interpolation couples all its nodes; otherwise each element couples its vertices'
+    bodies (elasticity, edge equalities, contacts inside an element).  A geom that may
+    collide with a flex (contype / conaffinity either way) adds its body to each of the
+    flex's elements; two flexes that may collide (or one with itself when it
+    self-collides) are coupled as wholes."""
+    nflex = int(m.nflex)
+    get = lambda name: _np(getattr(m, name))  # noqa: E731
+    vertadr, vertnum, vertbody = get("flex_vertadr"), get("flex_vertnum"), get("flex_vertbodyid")
+    elemnum, dataadr, dim, elem = get("flex_elemnum"), get("flex_elemdataadr"), get("flex_dim"), get("flex_elem")
+    interp, nodeadr, nodenum, nodebody = get("flex_interp"), get("flex_nodeadr"), get("flex_nodenum"), get("flex_nodebodyid")
+    whole: list[list[int]] = []          # all bodies of flex f
+    elements: list[list[list[int]]] = []  # per flex, the body list of each element
+    for f in range(nflex):
+        if int(interp[f]) != 0:
+            nodes = [int(b) for b in nodebody[int(nodeadr[f]) : int(nodeadr[f]) + int(nodenum[f])]]
+            whole.append(nodes)
+            elements.append([nodes] * int(elemnum[f]))
+            cp.bodies(nodes)
+            continue
+        v0 = int(vertadr[f])
+        whole.append([int(b) for b in vertbody[v0 : v0 + int(vertnum[f])]])
+        per = int(dim[f]) + 1
+        data = np.asarray(elem[int(dataadr[f]) : int(dataadr[f]) + per * int(elemnum[f])]).reshape(-1, per)
+        elements.append([[int(vertbody[v0 + int(v)]) for v in row] for row in data])
+        for bodies in elements[-1]:
+            cp.bodies(bodies)
+    f_type, f_aff = get("flex_contype"), get("flex_conaffinity")
+    g_type, g_aff, geom_bodyid = get("geom_contype"), get("geom_conaffinity"), get("geom_bodyid")
+    for f in range(nflex):
+        hits = np.flatnonzero((int(f_type[f]) & g_aff) | (g_type & int(f_aff[f])))
+        for g in hits:
+            for bodies in elements[f]:
+                cp.bodies([*bodies, int(geom_bodyid[g])])
+    selfcollide = get("flex_selfcollide")
+    for f in range(nflex):
+        for h in range(f, nflex):
+            may = (int(f_type[f]) & int(f_aff[h])) or (int(f_type[h]) & int(f_aff[f]))
+            if may and (f != h or int(selfcollide[f])):
+                cp.bodies(whole[f] + whole[h])
 
 
 def hessian_pattern(m: Any, body_groups: Sequence[Sequence[int]]) -> list[set[int]]:
     """Upper bound of H's off-diagonal pattern as a dof adjacency (MuJoCo dof order):
-    tree ancestry, every declared body group, equality constraints, and the native
-    collision candidates (sparse_hessian.py:62-118)."""
-    nv = int(m.nv)
-    dof_parentid = _np(m.dof_parentid)
-    body_parentid, body_dofadr, body_dofnum = _np(m.body_parentid), _np(m.body_dofadr), _np(m.body_dofnum)
-    adj: list[set[int]] = [set() for _ in range(nv)]
-    for d in range(nv):
-        p = int(dof_parentid[d])
-        while p >= 0:
-            adj[d].add(p)
-            adj[p].add(d)
-            p = int(dof_parentid[p])
-
-    def clique(bodies):
-        dofs = sorted({d for b in bodies for d in _chain(b, body_parentid, body_dofadr, body_dofnum)})
-        for a in dofs:
-            adj[a].update(x for x in dofs if x != a)
-
+    tree ancestry, every declared body group, equality constraints, flex couplings and
+    the native collision candidates (sparse_hessian.py:62-170)."""
+    cp = _Coupling(m)
     for group in body_groups:
-        clique(group)
+        cp.bodies(group)
     if int(getattr(m, "neq", 0) or 0):
-        eq_type, obj1, obj2 = _np(m.eq_type), _np(m.eq_obj1id), _np(m.eq_obj2id)
-        objtype = _np(m.eq_objtype)
-        site_bodyid = _np(getattr(m, "site_bodyid", None))
-        jnt_dofadr = _np(getattr(m, "jnt_dofadr", None))
-        for t, a, b, ot in zip(eq_type, obj1, obj2, objtype):
-            if t in (EQ_CONNECT, EQ_WELD):
-                if ot == OBJ_SITE:
-                    a, b = site_bodyid[a], site_bodyid[b]
-                clique((int(a), max(int(b), 0)))
-            elif t in (EQ_FLEX, EQ_FLEXVERT, EQ_FLEXSTRAIN):
-                continue
-            elif t == EQ_JOINT:
-                dofs = [int(jnt_dofadr[a])] + ([int(jnt_dofadr[b])] if b >= 0 else [])
-                for x in dofs:
-                    adj[x].update(y for y in dofs if y != x)
-            else:
-                raise ValueError(f"equality type {int(t)} is not supported")
+        _couple_equalities(m, cp)
     if int(getattr(m, "nflex", 0) or 0):
-        raise ValueError("flex objects are not supported by this pattern builder")
-    geom_bodyid = _np(getattr(m, "geom_bodyid", None))
+        _couple_flexes(m, cp)
     pairs = _np(getattr(m, "nxn_geom_pair_filtered", None))
     if pairs is not None and pairs.shape[0]:
-        for g1, g2 in pairs:
-            clique((int(geom_bodyid[g1]), int(geom_bodyid[g2])))
-    return adj
+        geom_bodyid = _np(m.geom_bodyid)
+        for g1, g2 in np.asarray(pairs).reshape(-1, 2):
+            cp.bodies([int(geom_bodyid[g1]), int(geom_bodyid[g2])])
+    return cp.adjacency()
+
+
+def _filled_upper(adj_e: list[set[int]]) -> np.ndarray:
+    """Boolean upper triangle of the factor's structure for a symmetric pattern given as
+    an adjacency in elimination order: eliminating k joins all its later neighbours."""
+    n = len(adj_e)
+    U = np.zeros((n, n), bool)
+    for k, nb in enumerate(adj_e):
+        later = [a for a in nb if a > k]
+        U[k, later] = True
+    for k in range(n):
+        later = np.flatnonzero(U[k])
+        if later.size > 1:
+            block = U[np.ix_(later, later)]
+            block |= np.triu(np.ones((later.size, later.size), bool), 1)
+            U[np.ix_(later, later)] = block
+    return U
+
+
+def _etree_levels(U: np.ndarray) -> list[list[int]]:
+    """Elimination-tree levels: a column's parent is its first later neighbour; a node
+    sits one level above its deepest child."""
+    n = U.shape[0]
+    depth = np.zeros(n, np.int64)
+    for k in range(n):
+        later = np.flatnonzero(U[k])
+        if later.size:
+            depth[later[0]] = max(depth[later[0]], depth[k] + 1)
+    return [[int(k) for k in np.flatnonzero(depth == lv)] for lv in range(int(depth.max(initial=0)) + 1)]
 
 
 def _symbolic(adj_e: list[set[int]]):
-    """Symbolic L'DL in elimination order: fill, row/column structures and the
-    elimination-tree levels (sparse_hessian.py:192-212)."""
-    n = len(adj_e)
-    upper = [{a for a in adj_e[k] if a > k} for k in range(n)]
-    for k in range(n):
-        later = sorted(upper[k])
-        for pos, a in enumerate(later):
-            upper[a].update(later[pos + 1 :])
-    colstruct = [sorted(upper[k]) for k in range(n)]
-    rowstruct: list[list[int]] = [[] for _ in range(n)]
-    for k in range(n):
-        for i in colstruct[k]:
-            rowstruct[i].append(k)
-    parent = [c[0] if c else -1 for c in colstruct]
-    level = [0] * n
-    for k in range(n):
-        if parent[k] >= 0:
-            level[parent[k]] = max(level[parent[k]], level[k] + 1)
-    levels: list[list[int]] = [[] for _ in range(max(level, default=0) + 1)]
-    for k in range(n):
-        levels[level[k]].append(k)
-    return rowstruct, colstruct, levels
+    """Symbolic L'DL in elimination order: (row structure, column structure, levels)
+    (sparse_hessian.py:192-212)."""
+    U = _filled_upper(adj_e)
+    n = U.shape[0]
+    colstruct = [[int(i) for i in np.flatnonzero(U[k])] for k in range(n)]
+    rowstruct = [[int(k) for k in np.flatnonzero(U[:, i])] for i in range(n)]
+    return rowstruct, colstruct, _etree_levels(U)
 
 
 def _team(nentries: int, maxterms: int, lanes: int) -> int:
-    """Lanes per entry of one level: the power of two that minimises sweeps x
-    (terms per lane + tree depth) (sparse_hessian.py:215-221)."""
-    best, best_cost = 1, None
-    for T in (1, 2, 4, 8, 16, 32):
-        sweeps = -(-nentries // (lanes // T))
-        cost = sweeps * (-(-maxterms // T) + 2 * int(np.log2(T)))
-        if best_cost is None or cost < best_cost:
-            best, best_cost = T, cost
-    return best
+    """Lanes per entry of one level: the power of two with the fewest steps, a step
+    count being sweeps x (terms per lane + two per stage of the team's reduction
+    tree) (sparse_hessian.py:215-221)."""
+    log2 = np.arange(6)
+    width = 1 << log2
+    sweeps = -(-nentries // (lanes // width))
+    steps = sweeps * (-(-maxterms // width) + 2 * log2)
+    return int(width[int(np.argmin(steps))])
+
+
+def _runs(ks: np.ndarray, a: np.ndarray, b: np.ndarray):
+    """Maximal stretches over which the elimination index and both slots advance by one:
+    (first a, first b, first k, length) per stretch."""
+    if ks.size == 0:
+        return []
+    step = (np.diff(ks) != 1) | (np.diff(a) != 1) | (np.diff(b) != 1)
+    starts = np.concatenate(([0], np.flatnonzero(step) + 1))
+    ends = np.concatenate((starts[1:], [ks.size]))
+    return [(int(a[s]), int(b[s]), int(ks[s]), int(e - s)) for s, e in zip(starts, ends)]
 
 
 def build_plan(m: Any, body_groups: Sequence[Sequence[int]], block: int, path: str = "fused") -> SparseHessianPlan:
-    """Symbolic factor and every index table of the numeric kernels
-    (sparse_hessian.py:229-402).  Elimination index e = nv - 1 - dof (leaves first).
-    Slots are row-major over L's rows (row structure, then the diagonal), followed by
-    one augmented row for the right-hand side."""
+    """Symbolic factor and every index table of the numeric kernels (table semantics of
+    sparse_hessian.py:229-402).  Elimination index e = nv - 1 - dof (leaves first).
+    Slots are row-major over L's rows (a row's off-diagonal entries in ascending
+    column order, then its diagonal), followed by one augmented row for the right-hand
+    side."""
     nv, nv_pad = int(m.nv), int(m.nv_pad)
-    adj = hessian_pattern(m, body_groups)
     n = nv
-    orig = [nv - 1 - e for e in range(n)]
-    adj_e = [{nv - 1 - a for a in adj[orig[e]]} for e in range(n)]
-    rowstruct, colstruct, levels = _symbolic(adj_e)
-    slot: dict[tuple[int, int], int] = {}
-    for i in range(n):
-        for k in rowstruct[i]:
-            slot[i, k] = len(slot)
-        slot[i, i] = len(slot)
-    nfac = len(slot)
-    rhs = nfac
-    for k in range(n):
-        slot[n, k] = len(slot)
-    nslots = len(slot)
-    if nslots >= 65536 or nfac + n > nv_pad * nv_pad:
-        raise ValueError("sparse Hessian factor does not fit the packed layout")
-    rs = [set(r) for r in rowstruct]
+    adj = hessian_pattern(m, body_groups)
+    orig = np.arange(n - 1, -1, -1)
+    U = _filled_upper([{nv - 1 - a for a in adj[orig[e]]} for e in range(n)])
+    L = U.T  # L[i, k]: entry (i, k), k < i, is in the factor
+    levels = _etree_levels(U)
+    # slot numbers: numpy walks the lower triangle (diagonal included) row-major
+    slot_of = np.full((n + 1, n), -1, np.int64)
+    rows, cols = np.nonzero(L | np.eye(n, dtype=bool))
+    slot_of[rows, cols] = np.arange(rows.size)
+    nfac = int(rows.size)
+    slot_of[n] = nfac + np.arange(n)
+    nslots = nfac + n
+    if nslots >= 65536 or nslots > nv_pad * nv_pad:
+        raise ValueError(f"sparse Hessian factor of {nslots} slots exceeds the packed (nv_pad, nv_pad) storage")
+    Lx = np.vstack([L, np.ones((1, n), bool)])  # the augmented row meets every column
     lvl_ptr, lvl_team, ent_slot, ent_col, run_ptr, run_ab, run_kl = [0], [], [], [], [0], [], []
     nterms = 0
-    for cols in levels:
-        entries = []
-        for j in cols:
-            for i in [j, *colstruct[j], n]:
-                ks = sorted(rs[j]) if i in (j, n) else sorted(rs[j] & rs[i])
-                runs: list[list[int]] = []
-                for k in ks:
-                    a, b = slot[i, k], slot[j, k]
-                    last = runs[-1] if runs else None
-                    if last and k == last[2] + last[3] and a == last[0] + last[3] and b == last[1] + last[3]:
-                        last[3] += 1
-                    else:
-                        runs.append([a, b, k, 1])
-                entries.append((slot[i, j], j if i == j else -1, runs, len(ks)))
-        entries.sort(key=lambda e: -e[3])  # stable: longest entries first
-        for s, c, runs, nt in entries:
+    for columns in levels:
+        found = []  # (slot, diagonal column or -1, runs, term count)
+        for j in columns:
+            below = np.flatnonzero(U[j])
+            for i in (j, *below.tolist(), n):
+                # terms: earlier columns k present in both row j and row i (the diagonal
+                # entry and the augmented row meet all of row j)
+                ks = np.flatnonzero(L[j] if i == j else (L[j] & Lx[i]))
+                found.append((int(slot_of[i, j]), j if i == j else -1, _runs(ks, slot_of[i, ks], slot_of[j, ks]),
+                              int(ks.size)))
+        # entries with many terms first (stable), so that a sweep's lanes finish together
+        order = np.argsort([-f[3] for f in found], kind="stable")
+        for q in order:
+            s, c, runs, nt = found[int(q)]
             ent_slot.append(s)
             ent_col.append(c)
-            for a, b, k, ln in runs:
-                run_ab.append(a | (b << 16))
-                run_kl.append(k | (ln << 16))
+            run_ab += [a | (b << 16) for a, b, _, _ in runs]
+            run_kl += [k | (ln << 16) for _, _, k, ln in runs]
             run_ptr.append(len(run_ab))
             nterms += nt
         lvl_ptr.append(len(ent_slot))
-        lvl_team.append(_team(len(entries), max(e[3] for e in entries), block))
-    by_slot = sorted(((s, ij) for ij, s in slot.items() if s < nfac))
-    gat, s_a, s_b, s_m = [], [], [], []
-    colind, rowi = _np(m.M_colind), _np(m.M_hinit_i)
-    csr = {(min(int(r), int(c)), max(int(r), int(c))): e for e, (r, c) in enumerate(zip(rowi, colind))}
-    for s, (i, j) in by_slot:
-        a, b = sorted((orig[i], orig[j]))
-        gat.append(a * nv_pad + b)
-        s_a.append(a)
-        s_b.append(b)
-        s_m.append(csr.get((a, b), -1))
-    f_lvl, f_row = [0], []
-    for cols in levels:
-        f_row += cols
-        f_lvl.append(len(f_row))
-    row_start = [slot[j, rowstruct[j][0]] if rowstruct[j] else slot[j, j] for j in range(n)]
-    rk_ptr, rk = [0], []
-    for j in range(n):
-        rk += rowstruct[j]
-        rk_ptr.append(len(rk))
-    # backward solve, root level first: a level's finished unknowns push their column
-    # terms to their descendants; an unknown receives at most one push per level
-    b_lvl, b_slot, b_src, b_dst = [0], [], [], []
-    for cols in reversed(levels):
-        for i in cols:
-            for j in rowstruct[i]:
-                b_slot.append(slot[i, j])
-                b_src.append(i)
-                b_dst.append(j)
-        b_lvl.append(len(b_slot))
-    for a in (lvl_ptr, ent_slot, run_ptr, f_lvl, f_row, row_start, rk_ptr, rk, b_lvl, b_slot, b_src, b_dst):
-        if max(a, default=0) >= 65536:
-            raise ValueError("sparse Hessian tables exceed 16-bit indices")
-    pair = [-1] * (nv * nv)
-    for a in range(nv):
-        for b in range(a, nv):
-            i, j = nv - 1 - a, nv - 1 - b
-            if (i, j) in slot and slot[i, j] < nfac:
-                pair[a * nv + b] = slot[i, j]
+        lvl_team.append(_team(len(found), max(f[3] for f in found), block))
+    # dense position and CSR entry of M behind every factor slot
+    colind, rowi = _np(m.M_colind).astype(np.int64), _np(m.M_hinit_i).astype(np.int64)
+    m_entry = np.full((nv, nv), -1, np.int64)
+    m_entry[np.minimum(rowi, colind), np.maximum(rowi, colind)] = np.arange(colind.size)
+    dof_hi, dof_lo = orig[rows], orig[cols]  # elimination row >= column  <=>  dof row <= column
+    s_a, s_b = np.minimum(dof_hi, dof_lo), np.maximum(dof_hi, dof_lo)
+    gat = s_a * nv_pad + s_b
+    s_m = m_entry[s_a, s_b]
+    pair = np.full((nv, nv), -1, np.int64)
+    pair[s_a, s_b] = np.arange(nfac)
+    reach = (pair >= 0) | (pair.T >= 0) | np.eye(nv, dtype=bool)
     words = (nv + 31) // 32
-    pmask = []
-    for a in range(nv):
-        bits = [0] * words
-        for b in range(nv):
-            if b == a or pair[min(a, b) * nv + max(a, b)] >= 0:
-                bits[b // 32] |= 1 << (b % 32)
-        pmask += bits
+    bits = np.zeros((nv, words * 32), np.uint64)
+    bits[:, :nv] = reach
+    pmask = (bits.reshape(nv, words, 32) << np.arange(32, dtype=np.uint64)).sum(axis=2)
+    # forward solve: unknowns by level, each with its row's slots and source columns
+    f_row = [k for columns in levels for k in columns]
+    f_lvl = np.concatenate(([0], np.cumsum([len(c) for c in levels])))
+    row_nnz = L.sum(axis=1)
+    row_first = np.where(row_nnz > 0, slot_of[np.arange(n), np.argmax(L, axis=1)], slot_of[np.arange(n), np.arange(n)])
+    rk = cols[rows != cols]
+    rk_ptr = np.concatenate(([0], np.cumsum(row_nnz)))
+    # backward solve, root level first: a finished unknown pushes its column terms down
+    # to the unknowns of its row; an unknown receives at most one push per level
+    b_lvl, b_slot, b_src, b_dst = [0], [], [], []
+    for columns in reversed(levels):
+        for i in columns:
+            js = np.flatnonzero(L[i])
+            b_slot += slot_of[i, js].tolist()
+            b_src += [i] * js.size
+            b_dst += js.tolist()
+        b_lvl.append(len(b_slot))
+    for table in (lvl_ptr, ent_slot, run_ptr, f_lvl, f_row, row_first, rk_ptr, rk, b_lvl, b_slot, b_src, b_dst):
+        if np.max(table, initial=0) >= 65536:
+            raise ValueError("a sparse Hessian index table does not fit 16 bits")
     nw = block // 32
     if 2 * nfac + n >= nv_pad * nv_pad - 1:
-        raise ValueError("packed H and factor do not fit hfactor")
+        raise ValueError("packed H, factor and 1/D leave no room for the violation counter in hfactor")
     init_tile = 4 * nv + 4 if path == "fused" else 0
     if 4 * (nslots + n + 2 * nw + init_tile) > MAX_SHARED_BYTES:
-        raise ValueError("the factor does not fit the block's shared memory")
+        raise ValueError("the per-world factor exceeds the shared-memory budget of one block")
     raw = dict(
         lvl_ptr=lvl_ptr, lvl_team=lvl_team, ent_slot=ent_slot, ent_col=ent_col, run_ptr=run_ptr,
-        run_ab=run_ab, run_kl=run_kl, orig=orig, b_lvl=b_lvl, b_slot=b_slot, b_src=b_src, b_dst=b_dst,
-        pair=pair, f_lvl=f_lvl, f_row=f_row, row_start=row_start, rk_ptr=rk_ptr, rk=rk or [0],
-        pmask=pmask, s_a=s_a, s_b=s_b, s_m=s_m, gat=gat,
+        run_ab=run_ab, run_kl=run_kl, orig=orig.tolist(), b_lvl=b_lvl, b_slot=b_slot, b_src=b_src, b_dst=b_dst,
+        pair=pair.reshape(-1).tolist(), f_lvl=f_lvl.tolist(), f_row=f_row, row_start=row_first.tolist(),
+        rk_ptr=rk_ptr.tolist(), rk=rk.tolist() or [0], pmask=pmask.reshape(-1).tolist(), s_a=s_a.tolist(),
+        s_b=s_b.tolist(), s_m=s_m.tolist(), gat=gat.tolist(),
     )
     raw["fsweep"], raw["bsweep"] = _pack_sweeps(raw) if path == "fused" else ([], [])
     tables = {}
@@ -376,16 +460,25 @@ def plan_for_model(m: Any, ctx: Any, body_groups, block: int, *, compact: bool =
         return None, "fused Newton not eligible (CPU)"
     if int(m.nv) < MIN_NV:
         return None, f"nv {int(m.nv)} < {MIN_NV}"
-    if int(getattr(m, "ntendon", 0) or 0) and getattr(m, "tendon_rows_possible", True):
-        return None, "tendon limit or frictionloss rows"
+    if int(getattr(m, "ntendon", 0) or 0):
+        # tendon limit and friction-loss rows couple the dofs a tendon spans, which the
+        # pattern does not cover: read the live model arrays (sparse_hessian.py:729-733);
+        # a model that has tendons but lacks the arrays is refused
+        limited = getattr(m, "tendon_limited_adr", None)
+        loss = getattr(m, "tendon_frictionloss", None)
+        if limited is None or loss is None or int(_np(limited).shape[0]) or bool((_np(loss) > 0).any()):
+            return None, "tendon limit or frictionloss rows"
+    from .. import binding
+
+    const = binding.upstream_constants()
     if fused_runtime and newton_fusion.eligible(m, ctx, compact=compact):
         if int(getattr(m, "nflex", 0) or 0):
             return None, "flex objects on the fused path"
         path, width = "fused", block
     elif (
-        int(m.opt.solver) == int(types.SolverType.NEWTON)
-        and int(m.opt.cone) == int(types.ConeType.PYRAMIDAL)
-        and int(m.opt.integrator) != int(types.IntegratorType.DISCRETE)
+        int(m.opt.solver) == const["solver_newton"]
+        and int(m.opt.cone) == const["cone_pyramidal"]
+        and int(m.opt.integrator) != const["integrator_discrete"]
         and m.opt.iterations > 0
         and not compact
         and not newton_fusion._sparse_compact(ctx)

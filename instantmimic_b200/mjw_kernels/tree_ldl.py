@@ -97,30 +97,32 @@ class GeneratedKernel:
 
 
 def tree_ldl_structure(rowadr, rownnz, colind):
-    """The CSR as tuples when it has the nested-ancestor form; else ``None``."""
+    """The CSR as tuples when it has the nested-ancestor form, else ``None``
+    (tree_ldl.py:66-91).  Nested-ancestor form: every row ends with its own dof; a
+    row of more than one entry is its parent's row (the dof before the last)
+    followed by the dof itself.  By induction over the dofs this makes every
+    ancestor's row a prefix of the row."""
     rowadr = np.asarray(rowadr, dtype=np.int64)
     rownnz = np.asarray(rownnz, dtype=np.int64)
     colind = np.asarray(colind, dtype=np.int64)
     nv = rowadr.size
-    if nv == 0 or rownnz.size != nv or (rownnz < 1).any():
+    if nv == 0 or rownnz.size != nv or (rownnz < 1).any() or (rowadr < 0).any():
         return None
     if (rowadr + rownnz > colind.size).any():
         return None
-    for k in range(nv):
-        row = colind[rowadr[k] : rowadr[k] + rownnz[k]]
-        if row[-1] != k or (row[:-1] >= k).any():
+    last = rowadr + rownnz - 1
+    if (colind[last] != np.arange(nv)).any():
+        return None
+    for k in np.flatnonzero(rownnz > 1):
+        head = colind[rowadr[k] : last[k]]
+        p = int(head[-1])
+        if p >= k or rownnz[p] != head.size or not np.array_equal(head, colind[rowadr[p] : rowadr[p] + head.size]):
             return None
-        for depth, anc in enumerate(row[:-1]):
-            # the ancestor's row must be exactly this row's first depth+1 entries
-            if rownnz[anc] != depth + 1:
-                return None
-            if not np.array_equal(colind[rowadr[anc] : rowadr[anc] + depth + 1], row[: depth + 1]):
-                return None
-    as_tuple = lambda a: tuple(int(v) for v in a)  # noqa: E731
-    return as_tuple(rowadr), as_tuple(rownnz), as_tuple(colind)
+    return tuple(rowadr.tolist()), tuple(rownnz.tolist()), tuple(colind.tolist())
 
 
 def _tree(rowadr, rownnz, colind):
+    """(parent, children) of the dof tree behind the CSR."""
     nv = len(rowadr)
     parent = [colind[rowadr[k] + rownnz[k] - 2] if rownnz[k] > 1 else -1 for k in range(nv)]
     children: list[list[int]] = [[] for _ in range(nv)]
@@ -130,87 +132,97 @@ def _tree(rowadr, rownnz, colind):
     return parent, children
 
 
-def _trunk_entry_count(rowadr, rownnz, trunk) -> int:
-    return sum(rownnz[i] for i in trunk)
-
-
 def _shared_bytes(rowadr, rownnz, groups: int, trunk) -> int:
-    """Bytes of the reference's trunk exchange arrays for one block of 32 worlds."""
+    """Bytes of the reference's trunk exchange arrays for one block of 32 worlds: every
+    group keeps its contribution to each trunk entry and trunk right-hand side, plus
+    the trunk solution once (tree_ldl.py:98-102)."""
     if not trunk:
         return 0
-    entries = _trunk_entry_count(rowadr, rownnz, trunk)
+    entries = int(sum(rownnz[i] for i in trunk))
     return 4 * 32 * (groups * (entries + len(trunk)) + len(trunk))
 
 
-def plan_tree_ldl(rowadr, rownnz, colind, groups: int) -> TreeLdlPlan:
-    """Shortest-critical-path plan with exactly ``groups`` groups.
+def _balance(parts, weight, groups: int):
+    """Longest-processing-time packing: parts by falling weight (index breaks ties),
+    each onto the currently lightest group (lowest group on ties).  Returns the
+    heaviest group's load and the groups' part lists."""
+    import heapq
 
-    Start with whole trees as parts.  Repeatedly take the heaviest part that still
-    has children, move its root dof to the trunk and let its children become
-    parts; after each move pack the parts onto the groups (heaviest first, always
-    onto the lightest group) and remember the cut with the shortest critical path.
-    """
+    heap = [(0, g) for g in range(groups)]
+    bins: list[list[int]] = [[] for _ in range(groups)]
+    for r in sorted(parts, key=lambda r: (-weight[r], r)):
+        load, g = heapq.heappop(heap)
+        bins[g].append(r)
+        heapq.heappush(heap, (load + weight[r], g))
+    return max(load for load, _ in heap), bins
+
+
+def plan_tree_ldl(rowadr, rownnz, colind, groups: int) -> TreeLdlPlan:
+    """Plan with exactly ``groups`` groups and the shortest critical path found by the
+    rule of tree_ldl.py:105-170: begin with whole trees as parts; keep cutting the
+    heaviest part that can still be cut (its root dof moves to the trunk, its
+    children become parts), and of all cuts seen keep the one whose heaviest group
+    plus trunk is shortest.  Costs are in update units: eliminating a dof whose row
+    has n entries takes n (n - 1) / 2 updates plus 2 n for scaling and the solves; a
+    trunk dof costs 2 n more for the exchange."""
+    import heapq
+
     nv = len(rowadr)
     parent, children = _tree(rowadr, rownnz, colind)
-    # eliminating a dof with n row entries: n (n - 1) / 2 updates + scaling + solve
-    cost = [n * (n - 1) // 2 + 2 * n for n in rownnz]
-    weight, size = list(cost), [1] * nv
-    for k in range(nv - 1, -1, -1):
+    own = [n * (n - 1) // 2 + 2 * n for n in rownnz]
+    weight, size = list(own), [1] * nv
+    for k in range(nv - 1, -1, -1):  # children before parents
         if parent[k] >= 0:
             weight[parent[k]] += weight[k]
             size[parent[k]] += size[k]
     roots = [k for k in range(nv) if parent[k] < 0]
-    dense_cost = sum(size[r] ** 3 // 3 for r in roots)
-
-    def pack(parts):
-        load = [0] * groups
-        bins: list[list[int]] = [[] for _ in range(groups)]
-        for r in sorted(parts, key=lambda r: (-weight[r], r)):
-            g = load.index(min(load))
-            load[g] += weight[r]
-            bins[g].append(r)
-        return max(load), bins
-
-    parts, trunk = list(roots), []
-    best = None
+    parts = set(roots)
+    cuttable = [(-weight[r], r) for r in roots if children[r]]
+    heapq.heapify(cuttable)
+    trunk: list[int] = []
+    trunk_cost = 0
+    best_span, best_trunk, best_bins = None, None, None
     while True:
-        heaviest, bins = pack(parts)
-        span = heaviest + sum(cost[k] + 2 * rownnz[k] for k in trunk)
-        if best is None or span < best[0]:
-            best = (span, sorted(trunk), bins)
-        candidates = [r for r in parts if children[r]]
-        if not candidates:
+        heaviest, bins = _balance(parts, weight, groups)
+        span = heaviest + trunk_cost
+        if best_span is None or span < best_span:
+            best_span, best_trunk, best_bins = span, sorted(trunk), bins
+        if not cuttable:
             break
-        r = max(candidates, key=lambda r: (weight[r], -r))
-        parts.remove(r)
+        _, r = heapq.heappop(cuttable)
+        parts.discard(r)
         trunk.append(r)
-        parts.extend(children[r])
-    span, trunk, bins = best
-    out = []
-    for part_roots in bins:
-        nodes, stack = [], list(part_roots)
-        while stack:
-            k = stack.pop()
-            nodes.append(k)
-            stack.extend(children[k])
-        out.append(tuple(sorted(nodes, reverse=True)))
-    return TreeLdlPlan(groups=tuple(out), trunk=tuple(trunk), span=span, dense_cost=dense_cost)
+        trunk_cost += own[r] + 2 * rownnz[r]
+        for c in children[r]:
+            parts.add(c)
+            if children[c]:
+                heapq.heappush(cuttable, (-weight[c], c))
+    group_dofs = []
+    for part_roots in best_bins:
+        members, todo = [], list(part_roots)
+        while todo:
+            k = todo.pop()
+            members.append(k)
+            todo.extend(children[k])
+        group_dofs.append(tuple(sorted(members, reverse=True)))  # leaves first
+    return TreeLdlPlan(groups=tuple(group_dofs), trunk=tuple(best_trunk), span=best_span,
+                       dense_cost=sum(size[r] ** 3 // 3 for r in roots))
 
 
 def best_tree_ldl_plan(rowadr, rownnz, colind) -> TreeLdlPlan:
-    """Fastest plan whose trunk exchange fits the shared-memory limit; fewest groups on ties."""
-    best = None
+    """Of the plans with 1..MAX_GROUPS groups whose trunk exchange fits the
+    shared-memory limit, the one with the shortest critical path (the fewest groups
+    among equals).  One group needs no exchange, so a plan always exists."""
+    fitting = []
     for groups in range(1, MAX_GROUPS + 1):
         plan = plan_tree_ldl(rowadr, rownnz, colind, groups)
-        if _shared_bytes(rowadr, rownnz, groups, plan.trunk) > MAX_SHARED_BYTES:
-            continue
-        if best is None or plan.span < best.span:
-            best = plan
-    assert best is not None  # a single group has no trunk exchange
-    return best
+        if _shared_bytes(rowadr, rownnz, groups, plan.trunk) <= MAX_SHARED_BYTES:
+            fitting.append(plan)
+    return min(fitting, key=lambda p: p.span)  # min keeps the first of equal spans
 
 
 def tree_ldl_beats_dense(plan: TreeLdlPlan) -> bool:
+    """The gate of tree_ldl.py:188-193."""
     return plan.span <= MAX_SHORT_SPAN or plan.dense_cost >= MIN_DENSE_TO_SPAN_RATIO * plan.span
 
 
@@ -349,10 +361,6 @@ def compile_plan(structure, plan: TreeLdlPlan, device: Any, generate: bool = Tru
         plan=plan, groups=len(plan.groups), cuda=True, struct=st, tables=(t_prog, t_ptr), nv=len(rowadr),
         kernel=kernel,
     )
-
-
-def scratch_for_plan(structure, plan: TreeLdlPlan, device: Any, generate: bool = True) -> TreeFactorSolveScratch:
-    return compile_plan(structure, plan, device, generate)
 
 
 def _to_numpy(a):

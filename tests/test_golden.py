@@ -143,7 +143,7 @@ def test_cuda_reproduces_sparse_and_msolve_fixtures(cuda_device):
     structure = tree_ldl.tree_ldl_structure(mm.M_rowadr, mm.M_rownnz, mm.M_colind)
     Mt, yt = torch.from_numpy(z["M"]).to(cuda_device), torch.from_numpy(z["y"]).to(cuda_device)
     for groups in (1, 4):
-        sc = tree_ldl.scratch_for_plan(structure, tree_ldl.plan_tree_ldl(*structure, groups), cuda_device)
+        sc = tree_ldl.compile_plan(structure, tree_ldl.plan_tree_ldl(*structure, groups), cuda_device)
         x = torch.zeros_like(yt)
         tree_ldl.tree_factor_solve(sc, Mt, x, yt)
         torch.cuda.synchronize()

@@ -207,7 +207,7 @@ def test_tree_kernel_matches_oracle_bitwise(oracle, cuda_device, tree, groups, g
     m, Mv, Md = _model_and_matrices(TREES[tree], worlds)
     structure = _structure(m)
     plan = tree_ldl.plan_tree_ldl(*structure, groups)
-    scratch = tree_ldl.scratch_for_plan(structure, plan, cuda_device, generate)
+    scratch = tree_ldl.compile_plan(structure, plan, cuda_device, generate)
     assert (scratch.kernel is not None) == generate
     y = np.random.default_rng(1).normal(size=(worlds, m.nv)).astype(np.float32)
     x = torch.zeros((worlds, m.nv), dtype=torch.float32, device=cuda_device)

@@ -67,6 +67,95 @@ def test_pattern_couples_tree_groups_and_collision_pairs():
     assert set(foot_r) <= adj[dofs(BOX_B)[0]]  # collision candidate pair
 
 
+def _body_dofs(m, b):
+    return list(range(int(m.body_dofadr[b]), int(m.body_dofadr[b]) + int(m.body_dofnum[b])))
+
+
+def test_equalities_and_site_welds_couple_their_bodies():
+    """tests/test_mjw_sparse_hessian.py:100-150: a connect between the two boxes, a weld
+    given through two sites, and a joint equality between two joints' first dofs."""
+    m = _legged_model()
+    m.neq = 3
+    m.eq_type = np.array([sparse_hessian.EQ_CONNECT, sparse_hessian.EQ_WELD, sparse_hessian.EQ_JOINT], np.int32)
+    m.eq_obj1id = np.array([BOX_A, 0, 2], np.int32)   # body, site, joint ids
+    m.eq_obj2id = np.array([BOX_B, 1, 5], np.int32)
+    m.eq_objtype = np.array([1, sparse_hessian.OBJ_SITE, 3], np.int32)
+    m.site_bodyid = np.array([FOOT_L, FORE_R], np.int32)
+    m.jnt_dofadr = np.array([0, 6, 9, 10, 12, 15, 16], np.int32)
+    adj = sparse_hessian.hessian_pattern(m, [])
+    a, b = _body_dofs(m, BOX_A), _body_dofs(m, BOX_B)
+    assert set(b) <= adj[a[0]] and set(a) <= adj[b[3]]
+    foot, fore = _body_dofs(m, FOOT_L), _body_dofs(m, FORE_R)
+    assert set(fore) <= adj[foot[0]]                      # the weld's sites sit on these bodies
+    assert set(_body_dofs(m, 10)) <= adj[foot[0]]         # ... and the fore-arm's chain comes along
+    assert 15 in adj[9] and 16 not in adj[9]              # joint equality: first dofs only
+    m.eq_type[2] = 3
+    with pytest.raises(ValueError, match="no coupling rule"):
+        sparse_hessian.hessian_pattern(m, [])
+
+
+def test_flex_couplings():
+    """sparse_hessian.py:121-170 / tests/test_mjw_sparse_hessian.py:174-188: every element
+    couples its vertices' bodies; a geom that may collide with the flex joins each
+    element; an interpolated flex couples all its nodes; flexes that may collide with
+    each other are coupled whole."""
+    # six free bodies (6 dofs each): bodies 1-4 carry the vertices of flex 0 (two
+    # triangles 0-1-2 and 1-2-3), bodies 5-6 are the nodes of the interpolated flex 1
+    joints = [(6, -1)] * 6 + [(6, -1)]  # body 7: a free box with a geom
+    parent, body = synthetic._tree_from_joints(joints)
+    m = put_model(parent, body_of_dof=body)
+    m.nflex = 2
+    m.flex_vertadr, m.flex_vertnum = np.array([0, 4], np.int32), np.array([4, 0], np.int32)
+    m.flex_vertbodyid = np.array([1, 2, 3, 4], np.int32)
+    m.flex_elemadr, m.flex_elemnum = np.array([0, 2], np.int32), np.array([2, 1], np.int32)
+    m.flex_elemdataadr, m.flex_dim = np.array([0, 6], np.int32), np.array([2, 2], np.int32)
+    m.flex_elem = np.array([0, 1, 2, 1, 2, 3, 0, 0, 0], np.int32)
+    m.flex_interp = np.array([0, 1], np.int32)
+    m.flex_nodeadr, m.flex_nodenum = np.array([0, 0], np.int32), np.array([0, 2], np.int32)
+    m.flex_nodebodyid = np.array([5, 6], np.int32)
+    m.flex_contype, m.flex_conaffinity = np.array([1, 0], np.int32), np.array([2, 0], np.int32)
+    m.flex_selfcollide = np.array([0, 0], np.int32)
+    m.ngeom = 1
+    m.geom_contype, m.geom_conaffinity = np.array([2], np.int32), np.array([0], np.int32)
+    m.geom_bodyid = np.array([7], np.int32)
+    adj = sparse_hessian.hessian_pattern(m, [])
+    d = lambda b: _body_dofs(m, b)  # noqa: E731
+    assert set(d(2)) | set(d(3)) <= adj[d(1)[0]]       # first triangle
+    assert set(d(4)) <= adj[d(2)[0]]                   # second triangle
+    assert d(4)[0] not in adj[d(1)[0]]                 # vertices 0 and 3 share no element
+    assert set(d(6)) <= adj[d(5)[0]]                   # interpolated flex: all nodes
+    assert set(d(1)) | set(d(4)) <= adj[d(7)[0]]       # the geom's body meets every element
+    assert d(5)[0] not in adj[d(7)[0]] and d(5)[0] not in adj[d(1)[0]]
+    m.flex_selfcollide[0] = 1
+    m.flex_conaffinity[0] = 3                          # flex 0 may now collide with itself
+    adj = sparse_hessian.hessian_pattern(m, [])
+    assert set(d(4)) <= adj[d(1)[0]]                   # coupled whole
+
+
+def test_tendon_gate_reads_the_model_arrays():
+    """sparse_hessian.py:729-733: tendons are fine unless one has a limit or friction loss."""
+    m = _legged_model()
+
+    class _Dev(np.ndarray):
+        device = SimpleNamespace(is_cuda=True)
+
+    m.body_parentid = m.body_parentid.view(_Dev)
+    ctx = SimpleNamespace()
+    groups = [[FOOT_L], [FOOT_R]]
+    m.ntendon = 2
+    plan, reason = sparse_hessian.plan_for_model(m, ctx, groups, 32)
+    assert plan is None and "tendon" in reason            # arrays absent: refused
+    m.tendon_limited_adr = np.zeros(0, np.int32)
+    m.tendon_frictionloss = np.zeros(2, np.float32)
+    plan, reason = sparse_hessian.plan_for_model(m, ctx, groups, 32)
+    assert plan is not None and reason == "enabled"
+    m.tendon_frictionloss = np.array([0.0, 0.3], np.float32)
+    assert sparse_hessian.plan_for_model(m, ctx, groups, 32)[0] is None
+    m.tendon_frictionloss = np.zeros(2, np.float32)
+    m.tendon_limited_adr = np.array([1], np.int32)
+    assert sparse_hessian.plan_for_model(m, ctx, groups, 32)[0] is None
+
+
 def _run_tables(plan, H, g):
     """Execute the factor and solve tables in numpy float64, each level as one
     parallel sweep over a snapshot, asserting no level writes what another lane of
