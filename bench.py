@@ -582,55 +582,63 @@ def main():
     e2e = None
     if not args.no_e2e:
         grouped = [host_batch.group_by_row_count(d)[0] for _, d in host]
-        pinned = [host_batch.pin_batch(d) for d in grouped]
-        pipe = host_batch.HostBatchPipeline(md, grouped[0], device, slots=2 if nb >= 2 else 1, sparse_groups=groups)
-        nslot = len(pipe.slots)
+        pinned = [host_batch.pin_batch(d, chunk=128) for d in grouped]
         ldj = int(dev[0].efc.J.stride(1))
-        h2d = float(np.mean([b.h2d_bytes(m_host.nv, ldj, m_host.nM) for b in pinned]))
-        d2h = float(np.mean([b.d2h_bytes(m_host.nv) for b in pinned]))
-        full_h2d = sum(t.numel() * t.element_size() for t in pinned[0].tensors.values())
-
-        def e2e_run(n):
-            total = 0.0
-            for k in range(n):
-                if k >= nslot:
-                    total += float(pipe.result(k - nslot)["solver_niter"][0])  # frees the slot step k reuses
-                pipe.submit(k, pinned[k % nb])
-            for k in range(max(n - nslot, 0), n):
-                total += float(pipe.result(k)["solver_niter"][0])
-            return total
-
-        torch.cuda.synchronize()
+        njmax = int(host[0][1].njmax)
         e2e_steps = min(args.steps, 50)
-        e2e_run(4)
-        dts = []
-        for _ in range(5):
-            timer.barrier()
-            t0 = time.perf_counter()
-            checksum = e2e_run(e2e_steps)
+
+        def e2e_measure(tight):
+            pipe = host_batch.HostBatchPipeline(md, grouped[0], device, slots=2 if nb >= 2 else 1,
+                                                sparse_groups=groups, tight=tight)
+            nslot = len(pipe.slots)
+
+            def run(n):
+                total = 0.0
+                for k in range(n):
+                    if k >= nslot:
+                        total += float(pipe.result(k - nslot)["solver_niter"][0])  # frees the slot step k reuses
+                    pipe.submit(k, pinned[k % nb])
+                for k in range(max(n - nslot, 0), n):
+                    total += float(pipe.result(k)["solver_niter"][0])
+                return total
+
             torch.cuda.synchronize()
-            dts.append(time.perf_counter() - t0)
-            timer.barrier()
-        dts = timer.max_over_ranks(dts)
-        dt, dt10, dt90 = percentiles(dts)
-        e2e = {
-            "value": world * args.nworld * e2e_steps / dt,
-            "unit": UNIT,
-            "h2d_bytes_per_step": int(h2d),
-            "d2h_bytes_per_step": int(d2h),
-            "steps": e2e_steps,
-            "ms_per_step": 1e3 * dt / e2e_steps,
-            "ms_per_step_p10": 1e3 * dt10 / e2e_steps,
-            "ms_per_step_p90": 1e3 * dt90 / e2e_steps,
-            "api": "instantmimic_b200.host_batch.HostBatchPipeline.submit / result",
-            "pipeline": f"{nslot} slots (copies of step k+1 overlap the solve of step k)",
-            "host_layout": "worlds grouped by descending row count; each chunk of 256 worlds copies rows "
-                           "[0, its largest nefc) of efc.J / D / aref / frictionloss in and of force / state out",
-            "h2d_bytes_full_arrays": int(full_h2d),
-            "h2d_gbs_per_gpu": h2d * e2e_steps / dt / 1e9,  # the copy is the limit of this path
-            "checksum": checksum,
-        }
-        del pipe, pinned
+            run(4)
+            dts = []
+            for _ in range(5):
+                timer.barrier()
+                t0 = time.perf_counter()
+                checksum = run(e2e_steps)
+                torch.cuda.synchronize()
+                dts.append(time.perf_counter() - t0)
+                timer.barrier()
+            dt, dt10, dt90 = percentiles(timer.max_over_ranks(dts))
+            h2d = float(np.mean([b.h2d_bytes(m_host.nv, ldj, m_host.nM, njmax, tight) for b in pinned]))
+            del pipe
+            return {
+                "value": world * args.nworld * e2e_steps / dt,
+                "unit": UNIT,
+                "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(pinned[0].d2h_bytes(m_host.nv, njmax)),
+                "steps": e2e_steps,
+                "ms_per_step": 1e3 * dt / e2e_steps,
+                "ms_per_step_p10": 1e3 * dt10 / e2e_steps,
+                "ms_per_step_p90": 1e3 * dt90 / e2e_steps,
+                "h2d_gbs_per_gpu": h2d * e2e_steps / dt / 1e9,  # the copy is the limit of this path
+                "copies": ("efc.J rows [0, largest nefc of each chunk of 128 worlds) by strided copies, worlds "
+                           "grouped by descending row count on the host" if tight else "whole arrays"),
+                "nslot": nslot,
+                "checksum": checksum,
+            }
+
+        tight, whole = e2e_measure(True), e2e_measure(False)
+        e2e = dict(tight if tight["value"] >= whole["value"] else whole)
+        e2e["api"] = "instantmimic_b200.host_batch.HostBatchPipeline.submit / result"
+        e2e["pipeline"] = f"{e2e.pop('nslot')} slots (copies of step k+1 overlap the solve of step k)"
+        other = whole if e2e["copies"] == tight["copies"] else tight
+        e2e["other_copy_mode"] = {k: other[k] for k in ("copies", "value", "ms_per_step", "h2d_bytes_per_step",
+                                                         "h2d_gbs_per_gpu")}
+        del pinned
 
     # ---- work counters -> flop count of one batch -------------------------------------
     runtime.solve_with_scratch(md, dev[0], scratch[0], use_optimized_kernel=True)

@@ -340,6 +340,16 @@ int imn_sparse_factor_nonfused(const ImnSparsePlan* plan, const uint8_t* done,
                                int32_t skip_unchanged, int32_t skip_noflip,
                                void* stream);
 
+/* Uploads a sparse plan (sparse_hessian.build_plan's tables, sparse_hessian.py:229-402,
+ * which the reference bakes into generated source instead).  `host_tables` holds HOST
+ * pointers and the counts; the call copies every table into one device allocation
+ * of the current device and returns a plan whose pointers are device pointers, ready
+ * for ImnCtx.sparse_plan and imn_sparse_factor_nonfused.  This and
+ * imn_tree_ldl_compile are the only entry points that allocate; both belong to model
+ * set-up, not to the step.  imn_sparse_plan_destroy frees the allocation. */
+int imn_sparse_plan_create(const ImnSparsePlan* host_tables, ImnSparsePlan** out);
+void imn_sparse_plan_destroy(ImnSparsePlan* plan);
+
 /* Launch geometry the library would use for (m, d): block width of one world
  * (newton_fusion.newton_block_dim, newton_fusion.py:325-327), worlds per CTA,
  * dynamic shared memory per CTA, whether J stays resident in shared memory. */

@@ -216,6 +216,8 @@ SYMBOLS = {
         C.c_int,
         [C.POINTER(ImnSparsePlan), P, P, I64, P, P, P, P, P, I64, P, P, I32, I32, I32, P],
     ),
+    "imn_sparse_plan_create": (C.c_int, [C.POINTER(ImnSparsePlan), C.POINTER(C.POINTER(ImnSparsePlan))]),
+    "imn_sparse_plan_destroy": (None, [C.POINTER(ImnSparsePlan)]),
     "imn_launch_info": (
         C.c_int,
         [C.POINTER(ImnModel), C.POINTER(ImnData), C.POINTER(ImnCtx), C.POINTER(ImnLaunchInfo)],

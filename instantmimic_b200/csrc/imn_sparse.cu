@@ -5,6 +5,7 @@
 // and solves (mode 4), or reloads the stored factor and solves (mode 5).
 // hfactor per world: [0, nfac) N = L D, [nfac, nfac + nv) 1/D.
 #include <stdio.h>
+#include <string.h>
 
 #include "imn_sparse.cuh"
 
@@ -91,4 +92,89 @@ extern "C" int imn_sparse_factor_nonfused(const ImnSparsePlan* plan, const uint8
   if (e != cudaSuccess)
     return imn::set_error("imn_sparse_factor_nonfused: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
   return IMN_OK;
+}
+
+// ---- plan upload ---------------------------------------------------------------
+// The host builds the index tables once per model; this is the one place where the
+// library allocates device memory: one slab that holds every table, freed by
+// imn_sparse_plan_destroy.
+namespace imn {
+
+struct OwnedSparsePlan {
+  ImnSparsePlan plan;  // first member: the pointer handed out is also the owner's
+  void* slab;
+};
+
+}  // namespace imn
+
+extern "C" int imn_sparse_plan_create(const ImnSparsePlan* host, ImnSparsePlan** out) {
+  if (!host || !out) return imn::set_error("imn_sparse_plan_create: NULL argument"), IMN_ERR_NULL;
+  *out = nullptr;
+  if (host->nv <= 0 || host->nfac <= 0 || host->nlevels <= 0 || host->nentries <= 0 || host->nruns < 0 ||
+      host->nback < 0 || host->nfsweep < 0 || host->nbsweep < 0 || !host->rk_ptr)
+    return imn::set_error("imn_sparse_plan_create: malformed plan"), IMN_ERR_SHAPE;
+  const int nv = host->nv, words = (nv + 31) / 32;
+  const size_t nrk = host->rk_ptr[nv] > 0 ? host->rk_ptr[nv] : 1;
+  struct Table {
+    const void* src;
+    size_t bytes;
+    const void** dst;
+  };
+  imn::OwnedSparsePlan* owned = new imn::OwnedSparsePlan();
+  owned->plan = *host;
+  ImnSparsePlan& d = owned->plan;
+#define TAB(field, count) {host->field, sizeof(*host->field) * (size_t)(count), (const void**)&d.field}
+  const Table tabs[] = {
+      TAB(lvl_ptr, host->nlevels + 1), TAB(lvl_team, host->nlevels), TAB(ent_slot, host->nentries),
+      TAB(ent_col, host->nentries),    TAB(run_ptr, host->nentries + 1), TAB(run_ab, host->nruns > 0 ? host->nruns : 1),
+      TAB(run_kl, host->nruns > 0 ? host->nruns : 1), TAB(orig, nv), TAB(b_lvl, host->nlevels + 1),
+      TAB(b_slot, host->nback > 0 ? host->nback : 1), TAB(b_src, host->nback > 0 ? host->nback : 1),
+      TAB(b_dst, host->nback > 0 ? host->nback : 1), TAB(pair, nv * nv), TAB(f_lvl, host->nlevels + 1),
+      TAB(f_row, nv), TAB(row_start, nv), TAB(rk_ptr, nv + 1), TAB(rk, nrk), TAB(pmask, nv * words),
+      TAB(s_a, host->nfac), TAB(s_b, host->nfac), TAB(s_m, host->nfac), TAB(gat, host->nfac),
+      TAB(fsweep, (size_t)host->nfsweep * 128), TAB(bsweep, (size_t)host->nbsweep * 32),
+  };
+#undef TAB
+  size_t total = 0;
+  for (const Table& t : tabs) {
+    if (t.bytes && !t.src) {
+      delete owned;
+      return imn::set_error("imn_sparse_plan_create: a table is NULL"), IMN_ERR_NULL;
+    }
+    total += (t.bytes + 15) & ~(size_t)15;
+  }
+  unsigned char* staging = new unsigned char[total]();
+  cudaError_t e = cudaMalloc(&owned->slab, total);
+  if (e != cudaSuccess) {
+    delete[] staging;
+    delete owned;
+    return imn::set_error("imn_sparse_plan_create: cudaMalloc of %zu bytes: %s", total, cudaGetErrorString(e)),
+           IMN_ERR_LAUNCH;
+  }
+  size_t off = 0;
+  for (const Table& t : tabs) {
+    if (t.bytes) {
+      memcpy(staging + off, t.src, t.bytes);
+      *t.dst = (const unsigned char*)owned->slab + off;
+    } else {
+      *t.dst = nullptr;
+    }
+    off += (t.bytes + 15) & ~(size_t)15;
+  }
+  e = cudaMemcpy(owned->slab, staging, total, cudaMemcpyHostToDevice);
+  delete[] staging;
+  if (e != cudaSuccess) {
+    cudaFree(owned->slab);
+    delete owned;
+    return imn::set_error("imn_sparse_plan_create: upload: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  }
+  *out = &owned->plan;
+  return IMN_OK;
+}
+
+extern "C" void imn_sparse_plan_destroy(ImnSparsePlan* plan) {
+  if (!plan) return;
+  imn::OwnedSparsePlan* owned = reinterpret_cast<imn::OwnedSparsePlan*>(plan);
+  cudaFree(owned->slab);
+  delete owned;
 }

@@ -10,12 +10,14 @@ construction:
 
 * host -> device copies of the inputs.  ``efc.J`` is 78 % of a humanoid batch and the
   solver never reads rows at or beyond a world's ``nefc``, so worlds are taken in
-  chunks and each chunk copies only rows ``[0, max nefc of the chunk)`` with one
-  strided copy per array (``imn_copy_rows`` = one ``cudaMemcpy2DAsync``).  A caller
-  that keeps its worlds grouped by row count gets tight copies; any order is correct.
+  chunks and each chunk copies only rows ``[0, max nefc of the chunk)`` of J with one
+  strided copy (``imn_copy_rows`` = one ``cudaMemcpy2DAsync``; a world's rows are one
+  contiguous segment of several KB).  A caller that keeps its worlds grouped by row
+  count gets tight copies; any order is correct.  The per-row vectors (D, aref,
+  frictionloss) are copied whole: their per-world segments are a few hundred bytes,
+  which a strided copy moves slower than the dead rows cost.
 * ``solve_with_scratch`` on the device buffers.
-* device -> host copies of the results, ``efc.force`` / ``efc.state`` again only up to
-  the chunk's largest row count.
+* device -> host copies of the results (whole arrays).
 
 Slots are independent (own device buffers, stream and pinned result buffers), so the
 copies of one batch overlap the solve of another.
@@ -46,17 +48,14 @@ class HostBatch:
     chunk_rows: list  # (first world, worlds, rows to copy) per chunk
     nworld: int
 
-    def h2d_bytes(self, nv: int, ldj: int, nM: int) -> int:
-        total = self.nworld * 4 * (3 + 3 * nv + nM)
-        for _, n, rows in self.chunk_rows:
-            total += n * rows * 4 * (ldj + 3)
-        return total
+    def h2d_bytes(self, nv: int, ldj: int, nM: int, njmax: int, tight: bool = True) -> int:
+        total = self.nworld * 4 * (3 + 3 * nv + nM + 3 * njmax)
+        if not tight:
+            return total + self.nworld * njmax * ldj * 4
+        return total + sum(n * rows * 4 * ldj for _, n, rows in self.chunk_rows)
 
-    def d2h_bytes(self, nv: int) -> int:
-        total = self.nworld * 4 * (3 * nv + 2)
-        for _, n, rows in self.chunk_rows:
-            total += n * rows * 8
-        return total
+    def d2h_bytes(self, nv: int, njmax: int) -> int:
+        return self.nworld * 4 * (3 * nv + 2 + 2 * njmax)
 
 
 def pin_batch(d: Any, chunk: int = 256) -> HostBatch:
@@ -95,10 +94,12 @@ class HostBatchPipeline:
     one shape.  ``submit`` enqueues copies + solve + copies and returns at once;
     ``result`` waits for that slot and returns its pinned result tensors."""
 
-    def __init__(self, m_dev: Any, template: Any, device: Any, *, slots: int = 2, sparse_groups=None):
+    def __init__(self, m_dev: Any, template: Any, device: Any, *, slots: int = 2, sparse_groups=None,
+                 tight: bool = True):
         import torch
 
         self.m = m_dev
+        self.tight = tight
         self.device = device
         self.slots = []
         for _ in range(slots):
@@ -134,22 +135,21 @@ class HostBatchPipeline:
         with torch.cuda.stream(sl["stream"]):
             for n in ("nefc", "ne", "nf", "M") + _IN_DOF:
                 getattr(dd, n).copy_(t[n], non_blocking=True)
-            for lo, n, rows in batch.chunk_rows:
-                if rows == 0:
-                    continue
-                self._rows(dd.efc.J, t["J"], lo, n, rows, False, handle)
-                for name in _IN_ROW:
-                    self._rows(getattr(dd.efc, name), t[name], lo, n, rows, False, handle)
+            for name in _IN_ROW:
+                getattr(dd.efc, name).copy_(t[name], non_blocking=True)
+            if self.tight:
+                for lo, n, rows in batch.chunk_rows:
+                    if rows:
+                        self._rows(dd.efc.J, t["J"], lo, n, rows, False, handle)
+            else:
+                dd.efc.J.copy_(t["J"], non_blocking=True)
             runtime.solve_with_scratch(self.m, dd, sl["sc"], use_optimized_kernel=True, stream=sl["stream"])
             out = sl["out"]
             for n in _OUT_DOF + ("solver_niter", "overflow"):
                 out[n].copy_(getattr(dd, n), non_blocking=True)
             out["Ma"].copy_(dd.efc.Ma, non_blocking=True)
-            for lo, n, rows in batch.chunk_rows:
-                if rows == 0:
-                    continue
-                for name in _OUT_ROW:
-                    self._rows(out[name], getattr(dd.efc, name), lo, n, rows, True, handle)
+            for name in _OUT_ROW:
+                out[name].copy_(getattr(dd.efc, name), non_blocking=True)
             sl["done"].record(sl["stream"])
         sl["batch"] = batch
 

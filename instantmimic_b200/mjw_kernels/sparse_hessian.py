@@ -448,6 +448,37 @@ def upload(plan: SparseHessianPlan, device: Any = "cuda") -> SparseHessianPlan:
     return plan
 
 
+class NativePlan:
+    """Owner of a plan uploaded by the library itself (``imn_sparse_plan_create``): one
+    device allocation for all tables, freed with the object.  ``struct`` is the C-ABI
+    plan with device pointers.  Equivalent to ``upload``, without torch."""
+
+    def __init__(self, plan: SparseHessianPlan):
+        import ctypes as C
+
+        from .. import _lib
+
+        host = host_struct(plan)
+        self._keep = plan.tables  # the host tables must outlive the call only
+        out = C.POINTER(abi.ImnSparsePlan)()
+        _lib.check(_lib.lib().imn_sparse_plan_create(C.byref(host), C.byref(out)), "imn_sparse_plan_create")
+        self._ptr = out
+        self.struct = out.contents
+
+    def close(self) -> None:
+        ptr, self._ptr = getattr(self, "_ptr", None), None
+        if ptr:
+            from .. import _lib
+
+            _lib.lib().imn_sparse_plan_destroy(ptr)
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown
+            pass
+
+
 def plan_for_model(m: Any, ctx: Any, body_groups, block: int, *, compact: bool = False,
                    fused_runtime: bool = True):
     """(plan, reason): the plan when the model qualifies, else ``None`` and why

@@ -25,9 +25,9 @@ def test_host_batch_pipeline_matches_oracle(oracle, cuda_device, grouped):
     pipe = host_batch.HostBatchPipeline(md, d, cuda_device, slots=2)
     batch = host_batch.pin_batch(d, chunk=128)
     full = d.nworld * 4 * (3 + 3 * m.nv + m.nM + d.njmax * (m.nv + 3))
-    assert batch.h2d_bytes(m.nv, m.nv, m.nM) <= full
+    assert batch.h2d_bytes(m.nv, m.nv, m.nM, d.njmax) <= full == batch.h2d_bytes(m.nv, m.nv, m.nM, d.njmax, tight=False)
     if grouped:
-        assert batch.h2d_bytes(m.nv, m.nv, m.nM) < 0.8 * full  # tight copies when worlds are grouped
+        assert batch.h2d_bytes(m.nv, m.nv, m.nM, d.njmax) < 0.8 * full  # tight copies when worlds are grouped
     for k in range(3):  # both slots, one reused
         pipe.submit(k, batch)
     for k in range(3):

@@ -256,3 +256,22 @@ def test_graph_capture_replay_matches_eager(cuda_device):
     g.replay()
     torch.cuda.synchronize()
     assert torch.equal(eager, dd.qacc)
+
+
+def test_torch_library_op_matches_the_direct_call(oracle, cuda_device):
+    """torch.ops.imnewton.solve: the same launch behind a registered torch operator."""
+    import torch
+
+    from instantmimic_b200 import mjw_model, torch_ops
+    from instantmimic_b200 import mjw_step_optimized as runtime
+
+    m, d, _ = synthetic.make_workload("humanoid", 128, seed=14)
+    want, _, _ = run_oracle(oracle, m, d)
+    md, dd = mjw_model.to_device(m, cuda_device), mjw_model.to_device(d, cuda_device)
+    scratch = runtime.make_optimized_fwd_position_scratch(md, dd, cuda_device)
+    handle = torch_ops.register_model(md, scratch)
+    torch_ops.solve_data(handle, dd)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(dd.qacc.cpu().numpy().view(np.uint32), want.qacc.view(np.uint32))
+    np.testing.assert_array_equal(dd.solver_niter.cpu().numpy(), want.solver_niter)
+    assert torch.library.opcheck is not None and hasattr(torch.ops.imnewton, "solve")

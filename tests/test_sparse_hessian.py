@@ -479,3 +479,26 @@ def test_sweep_records_restate_the_level_tables():
     big, _, _ = synthetic.make_workload("humanoid", 1, seed=0)
     nf = sparse_hessian.build_plan(big, _single_body_groups(big), 64, "nonfused")
     assert nf.tables["fsweep"].size == 0 and sparse_hessian.host_struct(nf).nfsweep == 0
+
+
+@pytest.mark.gpu
+def test_library_uploaded_plan_gives_the_same_bits(cuda_device):
+    """imn_sparse_plan_create: the tables in one device allocation made by the library."""
+    import torch
+
+    from instantmimic_b200 import mjw_step_optimized as runtime
+
+    m, d, _ = synthetic.make_workload("humanoid", 64, seed=12)
+    got, scratch, (md, dd) = _cuda_sparse(m, d, cuda_device, _single_body_groups(m))
+    plan = scratch.solver_context.sparse_hessian_plan
+    native = sparse_hessian.NativePlan(plan)
+    assert native.struct.nfac == plan.nfac and native.struct.nfsweep == plan.struct.nfsweep
+    plan.struct = native.struct
+    del scratch._imn_solve_call  # structs are cached per scratch
+    dd.qacc.zero_()
+    runtime.solve_with_scratch(md, dd, scratch, use_optimized_kernel=True)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(dd.qacc.cpu().numpy().view(np.uint32), got.qacc.view(np.uint32))
+    np.testing.assert_array_equal(dd.solver_niter.cpu().numpy(), got.solver_niter)
+    native.close()
+    native.close()  # idempotent
