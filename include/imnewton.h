@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define IMN_ABI_VERSION 2
+#define IMN_ABI_VERSION 3
 
 typedef enum ImnStatus {
   IMN_OK = 0,
@@ -117,6 +117,14 @@ typedef struct ImnData {
   int32_t* efc_state;     /* (W, R)   stride efc_ld */
   int32_t* solver_niter;  /* (W) */
   int32_t* overflow;      /* (W), bits are OR-ed in */
+  /* Optional, no counterpart in the reference (mujoco-warp pads every world to njmax
+   * rows): when non-NULL, world w's Jacobian starts at efc_J + J_world_offset[w]
+   * (elements) instead of efc_J + w * J_ld_world, and efc_J holds J_elems elements
+   * in all.  Lets a producer hand over J compactly -- only the nefc rows of each
+   * world, one world after the other, as MuJoCo C stores mjData.efc_J -- so that no
+   * dead row crosses PCIe.  Rows are still J_ld_row apart. */
+  const int64_t* J_world_offset; /* (W) or NULL */
+  int64_t J_elems;               /* extent of efc_J when J_world_offset is given */
 } ImnData;
 
 /* Static-pattern sparse L'DL of the Hessian: the tables that

@@ -15,7 +15,7 @@ I32 = C.c_int32
 I64 = C.c_int64
 F32 = C.c_float
 
-IMN_ABI_VERSION = 2
+IMN_ABI_VERSION = 3
 
 IMN_OK = 0
 IMN_ERR_NULL = -1
@@ -80,6 +80,8 @@ class ImnData(C.Structure):
         ("efc_state", P),
         ("solver_niter", P),
         ("overflow", P),
+        ("J_world_offset", P),
+        ("J_elems", I64),
     ]
 
 

@@ -9,7 +9,7 @@ import ctypes as C
 from typing import Any
 
 from . import abi, types
-from .arrays import addr, elem_strides, length, shape
+from .arrays import addr, elem_strides, itemsize, length, shape
 
 
 _UPSTREAM: dict | None = None
@@ -157,7 +157,11 @@ def data_struct(m: Any, d: Any) -> abi.ImnData:
         [d.qacc_smooth, d.qacc_warmstart, d.qfrc_smooth, d.qacc, d.qfrc_constraint, d.efc.Ma],
     )
     s.efc_J = addr(d.efc.J)
-    if s.njmax > 0:
+    if s.njmax > 0 and getattr(d.efc, "J_world_offset", None) is not None:
+        s.efc_ld = _same_ld(
+            "efc", [d.efc.D, d.efc.aref, d.efc.frictionloss, d.efc.force, d.efc.state]
+        )
+    elif s.njmax > 0:
         js = elem_strides(d.efc.J)
         if js[2] != 1:
             raise ValueError("efc.J needs a unit innermost stride")
@@ -181,6 +185,17 @@ def data_struct(m: Any, d: Any) -> abi.ImnData:
     s.efc_state = addr(d.efc.state)
     s.solver_niter = addr(d.solver_niter)
     s.overflow = addr(d.overflow)
+    offsets = getattr(d.efc, "J_world_offset", None)
+    if offsets is not None:
+        # compact J: (total rows, >= nv) with one int64 element offset per world
+        if itemsize(offsets) != 8 or length(offsets) < s.nworld:
+            raise ValueError("efc.J_world_offset must hold one int64 per world")
+        js = elem_strides(d.efc.J)
+        if len(js) != 2 or js[1] != 1:
+            raise ValueError("a compact efc.J is a (rows, nv) array with a unit innermost stride")
+        s.J_world_offset = addr(offsets)
+        s.J_ld_world, s.J_ld_row = 0, js[0]
+        s.J_elems = int(shape(d.efc.J)[0]) * js[0]
     return s
 
 

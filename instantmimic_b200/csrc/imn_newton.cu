@@ -145,9 +145,10 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
   s.nefc = nefc, s.ne = ne, s.nef = nef;
   const bool rowless = nefc_in == 0;
   const size_t dofo = (size_t)w * d.dof_ld, efco = (size_t)w * d.efc_ld;
-  s.Jg = d.efc_J + (size_t)w * d.J_ld_world;
+  s.Jg = d.efc_J + (d.J_world_offset ? (size_t)d.J_world_offset[w] : (size_t)w * d.J_ld_world);
   s.Jbeg = d.efc_J;
-  s.Jend = d.efc_J + (size_t)(d.nworld - 1) * d.J_ld_world + (size_t)d.njmax * d.J_ld_row;
+  s.Jend = d.efc_J + (d.J_world_offset ? (size_t)d.J_elems
+                                       : (size_t)(d.nworld - 1) * d.J_ld_world + (size_t)d.njmax * d.J_ld_row);
 
   // ---- load: TMA bulk copies for the 16-byte-aligned bulk of every array, plain
   // loads for the ragged ends -----------------------------------------------------
@@ -519,7 +520,8 @@ static int validate(const ImnModel* m, const ImnData* d, const ImnCtx* cx) {
   for (const void* p : need)
     if (!p) return set_error("imn_solve: a required Model/Data pointer is NULL"), IMN_ERR_NULL;
   if (d->dof_ld < m->nv || d->J_ld_row < m->nv || d->efc_ld < d->njmax || d->M_ld < m->nM ||
-      d->J_ld_world < (int64_t)d->njmax * d->J_ld_row)
+      (!d->J_world_offset && d->J_ld_world < (int64_t)d->njmax * d->J_ld_row) ||
+      (d->J_world_offset && d->J_elems < 0))
     return set_error("imn_solve: a stride is smaller than its extent"), IMN_ERR_SHAPE;
   if (d->J_ld_row > 4 * (int64_t)m->nv + 64)
     return set_error("imn_solve: efc.J row stride %lld is far larger than nv %d", (long long)d->J_ld_row, m->nv),

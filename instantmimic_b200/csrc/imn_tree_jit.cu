@@ -16,7 +16,19 @@
 // the trunk's solution) go through shared memory, column = lane.  Every statement is
 // the instruction's own float32 operation (explicit fmaf, IEEE division, contraction
 // off), in list order, so the results are bit-identical to the interpreter's.
+//
+// Memory.  Lane = world means that a plain load of M[world][e] touches 32 cache lines
+// per instruction, and the L1's one-line-per-cycle rate, not HBM, then bounds the
+// kernel (nM such loads per 32 worlds).  The generated kernel therefore stages its
+// block's tile -- 32 worlds x nM floats of M and 32 x nv of y, both contiguous -- in
+// shared memory: two TMA bulk copies on one mbarrier when the tile is whole and
+// 16-byte aligned (bounded wait), cooperative coalesced loads otherwise.  The
+// straight-line code reads the tile (stride nM between lanes: gcd(nM, 32)-way bank
+// conflicts), writes x over the consumed y, and the tile leaves by one bulk store.
+// Plans whose tile does not fit twice into an SM's shared memory, or whose nM shares
+// a factor of 8 or more with 32, keep the plain loads.
 #include <dlfcn.h>
+#include <stdlib.h>
 
 #include <mutex>
 #include <string>
@@ -100,6 +112,7 @@ void operands(const Ins& i, int reads[4], int& nread, int& write) {
 
 struct ImnTreeKernel {
   int nv = 0, nM = 0, groups = 0, nshared = 0;
+  bool staged = false;  // M and y tiles in shared memory
   std::string source;
   std::vector<char> cubin;
   cudaLibrary_t library = nullptr;
@@ -109,7 +122,8 @@ struct ImnTreeKernel {
 
 namespace {
 
-std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int owner, int nslot, int* nshared_out) {
+std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int owner, int nslot, int nv, int nM,
+                     bool allow_stage, bool* staged_out, int* nshared_out) {
   const int nstream = 2 * groups + 1;
   auto warp_of = [&](int st) { return st < groups ? st : (st == groups ? owner : st - groups - 1); };
   std::vector<std::vector<Ins>> streams(nstream);
@@ -130,6 +144,11 @@ std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int ow
   for (int sl = 0; sl < nslot; ++sl)
     if (users[sl] & (users[sl] - 1u)) shared_index[sl] = nshared++;
   *nshared_out = nshared;
+  // stage the tiles when two blocks' worth fit an SM's shared memory
+  const size_t tile_bytes =
+      16 + sizeof(float) * ((size_t)((32 * nM + 3) & ~3) + ((32 * nv + 3) & ~3) + 32 * (size_t)(nshared > 0 ? nshared : 1));
+  const bool staged = allow_stage && tile_bytes <= 113 * 1024;
+  *staged_out = staged;
   auto ref = [&](int sl) {
     return shared_index[sl] >= 0 ? "S[" + std::to_string(shared_index[sl] * 32) + "]" : "r" + std::to_string(sl);
   };
@@ -137,8 +156,8 @@ std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int ow
     for (const Ins& i : code) {
       const std::string d = i.op == OP_STORE_X ? "" : ref(i.dst);
       switch (i.op) {
-        case OP_LOAD_M: out += d + " = Mr[" + std::to_string(i.a) + "];\n"; break;
-        case OP_LOAD_Y: out += d + " = yr[" + std::to_string(i.a) + "];\n"; break;
+        case OP_LOAD_M: out += d + (staged ? " = Mt[" : " = Mr[") + std::to_string(i.a) + "];\n"; break;
+        case OP_LOAD_Y: out += d + (staged ? " = yt[" : " = yr[") + std::to_string(i.a) + "];\n"; break;
         case OP_ZERO: out += d + " = 0.0f;\n"; break;
         case OP_INV: out += d + " = 1.0f / " + ref(i.a) + ";\n"; break;
         case OP_UPD:
@@ -148,26 +167,83 @@ std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int ow
         case OP_SUBMUL: out += d + " = fmaf(-" + ref(i.a) + ", " + ref(i.b) + ", " + d + ");\n"; break;
         case OP_MUL: out += d + " = " + ref(i.a) + " * " + ref(i.b) + ";\n"; break;
         case OP_ADD: out += d + " = " + d + " + " + ref(i.a) + ";\n"; break;
-        case OP_STORE_X: out += "if (live) xr[" + std::to_string(i.dst) + "] = " + ref(i.a) + ";\n"; break;
+        case OP_STORE_X:
+          out += staged ? "yt[" + std::to_string(i.dst) + "] = " + ref(i.a) + ";\n"
+                        : "if (live) xr[" + std::to_string(i.dst) + "] = " + ref(i.a) + ";\n";
+          break;
         default: break;
       }
     }
   };
   std::string src;
-  src +=
-      "extern \"C\" __global__ void __launch_bounds__(" + std::to_string(32 * groups) +
-      ") tree_ldl_generated(const float* __restrict__ M, long long M_ld, const float* __restrict__ y,\n"
-      "    long long y_ld, float* __restrict__ x, long long x_ld, int nworld) {\n"
-      "  extern __shared__ float slots[];\n"
-      "  const int lw = threadIdx.x & 31, part = threadIdx.x >> 5;\n"
-      "  const int world = blockIdx.x * 32 + lw;\n"
-      "  const bool live = world < nworld;\n"
-      "  const int src = live ? world : nworld - 1;\n"
-      "  const float* Mr = M + (long long)src * M_ld;\n"
-      "  const float* yr = y + (long long)src * y_ld;\n"
-      "  float* xr = x + (long long)src * x_ld;\n"
-      "  float* S = slots + lw;\n"
-      "  switch (part) {\n";
+  const std::string threads = std::to_string(32 * groups);
+  src += "extern \"C\" __global__ void __launch_bounds__(" + threads +
+         ") tree_ldl_generated(const float* __restrict__ M, long long M_ld, const float* __restrict__ y,\n"
+         "    long long y_ld, float* __restrict__ x, long long x_ld, int nworld, int bulk) {\n"
+         "  extern __shared__ __align__(16) float slots[];\n"
+         "  const int lw = threadIdx.x & 31, part = threadIdx.x >> 5;\n"
+         "  const int world = blockIdx.x * 32 + lw;\n"
+         "  const bool live = world < nworld;\n"
+         "  const int src = live ? world : nworld - 1;\n";
+  if (!staged) {
+    src += "  const float* Mr = M + (long long)src * M_ld;\n"
+           "  const float* yr = y + (long long)src * y_ld;\n"
+           "  float* xr = x + (long long)src * x_ld;\n"
+           "  float* S = slots + lw;\n";
+  } else {
+    // tile layout: [bar 16 B][M 32 x nM][y 32 x nv][cross-warp slots]
+    const int nMt = 32 * nM, nyt = 32 * nv;
+    const std::string sM = std::to_string(nM), sV = std::to_string(nv);
+    src += "  float* tileM = slots + 4;\n"
+           "  float* tileY = tileM + " + std::to_string((nMt + 3) & ~3) + ";\n"
+           "  float* S = tileY + " + std::to_string((nyt + 3) & ~3) + " + lw;\n"
+           "  const float* Mt = tileM + lw * " + sM + ";\n"
+           "  float* yt = tileY + lw * " + sV + ";\n"
+           "  const int w0 = blockIdx.x * 32;\n"
+           "  const bool whole = bulk && w0 + 32 <= nworld;\n"
+           "  const unsigned bar = (unsigned)__cvta_generic_to_shared(slots);\n"
+           "  bool arrived = false;\n"
+           "  if (whole) {\n"
+           "    if (threadIdx.x == 0) {\n"
+           "      asm volatile(\"mbarrier.init.shared::cta.b64 [%0], 1;\" ::\"r\"(bar) : \"memory\");\n"
+           "      asm volatile(\"fence.mbarrier_init.release.cluster;\" ::: \"memory\");\n"
+           "      asm volatile(\"mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\" ::\"r\"(bar), \"r\"(" +
+           std::to_string(4 * (nMt + nyt)) + "u) : \"memory\");\n"
+           "      asm volatile(\"cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\"\n"
+           "                   ::\"r\"((unsigned)__cvta_generic_to_shared(tileM)), \"l\"(M + (long long)w0 * " + sM + "), \"r\"(" +
+           std::to_string(4 * nMt) + "u), \"r\"(bar) : \"memory\");\n"
+           "      asm volatile(\"cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\"\n"
+           "                   ::\"r\"((unsigned)__cvta_generic_to_shared(tileY)), \"l\"(y + (long long)w0 * " + sV + "), \"r\"(" +
+           std::to_string(4 * nyt) + "u), \"r\"(bar) : \"memory\");\n"
+           "    }\n"
+           "    __syncthreads();  // the barrier is initialised before anyone polls it\n"
+           "    // bounded wait; when it runs out the copies get one more bounded wait and the\n"
+           "    // tile is then loaded again with plain loads\n"
+           "    for (int round = 0; round < 2 && !arrived; ++round)\n"
+           "      for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) {\n"
+           "        unsigned ok;\n"
+           "        asm volatile(\"{\\n\\t.reg .pred p;\\n\\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\\n\\tselp.u32 %0, 1, 0, p;\\n\\t}\"\n"
+           "                     : \"=r\"(ok) : \"r\"(bar) : \"memory\");\n"
+           "        arrived = ok != 0;\n"
+           "      }\n"
+           "  }\n"
+           "  if (!__syncthreads_and(arrived)) {\n"
+           "    // partial or unaligned tile (or a copy that did not arrive): coalesced loads;\n"
+           "    // lanes past the last world repeat it\n"
+           "    for (int e = threadIdx.x; e < " + std::to_string(nMt) + "; e += " + threads + ") {\n"
+           "      const int r = e / " + sM + ", c = e - r * " + sM + ";\n"
+           "      const int wr = w0 + r < nworld ? w0 + r : nworld - 1;\n"
+           "      tileM[e] = M[(long long)wr * M_ld + c];\n"
+           "    }\n"
+           "    for (int e = threadIdx.x; e < " + std::to_string(nyt) + "; e += " + threads + ") {\n"
+           "      const int r = e / " + sV + ", c = e - r * " + sV + ";\n"
+           "      const int wr = w0 + r < nworld ? w0 + r : nworld - 1;\n"
+           "      tileY[e] = y[(long long)wr * y_ld + c];\n"
+           "    }\n"
+           "    __syncthreads();\n"
+           "  }\n";
+  }
+  src += "  switch (part) {\n";
   for (int j = 0; j < groups; ++j) {
     src += "  case " + std::to_string(j) + ": {\n";
     // register variables of this warp
@@ -186,7 +262,28 @@ std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int ow
     emit(src, streams[groups + 1 + j]);
     src += "  } break;\n";
   }
-  src += "  default: break;\n  }\n}\n";
+  src += "  default: break;\n  }\n";
+  if (staged) {
+    const std::string sV = std::to_string(nv);
+    src += "  // every thread's writes of x become visible to the bulk store's proxy\n"
+           "  asm volatile(\"fence.proxy.async.shared::cta;\" ::: \"memory\");\n"
+           "  __syncthreads();  // x of every world is in the tile\n"
+           "  if (whole && x_ld == " + sV + ") {\n"
+           "    if (threadIdx.x == 0) {\n"
+           "      asm volatile(\"cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;\"\n"
+           "                   ::\"l\"(x + (long long)w0 * " + sV + "), \"r\"((unsigned)__cvta_generic_to_shared(tileY)), \"r\"(" +
+           std::to_string(4 * 32 * nv) + "u) : \"memory\");\n"
+           "      asm volatile(\"cp.async.bulk.commit_group;\" ::: \"memory\");\n"
+           "      asm volatile(\"cp.async.bulk.wait_group.read 0;\" ::: \"memory\");\n"
+           "    }\n"
+           "  } else {\n"
+           "    for (int e = threadIdx.x; e < " + std::to_string(32 * nv) + "; e += " + threads + ") {\n"
+           "      const int r = e / " + sV + ", c = e - r * " + sV + ";\n"
+           "      if (w0 + r < nworld) x[(long long)(w0 + r) * x_ld + c] = tileY[e];\n"
+           "    }\n"
+           "  }\n";
+  }
+  src += "}\n";
   return src;
 }
 
@@ -216,7 +313,18 @@ extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr
   if (!rt) return imn::set_error("imn_tree_ldl_compile: NVRTC (libnvrtc.so.12) could not be loaded"), IMN_ERR_UNSUPPORTED;
   ImnTreeKernel* k = new ImnTreeKernel;
   k->nv = nv, k->nM = nM, k->groups = groups;
-  k->source = generate(prog, prog_ptr, groups, owner, nslot, &k->nshared);
+  {
+    // stage when two blocks' tiles fit an SM and the lane stride nM does not pile the
+    // lanes onto a few banks; IMN_TREE_STAGE=0 keeps the plain loads (for comparisons)
+    int gcd = nM, b = 32;
+    while (b) {
+      const int t = gcd % b;
+      gcd = b, b = t;
+    }
+    const char* env = getenv("IMN_TREE_STAGE");
+    k->staged = !(env && env[0] == '0') && gcd < 8;
+  }
+  k->source = generate(prog, prog_ptr, groups, owner, nslot, nv, nM, k->staged, &k->staged, &k->nshared);
   nvrtcProgram_t p = nullptr;
   int rc = rt->create(&p, k->source.c_str(), "tree_ldl_generated.cu", 0, nullptr, nullptr);
   if (rc) {
@@ -271,7 +379,8 @@ extern "C" int imn_tree_ldl_compiled_solve(ImnTreeKernel* k, const float* M, int
   if (nworld < 0 || M_ld < k->nM || y_ld < k->nv || x_ld < k->nv)
     return imn::set_error("imn_tree_ldl_compiled_solve: a stride is smaller than its extent"), IMN_ERR_SHAPE;
   if (nworld == 0) return IMN_OK;
-  const size_t bytes = (size_t)(k->nshared > 0 ? k->nshared : 1) * 32 * sizeof(float);
+  size_t bytes = (size_t)(k->nshared > 0 ? k->nshared : 1) * 32 * sizeof(float);
+  if (k->staged) bytes += 16 + sizeof(float) * ((size_t)((32 * k->nM + 3) & ~3) + ((32 * k->nv + 3) & ~3));
   if (bytes > 227 * 1024)
     return imn::set_error("imn_tree_ldl_compiled_solve: %zu bytes of shared memory per block (max %d)", bytes,
                           227 * 1024),
@@ -293,7 +402,11 @@ extern "C" int imn_tree_ldl_compiled_solve(ImnTreeKernel* k, const float* M, int
   lock.unlock();
   long long mld = M_ld, yld = y_ld, xld = x_ld;
   int nw = nworld;
-  void* args[] = {&M, &mld, &y, &yld, &x, &xld, &nw};
+  // bulk copies need contiguous worlds and 16-byte aligned tiles (a tile is 32 worlds:
+  // 128 nM and 128 nv bytes, so the base addresses decide)
+  int bulk = k->staged && M_ld == k->nM && y_ld == k->nv && (reinterpret_cast<uintptr_t>(M) & 15) == 0 &&
+             (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0;
+  void* args[] = {&M, &mld, &y, &yld, &x, &xld, &nw, &bulk};
   cudaError_t e = cudaLaunchKernel(reinterpret_cast<const void*>(k->kernel), dim3((nworld + 31) / 32),
                                    dim3(32 * k->groups), args, bytes, (cudaStream_t)stream);
   if (e != cudaSuccess)

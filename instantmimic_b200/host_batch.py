@@ -9,13 +9,15 @@ What it does per batch, all on one stream per slot and with nothing allocated af
 construction:
 
 * host -> device copies of the inputs.  ``efc.J`` is 78 % of a humanoid batch and the
-  solver never reads rows at or beyond a world's ``nefc``, so worlds are taken in
-  chunks and each chunk copies only rows ``[0, max nefc of the chunk)`` of J with one
-  strided copy (``imn_copy_rows`` = one ``cudaMemcpy2DAsync``; a world's rows are one
-  contiguous segment of several KB).  A caller that keeps its worlds grouped by row
-  count gets tight copies; any order is correct.  The per-row vectors (D, aref,
-  frictionloss) are copied whole: their per-world segments are a few hundred bytes,
-  which a strided copy moves slower than the dead rows cost.
+  solver never reads rows at or beyond a world's ``nefc``.  Three ways to move it:
+  ``"compact"`` (default) keeps J on the host as the ``nefc`` rows of each world back to
+  back, as MuJoCo C stores ``mjData.efc_J``, copies that one contiguous block and tells
+  the kernel where each world starts (``ImnData.J_world_offset``); ``"rows"`` keeps the
+  padded layout and copies rows ``[0, max nefc of the chunk)`` of chunks of worlds
+  with strided copies (``imn_copy_rows`` = ``cudaMemcpy2DAsync``; tight when the caller
+  groups its worlds by row count, slower per byte than a contiguous copy);
+  ``"whole"`` copies the padded array.  The per-row vectors (D, aref, frictionloss) are
+  copied whole: their per-world segments are a few hundred bytes.
 * ``solve_with_scratch`` on the device buffers.
 * device -> host copies of the results (whole arrays).
 
@@ -48,11 +50,13 @@ class HostBatch:
     chunk_rows: list  # (first world, worlds, rows to copy) per chunk
     nworld: int
 
-    def h2d_bytes(self, nv: int, ldj: int, nM: int, njmax: int, tight: bool = True) -> int:
+    def h2d_bytes(self, nv: int, ldj: int, nM: int, njmax: int, mode: str = "compact") -> int:
         total = self.nworld * 4 * (3 + 3 * nv + nM + 3 * njmax)
-        if not tight:
+        if mode == "whole":
             return total + self.nworld * njmax * ldj * 4
-        return total + sum(n * rows * 4 * ldj for _, n, rows in self.chunk_rows)
+        if mode == "rows":
+            return total + sum(n * rows * 4 * ldj for _, n, rows in self.chunk_rows)
+        return total + int(self.tensors["Jc"].numel()) * 4 + 8 * self.nworld
 
     def d2h_bytes(self, nv: int, njmax: int) -> int:
         return self.nworld * 4 * (3 * nv + 2 + 2 * njmax)
@@ -66,6 +70,8 @@ def pin_batch(d: Any, chunk: int = 256) -> HostBatch:
     pin = lambda a: torch.from_numpy(np.ascontiguousarray(a)).pin_memory()  # noqa: E731
     t = {n: pin(getattr(d, n)) for n in ("nefc", "ne", "nf", "M") + _IN_DOF}
     t["J"] = pin(d.efc.J)
+    compact = mjw_model.compact_jacobian(d)
+    t["Jc"], t["Joff"] = pin(compact.efc.J), pin(compact.efc.J_world_offset)
     for n in _IN_ROW:
         t[n] = pin(getattr(d.efc, n))
     nefc = np.minimum(np.asarray(d.nefc), d.njmax)
@@ -95,16 +101,22 @@ class HostBatchPipeline:
     ``result`` waits for that slot and returns its pinned result tensors."""
 
     def __init__(self, m_dev: Any, template: Any, device: Any, *, slots: int = 2, sparse_groups=None,
-                 tight: bool = True):
+                 mode: str = "compact"):
         import torch
 
+        if mode not in ("compact", "rows", "whole"):
+            raise ValueError("mode must be compact, rows or whole")
         self.m = m_dev
-        self.tight = tight
+        self.mode = mode
         self.device = device
         self.slots = []
         for _ in range(slots):
             dd = mjw_model.to_device(mjw_model.make_data(_host_model_view(m_dev), template.nworld, template.njmax),
                                      device)
+            if mode == "compact":
+                # the same storage as (all rows, nv); every submit says where worlds start
+                dd.efc.J = dd.efc.J.view(template.nworld * template.njmax, -1)
+                dd.efc.J_world_offset = torch.zeros(template.nworld, dtype=torch.int64, device=device)
             sc = runtime.make_optimized_fwd_position_scratch(m_dev, dd, device)
             if sparse_groups is not None:
                 runtime.refresh_sparse_hessian(m_dev, dd, sc, sparse_groups, device)
@@ -137,7 +149,10 @@ class HostBatchPipeline:
                 getattr(dd, n).copy_(t[n], non_blocking=True)
             for name in _IN_ROW:
                 getattr(dd.efc, name).copy_(t[name], non_blocking=True)
-            if self.tight:
+            if self.mode == "compact":
+                dd.efc.J[: t["Jc"].shape[0]].copy_(t["Jc"], non_blocking=True)
+                dd.efc.J_world_offset.copy_(t["Joff"], non_blocking=True)
+            elif self.mode == "rows":
                 for lo, n, rows in batch.chunk_rows:
                     if rows:
                         self._rows(dd.efc.J, t["J"], lo, n, rows, False, handle)

@@ -131,7 +131,7 @@ class SolveCall:
 
 _KEY_DATA = ("nefc", "ne", "nf", "qacc_smooth", "qacc_warmstart", "qfrc_smooth", "M", "qacc",
              "qfrc_constraint", "solver_niter", "overflow")
-_KEY_EFC = ("J", "D", "aref", "frictionloss", "force", "state", "Ma")
+_KEY_EFC = ("J", "D", "aref", "frictionloss", "force", "state", "Ma", "J_world_offset")
 _KEY_CTX = ("Jaref", "jv", "search", "mv", "grad", "h", "hfactor", "quad_changed_ids", "newton_dof_union",
             "world_order") + binding._CTX_WORLD_ARRAYS
 
@@ -146,7 +146,7 @@ def _key(m, d, ctx, nsolving):
     return (
         id(m), id(d), id(ctx), id(plan), addr(nsolving),
         tuple(addr(getattr(d, n)) for n in _KEY_DATA),
-        tuple(addr(getattr(d.efc, n)) for n in _KEY_EFC),
+        tuple(addr(getattr(d.efc, n, None)) for n in _KEY_EFC),
         tuple(addr(getattr(ctx, n, None)) for n in _KEY_CTX),
         addr(m.opt.tolerance), addr(m.opt.ls_tolerance), addr(m.stat.meaninertia),
         int(m.opt.iterations), int(m.opt.ls_iterations), int(m.opt.disableflags),

@@ -94,6 +94,9 @@ class Constraint:
     force: Any
     state: Any
     Ma: Any
+    # optional compact layout of J: (total rows, nv) with one int64 element offset per
+    # world (see compact_jacobian); None for mujoco-warp's padded (nworld, njmax, nv)
+    J_world_offset: Any = None
 
 
 @dataclass
@@ -260,6 +263,21 @@ def make_data(m: Model, nworld: int, njmax: int) -> Data:
     )
 
 
+def compact_jacobian(d: Data) -> Data:
+    """Host ``Data`` whose ``efc.J`` holds only the ``nefc`` rows of each world, one world
+    after the other (as MuJoCo C stores ``mjData.efc_J``), with ``efc.J_world_offset``
+    naming each world's first element.  The solver reads the same rows; nothing else
+    changes."""
+    nefc = np.minimum(np.asarray(d.nefc), d.njmax).astype(np.int64)
+    ld = int(d.efc.J.shape[2])
+    live = np.arange(d.njmax)[None, :] < nefc[:, None]
+    rows = np.ascontiguousarray(d.efc.J[live])  # world-major, rows ascending
+    if rows.shape[0] == 0:
+        rows = np.zeros((1, ld), np.float32)
+    offsets = (np.concatenate(([0], np.cumsum(nefc)[:-1])) * ld).astype(np.int64)
+    return replace(d, efc=replace(d.efc, J=rows, J_world_offset=offsets))
+
+
 def _map_arrays(obj: Any, fn):
     """Copy of a (nested) dataclass / namespace with ``fn`` applied to every array."""
     if isinstance(obj, np.ndarray):
@@ -305,7 +323,9 @@ def slice_worlds(d: Data, lo: int, hi: int) -> Data:
     def cut(a):
         return a[lo:hi]
 
-    efc = replace(d.efc, **{f.name: cut(getattr(d.efc, f.name)) for f in fields(d.efc)})
+    if d.efc.J_world_offset is not None:
+        raise ValueError("slice_worlds works on the padded efc.J layout")
+    efc = replace(d.efc, **{f.name: cut(getattr(d.efc, f.name)) for f in fields(d.efc) if f.name != "J_world_offset"})
     out = replace(
         d,
         nworld=hi - lo,

@@ -501,7 +501,7 @@ static void solve_world(const ImnModel* m, const ImnData* d, const ImnCtx* ctx, 
   w.ne = d->ne[wid];
   w.nf = d->nf[wid];
   w.ldj = (int)d->J_ld_row;
-  w.J = d->efc_J + (size_t)wid * d->J_ld_world;
+  w.J = d->efc_J + (d->J_world_offset ? (size_t)d->J_world_offset[wid] : (size_t)wid * d->J_ld_world);
   w.D = d->efc_D + (size_t)wid * d->efc_ld;
   w.aref = d->efc_aref + (size_t)wid * d->efc_ld;
   w.floss = d->efc_frictionloss + (size_t)wid * d->efc_ld;

@@ -12,8 +12,8 @@ from helpers import run_oracle
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("grouped", [False, True])
-def test_host_batch_pipeline_matches_oracle(oracle, cuda_device, grouped):
+@pytest.mark.parametrize("mode,grouped", [("compact", False), ("rows", False), ("rows", True), ("whole", False)])
+def test_host_batch_pipeline_matches_oracle(oracle, cuda_device, mode, grouped):
     import torch
 
     m, d, _ = synthetic.make_workload("humanoid", 700, seed=5, rowless_fraction=0.05)
@@ -22,12 +22,13 @@ def test_host_batch_pipeline_matches_oracle(oracle, cuda_device, grouped):
         assert (np.diff(d.nefc) <= 0).all()
     want, _, _ = run_oracle(oracle, m, d)
     md = mjw_model.to_device(m, cuda_device)
-    pipe = host_batch.HostBatchPipeline(md, d, cuda_device, slots=2)
+    pipe = host_batch.HostBatchPipeline(md, d, cuda_device, slots=2, mode=mode)
     batch = host_batch.pin_batch(d, chunk=128)
     full = d.nworld * 4 * (3 + 3 * m.nv + m.nM + d.njmax * (m.nv + 3))
-    assert batch.h2d_bytes(m.nv, m.nv, m.nM, d.njmax) <= full == batch.h2d_bytes(m.nv, m.nv, m.nM, d.njmax, tight=False)
-    if grouped:
-        assert batch.h2d_bytes(m.nv, m.nv, m.nM, d.njmax) < 0.8 * full  # tight copies when worlds are grouped
+    moved = batch.h2d_bytes(m.nv, m.nv, m.nM, d.njmax, mode)
+    assert moved <= full + 8 * d.nworld and batch.h2d_bytes(m.nv, m.nv, m.nM, d.njmax, "whole") == full
+    if grouped or mode == "compact":
+        assert moved < 0.8 * full  # no dead rows (compact) or few (rows of grouped worlds)
     for k in range(3):  # both slots, one reused
         pipe.submit(k, batch)
     for k in range(3):

@@ -220,6 +220,41 @@ def test_tree_kernel_matches_oracle_bitwise(oracle, cuda_device, tree, groups, g
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("layout", ["contiguous", "padded", "offset"])
+def test_generated_tree_kernel_tile_paths(oracle, cuda_device, layout):
+    """The generated kernel brings a block's 32 worlds of M and y into shared memory:
+    by TMA bulk copies when worlds are contiguous and 16-byte aligned, by plain loads
+    for padded strides, an unaligned base, and the last partial block.  Same bits on
+    every path."""
+    import torch
+
+    worlds = 32 * 3 + 5
+    m, Mv, _ = _model_and_matrices(TREES["humanoid"], worlds)
+    structure = _structure(m)
+    plan = tree_ldl.best_tree_ldl_plan(*structure)
+    scratch = tree_ldl.compile_plan(structure, plan, cuda_device, True)
+    assert scratch.kernel is not None and "tileM" in scratch.kernel.info()["source"]
+    y = np.random.default_rng(2).normal(size=(worlds, m.nv)).astype(np.float32)
+    want = oracle.tree_ldl_solve(structure, plan, Mv, y)
+    if layout == "contiguous":
+        Mt, yt = torch.from_numpy(Mv).to(cuda_device), torch.from_numpy(y).to(cuda_device)
+        x = torch.full((worlds, m.nv), 7.0, device=cuda_device)
+    elif layout == "padded":
+        Mt = torch.zeros((worlds, m.nM + 2), device=cuda_device)[:, : m.nM]
+        yt = torch.zeros((worlds, m.nv + 6), device=cuda_device)[:, : m.nv]
+        Mt.copy_(torch.from_numpy(Mv)), yt.copy_(torch.from_numpy(y))
+        x = torch.full((worlds, m.nv + 1), 7.0, device=cuda_device)[:, : m.nv]
+    else:  # contiguous worlds whose first element sits 4 bytes past a 16-byte boundary
+        Mt = torch.zeros(worlds * m.nM + 1, device=cuda_device)[1:].view(worlds, m.nM)
+        yt = torch.zeros(worlds * m.nv + 1, device=cuda_device)[1:].view(worlds, m.nv)
+        Mt.copy_(torch.from_numpy(Mv)), yt.copy_(torch.from_numpy(y))
+        x = torch.full((worlds, m.nv), 7.0, device=cuda_device)
+    tree_ldl.tree_factor_solve(scratch, Mt, x, yt)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(x.cpu().numpy(), want)
+
+
+@pytest.mark.gpu
 def test_model_scratch_selects_tree_solve_and_solves_qacc_smooth(oracle, cuda_device):
     import torch
 

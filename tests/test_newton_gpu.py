@@ -275,3 +275,16 @@ def test_torch_library_op_matches_the_direct_call(oracle, cuda_device):
     np.testing.assert_array_equal(dd.qacc.cpu().numpy().view(np.uint32), want.qacc.view(np.uint32))
     np.testing.assert_array_equal(dd.solver_niter.cpu().numpy(), want.solver_niter)
     assert torch.library.opcheck is not None and hasattr(torch.ops.imnewton, "solve")
+
+
+@pytest.mark.parametrize("name,worlds", [("humanoid", 200), ("snu", 48)])
+def test_compact_jacobian_layout(oracle, cuda_device, name, worlds):
+    """efc.J as only the nefc rows of each world (J_world_offset), resident and streamed
+    kernels: same bits as the padded layout."""
+    from instantmimic_b200 import mjw_model
+
+    m, d, _ = synthetic.make_workload(name, worlds, seed=15, rowless_fraction=0.1)
+    want, wctx, _ = run_oracle(oracle, m, d)
+    got, gctx, _, _ = run_cuda(m, mjw_model.compact_jacobian(d), cuda_device)
+    _check(got, want, gctx, wctx)
+    np.testing.assert_array_equal(got.qacc.view(np.uint32), want.qacc.view(np.uint32))

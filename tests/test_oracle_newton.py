@@ -94,3 +94,17 @@ def test_work_counters_are_consistent(oracle):
     assert (st[rows, 2] >= 1).all() and (st[rows, 2] <= st[rows, 3]).all()      # a factorisation needs a gradient
     assert (st[rows, 0] >= niter[rows]).all() and (st[rows, 0] <= niter[rows] * (m.opt.ls_iterations + 2)).all()
     assert (st[rows, 1] >= st[rows, 2] - 1).all()                                # every refactorisation had a flip
+
+
+def test_compact_jacobian_layout_gives_the_same_solve(oracle):
+    """efc.J handed over as the nefc rows of each world back to back (J_world_offset)."""
+    from instantmimic_b200 import mjw_model
+
+    m, d, _ = synthetic.make_workload("humanoid", 40, seed=6, rowless_fraction=0.1)
+    want, _, _ = run_oracle(oracle, m, d)
+    dc = mjw_model.compact_jacobian(d)
+    assert dc.efc.J.shape == (int(d.nefc.sum()), m.nv) and dc.efc.J_world_offset[1] == d.nefc[0] * m.nv
+    got, _, _ = run_oracle(oracle, m, dc)
+    np.testing.assert_array_equal(got.qacc.view(np.uint32), want.qacc.view(np.uint32))
+    np.testing.assert_array_equal(got.solver_niter, want.solver_niter)
+    np.testing.assert_array_equal(got.efc.state, want.efc.state)
