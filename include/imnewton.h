@@ -246,6 +246,45 @@ typedef struct ImnBlockedPlan {
   int32_t nM;
 } ImnBlockedPlan;
 
+/* mujoco mjtJoint values (Model.jnt_type). */
+enum { IMN_JNT_FREE = 0, IMN_JNT_BALL = 1, IMN_JNT_SLIDE = 2, IMN_JNT_HINGE = 3 };
+
+/* Inputs of the implicit-fast matrix A = M - h qDeriv (mjw_step_optimized.py:4172-4295):
+ * the passive joint damping and the actuator-centric actuation term
+ * sum_a moment_a moment_a^T gain_a, with the actuator moments in mujoco-warp's
+ * per-world CSR (Data.moment_rownnz / moment_rowadr / moment_colind /
+ * actuator_moment) and gain_a = d(actuator force)/d(actuator velocity), the
+ * `vel` buffer that upstream's _qderiv_actuator_passive_vel fills. */
+typedef struct ImnImplicit {
+  int32_t nv, nM, nu;
+  int32_t actuation;           /* !(opt.disableflags & ACTUATION)                */
+  int32_t damper;              /* !(opt.disableflags & DAMPER)                   */
+  float timestep;              /* opt.timestep                                   */
+  const float* dof_damping;    /* (nv)                                           */
+  const int32_t* M_elemid;     /* (nv, nv): entry of M for (i, j), -1 if none    */
+  const int32_t* moment_rownnz; /* (W, nu)                                       */
+  const int32_t* moment_rowadr; /* (W, nu)                                       */
+  const int32_t* moment_colind; /* (W, moment_ld) dofs, ascending within a row   */
+  const float* actuator_moment; /* (W, moment_ld)                                */
+  int64_t moment_ld;
+  const float* actuator_velocity_gain; /* (W, nu)                                */
+} ImnImplicit;
+
+/* State advanced by the integrator (upstream _advance, called through
+ * _advance_with_scratch, mjw_step_optimized.py:4823-4847). */
+typedef struct ImnAdvance {
+  int32_t nv, nq, njnt;
+  float timestep;
+  const int32_t* jnt_type;    /* (njnt) IMN_JNT_*                                */
+  const int32_t* jnt_dofadr;  /* (njnt)                                          */
+  const int32_t* jnt_qposadr; /* (njnt)                                          */
+  float* qvel;                /* (W, nv)  in/out                                 */
+  int64_t qvel_ld;
+  float* qpos;                /* (W, nq)  in/out                                 */
+  int64_t qpos_ld;
+  float* time;                /* (W) in/out, may be NULL                         */
+} ImnAdvance;
+
 /* ---- entry points ------------------------------------------------------- */
 
 /* Replaces solve_with_scratch's monolithic fused branch:
@@ -347,6 +386,21 @@ int imn_sparse_factor_nonfused(const ImnSparsePlan* plan, const uint8_t* done,
                                float* decrement, int32_t nworld,
                                int32_t skip_unchanged, int32_t skip_noflip,
                                void* stream);
+
+/* Replaces deriv_smooth_vel_dense_actuator_centric (mjw_step_optimized.py:4172-4412;
+ * kernels :629-669 and upstream derivative._qderiv_actuator_passive): out = M - h qDeriv
+ * in M's CSR layout, (W, nM).  The factor/solve of the result is
+ * imn_tree_ldl_compiled_solve / imn_blocked_dense_factor_solve with y = efc.Ma.
+ * Tendon damping and fluid terms are not included. */
+int imn_implicit_matrix(const ImnImplicit* p, const float* M, int64_t M_ld, float* out,
+                        int64_t out_ld, int32_t nworld, void* stream);
+
+/* Replaces upstream _advance as called by _advance_with_scratch
+ * (mjw_step_optimized.py:4823-4847) for models without actuator activations:
+ * qvel += h qacc; qpos moves with the new qvel (free and ball joints on the unit
+ * quaternions); time += h. */
+int imn_advance(const ImnAdvance* p, const float* qacc, int64_t qacc_ld, int32_t nworld,
+                void* stream);
 
 /* Uploads a sparse plan (sparse_hessian.build_plan's tables, sparse_hessian.py:229-402,
  * which the reference bakes into generated source instead).  `host_tables` holds HOST

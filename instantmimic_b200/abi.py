@@ -183,6 +183,21 @@ class ImnBlockedPlan(C.Structure):
     ]
 
 
+class ImnImplicit(C.Structure):
+    _fields_ = [
+        ("nv", I32), ("nM", I32), ("nu", I32), ("actuation", I32), ("damper", I32), ("timestep", C.c_float),
+        ("dof_damping", P), ("M_elemid", P), ("moment_rownnz", P), ("moment_rowadr", P), ("moment_colind", P),
+        ("actuator_moment", P), ("moment_ld", I64), ("actuator_velocity_gain", P),
+    ]
+
+
+class ImnAdvance(C.Structure):
+    _fields_ = [
+        ("nv", I32), ("nq", I32), ("njnt", I32), ("timestep", C.c_float), ("jnt_type", P), ("jnt_dofadr", P),
+        ("jnt_qposadr", P), ("qvel", P), ("qvel_ld", I64), ("qpos", P), ("qpos_ld", I64), ("time", P),
+    ]
+
+
 class ImnLaunchInfo(C.Structure):
     _fields_ = [
         ("world_threads", I32),
@@ -218,6 +233,8 @@ SYMBOLS = {
         C.c_int,
         [C.POINTER(ImnSparsePlan), P, P, I64, P, P, P, P, P, I64, P, P, I32, I32, I32, P],
     ),
+    "imn_implicit_matrix": (C.c_int, [C.POINTER(ImnImplicit), P, I64, P, I64, I32, P]),
+    "imn_advance": (C.c_int, [C.POINTER(ImnAdvance), P, I64, I32, P]),
     "imn_sparse_plan_create": (C.c_int, [C.POINTER(ImnSparsePlan), C.POINTER(C.POINTER(ImnSparsePlan))]),
     "imn_sparse_plan_destroy": (None, [C.POINTER(ImnSparsePlan)]),
     "imn_launch_info": (

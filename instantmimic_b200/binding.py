@@ -47,6 +47,8 @@ def upstream_constants(module_types: Any = None, module_solver: Any = None) -> d
         "overflow_iterations": member("OverflowType", "ITERATIONS", types.OverflowType.ITERATIONS),
         "overflow_ls_iterations": member("OverflowType", "LS_ITERATIONS", types.OverflowType.LS_ITERATIONS),
         "disable_warmstart": member("DisableBit", "WARMSTART", types.DisableBit.WARMSTART),
+        "disable_damper": member("DisableBit", "DAMPER", types.DisableBit.DAMPER),
+        "disable_actuation": member("DisableBit", "ACTUATION", types.DisableBit.ACTUATION),
         "solver_newton": member("SolverType", "NEWTON", types.SolverType.NEWTON),
         "cone_pyramidal": member("ConeType", "PYRAMIDAL", types.ConeType.PYRAMIDAL),
         "integrator_discrete": member("IntegratorType", "DISCRETE", types.IntegratorType.DISCRETE),
@@ -251,4 +253,59 @@ def ctx_struct(d_struct: abi.ImnData, ctx: Any, nsolving: Any, sparse_plan_struc
     if stats is not None and (tuple(shape(stats)) != (d_struct.nworld, 4) or elem_strides(stats) != (4, 1)):
         raise ValueError("ctx.stats must be a contiguous (nworld, 4) int32 array")
     s.stats = addr(stats)
+    return s
+
+
+def _timestep(m: Any) -> float:
+    """opt.timestep: a scalar, or mujoco-warp's per-world array, which must be uniform
+    (the kernels take one step size per launch)."""
+    from .arrays import to_host
+
+    h = m.opt.timestep
+    if isinstance(h, (int, float)):
+        return float(h)
+    values = to_host(h).reshape(-1)
+    if values.size == 0 or (values != values[0]).any():
+        raise ValueError("the integrator kernels need one timestep for all worlds")
+    return float(values[0])
+
+
+def implicit_struct(m: Any, d: Any, velocity_gain: Any) -> abi.ImnImplicit:
+    """``velocity_gain``: (nworld, nu) d(actuator force)/d(actuator velocity), or None."""
+    c = upstream_constants()
+    s = abi.ImnImplicit()
+    flags = int(m.opt.disableflags)
+    s.nv, s.nM = int(m.nv), int(shape(m.M_colind)[0])
+    s.nu = int(getattr(m, "nu", 0) or 0)
+    s.actuation = 0 if flags & c["disable_actuation"] else 1
+    s.damper = 0 if flags & c["disable_damper"] else 1
+    s.timestep = _timestep(m)
+    s.dof_damping = addr(m.dof_damping)
+    s.M_elemid = addr(m.M_elemid)
+    if s.nu and s.actuation:
+        if velocity_gain is None:
+            raise ValueError("an actuated model needs the actuators' velocity gains")
+        for name in ("moment_rownnz", "moment_rowadr"):
+            a = getattr(d, name)
+            if tuple(shape(a)) != (int(d.nworld), s.nu) or elem_strides(a) != (s.nu, 1):
+                raise ValueError(f"d.{name} must be a contiguous (nworld, nu) array")
+            setattr(s, name, addr(a))
+        if elem_strides(d.moment_colind) != elem_strides(d.actuator_moment) or elem_strides(d.actuator_moment)[1] != 1:
+            raise ValueError("d.moment_colind and d.actuator_moment must share one layout")
+        if tuple(shape(velocity_gain)) != (int(d.nworld), s.nu) or elem_strides(velocity_gain) != (s.nu, 1):
+            raise ValueError("velocity gains must be a contiguous (nworld, nu) array")
+        s.moment_colind, s.actuator_moment = addr(d.moment_colind), addr(d.actuator_moment)
+        s.moment_ld = elem_strides(d.actuator_moment)[0]
+        s.actuator_velocity_gain = addr(velocity_gain)
+    return s
+
+
+def advance_struct(m: Any, d: Any) -> abi.ImnAdvance:
+    s = abi.ImnAdvance()
+    s.nv, s.nq, s.njnt = int(m.nv), int(m.nq), int(m.njnt)
+    s.timestep = _timestep(m)
+    s.jnt_type, s.jnt_dofadr, s.jnt_qposadr = addr(m.jnt_type), addr(m.jnt_dofadr), addr(m.jnt_qposadr)
+    s.qvel, s.qvel_ld = addr(d.qvel), _row_ld(d.qvel)
+    s.qpos, s.qpos_ld = addr(d.qpos), _row_ld(d.qpos)
+    s.time = addr(getattr(d, "time", None))
     return s

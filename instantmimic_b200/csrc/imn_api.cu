@@ -55,6 +55,126 @@ __global__ void __launch_bounds__(256) mul_m_kernel(const int nv, const int* __r
   }
 }
 
+// The same product for large batches, tile by tile: a block takes 32 consecutive
+// worlds, lane = world.  With one warp per world (above) a lane gathers M[madr] and
+// v[col] from all over its world's row, every load instruction touches ~10 cache lines
+// and the L1's one-line-per-cycle rate bounds the kernel at a sixth of the HBM rate.
+// Here the tile -- 32 x nM floats of M, 32 x nv of v, both contiguous -- arrives in
+// shared memory by two TMA bulk copies on one mbarrier (bounded wait; plain coalesced
+// loads for a partial, strided or unaligned tile), the table entry is the same for all
+// lanes (one broadcast read), a lane reads its own world's M and v from the tile
+// (stride nM / nv between lanes: gcd(stride, 32)-way bank conflicts) and keeps a row's
+// running sum in a register.  The warps of a block split the rows by stored entries.
+// Results leave through the tile by one bulk store.  Sums are formed in table order,
+// so the bits equal mul_m_kernel's.
+static const int kTileWarps = 4;
+
+__global__ void __launch_bounds__(32 * kTileWarps)
+    mul_m_tile_kernel(const int nv, const int nM, const int* __restrict__ rowadr, const int* __restrict__ col,
+                      const int* __restrict__ madr, const float* __restrict__ M, const int64_t M_ld,
+                      const float* __restrict__ v, const int64_t v_ld, float* __restrict__ out, const int64_t out_ld,
+                      float* __restrict__ copy_to, int* __restrict__ niter, float* __restrict__ zero, const int nworld,
+                      const int bulk) {
+  extern __shared__ __align__(16) float tile[];
+  const int nnz = rowadr[nv];
+  float* Mt = tile + 4;  // the first 16 bytes hold the mbarrier
+  float* vt = Mt + ((32 * nM + 3) & ~3);
+  float* ot = vt + ((32 * nv + 3) & ~3);
+  uint32_t* tab = reinterpret_cast<uint32_t*>(ot + ((32 * nv + 3) & ~3));
+  int* radr = reinterpret_cast<int*>(tab + nnz);
+  const int lw = threadIdx.x & 31, part = threadIdx.x >> 5;
+  const int w0 = blockIdx.x * 32;
+  const bool whole = bulk && w0 + 32 <= nworld;
+  const unsigned bar = (unsigned)__cvta_generic_to_shared(tile);
+  if (whole && threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(128u * (unsigned)(nM + nv))
+                 : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     (unsigned)__cvta_generic_to_shared(Mt)),
+                 "l"(M + (size_t)w0 * nM), "r"(128u * (unsigned)nM), "r"(bar)
+                 : "memory");
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     (unsigned)__cvta_generic_to_shared(vt)),
+                 "l"(v + (size_t)w0 * nv), "r"(128u * (unsigned)nv), "r"(bar)
+                 : "memory");
+  }
+  for (int e = threadIdx.x; e < nnz; e += blockDim.x) tab[e] = (uint32_t)col[e] | ((uint32_t)madr[e] << 16);
+  for (int i = threadIdx.x; i <= nv; i += blockDim.x) radr[i] = rowadr[i];
+  __syncthreads();  // tables staged, barrier initialised
+  bool arrived = false;
+  if (whole) {
+    // bounded wait; if it runs out the copies get one more bounded wait and the tile is
+    // then loaded again with plain loads
+#pragma unroll 1
+    for (int round = 0; round < 2 && !arrived; ++round)
+#pragma unroll 1
+      for (int tries = 0; tries < (1 << 22) && !arrived; ++tries) {
+        unsigned ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok)
+                     : "r"(bar)
+                     : "memory");
+        arrived = ok != 0;
+      }
+  }
+  if (!__syncthreads_and(arrived)) {
+    for (int e = threadIdx.x; e < 32 * nM; e += blockDim.x) {
+      const int r = e / nM, c = e - r * nM;
+      Mt[e] = M[(size_t)min(w0 + r, nworld - 1) * M_ld + c];
+    }
+    for (int e = threadIdx.x; e < 32 * nv; e += blockDim.x) {
+      const int r = e / nv, c = e - r * nv;
+      vt[e] = v[(size_t)min(w0 + r, nworld - 1) * v_ld + c];
+    }
+    __syncthreads();
+  }
+  // rows of this warp: the stored entries are cut into kTileWarps near-equal runs
+  const float* Mw = Mt + lw * nM;
+  const float* vw = vt + lw * nv;
+  float* ow = ot + lw * nv;
+  const int lo = (int)(((long long)nnz * part) / kTileWarps), hi = (int)(((long long)nnz * (part + 1)) / kTileWarps);
+#pragma unroll 1
+  for (int i = 0; i < nv; ++i) {
+    const int k0 = radr[i], k1 = radr[i + 1];
+    if (k0 < lo || k0 >= hi) continue;  // a row belongs to the warp its first entry falls to
+    float s = 0.0f;
+#pragma unroll 4
+    for (int k = k0; k < k1; ++k) {
+      const uint32_t p = tab[k];
+      s = fmaf(Mw[p >> 16], vw[p & 0xFFFF], s);
+    }
+    ow[i] = s;
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  if (whole && out_ld == nv) {
+    if (threadIdx.x == 0) {
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(out + (size_t)w0 * nv),
+                   "r"((unsigned)__cvta_generic_to_shared(ot)), "r"(128u * (unsigned)nv)
+                   : "memory");
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  } else {
+    for (int e = threadIdx.x; e < 32 * nv; e += blockDim.x) {
+      const int r = e / nv, c = e - r * nv;
+      if (w0 + r < nworld) out[(size_t)(w0 + r) * out_ld + c] = ot[e];
+    }
+  }
+  if (copy_to || zero)
+    for (int e = threadIdx.x; e < 32 * nv; e += blockDim.x) {
+      const int r = e / nv, c = e - r * nv;
+      if (w0 + r < nworld) {
+        if (copy_to) copy_to[(size_t)(w0 + r) * v_ld + c] = vt[e];
+        if (zero) zero[(size_t)(w0 + r) * v_ld + c] = 0.0f;
+      }
+    }
+  if (niter && threadIdx.x < 32 && w0 + threadIdx.x < nworld) niter[w0 + threadIdx.x] = 0;
+  // shared memory must stay valid until the bulk store has read it
+  if (whole && out_ld == nv && threadIdx.x == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+
 static int launch_mul_m(const ImnModel* m, const float* M, int64_t M_ld, const float* v, int64_t v_ld,
                         float* out, int64_t out_ld, float* copy_to, int* niter, float* zero, int nworld,
                         cudaStream_t stream) {
@@ -63,6 +183,32 @@ static int launch_mul_m(const ImnModel* m, const float* M, int64_t M_ld, const f
   // the symmetric tables list every stored entry at most twice
   const size_t bytes = ((size_t)2 * m->nM + m->nv + 1) * sizeof(uint32_t);
   if (bytes > 48 * 1024) return set_error("mul_m: nM %d too large", m->nM), IMN_ERR_LIMIT;
+  {
+    // tiles of 32 worlds for batches that fill the GPU, when the lane stride nM does not
+    // pile the lanes onto a few banks and four tiles fit an SM's shared memory
+    int g = m->nM, b = 32;
+    while (b) {
+      const int t = g % b;
+      g = b, b = t;
+    }
+    const size_t tile_bytes = 16 + sizeof(float) * ((size_t)((32 * m->nM + 3) & ~3) + 2 * (size_t)((32 * m->nv + 3) & ~3)) +
+                              bytes;
+    if (nworld >= 4096 && g < 8 && tile_bytes <= 56 * 1024) {
+      const int bulk = M_ld == m->nM && v_ld == m->nv && (reinterpret_cast<uintptr_t>(M) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(v) & 15) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+      cudaError_t e = cudaFuncSetAttribute(mul_m_tile_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_bytes);
+      if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(mul_m_tile_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 cudaSharedmemCarveoutMaxShared);
+      if (e != cudaSuccess) return set_error("mul_m: cudaFuncSetAttribute: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+      mul_m_tile_kernel<<<(nworld + 31) / 32, 32 * kTileWarps, tile_bytes, stream>>>(
+          m->nv, m->nM, m->M_mulm_rowadr, m->M_mulm_col, m->M_mulm_madr, M, M_ld, v, v_ld, out, out_ld, copy_to, niter,
+          zero, nworld, bulk);
+      e = cudaGetLastError();
+      if (e != cudaSuccess) return set_error("mul_m: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+      return IMN_OK;
+    }
+  }
   const int warps = 8;
   int sms = 148;
   {

@@ -1,0 +1,173 @@
+// imn_integrate.cu -- the implicit-fast integrator's tail, the step right after the
+// constraint solve (reference: _integrate, mjw_step_optimized.py:5209-5297):
+//
+//   1. A = M - h qDeriv on M's sparsity, qDeriv = d(qfrc_smooth)/d(qvel) restricted to
+//      the actuator term  sum_a moment_a moment_a^T dforce_a/dvelocity_a  (the
+//      actuator-centric assembly, mjw_step_optimized.py:629-669, 4172-4295) and the
+//      passive joint damping  -diag(dof_damping)  (upstream _qderiv_actuator_passive);
+//   2. x = A^-1 efc.Ma  -- the tree L'DL / blocked dense kernels (imn_msolve.cu,
+//      imn_tree_jit.cu), launched by the host layer between the two kernels here;
+//   3. the advance  qvel += h x, qpos integrated on its manifold with the new qvel,
+//      time += h  (upstream _advance through _advance_with_scratch,
+//      mjw_step_optimized.py:4823-4847).
+//
+// RESTATED: the arithmetic of steps 1 and 3 lives in mujoco-warp (derivative.py,
+// forward.py), whose source is not available; what follows is MuJoCo's published
+// semi-implicit update (mj_advance, mju_quatIntegrate) and the derivative terms named
+// above, with a fixed summation order.  The reference adds the actuator products with
+// atomics in whatever order the hardware picks; here an entry receives them in
+// ascending actuator order, so results are reproducible bit for bit (and equal to the
+// CPU oracle's).  Tendon damping, fluid forces and the free-body correction of
+// mujoco-warp 3.16 are not part of this file.
+#include "imn_common.cuh"
+
+namespace imn {
+
+// One warp per world.  qD is assembled in the warp's shared-memory row (nM floats),
+// then A = M - h qD leaves coalesced.
+static const int kMatrixWarps = 8;
+
+__global__ void __launch_bounds__(32 * kMatrixWarps)
+    implicit_matrix_kernel(const ImnImplicit P, const float* __restrict__ M, const int64_t M_ld,
+                           float* __restrict__ out, const int64_t out_ld, const int nworld) {
+  extern __shared__ float qd_all[];
+  const int lane = threadIdx.x & 31, w = blockIdx.x * kMatrixWarps + (threadIdx.x >> 5);
+  if (w >= nworld) return;
+  float* qd = qd_all + (threadIdx.x >> 5) * ((P.nM + 3) & ~3);
+  for (int e = lane; e < P.nM; e += 32) qd[e] = 0.0f;
+  __syncwarp();
+  if (P.nu > 0 && P.actuation) {
+    const int* rownnz = P.moment_rownnz + (size_t)w * P.nu;
+    const int* rowadr = P.moment_rowadr + (size_t)w * P.nu;
+    const int* colind = P.moment_colind + (size_t)w * P.moment_ld;
+    const float* moment = P.actuator_moment + (size_t)w * P.moment_ld;
+    const float* gain = P.actuator_velocity_gain + (size_t)w * P.nu;
+#pragma unroll 1
+    for (int a = 0; a < P.nu; ++a) {
+      const float vel = gain[a];
+      const int n = rownnz[a];
+      if (vel == 0.0f || n <= 0) continue;  // warp-uniform
+      const int base = rowadr[a];
+      // pairs (ri >= rj) of the actuator's moment row; distinct pairs hit distinct
+      // entries of M, so the lanes never collide within one actuator
+#pragma unroll 1
+      for (int p = lane; p < n * (n + 1) / 2; p += 32) {
+        int ri = (int)((sqrtf(8.0f * (float)p + 1.0f) - 1.0f) * 0.5f);
+        while ((ri + 1) * (ri + 2) / 2 <= p) ++ri;
+        while (ri * (ri + 1) / 2 > p) --ri;
+        const int rj = p - ri * (ri + 1) / 2;
+        const int di = colind[base + ri], dj = colind[base + rj];
+        const int e = P.M_elemid[di * P.nv + dj];
+        if (e < 0) continue;
+        const float c = (moment[base + ri] * moment[base + rj]) * vel;
+        if (c != 0.0f) qd[e] = qd[e] + c;
+      }
+      __syncwarp();
+    }
+  }
+  if (P.damper)
+    for (int i = lane; i < P.nv; i += 32) {
+      const int e = P.M_elemid[i * P.nv + i];
+      qd[e] = qd[e] - P.dof_damping[i];
+    }
+  __syncwarp();
+  const float* Mw = M + (size_t)w * M_ld;
+  float* ow = out + (size_t)w * out_ld;
+  for (int e = lane; e < P.nM; e += 32) ow[e] = Mw[e] - P.timestep * qd[e];
+}
+
+__device__ __forceinline__ void quat_integrate(float q[4], const float w[3], float h) {
+  // q <- normalise(q (x) [cos(a/2), axis sin(a/2)]),  a = h |w|,  axis = w / |w|
+  const float norm = sqrtf(w[0] * w[0] + w[1] * w[1] + w[2] * w[2]);
+  float r[4] = {1.0f, 0.0f, 0.0f, 0.0f};
+  if (norm >= IMN_MJ_MINVAL) {
+    const float half = 0.5f * (h * norm);
+    const float s = sinf(half) / norm;
+    r[0] = cosf(half), r[1] = w[0] * s, r[2] = w[1] * s, r[3] = w[2] * s;
+  }
+  const float a = q[0], b = q[1], c = q[2], d = q[3];
+  float o[4] = {a * r[0] - b * r[1] - c * r[2] - d * r[3], a * r[1] + b * r[0] + c * r[3] - d * r[2],
+                a * r[2] - b * r[3] + c * r[0] + d * r[1], a * r[3] + b * r[2] - c * r[1] + d * r[0]};
+  const float len = sqrtf(o[0] * o[0] + o[1] * o[1] + o[2] * o[2] + o[3] * o[3]);
+  if (len < IMN_MJ_MINVAL) {
+    q[0] = 1.0f, q[1] = q[2] = q[3] = 0.0f;
+    return;
+  }
+  const float inv = 1.0f / len;
+  q[0] = o[0] * inv, q[1] = o[1] * inv, q[2] = o[2] * inv, q[3] = o[3] * inv;
+}
+
+// One thread per (world, joint): the joint's dofs get their new velocity, then its
+// coordinates move with it.
+__global__ void __launch_bounds__(256)
+    advance_kernel(const ImnAdvance P, const float* __restrict__ qacc, const int64_t qacc_ld, const int nworld) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (int64_t)nworld * P.njnt) return;
+  const int w = (int)(t / P.njnt), j = (int)(t - (int64_t)w * P.njnt);
+  const float h = P.timestep;
+  const int type = P.jnt_type[j], dof = P.jnt_dofadr[j], pos = P.jnt_qposadr[j];
+  float* qvel = P.qvel + (size_t)w * P.qvel_ld + dof;
+  float* qpos = P.qpos + (size_t)w * P.qpos_ld + pos;
+  const float* acc = qacc + (size_t)w * qacc_ld + dof;
+  const int ndof = type == IMN_JNT_FREE ? 6 : (type == IMN_JNT_BALL ? 3 : 1);
+  float v[6];
+  for (int k = 0; k < ndof; ++k) {
+    v[k] = qvel[k] + h * acc[k];
+    qvel[k] = v[k];
+  }
+  if (type == IMN_JNT_FREE) {
+    for (int k = 0; k < 3; ++k) qpos[k] = qpos[k] + h * v[k];
+    float q[4] = {qpos[3], qpos[4], qpos[5], qpos[6]};
+    quat_integrate(q, v + 3, h);
+    for (int k = 0; k < 4; ++k) qpos[3 + k] = q[k];
+  } else if (type == IMN_JNT_BALL) {
+    float q[4] = {qpos[0], qpos[1], qpos[2], qpos[3]};
+    quat_integrate(q, v, h);
+    for (int k = 0; k < 4; ++k) qpos[k] = q[k];
+  } else {
+    qpos[0] = qpos[0] + h * v[0];
+  }
+  if (j == 0 && P.time) P.time[w] = P.time[w] + h;
+}
+
+}  // namespace imn
+
+extern "C" int imn_implicit_matrix(const ImnImplicit* p, const float* M, int64_t M_ld, float* out, int64_t out_ld,
+                                   int32_t nworld, void* stream) {
+  if (!p || !M || !out || !p->M_elemid) return imn::set_error("imn_implicit_matrix: NULL argument"), IMN_ERR_NULL;
+  if (p->nv <= 0 || p->nM <= 0 || p->nu < 0 || nworld < 0 || M_ld < p->nM || out_ld < p->nM)
+    return imn::set_error("imn_implicit_matrix: bad extent or stride"), IMN_ERR_SHAPE;
+  if (p->damper && !p->dof_damping) return imn::set_error("imn_implicit_matrix: dof_damping is NULL"), IMN_ERR_NULL;
+  if (p->nu > 0 && p->actuation &&
+      (!p->moment_rownnz || !p->moment_rowadr || !p->moment_colind || !p->actuator_moment ||
+       !p->actuator_velocity_gain || p->moment_ld <= 0))
+    return imn::set_error("imn_implicit_matrix: an actuator array is NULL"), IMN_ERR_NULL;
+  if (nworld == 0) return IMN_OK;
+  const size_t bytes = sizeof(float) * (size_t)((p->nM + 3) & ~3) * imn::kMatrixWarps;
+  if (bytes > 227 * 1024) return imn::set_error("imn_implicit_matrix: nM %d too large", p->nM), IMN_ERR_LIMIT;
+  if (bytes > 48 * 1024) {
+    cudaError_t e =
+        cudaFuncSetAttribute(imn::implicit_matrix_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess)
+      return imn::set_error("imn_implicit_matrix: cudaFuncSetAttribute: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  }
+  imn::implicit_matrix_kernel<<<(nworld + imn::kMatrixWarps - 1) / imn::kMatrixWarps, 32 * imn::kMatrixWarps, bytes,
+                                (cudaStream_t)stream>>>(*p, M, M_ld, out, out_ld, nworld);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return imn::set_error("imn_implicit_matrix: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  return IMN_OK;
+}
+
+extern "C" int imn_advance(const ImnAdvance* p, const float* qacc, int64_t qacc_ld, int32_t nworld, void* stream) {
+  if (!p || !qacc || !p->qvel || !p->qpos || !p->jnt_type || !p->jnt_dofadr || !p->jnt_qposadr)
+    return imn::set_error("imn_advance: NULL argument"), IMN_ERR_NULL;
+  if (p->njnt <= 0 || p->nv <= 0 || p->nq < p->nv || nworld < 0 || qacc_ld < p->nv || p->qvel_ld < p->nv ||
+      p->qpos_ld < p->nq)
+    return imn::set_error("imn_advance: bad extent or stride"), IMN_ERR_SHAPE;
+  if (nworld == 0) return IMN_OK;
+  const int64_t threads = (int64_t)nworld * p->njnt;
+  imn::advance_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p, qacc, qacc_ld, nworld);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return imn::set_error("imn_advance: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  return IMN_OK;
+}

@@ -44,6 +44,7 @@ class Option:
     disableflags: int = 0
     warn_overflow: int = 0
     graph_conditional: bool = True
+    timestep: Any = None  # float array, length 1 or nworld
 
 
 @dataclass
@@ -79,6 +80,19 @@ class Model:
     ntendon: int = 0
     geom_bodyid: Any = None
     nxn_geom_pair_filtered: Any = None
+    # integrator-facing tables (joints, damping, M's dense-position index, actuators)
+    nq: int = 0
+    njnt: int = 0
+    nu: int = 0
+    jnt_type: Any = None
+    jnt_dofadr: Any = None
+    jnt_qposadr: Any = None
+    dof_damping: Any = None
+    M_elemid: Any = None  # (nv, nv): CSR entry of (i, j) for j an ancestor of i or i itself, else -1
+
+    @property
+    def nactuator(self) -> int:
+        return self.nu
 
     @property
     def nM(self) -> int:
@@ -115,6 +129,15 @@ class Data:
     efc: Constraint
     solver_niter: Any
     overflow: Any
+    # integrator state and the actuator moments (mujoco-warp's per-world CSR); None
+    # when only the solve is used
+    qpos: Any = None
+    qvel: Any = None
+    time: Any = None
+    moment_rownnz: Any = None
+    moment_rowadr: Any = None
+    moment_colind: Any = None
+    actuator_moment: Any = None
 
 
 def ancestor_csr(dof_parentid: np.ndarray):
@@ -180,6 +203,7 @@ def put_model(
     warmstart: bool = True,
     nv_pad: int | None = None,
     body_of_dof=None,
+    timestep: float = 1.0 / 120.0,
 ) -> Model:
     """Host ``Model`` of a kinematic tree given one parent index per dof."""
     parent = np.asarray(dof_parentid, dtype=np.int32)
@@ -193,6 +217,7 @@ def put_model(
         ls_tolerance=np.array([ls_tolerance], np.float32),
         impratio_invsqrt=np.array([1.0], np.float32),
         disableflags=0 if warmstart else int(types.DisableBit.WARMSTART),
+        timestep=np.array([timestep], np.float32),
     )
     if body_of_dof is None:
         # one body per dof: a chain of single-dof bodies under the world body 0
@@ -209,7 +234,34 @@ def put_model(
             p = int(parent[dof])
             body_parentid[b] = int(body_of_dof[p]) if p >= 0 else 0
         body_dofnum[b] += 1
+    # joints: a body with 6 dofs hangs on a free joint, with 3 on a ball joint, any other
+    # count is that many hinges
+    jnt_type, jnt_dofadr, jnt_qposadr, nq = [], [], [], 0
+    for b in range(1, nbody):
+        first, count = int(body_dofadr[b]), int(body_dofnum[b])
+        if first < 0:
+            continue
+        kinds = [(types.JointType.FREE, 6, 7)] if count == 6 else (
+            [(types.JointType.BALL, 3, 4)] if count == 3 else [(types.JointType.HINGE, 1, 1)] * count)
+        for kind, ndof, npos in kinds:
+            jnt_type.append(int(kind)), jnt_dofadr.append(first), jnt_qposadr.append(nq)
+            first += ndof
+            nq += npos
+    order = np.argsort(jnt_dofadr, kind="stable")
+    jnt_type = np.asarray(jnt_type, np.int32)[order]
+    jnt_dofadr = np.asarray(jnt_dofadr, np.int32)[order]
+    sizes = np.where(jnt_type == int(types.JointType.FREE), 7, np.where(jnt_type == int(types.JointType.BALL), 4, 1))
+    jnt_qposadr = np.concatenate(([0], np.cumsum(sizes)[:-1])).astype(np.int32)
+    elemid = np.full((nv, nv), -1, np.int32)
+    elemid[rowidx, colind] = np.arange(colind.size, dtype=np.int32)
     return Model(
+        nq=int(nq),
+        njnt=int(jnt_type.size),
+        jnt_type=jnt_type,
+        jnt_dofadr=jnt_dofadr,
+        jnt_qposadr=jnt_qposadr,
+        dof_damping=np.zeros(nv, np.float32),
+        M_elemid=elemid,
         nv=nv,
         nv_pad=newton_nv_pad(nv) if nv_pad is None else int(nv_pad),
         opt=opt,

@@ -68,6 +68,13 @@ class OptimizedFwdPositionScratch:
     # single-tile factor/solve of M for models below the blocked kernel's dof count
     # that have no tree plan (the reference's per-tile kernels, :672-750, 793-838)
     tile_factor_solve: Any = None
+    # implicit-fast integrator buffers (mjw_step_optimized.py:470-480): M - h qDeriv in
+    # M's layout, the solved acceleration, the actuators' velocity gains
+    implicit_qderiv: Any = None
+    implicit_qacc: Any = None
+    implicit_actuator_vel: Any = None
+    advance_call: Any = None
+    pre_advance_modifier: Any = None
 
 
 def _constraint_rows_impossible(m: Any, ball_joint_limits: Sequence[Any] = ()) -> bool:
@@ -368,3 +375,99 @@ def fwd_acceleration_solve(m: Any, d: Any, scratch: OptimizedFwdPositionScratch,
         m, d, d.M, d.qacc_smooth, d.qfrc_smooth, scratch.dense_factor_solve,
         tree_factor_solve=scratch.tree_factor_solve, stream=stream,
     )
+
+
+# ---- the implicit-fast integrator's tail (mjw_step_optimized.py:5209-5297) --------------
+
+
+def attach_implicit_scratch(m: Any, d: Any, scratch: OptimizedFwdPositionScratch, device: Any = "cuda") -> None:
+    """Buffers of the implicit-fast tail: ``implicit_qderiv`` (nworld, nM),
+    ``implicit_qacc`` (nworld, nv) and, for actuated models, ``implicit_actuator_vel``
+    (nworld, nu)."""
+    import torch
+
+    nM = int(m.M_colind.shape[0])
+    scratch.implicit_qderiv = torch.zeros((d.nworld, nM), dtype=torch.float32, device=device)
+    scratch.implicit_qacc = torch.zeros((d.nworld, m.nv), dtype=torch.float32, device=device)
+    nu = int(getattr(m, "nu", 0) or 0)
+    scratch.implicit_actuator_vel = torch.zeros((d.nworld, nu), dtype=torch.float32, device=device) if nu else None
+
+
+def actuator_velocity_gain(m: Any, d: Any, out: Any) -> None:
+    """out[w, a] = d(actuator force)/d(actuator velocity): the ``vel`` buffer of upstream's
+    ``derivative._qderiv_actuator_passive_vel`` (call site mjw_step_optimized.py:4198-4225),
+    RESTATED from MuJoCo's actuator model for stateless actuators with fixed or affine
+    gain and bias: force = gain ctrl + bias with gain = g0 + g1 length + g2 velocity and
+    bias = b0 + b1 length + b2 velocity, hence g2 ctrl + b2.  Muscle and user types, and
+    actuators with activation dynamics, are refused."""
+    from . import types as T
+    from .arrays import as_torch, to_host
+
+    gain_t, bias_t, dyn_t = (to_host(getattr(m, n)) for n in ("actuator_gaintype", "actuator_biastype", "actuator_dyntype"))
+    if (dyn_t != int(T.DynType.NONE)).any():
+        raise RuntimeError("actuators with activation dynamics are outside this integrator tail")
+    if (gain_t > int(T.GainType.AFFINE)).any() or (bias_t > int(T.BiasType.AFFINE)).any():
+        raise RuntimeError("muscle and user actuators need upstream's velocity derivative")
+    g2 = as_torch(m.actuator_gainprm)[..., 2] * as_torch(m.actuator_gaintype).eq(int(T.GainType.AFFINE))
+    b2 = as_torch(m.actuator_biasprm)[..., 2] * as_torch(m.actuator_biastype).eq(int(T.BiasType.AFFINE))
+    as_torch(out).copy_(g2 * as_torch(d.ctrl) + b2)
+
+
+def deriv_smooth_vel_dense_actuator_centric(m: Any, d: Any, out: Any, scratch: OptimizedFwdPositionScratch,
+                                            stream=None) -> None:
+    """out = M - h qDeriv in M's layout (mjw_step_optimized.py:4172-4412): actuator term
+    from ``scratch.implicit_actuator_vel`` and the per-world moment rows, joint damping.
+    Models with tendons or fluid forces keep the upstream assembly."""
+    if int(getattr(m, "ntendon", 0) or 0) or bool(getattr(m, "has_fluid", False)):
+        raise RuntimeError("tendon damping and fluid terms are outside this assembly")
+    from .arrays import addr, elem_strides
+
+    ps = binding.implicit_struct(m, d, getattr(scratch, "implicit_actuator_vel", None))
+    rc = _lib.lib().imn_implicit_matrix(C.byref(ps), addr(d.M), elem_strides(d.M)[0], addr(out),
+                                        elem_strides(out)[0], int(d.nworld), _lib.current_stream_handle(stream))
+    _lib.check(rc, "imn_implicit_matrix")
+
+
+def _advance_with_scratch(m: Any, d: Any, qacc: Any, scratch: OptimizedFwdPositionScratch | None = None,
+                          qvel: Any = None, stream=None) -> None:
+    """qvel += h qacc, qpos moved with the new qvel, time += h
+    (mjw_step_optimized.py:4823-4847).  A ``pre_advance_modifier`` or a preallocated
+    ``advance_call`` on the scratch takes precedence, as in the reference."""
+    modifier = getattr(scratch, "pre_advance_modifier", None) if scratch is not None else None
+    if modifier is not None:
+        qacc, qvel = modifier.apply(m, d, qacc, qvel)
+    call = getattr(scratch, "advance_call", None) if scratch is not None else None
+    if call is not None:
+        call(m, d, qacc) if qvel is None else call(m, d, qacc, qvel)
+        return
+    if qvel is not None:
+        raise RuntimeError("an externally integrated qvel needs the caller's advance_call")
+    if int(getattr(m, "na", 0) or 0):
+        raise RuntimeError("actuator activations are outside this advance")
+    from .arrays import addr, elem_strides
+
+    ps = binding.advance_struct(m, d)
+    rc = _lib.lib().imn_advance(C.byref(ps), addr(qacc), elem_strides(qacc)[0], int(d.nworld),
+                                _lib.current_stream_handle(stream))
+    _lib.check(rc, "imn_advance")
+
+
+def implicitfast_integrate(m: Any, d: Any, scratch: OptimizedFwdPositionScratch, stream=None) -> None:
+    """The implicit-fast branch of ``_integrate`` (mjw_step_optimized.py:5241-5297):
+    (M - h qDeriv) x = efc.Ma through the tree L'DL or blocked dense kernel, then the
+    advance with x.  The free-body correction of mujoco-warp 3.16
+    (``_implicit_free_body_correction``, :3768-3780) is upstream-only and not applied."""
+    from . import binding as B
+
+    if int(m.opt.integrator) != int(B.types.IntegratorType.IMPLICITFAST):
+        raise NotImplementedError("only the implicit-fast integrator has a path here")
+    if scratch.implicit_qderiv is None or scratch.implicit_qacc is None:
+        raise RuntimeError("implicit-fast scratch is not attached (attach_implicit_scratch)")
+    if int(getattr(m, "nu", 0) or 0) and not (int(m.opt.disableflags) & B.upstream_constants()["disable_actuation"]):
+        actuator_velocity_gain(m, d, scratch.implicit_actuator_vel)
+    deriv_smooth_vel_dense_actuator_centric(m, d, scratch.implicit_qderiv, scratch, stream=stream)
+    _factor_solve_i_dense(
+        m, d, scratch.implicit_qderiv, scratch.implicit_qacc, d.efc.Ma, scratch.dense_factor_solve,
+        tree_factor_solve=scratch.tree_factor_solve, stream=stream,
+    )
+    _advance_with_scratch(m, d, scratch.implicit_qacc, scratch, stream=stream)

@@ -41,7 +41,35 @@ class IntegratorType(enum.IntEnum):
 
 
 class DisableBit(enum.IntFlag):
+    # mjtDisableBit; the adapter reads the live values when mujoco-warp is importable
+    DAMPER = 1 << 6
     WARMSTART = 1 << 8
+    ACTUATION = 1 << 10
+
+
+class JointType(enum.IntEnum):
+    FREE = 0
+    BALL = 1
+    SLIDE = 2
+    HINGE = 3
+
+
+class GainType(enum.IntEnum):
+    FIXED = 0
+    AFFINE = 1
+    MUSCLE = 2
+    USER = 3
+
+
+class BiasType(enum.IntEnum):
+    NONE = 0
+    AFFINE = 1
+    MUSCLE = 2
+    USER = 3
+
+
+class DynType(enum.IntEnum):
+    NONE = 0
 
 
 class OverflowType(enum.IntFlag):

@@ -71,6 +71,28 @@ def mul_m(m: Any, M, v, out) -> None:
                        v.strides[0] // 4, out.ctypes.data, out.strides[0] // 4, M.shape[0])
 
 
+def implicit_matrix(m: Any, d: Any, velocity_gain=None):
+    """A = M - h qDeriv of host containers; returns (nworld, nM)."""
+    import numpy as np
+
+    ps = binding.implicit_struct(m, d, velocity_gain)
+    out = np.zeros((d.nworld, m.M_colind.shape[0]), np.float32)
+    fn = lib().oracle_implicit_matrix
+    fn.restype = C.c_int
+    fn.argtypes = [C.POINTER(abi.ImnImplicit), abi.P, abi.I64, abi.P, abi.I64, C.c_int]
+    fn(C.byref(ps), d.M.ctypes.data, d.M.strides[0] // 4, out.ctypes.data, out.shape[1], d.nworld)
+    return out
+
+
+def advance(m: Any, d: Any, qacc) -> None:
+    """qvel, qpos, time of host Data advanced in place."""
+    ps = binding.advance_struct(m, d)
+    fn = lib().oracle_advance
+    fn.restype = C.c_int
+    fn.argtypes = [C.POINTER(abi.ImnAdvance), abi.P, abi.I64, C.c_int]
+    fn(C.byref(ps), qacc.ctypes.data, qacc.strides[0] // 4, d.nworld)
+
+
 def _i32(a):
     import numpy as np
 
