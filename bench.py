@@ -645,9 +645,12 @@ def main():
         del pinned
 
     # ---- work counters -> flop count of one batch -------------------------------------
-    runtime.solve_with_scratch(md, dev[0], scratch[0], use_optimized_kernel=True)
+    counting = runtime.make_optimized_fwd_position_scratch(md, dev[0], device, with_stats=True)
+    if groups is not None:
+        runtime.refresh_sparse_hessian(md, dev[0], counting, groups, device)
+    runtime.solve_with_scratch(md, dev[0], counting, use_optimized_kernel=True)
     torch.cuda.synchronize()
-    stats = scratch[0].solver_context.stats.cpu().numpy()
+    stats = counting.solver_context.stats.cpu().numpy()
     state0 = dev[0].efc.state.cpu().numpy()
     plan0 = getattr(scratch[0].solver_context, "sparse_hessian_plan", None)
     flops = algorithmic_flops(m_host, host[0][1], dev[0].solver_niter.cpu().numpy(), stats, state0, plan0)

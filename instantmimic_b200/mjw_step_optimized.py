@@ -28,7 +28,7 @@ class SolverContext:
     can report (call site mjw_step_optimized.py:2517).  The kernel keeps its
     working set on chip; these buffers receive the final values per world."""
 
-    def __init__(self, m: Any, d: Any, device: Any, *, with_matrices: bool = False):
+    def __init__(self, m: Any, d: Any, device: Any, *, with_matrices: bool = False, with_stats: bool = False):
         import torch
 
         W, nv, R, P = d.nworld, m.nv, d.njmax, m.nv_pad
@@ -46,10 +46,12 @@ class SolverContext:
         self.quad_changed_ids = i(W, R)
         self.quad_changed_count, self.state_changed_count = i(W), i(W)
         self.sparse_hessian_plan = None
-        # scratch of the fused kernel: worlds ordered by row count (no counterpart upstream)
-        self.world_order = i(W)
-        # work counters of each world's solve (passes, flips, factorisations, gradients)
-        self.stats = i(W, 4)
+        # scratch of the fused kernel: worlds ordered by row count, then the first position of
+        # each row-count bucket (no counterpart upstream)
+        self.world_order = i(W + 8)
+        # work counters of each world's solve (passes, flips, factorisations, gradients);
+        # counting costs the kernel ~9 %, so the array exists only on request
+        self.stats = i(W, 4) if with_stats else None
 
 
 @dataclass
@@ -177,6 +179,7 @@ def make_optimized_fwd_position_scratch(
     *,
     include_optimized_kernel_scratch: bool = True,
     with_matrices: bool = False,
+    with_stats: bool = False,
     ball_joint_limits: Sequence[Any] = (),
 ) -> OptimizedFwdPositionScratch:
     """Solver context, nsolving counter, the M-side factor/solve plans and the
@@ -187,7 +190,7 @@ def make_optimized_fwd_position_scratch(
 
     ctx = nsolving = None
     if d.njmax > 0 and m.nv > 0:
-        ctx = SolverContext(m, d, device, with_matrices=with_matrices)
+        ctx = SolverContext(m, d, device, with_matrices=with_matrices, with_stats=with_stats)
         newton_fusion.attach_scratch(m, d, ctx, device)
         nsolving = torch.zeros((1,), dtype=torch.int32, device=device)
     dense = indexed_factor.create_blocked_dense_factor_solve_scratch(m, d, device)

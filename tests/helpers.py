@@ -45,7 +45,7 @@ def run_cuda(m, d, device, matrices=True, use_optimized_kernel=True, ordered=Tru
 
     md = mjw_model.to_device(m, device)
     dd = mjw_model.to_device(copy.deepcopy(d), device)
-    scratch = runtime.make_optimized_fwd_position_scratch(md, dd, device, with_matrices=matrices)
+    scratch = runtime.make_optimized_fwd_position_scratch(md, dd, device, with_matrices=matrices, with_stats=matrices)
     if not ordered and scratch.solver_context is not None:
         scratch.solver_context.world_order = None
     runtime.solve_with_scratch(md, dd, scratch, use_optimized_kernel=use_optimized_kernel)
