@@ -208,19 +208,11 @@ typedef struct ImnCtx {
   int32_t* dof_union;          /* (W, nv + 1) */
   int32_t* nsolving;           /* (1): nworld minus the worlds that finished */
   const ImnSparsePlan* sparse_plan; /* HOST pointer or NULL (dense factor)    */
-  int32_t* world_order; /* optional scratch (W + 8): when given, imn_solve fills it with
-                         * the worlds ordered by descending row count (then the first
-                         * position of each of three row-count buckets) and hands the
+  int32_t* world_order; /* optional scratch (W): when given, imn_solve fills it with
+                         * the worlds ordered by descending row count and hands the
                          * worlds to the GPU in that order (long solves first, which
-                         * shortens the tail of the launch).  Batches of 4096 worlds or
-                         * more whose J stays in shared memory are then launched bucket
-                         * by bucket, each with the shared memory its rows need, the
-                         * buckets concurrently on two side streams of the library that
-                         * fork from and join `stream` (capturable; the side streams
-                         * are created by the first such call on a device, which must
-                         * come before any stream capture -- a capturing first call
-                         * falls back to one launch).  Results do not depend on any
-                         * of this                                                */
+                         * shortens the tail of the launch); results do not depend
+                         * on it                                                  */
   int32_t* stats;       /* optional (W, 4), no counterpart in the reference: work
                          * counters of each world's solve, from which the flop count
                          * of a batch is computed -- [0] row-evaluation passes of the

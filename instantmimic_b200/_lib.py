@@ -50,3 +50,25 @@ def current_stream_handle(stream=None) -> int:
     if isinstance(stream, int):
         return stream
     return int(stream.cuda_stream)
+
+
+_NVTX = None
+
+
+def nvtx(name: str):
+    """NVTX range around a C-ABI call when profiling is asked for (environment variable
+    ``IMN_NVTX=1``); otherwise a no-op context.  The reference wraps the same stages in
+    upstream's ``event_scope`` and names its kernels for profilers
+    (src/instantmimic/utils/mjw_step_optimized.py:2683, utils/warp_kernels.py:11-14)."""
+    global _NVTX
+    if _NVTX is None:
+        import contextlib
+        import os
+
+        if os.environ.get("IMN_NVTX", "0") not in ("", "0"):
+            import torch
+
+            _NVTX = torch.cuda.nvtx.range
+        else:
+            _NVTX = lambda name: contextlib.nullcontext()  # noqa: E731
+    return _NVTX(name)

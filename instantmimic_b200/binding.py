@@ -246,8 +246,8 @@ def ctx_struct(d_struct: abi.ImnData, ctx: Any, nsolving: Any, sparse_plan_struc
     if sparse_plan_struct is not None:
         s.sparse_plan = C.pointer(sparse_plan_struct)
     order = get("world_order")
-    if order is not None and length(order) < d_struct.nworld + 8:
-        raise ValueError("ctx.world_order must hold nworld + 8 int32")
+    if order is not None and length(order) < d_struct.nworld:
+        raise ValueError("ctx.world_order must hold one int32 per world")
     s.world_order = addr(order)
     stats = get("stats")
     if stats is not None and (tuple(shape(stats)) != (d_struct.nworld, 4) or elem_strides(stats) != (4, 1)):

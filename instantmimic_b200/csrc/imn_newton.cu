@@ -27,8 +27,6 @@
 // receives its terms.
 #include <stdio.h>
 
-#include <mutex>
-
 #include "imn_newton_factor.cuh"
 #include "imn_newton_ls.cuh"
 
@@ -52,9 +50,7 @@ __device__ unsigned long long g_prof[16];
 
 struct Geom {
   int nv, njmax, ldj, ldu, nM, bd;
-  int jrows;  // rows of J held in shared memory (the launch's row cap when resident, else 32)
-  int rows;   // most rows a world of this launch has (njmax, or its bucket's upper bound)
-  int bucket; // -1: the launch takes every world; else the row-count bucket it takes
+  int jrows;  // rows of J held in shared memory (njmax when resident, else 32)
   // offsets in 4-byte words; every region starts on a 16-byte boundary
   int oBar, oJ, oA, oVec, nv4, oM, oRowF, oRowI, r4, oUni, total;
   // polls a copy wait may take before the world gives up, and the failure-path test
@@ -70,20 +66,17 @@ static int g_withhold_copies = 0;
 
 static inline int up4(int n) { return (n + 3) & ~3; }
 
-static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident, const ImnSparsePlan* sp = nullptr,
-                      int rows = -1, int bucket = -1) {
+static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident, const ImnSparsePlan* sp = nullptr) {
   Geom g;
   g.nv = m.nv;
   g.njmax = d.njmax;
-  g.rows = rows < 0 ? d.njmax : rows;
-  g.bucket = bucket;
   g.ldj = (int)d.J_ld_row;
   g.ldu = up4(m.nv + 1);
   g.nM = m.nM;
   g.bd = m.nv_pad >= 64 ? 64 : 32;
-  g.jrows = resident ? g.rows : 32;
+  g.jrows = resident ? d.njmax : 32;
   g.nv4 = up4(m.nv);
-  g.r4 = up4(g.rows);
+  g.r4 = up4(d.njmax);
   int o = 0;
   g.oBar = o, o += 4;
   // a streamed tile may start up to three floats into its buffer and end on a 16-byte boundary
@@ -107,15 +100,7 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
                                              const ImnSparsePlan& sp) {
   extern __shared__ __align__(16) float smem[];
   const int lane = threadIdx.x;
-  int slot = blockIdx.x;
-  if (g.bucket >= 0) {
-    // the ordering pass left the first position of every bucket behind the order
-    const int* first = cx.world_order + d.nworld;
-    const int begin = first[g.bucket], end = first[g.bucket + 1];
-    if (slot >= end - begin) return;
-    slot += begin;
-  }
-  const int w = cx.world_order ? cx.world_order[slot] : slot;
+  const int w = cx.world_order ? cx.world_order[blockIdx.x] : (int)blockIdx.x;
   const int nv = g.nv, R = g.njmax, nv4 = g.nv4, r4 = g.r4;
 
   void* bar = smem + g.oBar;
@@ -468,25 +453,16 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
   }
 }
 
-// Two entry points over the same body: with J resident the compiler is left its own
-// register choice; the streamed variants hold more worlds per SM in shared memory than
+// Two entry points over the same body: with J resident shared memory, not registers,
+// limits the worlds per SM, so the compiler is told that one CTA per SM is enough and
+// plans without a register target of its own (no spills; measured 2 % faster than the
+// bound-less default); the streamed variants hold more worlds per SM in shared memory than
 // an uncapped register count would allow, so theirs is capped at 128 (16 warps per SM).
 // STATS compiles the work counters of ImnCtx.stats in: four more live values in a
 // kernel that is short of registers cost 9 % of its speed (measured), so the counting
 // variants run only for callers that pass the stats array.
-// MINB caps the registers so that MINB worlds fit an SM: launches over worlds with few
-// rows need little shared memory per world and are limited by registers instead.
-#ifndef IMN_MINB0
-#define IMN_MINB0 1
-#endif
-#ifndef IMN_MINB1
-#define IMN_MINB1 16
-#endif
-#ifndef IMN_MINB2
-#define IMN_MINB2 18
-#endif
-template <bool SPARSE, bool STATS, int MINB>
-__global__ void __launch_bounds__(32, MINB) newton_kernel_resident(const ImnModel m, const ImnData d, const ImnCtx cx,
+template <bool SPARSE, bool STATS>
+__global__ void __launch_bounds__(32, 1) newton_kernel_resident(const ImnModel m, const ImnData d, const ImnCtx cx,
                                                                    const Geom g, const ImnSparsePlan sp) {
   newton_world<true, SPARSE, STATS>(m, d, cx, g, sp);
 }
@@ -501,17 +477,10 @@ __global__ void fill_nsolving(int* nsolving, int value) { *nsolving = value; }
 // The hardware hands CTAs to SMs in index order and a world's solve time grows with
 // its row count, so worlds are launched by descending row count: the long solves
 // start first and the launch ends with short ones instead of a few stragglers.  One
-// CTA sorts the worlds into 63 classes of row count (counting sort through shared
+// CTA sorts the worlds into 64 classes of row count (counting sort through shared
 // memory); the order inside a class depends on atomics and is irrelevant: every
-// world is solved independently of which CTA takes it.  The scratch holds nworld + 8
-// ints: the order, then the first position of each row-count bucket and the total.
-#define IMN_ORDER_CLASSES 63
-#define IMN_BUCKETS 3
-// Row-count buckets: more than 3/4 of njmax, more than 1/2, the rest.  A launch over one
-// bucket sizes its shared memory by the bucket's upper bound.
-__host__ __device__ inline int bucket_rows(int njmax, int b) {
-  return b == 0 ? njmax : (b == 1 ? (3 * njmax) / 4 : njmax / 2);
-}
+// world is solved independently of which CTA takes it.
+#define IMN_ORDER_CLASSES 64
 __global__ void __launch_bounds__(1024) order_worlds_kernel(const int* __restrict__ nefc, int njmax, int nworld,
                                                             int* __restrict__ order, int* nsolving) {
   __shared__ int count[IMN_ORDER_CLASSES], start[IMN_ORDER_CLASSES];
@@ -519,24 +488,16 @@ __global__ void __launch_bounds__(1024) order_worlds_kernel(const int* __restric
   if (tid < IMN_ORDER_CLASSES) count[tid] = 0;
   if (tid == 0 && nsolving) *nsolving = nworld;
   __syncthreads();
-  // 21 classes per bucket, the largest row counts first; no class straddles a bucket
+  // class 0 holds the largest row counts
   auto cls = [&](int n) {
     n = min(max(n, 0), njmax);
-    const int b = n > bucket_rows(njmax, 1) ? 0 : (n > bucket_rows(njmax, 2) ? 1 : 2);
-    const int hi = bucket_rows(njmax, b), lo = b == 2 ? -1 : bucket_rows(njmax, b + 1);
-    const int per = IMN_ORDER_CLASSES / IMN_BUCKETS;
-    return b * per + (int)(((long long)(hi - n) * per) / (hi - lo));
+    return (int)(((long long)(njmax - n) * IMN_ORDER_CLASSES) / (njmax + 1));
   };
   for (int w = tid; w < nworld; w += blockDim.x) atomicAdd(&count[cls(nefc[w])], 1);
   __syncthreads();
   if (tid == 0) {
     int run = 0;
-    for (int c = 0; c < IMN_ORDER_CLASSES; ++c) {
-      // first position of each bucket, then the total, behind the order
-      if (c % (IMN_ORDER_CLASSES / IMN_BUCKETS) == 0) order[nworld + c / (IMN_ORDER_CLASSES / IMN_BUCKETS)] = run;
-      start[c] = run, run += count[c];
-    }
-    order[nworld + IMN_BUCKETS] = run;
+    for (int c = 0; c < IMN_ORDER_CLASSES; ++c) start[c] = run, run += count[c];
   }
   __syncthreads();
   for (int w = tid; w < nworld; w += blockDim.x) order[atomicAdd(&start[cls(nefc[w])], 1)] = w;
@@ -594,44 +555,6 @@ static int validate(const ImnModel* m, const ImnData* d, const ImnCtx* cx) {
 static int worlds_per_sm(int bytes, int cap = 16) {
   const int n = (228 * 1024) / (bytes + 1024);
   return n < cap ? n : cap;
-}
-
-// Batches of at least this many worlds are launched bucket by bucket.
-static const int kBucketMinWorlds = 4096;
-
-// Side streams of the bucketed launch, per device: the bucket of the longest solves
-// runs on the caller's stream, the other two on these, forked and joined with events
-// (all of it can be recorded into a CUDA graph).  Created on the first bucketed launch
-// of a device, which therefore must not happen during stream capture: a launch that
-// finds its stream capturing before the streams exist takes all worlds in one launch.
-struct SideStreams {
-  cudaStream_t stream[IMN_BUCKETS - 1];
-  cudaEvent_t fork, join[IMN_BUCKETS - 1];
-  bool ready;
-};
-static SideStreams g_side[64];
-static std::mutex g_side_mutex;
-
-static SideStreams* side_streams(cudaStream_t stream) {
-  int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
-  SideStreams& a = g_side[dev];
-  if (a.ready) return &a;
-  cudaStreamCaptureStatus status = cudaStreamCaptureStatusNone;
-  if (cudaStreamIsCapturing(stream, &status) != cudaSuccess || status != cudaStreamCaptureStatusNone) {
-    cudaGetLastError();
-    return nullptr;
-  }
-  bool ok = cudaEventCreateWithFlags(&a.fork, cudaEventDisableTiming) == cudaSuccess;
-  for (int k = 0; k < IMN_BUCKETS - 1 && ok; ++k)
-    ok = cudaStreamCreateWithFlags(&a.stream[k], cudaStreamNonBlocking) == cudaSuccess &&
-         cudaEventCreateWithFlags(&a.join[k], cudaEventDisableTiming) == cudaSuccess;
-  if (!ok) {
-    cudaGetLastError();
-    return nullptr;
-  }
-  a.ready = true;
-  return &a;
 }
 
 // J resident in shared memory or streamed through the 32-row tile.  Resident J is
@@ -717,49 +640,11 @@ extern "C" int imn_solve(const ImnModel* m, const ImnData* d, const ImnCtx* cx, 
   else if (cx->nsolving)
     imn::fill_nsolving<<<1, 1, 0, stream>>>(cx->nsolving, d->nworld);
 
-  // Large batches with J resident: one launch per row-count bucket, each with the
-  // shared memory its bucket needs, so that worlds with few rows do not pay for njmax
-  // rows and more of them share an SM.  The buckets run concurrently: the first (longest
-  // solves) on the caller's stream, the others on side streams forked after the
-  // ordering pass and joined before the call's work ends.
-  imn::Geom gb[IMN_BUCKETS];
-  bool bucketed = res && cx->world_order && !cx->stats && d->nworld >= imn::kBucketMinWorlds;
-  if (bucketed) {
-    for (int b = 0; b < IMN_BUCKETS; ++b)
-      gb[b] = imn::make_geom(*m, *d, true, cx->sparse_plan, imn::bucket_rows(d->njmax, b), b);
-    bucketed = imn::worlds_per_sm(gb[2].total * 4, IMN_MINB2) > imn::worlds_per_sm(gb[0].total * 4);
-  }
-  imn::SideStreams* side = bucketed ? imn::side_streams(stream) : nullptr;
-  if (side) {
-    const Kernel kerns[IMN_BUCKETS] = {
-        sparse ? (Kernel)imn::newton_kernel_resident<true, false, IMN_MINB0> : (Kernel)imn::newton_kernel_resident<false, false, IMN_MINB0>,
-        sparse ? (Kernel)imn::newton_kernel_resident<true, false, IMN_MINB1> : (Kernel)imn::newton_kernel_resident<false, false, IMN_MINB1>,
-        sparse ? (Kernel)imn::newton_kernel_resident<true, false, IMN_MINB2> : (Kernel)imn::newton_kernel_resident<false, false, IMN_MINB2>,
-    };
-    for (int b = 0; b < IMN_BUCKETS; ++b) {
-      const cudaError_t e = prepare(kerns[b], gb[b].total * 4);
-      if (e != cudaSuccess)
-        return imn::set_error("imn_solve: cudaFuncSetAttribute: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
-    }
-    std::lock_guard<std::mutex> lock(imn::g_side_mutex);  // a wait binds to the record before it
-    cudaError_t e = cudaEventRecord(side->fork, stream);
-    kerns[0]<<<d->nworld, 32, gb[0].total * 4, stream>>>(*m, *d, *cx, gb[0], sp);
-    for (int b = 1; b < IMN_BUCKETS && e == cudaSuccess; ++b) {
-      cudaStream_t s2 = side->stream[b - 1];
-      e = cudaStreamWaitEvent(s2, side->fork, 0);
-      if (e == cudaSuccess) kerns[b]<<<d->nworld, 32, gb[b].total * 4, s2>>>(*m, *d, *cx, gb[b], sp);
-      if (e == cudaSuccess) e = cudaEventRecord(side->join[b - 1], s2);
-      if (e == cudaSuccess) e = cudaStreamWaitEvent(stream, side->join[b - 1], 0);
-    }
-    if (e == cudaSuccess) e = cudaGetLastError();
-    if (e != cudaSuccess) return imn::set_error("imn_solve: bucketed launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
-    return IMN_OK;
-  }
-  Kernel kern = sparse ? (res ? (Kernel)imn::newton_kernel_resident<true, false, IMN_MINB0> : (Kernel)imn::newton_kernel_streamed<true, false>)
-                       : (res ? (Kernel)imn::newton_kernel_resident<false, false, IMN_MINB0> : (Kernel)imn::newton_kernel_streamed<false, false>);
+  Kernel kern = sparse ? (res ? (Kernel)imn::newton_kernel_resident<true, false> : (Kernel)imn::newton_kernel_streamed<true, false>)
+                       : (res ? (Kernel)imn::newton_kernel_resident<false, false> : (Kernel)imn::newton_kernel_streamed<false, false>);
   if (cx->stats)
-    kern = sparse ? (res ? (Kernel)imn::newton_kernel_resident<true, true, IMN_MINB0> : (Kernel)imn::newton_kernel_streamed<true, true>)
-                  : (res ? (Kernel)imn::newton_kernel_resident<false, true, IMN_MINB0> : (Kernel)imn::newton_kernel_streamed<false, true>);
+    kern = sparse ? (res ? (Kernel)imn::newton_kernel_resident<true, true> : (Kernel)imn::newton_kernel_streamed<true, true>)
+                  : (res ? (Kernel)imn::newton_kernel_resident<false, true> : (Kernel)imn::newton_kernel_streamed<false, true>);
   {
     const cudaError_t e = prepare(kern, bytes);
     if (e != cudaSuccess)

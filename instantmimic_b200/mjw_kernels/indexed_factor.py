@@ -109,14 +109,19 @@ def _launch(scratch, M, y, U, x, active, nworld, rhs_count, mode, stream):
     for name, a in (("y", y), ("x", x), ("U", U)):
         if not is_contiguous(a):
             raise ValueError(f"blocked dense factor/solve needs a contiguous {name}")
-    rc = _lib.lib().imn_blocked_dense_factor_solve(
+    with _lib.nvtx("imn_blocked_dense_factor_solve"):
+        rc = _launch_call(scratch, M, y, U, x, active, nworld, rhs_count, mode, stream)
+    _lib.check(rc, "imn_blocked_dense_factor_solve")
+
+
+def _launch_call(scratch, M, y, U, x, active, nworld, rhs_count, mode, stream):
+    return _lib.lib().imn_blocked_dense_factor_solve(
         C.byref(scratch.struct),
         addr(M) if M is not None else None,
         elem_strides(M)[0] if M is not None else 0,
         addr(y), addr(U), addr(x), addr(active), int(nworld), int(rhs_count), int(mode),
         _lib.current_stream_handle(stream),
     )
-    _lib.check(rc, "imn_blocked_dense_factor_solve")
 
 
 def blocked_dense_factor_solve(

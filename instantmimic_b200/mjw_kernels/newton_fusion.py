@@ -123,9 +123,10 @@ class SolveCall:
         return info
 
     def __call__(self, stream=None) -> None:
-        rc = _lib.lib().imn_solve(
-            C.byref(self.m), C.byref(self.d), C.byref(self.c), _lib.current_stream_handle(stream)
-        )
+        with _lib.nvtx("imn_solve"):
+            rc = _lib.lib().imn_solve(
+                C.byref(self.m), C.byref(self.d), C.byref(self.c), _lib.current_stream_handle(stream)
+            )
         _lib.check(rc, "imn_solve")
 
 

@@ -393,10 +393,11 @@ def tree_factor_solve(scratch: TreeFactorSolveScratch, M: Any, x: Any, y: Any, s
             raise ValueError("tree_factor_solve needs rows of contiguous floats")
     nworld = int(M.shape[0])
     if scratch.kernel is not None:
-        rc = _lib.lib().imn_tree_ldl_compiled_solve(
-            scratch.kernel.handle, addr(M), elem_strides(M)[0], addr(y), elem_strides(y)[0], addr(x),
-            elem_strides(x)[0], nworld, _lib.current_stream_handle(stream),
-        )
+        with _lib.nvtx("imn_tree_ldl_compiled_solve"):
+            rc = _lib.lib().imn_tree_ldl_compiled_solve(
+                scratch.kernel.handle, addr(M), elem_strides(M)[0], addr(y), elem_strides(y)[0], addr(x),
+                elem_strides(x)[0], nworld, _lib.current_stream_handle(stream),
+            )
         _lib.check(rc, "imn_tree_ldl_compiled_solve")
         return
     rc = _lib.lib().imn_tree_ldl_solve(

@@ -89,6 +89,11 @@ class Model:
     jnt_qposadr: Any = None
     dof_damping: Any = None
     M_elemid: Any = None  # (nv, nv): CSR entry of (i, j) for j an ancestor of i or i itself, else -1
+    actuator_gaintype: Any = None
+    actuator_biastype: Any = None
+    actuator_dyntype: Any = None
+    actuator_gainprm: Any = None  # (nu, 10)
+    actuator_biasprm: Any = None  # (nu, 10)
 
     @property
     def nactuator(self) -> int:
@@ -138,6 +143,7 @@ class Data:
     moment_rowadr: Any = None
     moment_colind: Any = None
     actuator_moment: Any = None
+    ctrl: Any = None
 
 
 def ancestor_csr(dof_parentid: np.ndarray):

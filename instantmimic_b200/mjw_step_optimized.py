@@ -46,9 +46,8 @@ class SolverContext:
         self.quad_changed_ids = i(W, R)
         self.quad_changed_count, self.state_changed_count = i(W), i(W)
         self.sparse_hessian_plan = None
-        # scratch of the fused kernel: worlds ordered by row count, then the first position of
-        # each row-count bucket (no counterpart upstream)
-        self.world_order = i(W + 8)
+        # scratch of the fused kernel: worlds ordered by row count (no counterpart upstream)
+        self.world_order = i(W)
         # work counters of each world's solve (passes, flips, factorisations, gradients);
         # counting costs the kernel ~9 %, so the array exists only on request
         self.stats = i(W, 4) if with_stats else None
@@ -225,7 +224,8 @@ def _solver_compact_enabled(m: Any) -> bool:
 def _rowless_handoff(m: Any, d: Any, stream=None) -> None:
     ms = binding.model_struct(m)
     ds = binding.data_struct(m, d)
-    rc = _lib.lib().imn_rowless_handoff(C.byref(ms), C.byref(ds), _lib.current_stream_handle(stream))
+    with _lib.nvtx("imn_rowless_handoff"):
+        rc = _lib.lib().imn_rowless_handoff(C.byref(ms), C.byref(ds), _lib.current_stream_handle(stream))
     _lib.check(rc, "imn_rowless_handoff")
 
 
