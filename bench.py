@@ -60,6 +60,8 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--no-aux", action="store_true")
+    p.add_argument("--no-strong", action="store_true")
+    p.add_argument("--no-graph", action="store_true")
     p.add_argument("--aux-nworld", type=int, default=65536, help="worlds of the M-side kernel timings")
     p.add_argument("--sparse-hessian", default="on", choices=["on", "off"],
                    help="install the static-pattern sparse Hessian plan (single-body contact groups)")
@@ -550,13 +552,15 @@ def main():
     niter = np.concatenate([dd.solver_niter.cpu().numpy() for dd in dev])
 
     # the same steps as one CUDA-graph replay (the reference's step runs inside a graph)
-    graph_steps = min(args.steps, 4 * nb)
-    graph = graph_of(torch, step, graph_steps)
-    graph_ms = timer.max_over_ranks([time_graph(torch, graph, graph_steps)])[0]
+    graph_ms = None
+    if not args.no_graph:
+        graph_steps = min(args.steps, 4 * nb)
+        graph = graph_of(torch, step, graph_steps)
+        graph_ms = timer.max_over_ranks([time_graph(torch, graph, graph_steps)])[0]
 
     # ---- strong scaling: a fixed total of worlds divided over the GPUs --------------
     strong = None
-    if args.nworld >= STRONG_TOTAL_WORLDS // world and STRONG_TOTAL_WORLDS % world == 0:
+    if not args.no_strong and args.nworld >= STRONG_TOTAL_WORLDS // world and STRONG_TOTAL_WORLDS % world == 0:
         Ws = STRONG_TOTAL_WORLDS // world
         sdev = [mjw_model.slice_worlds(dd, 0, Ws) for dd in dev]
         ssc = [runtime.make_optimized_fwd_position_scratch(md, dd, device) for dd in sdev]

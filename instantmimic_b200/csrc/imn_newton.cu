@@ -461,8 +461,11 @@ __device__ __forceinline__ void newton_world(const ImnModel& m, const ImnData& d
 // STATS compiles the work counters of ImnCtx.stats in: four more live values in a
 // kernel that is short of registers cost 9 % of its speed (measured), so the counting
 // variants run only for callers that pass the stats array.
+#ifndef IMN_RESIDENT_MIN_BLOCKS
+#define IMN_RESIDENT_MIN_BLOCKS 1
+#endif
 template <bool SPARSE, bool STATS>
-__global__ void __launch_bounds__(32, 1) newton_kernel_resident(const ImnModel m, const ImnData d, const ImnCtx cx,
+__global__ void __launch_bounds__(32, IMN_RESIDENT_MIN_BLOCKS) newton_kernel_resident(const ImnModel m, const ImnData d, const ImnCtx cx,
                                                                    const Geom g, const ImnSparsePlan sp) {
   newton_world<true, SPARSE, STATS>(m, d, cx, g, sp);
 }
