@@ -463,7 +463,8 @@ def run_sweep(args, torch, timer, world, rank, device, peak):
                 dd.efc = copy.copy(dev_arrays.efc)
                 for name in ("J", "D", "aref", "frictionloss", "force", "state", "Ma"):
                     setattr(dd.efc, name, rep(getattr(dev_arrays.efc, name)))
-                scratch = runtime.make_optimized_fwd_position_scratch(md, dd, device)
+                scratch = runtime.make_optimized_fwd_position_scratch(md, dd, device,
+                                                                      include_optimized_kernel_scratch=False)
                 step = lambda k: runtime.solve_with_scratch(md, dd, scratch, use_optimized_kernel=True)  # noqa: E731
                 for _ in range(3):
                     step(0)
