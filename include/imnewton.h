@@ -285,6 +285,49 @@ typedef struct ImnAdvance {
   float* time;                /* (W) in/out, may be NULL                         */
 } ImnAdvance;
 
+/* Directional ball-joint limits (ball_limits.py:205-318 BallLimitBuffers /
+ * make_ball_limit_buffers) and the constraint-row arrays of mujoco_warp `Data` they are
+ * appended to (ball_limits.py:259-281).  Dense Jacobian only. */
+typedef struct ImnBallLimits {
+  int32_t njoint;              /* limited ball joints                             */
+  int32_t nv, njmax;
+  int32_t refsafe;             /* !(opt.disableflags & REFSAFE)                   */
+  int32_t limit_joint_type;    /* types.ConstraintType.LIMIT_JOINT                */
+  float timestep;
+  const int32_t* qadr;         /* (njoint) qpos address of the joint's quaternion */
+  const int32_t* dadr;         /* (njoint) first dof                              */
+  const int32_t* joint;        /* (njoint) joint id (efc.id)                      */
+  const float* neutral;        /* (njoint, 4) wxyz                                */
+  const float* frame;          /* (njoint, 4) wxyz                                */
+  const float* swing;          /* (njoint, 4) 1 / tan^2(angle / 2): +x, +y, -x, -y */
+  const float* twist;          /* (njoint, 2) lower, upper                        */
+  const float* minimum_h;      /* (njoint)                                        */
+  const float* margin;         /* (njoint)                                        */
+  const float* solref;         /* (njoint, 2)                                     */
+  const float* solimp;         /* (njoint, 5)                                     */
+  const float* invweight;      /* (n_invweight, nv) dof_invweight0, world % n     */
+  int32_t n_invweight;
+  const float* qpos;           /* (W, nq) */
+  int64_t qpos_ld;
+  const float* qvel;           /* (W, nv) */
+  int64_t qvel_ld;
+  int32_t* nefc;               /* (W) in/out */
+  int32_t* nl;                 /* (W) in/out, may be NULL */
+  int32_t* efc_type;           /* (W, R) stride efc_ld */
+  int32_t* efc_id;
+  float* efc_J;                /* (W, R, >= nv) */
+  int64_t J_ld_world, J_ld_row;
+  float* efc_pos;
+  float* efc_margin;
+  float* efc_D;
+  float* efc_vel;
+  float* efc_aref;
+  float* efc_frictionloss;
+  int64_t efc_ld;
+  int32_t* overflow;           /* (W) rows that found no room, may be NULL        */
+  int32_t* singular;           /* (W) candidates at the chart's antipode, may be NULL */
+} ImnBallLimits;
+
 /* ---- entry points ------------------------------------------------------- */
 
 /* Replaces solve_with_scratch's monolithic fused branch:
@@ -401,6 +444,11 @@ int imn_implicit_matrix(const ImnImplicit* p, const float* M, int64_t M_ld, floa
  * quaternions); time += h. */
 int imn_advance(const ImnAdvance* p, const float* qacc, int64_t qacc_ld, int32_t nworld,
                 void* stream);
+
+/* Replaces BallLimitBuffers.launch (ball_limits.py:221-282, kernel :36-203): appends the
+ * violated directional limit rows of every limited ball joint to each world's rows, in
+ * (joint, kind) order. */
+int imn_ball_limit_rows(const ImnBallLimits* p, int32_t nworld, void* stream);
 
 /* Uploads a sparse plan (sparse_hessian.build_plan's tables, sparse_hessian.py:229-402,
  * which the reference bakes into generated source instead).  `host_tables` holds HOST

@@ -198,6 +198,18 @@ class ImnAdvance(C.Structure):
     ]
 
 
+class ImnBallLimits(C.Structure):
+    _fields_ = [
+        ("njoint", I32), ("nv", I32), ("njmax", I32), ("refsafe", I32), ("limit_joint_type", I32),
+        ("timestep", C.c_float), ("qadr", P), ("dadr", P), ("joint", P), ("neutral", P), ("frame", P), ("swing", P),
+        ("twist", P), ("minimum_h", P), ("margin", P), ("solref", P), ("solimp", P), ("invweight", P),
+        ("n_invweight", I32), ("qpos", P), ("qpos_ld", I64), ("qvel", P), ("qvel_ld", I64), ("nefc", P), ("nl", P),
+        ("efc_type", P), ("efc_id", P), ("efc_J", P), ("J_ld_world", I64), ("J_ld_row", I64), ("efc_pos", P),
+        ("efc_margin", P), ("efc_D", P), ("efc_vel", P), ("efc_aref", P), ("efc_frictionloss", P), ("efc_ld", I64),
+        ("overflow", P), ("singular", P),
+    ]
+
+
 class ImnLaunchInfo(C.Structure):
     _fields_ = [
         ("world_threads", I32),
@@ -235,6 +247,7 @@ SYMBOLS = {
     ),
     "imn_implicit_matrix": (C.c_int, [C.POINTER(ImnImplicit), P, I64, P, I64, I32, P]),
     "imn_advance": (C.c_int, [C.POINTER(ImnAdvance), P, I64, I32, P]),
+    "imn_ball_limit_rows": (C.c_int, [C.POINTER(ImnBallLimits), I32, P]),
     "imn_sparse_plan_create": (C.c_int, [C.POINTER(ImnSparsePlan), C.POINTER(C.POINTER(ImnSparsePlan))]),
     "imn_sparse_plan_destroy": (None, [C.POINTER(ImnSparsePlan)]),
     "imn_launch_info": (

@@ -49,6 +49,8 @@ def upstream_constants(module_types: Any = None, module_solver: Any = None) -> d
         "disable_warmstart": member("DisableBit", "WARMSTART", types.DisableBit.WARMSTART),
         "disable_damper": member("DisableBit", "DAMPER", types.DisableBit.DAMPER),
         "disable_actuation": member("DisableBit", "ACTUATION", types.DisableBit.ACTUATION),
+        "disable_refsafe": member("DisableBit", "REFSAFE", types.DisableBit.REFSAFE),
+        "constraint_limit_joint": member("ConstraintType", "LIMIT_JOINT", types.ConstraintType.LIMIT_JOINT),
         "solver_newton": member("SolverType", "NEWTON", types.SolverType.NEWTON),
         "cone_pyramidal": member("ConeType", "PYRAMIDAL", types.ConeType.PYRAMIDAL),
         "integrator_discrete": member("IntegratorType", "DISCRETE", types.IntegratorType.DISCRETE),

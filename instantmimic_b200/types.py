@@ -45,6 +45,18 @@ class DisableBit(enum.IntFlag):
     DAMPER = 1 << 6
     WARMSTART = 1 << 8
     ACTUATION = 1 << 10
+    REFSAFE = 1 << 11
+
+
+class ConstraintType(enum.IntEnum):
+    EQUALITY = 0
+    FRICTION_DOF = 1
+    FRICTION_TENDON = 2
+    LIMIT_JOINT = 3
+    LIMIT_TENDON = 4
+    CONTACT_FRICTIONLESS = 5
+    CONTACT_PYRAMIDAL = 6
+    CONTACT_ELLIPTIC = 7
 
 
 class JointType(enum.IntEnum):

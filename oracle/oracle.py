@@ -93,6 +93,17 @@ def advance(m: Any, d: Any, qacc) -> None:
     fn(C.byref(ps), qacc.ctypes.data, qacc.strides[0] // 4, d.nworld)
 
 
+def ball_limit_rows(tables: dict, njoint: int, m: Any, d: Any, overflow, singular) -> None:
+    """Append the directional ball-limit rows to host ``Data`` in place."""
+    from instantmimic_b200.mjw_kernels import ball_limits
+
+    ps = ball_limits.rows_struct(tables, njoint, m, d, overflow, singular)
+    fn = lib().oracle_ball_limit_rows
+    fn.restype = C.c_int
+    fn.argtypes = [C.POINTER(abi.ImnBallLimits), C.c_int]
+    fn(C.byref(ps), d.nworld)
+
+
 def _i32(a):
     import numpy as np
 

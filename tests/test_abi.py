@@ -33,7 +33,7 @@ def test_library_exports_every_declared_symbol():
 
 def test_ctypes_structs_match_the_compiler(tmp_path):
     structs = ["ImnModel", "ImnData", "ImnCtx", "ImnSparsePlan", "ImnTreePlan", "ImnBlockedPlan", "ImnLaunchInfo",
-               "ImnImplicit", "ImnAdvance"]
+               "ImnImplicit", "ImnAdvance", "ImnBallLimits"]
     src = tmp_path / "sizes.c"
     body = "".join(f'  printf("{s} %zu\\n", sizeof({s}));\n' for s in structs)
     src.write_text(f'#include <stdio.h>\n#include "{HEADER}"\nint main(void) {{\n{body}  return 0;\n}}\n')
