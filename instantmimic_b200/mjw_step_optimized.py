@@ -76,6 +76,8 @@ class OptimizedFwdPositionScratch:
     implicit_actuator_vel: Any = None
     advance_call: Any = None
     pre_advance_modifier: Any = None
+    # directional ball-joint limit rows (mjw_step_optimized.py:2241-2249)
+    ball_limit_buffers: Any = None
 
 
 def _constraint_rows_impossible(m: Any, ball_joint_limits: Sequence[Any] = ()) -> bool:
@@ -199,7 +201,13 @@ def make_optimized_fwd_position_scratch(
         # below the blocked kernel's dof count the reference factors M tile by tile; the
         # same kernel does it here with one 16- or 32-wide tile per world
         tile = indexed_factor.create_blocked_dense_factor_solve_scratch(m, d, device, minimum_nv=1)
+    ball_buffers = None
+    if ball_joint_limits and all(hasattr(d.efc, n) for n in ("pos", "margin", "vel", "type", "id")):
+        from .mjw_kernels import ball_limits
+
+        ball_buffers = ball_limits.make_ball_limit_buffers(ball_joint_limits, m, d, device)
     scratch = OptimizedFwdPositionScratch(
+        ball_limit_buffers=ball_buffers,
         solver_context=ctx,
         solver_nsolving=nsolving,
         constraint_free=_constraint_rows_impossible(m, ball_joint_limits),
@@ -378,6 +386,20 @@ def fwd_acceleration_solve(m: Any, d: Any, scratch: OptimizedFwdPositionScratch,
         m, d, d.M, d.qacc_smooth, d.qfrc_smooth, scratch.dense_factor_solve,
         tree_factor_solve=scratch.tree_factor_solve, stream=stream,
     )
+
+
+def append_ball_limit_rows(m: Any, d: Any, scratch: OptimizedFwdPositionScratch, stream=None) -> None:
+    """The directional ball-limit rows of this step, appended to the rows the constraint
+    stage has produced so far: what the reference's ``_BallLimitConstraintCall`` does
+    right after upstream's native ball-limit launch (mjw_step_optimized.py:355-388) --
+    counters cleared, then ``BallLimitBuffers.launch``.  The upstream constraint stage
+    itself is not part of this library; the caller invokes this at the same point."""
+    buffers = scratch.ball_limit_buffers
+    if buffers is None:
+        return
+    buffers.overflow.zero_()
+    buffers.singular.zero_()
+    buffers.launch(m, d, stream=stream)
 
 
 # ---- the implicit-fast integrator's tail (mjw_step_optimized.py:5209-5297) --------------
