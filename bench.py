@@ -433,6 +433,66 @@ SWEEP_NEFC = (32, 128, 512)
 SWEEP_WORLDS = (4096, 16384, 65536)
 
 
+def stage_kernels(args, torch, md, m_host, device, timed):
+    """The stages either side of the solve at the batch of the M-side timings: the
+    implicit-fast tail (A = M - h qDeriv, advance) and the body-tree stages (com_vel,
+    crb, rne).  Random device-resident state of the workload's shapes; one position
+    servo per actuated dof."""
+    from dataclasses import replace
+    from types import SimpleNamespace
+
+    import numpy as np
+
+    from instantmimic_b200 import mjw_step_optimized as runtime
+    from instantmimic_b200.mjw_kernels import tree_fusion, velocity_fusion
+
+    W, nv, nM, nq = args.aux_nworld, m_host.nv, m_host.nM, m_host.nq
+    nbody = int(np.asarray(m_host.body_parentid).size)
+    nu = max(nv - 6, 1)
+    gen = torch.Generator(device=device).manual_seed(11)
+    rnd = lambda *s: torch.randn(*s, device=device, generator=gen)  # noqa: E731
+    dofs = torch.arange(nv - nu, nv, device=device, dtype=torch.int32)
+
+    def batch():
+        qpos = rnd(W, nq)
+        d = SimpleNamespace(
+            nworld=W, M=rnd(W, nM), qvel=rnd(W, nv), qpos=qpos, time=torch.zeros(W, device=device),
+            moment_rownnz=torch.ones(W, nu, dtype=torch.int32, device=device),
+            moment_rowadr=torch.arange(nu, dtype=torch.int32, device=device).repeat(W, 1),
+            moment_colind=dofs.repeat(W, 1).contiguous(), actuator_moment=torch.ones(W, nu, device=device),
+            cinert=rnd(W, nbody, 10), crb=torch.empty(W, nbody, 10, device=device), cdof=rnd(W, nv, 6),
+            cdof_dot=rnd(W, nv, 6), cvel=rnd(W, nbody, 6), cacc=torch.empty(W, nbody, 6, device=device),
+            cfrc_int=torch.empty(W, nbody, 6, device=device), qfrc_bias=torch.empty(W, nv, device=device))
+        return d
+
+    big = [batch(), batch()]
+    qacc = 1e-3 * rnd(W, nv)
+    out = torch.empty(W, nM, device=device)
+    mm = replace(md)
+    mm.nu = nu
+    mm.dof_damping = torch.rand(nv, device=device)
+    sc = SimpleNamespace(implicit_actuator_vel=-10.0 * torch.rand(W, nu, device=device), advance_call=None,
+                         pre_advance_modifier=None)
+    tree = tree_fusion.create_tree_reduction_scratch(mm, deterministic=True)
+    res = {}
+
+    def put(name, t, floats_per_world):
+        alg = 4.0 * W * floats_per_world
+        res[name] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg}
+
+    t = timed(lambda k: runtime.deriv_smooth_vel_dense_actuator_centric(mm, big[k % 2], out, sc))
+    put("implicit_matrix_kernel", t, 2 * nM + 5 * nu)
+    t = timed(lambda k: runtime._advance_with_scratch(mm, big[k % 2], qacc, sc))
+    put("advance_kernel", t, 3 * nv + 2 * nq + 2)
+    t = timed(lambda k: velocity_fusion.com_vel(mm, big[k % 2], tree))
+    put("com_vel_kernel", t, nv + 12 * nv + 6 * nbody)
+    t = timed(lambda k: tree_fusion.crb(mm, big[k % 2], tree))
+    put("crb_kernel", t, 20 * nbody + 6 * nv + nM)
+    t = timed(lambda k: tree_fusion.rne(mm, big[k % 2], tree))
+    put("rne_kernel", t, 10 * nbody + 6 * nbody + 13 * nv + 12 * nbody + nv)
+    return res
+
+
 def run_sweep(args, torch, timer, world, rank, device, peak):
     """The isolated sweep: nv x nefc x batch, generic rows on tree-ancestor patterns,
     dense factor; worlds sharded over the ranks.  Inputs of 2048 generated worlds are
@@ -702,6 +762,8 @@ def main():
         alg = 4.0 * W * (nM + 2 * nv)
         aux["mul_m_kernel"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg}
         del big, outv
+        torch.cuda.empty_cache()
+        aux.update(stage_kernels(args, torch, md, m_host, device, timed))
         torch.cuda.empty_cache()
 
     sweep = run_sweep(args, torch, timer, world, rank, device, peak) if sweep_mode else None

@@ -30,7 +30,7 @@
 extern "C" {
 #endif
 
-#define IMN_ABI_VERSION 3
+#define IMN_ABI_VERSION 4
 
 typedef enum ImnStatus {
   IMN_OK = 0,
@@ -285,6 +285,35 @@ typedef struct ImnAdvance {
   float* time;                /* (W) in/out, may be NULL                         */
 } ImnAdvance;
 
+/* Body tree and the model tables of the smooth-dynamics stages that walk it
+ * (tree_fusion.py:27-50 TreeReductionScratch / create_tree_reduction_scratch; the
+ * kernels' model arguments, tree_fusion.py:192-206, 209-222, velocity_fusion.py:15-29).
+ * All pointers are device pointers.  Tables a call does not read may be NULL. */
+typedef struct ImnBodyTree {
+  int32_t nbody, nv, nM, nlevels;
+  const int32_t* body_parentid; /* (nbody)                                          */
+  const int32_t* level_bodies;  /* (nbody) m.body_tree concatenated, level 0 first  */
+  const int32_t* level_offsets; /* (nlevels + 1)                                    */
+  const int32_t* child_ptr;     /* (nbody + 1) by position in level_bodies: the     */
+  const int32_t* child_ids;     /* children of that body in level-list order (the
+                                 * world body is nobody's child); no counterpart in
+                                 * the reference, which scans the whole next level  */
+  const int32_t* body_jntnum;   /* (nbody) */
+  const int32_t* body_jntadr;   /* (nbody) */
+  const int32_t* body_dofadr;   /* (nbody) */
+  const int32_t* body_dofnum;   /* (nbody) */
+  const int32_t* jnt_type;      /* (njnt) IMN_JNT_*                                 */
+  const int32_t* dof_bodyid;    /* (nv) */
+  const int32_t* dof_parentid;  /* (nv) */
+  const float* dof_armature;    /* (n_armature, nv), world w reads row w % n        */
+  int32_t n_armature;
+  const int32_t* M_rownnz;      /* (nv) */
+  const int32_t* M_rowadr;      /* (nv) */
+  const float* gravity;         /* (n_gravity, 3) opt.gravity, world w reads w % n  */
+  int32_t n_gravity;
+  int32_t gravity_enabled;      /* !(opt.disableflags & GRAVITY)                    */
+} ImnBodyTree;
+
 /* Directional ball-joint limits (ball_limits.py:205-318 BallLimitBuffers /
  * make_ball_limit_buffers) and the constraint-row arrays of mujoco_warp `Data` they are
  * appended to (ball_limits.py:259-281).  Dense Jacobian only. */
@@ -449,6 +478,35 @@ int imn_advance(const ImnAdvance* p, const float* qacc, int64_t qacc_ld, int32_t
  * violated directional limit rows of every limited ball joint to each world's rows, in
  * (joint, kind) order. */
 int imn_ball_limit_rows(const ImnBallLimits* p, int32_t nworld, void* stream);
+
+/* Replaces accumulate (tree_fusion.py:138-170; kernels :52-135): every body's value is
+ * added to its parent's, deepest level first, `components` floats per body, in place.
+ * values is (W, nbody, components) with world stride `world_ld` floats.  With
+ * skip_root_parent the world body receives nothing.  Children are added in level-list
+ * order, one writer per parent: the reference's deterministic mode, bit for bit.
+ * subtree_com_accumulate (:173-183) is this call with 3 components. */
+int imn_body_tree_accumulate(const ImnBodyTree* tree, float* values, int64_t world_ld,
+                             int32_t components, int32_t skip_root_parent, int32_t nworld,
+                             void* stream);
+
+/* Replaces crb (tree_fusion.py:186-206): crb = cinert summed up the tree (10 floats per
+ * body, the world body kept out), then M on its CSR rows (ancestors ascending, diagonal
+ * last; every stored entry is written).  cinert, crb: (W, nbody, 10); cdof: (W, nv, 6). */
+int imn_crb(const ImnBodyTree* tree, const float* cinert, const float* cdof, float* crb,
+            float* M, int64_t M_ld, int32_t nworld, void* stream);
+
+/* Replaces rne (tree_fusion.py:209-222; no acceleration term): cacc down the tree from
+ * -gravity, cfrc_int = cinert cacc + cvel x* (cinert cvel) summed up the tree,
+ * qfrc_bias = cdof . cfrc_int[dof's body].  cacc, cfrc_int, cvel: (W, nbody, 6);
+ * cdof, cdof_dot: (W, nv, 6). */
+int imn_rne(const ImnBodyTree* tree, const float* cinert, const float* cvel, const float* cdof,
+            const float* cdof_dot, const float* qvel, int64_t qvel_ld, float* cacc,
+            float* cfrc_int, float* qfrc_bias, int64_t bias_ld, int32_t nworld, void* stream);
+
+/* Replaces com_vel (velocity_fusion.py:105-126, kernel :15-103): body velocities cvel by
+ * depth and cdof_dot = cvel x cdof per dof, joint by joint. */
+int imn_com_vel(const ImnBodyTree* tree, const float* qvel, int64_t qvel_ld, const float* cdof,
+                float* cvel, float* cdof_dot, int32_t nworld, void* stream);
 
 /* Uploads a sparse plan (sparse_hessian.build_plan's tables, sparse_hessian.py:229-402,
  * which the reference bakes into generated source instead).  `host_tables` holds HOST

@@ -15,7 +15,7 @@ I32 = C.c_int32
 I64 = C.c_int64
 F32 = C.c_float
 
-IMN_ABI_VERSION = 3
+IMN_ABI_VERSION = 4
 
 IMN_OK = 0
 IMN_ERR_NULL = -1
@@ -198,6 +198,16 @@ class ImnAdvance(C.Structure):
     ]
 
 
+class ImnBodyTree(C.Structure):
+    _fields_ = [
+        ("nbody", I32), ("nv", I32), ("nM", I32), ("nlevels", I32), ("body_parentid", P), ("level_bodies", P),
+        ("level_offsets", P), ("child_ptr", P), ("child_ids", P), ("body_jntnum", P), ("body_jntadr", P),
+        ("body_dofadr", P), ("body_dofnum", P), ("jnt_type", P), ("dof_bodyid", P), ("dof_parentid", P),
+        ("dof_armature", P), ("n_armature", I32), ("M_rownnz", P), ("M_rowadr", P), ("gravity", P),
+        ("n_gravity", I32), ("gravity_enabled", I32),
+    ]
+
+
 class ImnBallLimits(C.Structure):
     _fields_ = [
         ("njoint", I32), ("nv", I32), ("njmax", I32), ("refsafe", I32), ("limit_joint_type", I32),
@@ -248,6 +258,10 @@ SYMBOLS = {
     "imn_implicit_matrix": (C.c_int, [C.POINTER(ImnImplicit), P, I64, P, I64, I32, P]),
     "imn_advance": (C.c_int, [C.POINTER(ImnAdvance), P, I64, I32, P]),
     "imn_ball_limit_rows": (C.c_int, [C.POINTER(ImnBallLimits), I32, P]),
+    "imn_body_tree_accumulate": (C.c_int, [C.POINTER(ImnBodyTree), P, I64, I32, I32, I32, P]),
+    "imn_crb": (C.c_int, [C.POINTER(ImnBodyTree), P, P, P, P, I64, I32, P]),
+    "imn_rne": (C.c_int, [C.POINTER(ImnBodyTree), P, P, P, P, P, I64, P, P, P, I64, I32, P]),
+    "imn_com_vel": (C.c_int, [C.POINTER(ImnBodyTree), P, I64, P, P, P, I32, P]),
     "imn_sparse_plan_create": (C.c_int, [C.POINTER(ImnSparsePlan), C.POINTER(C.POINTER(ImnSparsePlan))]),
     "imn_sparse_plan_destroy": (None, [C.POINTER(ImnSparsePlan)]),
     "imn_launch_info": (

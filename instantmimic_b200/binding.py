@@ -48,6 +48,7 @@ def upstream_constants(module_types: Any = None, module_solver: Any = None) -> d
         "overflow_ls_iterations": member("OverflowType", "LS_ITERATIONS", types.OverflowType.LS_ITERATIONS),
         "disable_warmstart": member("DisableBit", "WARMSTART", types.DisableBit.WARMSTART),
         "disable_damper": member("DisableBit", "DAMPER", types.DisableBit.DAMPER),
+        "disable_gravity": member("DisableBit", "GRAVITY", types.DisableBit.GRAVITY),
         "disable_actuation": member("DisableBit", "ACTUATION", types.DisableBit.ACTUATION),
         "disable_refsafe": member("DisableBit", "REFSAFE", types.DisableBit.REFSAFE),
         "constraint_limit_joint": member("ConstraintType", "LIMIT_JOINT", types.ConstraintType.LIMIT_JOINT),

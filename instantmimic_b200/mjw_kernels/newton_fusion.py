@@ -134,7 +134,7 @@ _KEY_DATA = ("nefc", "ne", "nf", "qacc_smooth", "qacc_warmstart", "qfrc_smooth",
              "qfrc_constraint", "solver_niter", "overflow")
 _KEY_EFC = ("J", "D", "aref", "frictionloss", "force", "state", "Ma", "J_world_offset")
 _KEY_CTX = ("Jaref", "jv", "search", "mv", "grad", "h", "hfactor", "quad_changed_ids", "newton_dof_union",
-            "world_order") + binding._CTX_WORLD_ARRAYS
+            "world_order", "stats") + binding._CTX_WORLD_ARRAYS
 
 
 def _key(m, d, ctx, nsolving):

@@ -45,6 +45,7 @@ class Option:
     warn_overflow: int = 0
     graph_conditional: bool = True
     timestep: Any = None  # float array, length 1 or nworld
+    gravity: Any = None  # (1 or nworld, 3)
 
 
 @dataclass
@@ -94,6 +95,12 @@ class Model:
     actuator_dyntype: Any = None
     actuator_gainprm: Any = None  # (nu, 10)
     actuator_biasprm: Any = None  # (nu, 10)
+    # body tree and the tables of the smooth-dynamics stages (tree_fusion / velocity_fusion)
+    body_tree: Any = None  # list of int arrays: the bodies of each depth, world body first
+    body_jntadr: Any = None
+    body_jntnum: Any = None
+    dof_bodyid: Any = None
+    dof_armature: Any = None  # (1 or nworld, nv)
 
     @property
     def nactuator(self) -> int:
@@ -144,6 +151,18 @@ class Data:
     moment_colind: Any = None
     actuator_moment: Any = None
     ctrl: Any = None
+    # smooth-dynamics state (None when only the solve is used): per-body spatial
+    # inertias (10), composite inertias, velocities, accelerations, forces (6), per-dof
+    # motion axes and their time derivatives (6), subtree centres of mass (3)
+    cinert: Any = None
+    crb: Any = None
+    cdof: Any = None
+    cdof_dot: Any = None
+    cvel: Any = None
+    cacc: Any = None
+    cfrc_int: Any = None
+    qfrc_bias: Any = None
+    subtree_com: Any = None
 
 
 def ancestor_csr(dof_parentid: np.ndarray):
@@ -243,10 +262,12 @@ def put_model(
     # joints: a body with 6 dofs hangs on a free joint, with 3 on a ball joint, any other
     # count is that many hinges
     jnt_type, jnt_dofadr, jnt_qposadr, nq = [], [], [], 0
+    body_jntnum = np.zeros(nbody, np.int32)
     for b in range(1, nbody):
         first, count = int(body_dofadr[b]), int(body_dofnum[b])
         if first < 0:
             continue
+        body_jntnum[b] = 1 if count in (3, 6) else count
         kinds = [(types.JointType.FREE, 6, 7)] if count == 6 else (
             [(types.JointType.BALL, 3, 4)] if count == 3 else [(types.JointType.HINGE, 1, 1)] * count)
         for kind, ndof, npos in kinds:
@@ -258,6 +279,13 @@ def put_model(
     jnt_dofadr = np.asarray(jnt_dofadr, np.int32)[order]
     sizes = np.where(jnt_type == int(types.JointType.FREE), 7, np.where(jnt_type == int(types.JointType.BALL), 4, 1))
     jnt_qposadr = np.concatenate(([0], np.cumsum(sizes)[:-1])).astype(np.int32)
+    # bodies are numbered in dof order, so a body's joints are consecutive
+    body_jntadr = np.concatenate(([0], np.cumsum(body_jntnum)[:-1])).astype(np.int32)
+    depth = np.zeros(nbody, np.int32)
+    for b in range(1, nbody):
+        depth[b] = depth[body_parentid[b]] + 1
+    body_tree = [np.flatnonzero(depth == k).astype(np.int32) for k in range(int(depth.max()) + 1)]
+    opt.gravity = np.array([[0.0, 0.0, -9.81]], np.float32)
     elemid = np.full((nv, nv), -1, np.int32)
     elemid[rowidx, colind] = np.arange(colind.size, dtype=np.int32)
     return Model(
@@ -285,6 +313,11 @@ def put_model(
         body_parentid=body_parentid,
         body_dofadr=body_dofadr,
         body_dofnum=body_dofnum,
+        body_tree=body_tree,
+        body_jntadr=body_jntadr,
+        body_jntnum=body_jntnum,
+        dof_bodyid=body_of_dof.copy(),
+        dof_armature=np.zeros((1, nv), np.float32),
         geom_bodyid=np.zeros(0, np.int32),
         nxn_geom_pair_filtered=np.zeros((0, 2), np.int32),
     )
@@ -340,6 +373,8 @@ def _map_arrays(obj: Any, fn):
     """Copy of a (nested) dataclass / namespace with ``fn`` applied to every array."""
     if isinstance(obj, np.ndarray):
         return fn(obj)
+    if isinstance(obj, list):
+        return [_map_arrays(v, fn) for v in obj]
     if is_dataclass(obj) and not isinstance(obj, type):
         return replace(obj, **{f.name: _map_arrays(getattr(obj, f.name), fn) for f in fields(obj)})
     if isinstance(obj, SimpleNamespace):
@@ -363,6 +398,8 @@ def to_host(obj: Any):
             return o.detach().cpu().numpy()
         if isinstance(o, np.ndarray):
             return o.copy()
+        if isinstance(o, list):
+            return [conv(v) for v in o]
         if is_dataclass(o) and not isinstance(o, type):
             return replace(o, **{f.name: conv(getattr(o, f.name)) for f in fields(o)})
         if isinstance(o, SimpleNamespace):

@@ -78,6 +78,9 @@ class OptimizedFwdPositionScratch:
     pre_advance_modifier: Any = None
     # directional ball-joint limit rows (mjw_step_optimized.py:2241-2249)
     ball_limit_buffers: Any = None
+    # level tables of the body tree for subtree_com / crb / rne / com_vel
+    # (mjw_step_optimized.py:518, 2575-2577)
+    tree_reduction: Any = None
 
 
 def _constraint_rows_impossible(m: Any, ball_joint_limits: Sequence[Any] = ()) -> bool:
@@ -206,7 +209,13 @@ def make_optimized_fwd_position_scratch(
         from .mjw_kernels import ball_limits
 
         ball_buffers = ball_limits.make_ball_limit_buffers(ball_joint_limits, m, d, device)
+    tree_reduction = None
+    if include_optimized_kernel_scratch and getattr(m, "body_tree", None):
+        from .mjw_kernels import tree_fusion
+
+        tree_reduction = tree_fusion.create_tree_reduction_scratch(m)
     scratch = OptimizedFwdPositionScratch(
+        tree_reduction=tree_reduction,
         ball_limit_buffers=ball_buffers,
         solver_context=ctx,
         solver_nsolving=nsolving,
@@ -223,6 +232,16 @@ def make_optimized_fwd_position_scratch(
     if logger.isEnabledFor(logging.INFO) and newton_fusion._on_cuda(m):
         log_kernel_selection(m, d, scratch)
     return scratch
+
+
+def _select_tree_reduction(scratch: Any, use_optimized_kernel: bool | None):
+    """The tree scratch a step uses (mjw_step_optimized.py:2887-2894): the optimized
+    kernels when asked for, and always when the scratch was made for ordered sums (a
+    numerical requirement of its owner, not a speed choice)."""
+    tree = getattr(scratch, "tree_reduction", None)
+    if use_optimized_kernel or (tree is not None and tree.deterministic):
+        return tree
+    return None
 
 
 def _solver_compact_enabled(m: Any) -> bool:

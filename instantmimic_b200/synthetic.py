@@ -378,3 +378,39 @@ def make_sweep_point(nv: int, nefc: int, nworld: int, seed: int = 0, *, couple: 
     m = put_model(parent, body_of_dof=body, **opts)
     d, Mdense = make_problem(m, nworld, nefc, seed, nefc_range=(nefc, nefc), rows="generic", couple=couple)
     return m, d, Mdense
+
+
+def add_smooth_state(m: Model, d, seed: int = 0):
+    """Fills host ``Data`` with a random but physical smooth-dynamics state: per-body
+    spatial inertias about a common origin (positive mass, positive definite rotational
+    part), motion axes ``cdof`` of unit scale, joint velocities, and empty outputs
+    (``crb``, ``M``, ``cvel``, ``cdof_dot``, ``cacc``, ``cfrc_int``, ``qfrc_bias``,
+    ``subtree_com``).  ``cvel`` / ``cdof_dot`` are left zero: run ``com_vel`` to make them
+    consistent with ``qvel``."""
+    rng = np.random.default_rng(seed)
+    W, nv, nbody = d.nworld, m.nv, int(np.asarray(m.body_parentid).size)
+    f32 = lambda a: np.ascontiguousarray(a, dtype=np.float32)  # noqa: E731
+    mass = rng.uniform(0.5, 5.0, (W, nbody))
+    com = rng.uniform(-0.3, 0.3, (W, nbody, 3))
+    a = rng.normal(0.0, 0.1, (W, nbody, 3, 3))
+    inertia = a @ np.swapaxes(a, -1, -2) + 0.02 * np.eye(3)
+    c2 = (com * com).sum(-1)
+    about_origin = inertia + mass[..., None, None] * (c2[..., None, None] * np.eye(3) - com[..., :, None] * com[..., None, :])
+    cinert = np.concatenate(
+        [
+            np.stack([about_origin[..., 0, 0], about_origin[..., 1, 1], about_origin[..., 2, 2],
+                      about_origin[..., 0, 1], about_origin[..., 0, 2], about_origin[..., 1, 2]], -1),
+            mass[..., None] * com,
+            mass[..., None],
+        ],
+        -1,
+    )
+    cinert[:, 0] = 0.0  # the world body carries no inertia
+    d.cinert = f32(cinert)
+    d.cdof = f32(rng.normal(0.0, 0.6, (W, nv, 6)))
+    d.qvel = f32(rng.normal(0.0, 0.5, (W, nv)))
+    z = lambda *s: np.zeros(s, np.float32)  # noqa: E731
+    d.crb, d.cvel, d.cacc, d.cfrc_int = z(W, nbody, 10), z(W, nbody, 6), z(W, nbody, 6), z(W, nbody, 6)
+    d.cdof_dot, d.qfrc_bias, d.subtree_com = z(W, nv, 6), z(W, nv), f32(rng.uniform(0.1, 1.0, (W, nbody, 3)))
+    m.dof_armature = f32(rng.uniform(0.0, 0.05, (1, nv)))
+    return d

@@ -41,11 +41,15 @@ class IntegratorType(enum.IntEnum):
 
 
 class DisableBit(enum.IntFlag):
-    # mjtDisableBit; the adapter reads the live values when mujoco-warp is importable
+    # mjtDisableBit as laid out since MuJoCo split PASSIVE into SPRING and DAMPER (the
+    # reference names both, so it runs on such a release); the adapter reads the live
+    # values when mujoco-warp is importable
+    SPRING = 1 << 5
     DAMPER = 1 << 6
-    WARMSTART = 1 << 8
-    ACTUATION = 1 << 10
-    REFSAFE = 1 << 11
+    GRAVITY = 1 << 7
+    WARMSTART = 1 << 9
+    ACTUATION = 1 << 11
+    REFSAFE = 1 << 12
 
 
 class ConstraintType(enum.IntEnum):
