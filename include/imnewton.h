@@ -259,7 +259,8 @@ typedef struct ImnImplicit {
   int32_t nv, nM, nu;
   int32_t actuation;           /* !(opt.disableflags & ACTUATION)                */
   int32_t damper;              /* !(opt.disableflags & DAMPER)                   */
-  float timestep;              /* opt.timestep                                   */
+  const float* timestep;       /* opt.timestep (n_timestep): world w reads w % n  */
+  int32_t n_timestep;
   const float* dof_damping;    /* (nv)                                           */
   const int32_t* M_elemid;     /* (nv, nv): entry of M for (i, j), -1 if none    */
   const int32_t* moment_rownnz; /* (W, nu)                                       */
@@ -274,7 +275,8 @@ typedef struct ImnImplicit {
  * _advance_with_scratch, mjw_step_optimized.py:4823-4847). */
 typedef struct ImnAdvance {
   int32_t nv, nq, njnt;
-  float timestep;
+  const float* timestep;      /* opt.timestep (n_timestep): world w reads w % n   */
+  int32_t n_timestep;
   const int32_t* jnt_type;    /* (njnt) IMN_JNT_*                                */
   const int32_t* jnt_dofadr;  /* (njnt)                                          */
   const int32_t* jnt_qposadr; /* (njnt)                                          */
@@ -322,7 +324,8 @@ typedef struct ImnBallLimits {
   int32_t nv, njmax;
   int32_t refsafe;             /* !(opt.disableflags & REFSAFE)                   */
   int32_t limit_joint_type;    /* types.ConstraintType.LIMIT_JOINT                */
-  float timestep;
+  const float* timestep;       /* opt.timestep (n_timestep): world w reads w % n  */
+  int32_t n_timestep;
   const int32_t* qadr;         /* (njoint) qpos address of the joint's quaternion */
   const int32_t* dadr;         /* (njoint) first dof                              */
   const int32_t* joint;        /* (njoint) joint id (efc.id)                      */

@@ -185,7 +185,7 @@ class ImnBlockedPlan(C.Structure):
 
 class ImnImplicit(C.Structure):
     _fields_ = [
-        ("nv", I32), ("nM", I32), ("nu", I32), ("actuation", I32), ("damper", I32), ("timestep", C.c_float),
+        ("nv", I32), ("nM", I32), ("nu", I32), ("actuation", I32), ("damper", I32), ("timestep", P), ("n_timestep", I32),
         ("dof_damping", P), ("M_elemid", P), ("moment_rownnz", P), ("moment_rowadr", P), ("moment_colind", P),
         ("actuator_moment", P), ("moment_ld", I64), ("actuator_velocity_gain", P),
     ]
@@ -193,7 +193,7 @@ class ImnImplicit(C.Structure):
 
 class ImnAdvance(C.Structure):
     _fields_ = [
-        ("nv", I32), ("nq", I32), ("njnt", I32), ("timestep", C.c_float), ("jnt_type", P), ("jnt_dofadr", P),
+        ("nv", I32), ("nq", I32), ("njnt", I32), ("timestep", P), ("n_timestep", I32), ("jnt_type", P), ("jnt_dofadr", P),
         ("jnt_qposadr", P), ("qvel", P), ("qvel_ld", I64), ("qpos", P), ("qpos_ld", I64), ("time", P),
     ]
 
@@ -211,7 +211,7 @@ class ImnBodyTree(C.Structure):
 class ImnBallLimits(C.Structure):
     _fields_ = [
         ("njoint", I32), ("nv", I32), ("njmax", I32), ("refsafe", I32), ("limit_joint_type", I32),
-        ("timestep", C.c_float), ("qadr", P), ("dadr", P), ("joint", P), ("neutral", P), ("frame", P), ("swing", P),
+        ("timestep", P), ("n_timestep", I32), ("qadr", P), ("dadr", P), ("joint", P), ("neutral", P), ("frame", P), ("swing", P),
         ("twist", P), ("minimum_h", P), ("margin", P), ("solref", P), ("solimp", P), ("invweight", P),
         ("n_invweight", I32), ("qpos", P), ("qpos_ld", I64), ("qvel", P), ("qvel_ld", I64), ("nefc", P), ("nl", P),
         ("efc_type", P), ("efc_id", P), ("efc_J", P), ("J_ld_world", I64), ("J_ld_row", I64), ("efc_pos", P),

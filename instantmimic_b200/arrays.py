@@ -128,6 +128,24 @@ def to_host(a: Any) -> np.ndarray:
     return np.asarray(a)
 
 
+_TABLES: dict = {}
+
+
+def table_to_host(a: Any) -> np.ndarray:
+    """Host copy of a constant model table, read from the device once per buffer: a copy
+    in every call would synchronise the stream and cannot be captured in a CUDA graph.
+    Only for arrays whose contents never change after model set-up."""
+    if isinstance(a, np.ndarray):
+        return a
+    key = (addr(a), tuple(shape(a)))
+    hit = _TABLES.get(key)
+    if hit is None:
+        if len(_TABLES) > 256:
+            _TABLES.clear()
+        hit = _TABLES[key] = np.array(to_host(a), copy=True)
+    return hit
+
+
 def as_torch(a: Any):
     """Zero-copy torch view of a caller's array (device arrays through
     ``__cuda_array_interface__``, which Warp arrays provide)."""

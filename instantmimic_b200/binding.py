@@ -9,7 +9,7 @@ import ctypes as C
 from typing import Any
 
 from . import abi, types
-from .arrays import addr, elem_strides, itemsize, length, shape
+from .arrays import addr, elem_strides, is_contiguous, itemsize, length, shape
 
 
 _UPSTREAM: dict | None = None
@@ -259,18 +259,16 @@ def ctx_struct(d_struct: abi.ImnData, ctx: Any, nsolving: Any, sparse_plan_struc
     return s
 
 
-def _timestep(m: Any) -> float:
-    """opt.timestep: a scalar, or mujoco-warp's per-world array, which must be uniform
-    (the kernels take one step size per launch)."""
-    from .arrays import to_host
-
+def _timestep(m: Any) -> tuple[int, int]:
+    """Address and length of opt.timestep, mujoco-warp's per-world float array (world w
+    reads element w % n, in the kernels, like every other per-world option)."""
     h = m.opt.timestep
-    if isinstance(h, (int, float)):
-        return float(h)
-    values = to_host(h).reshape(-1)
-    if values.size == 0 or (values != values[0]).any():
-        raise ValueError("the integrator kernels need one timestep for all worlds")
-    return float(values[0])
+    if isinstance(h, (int, float)) or h is None:
+        raise ValueError("m.opt.timestep must be a float array of length 1 or nworld, next to the other arrays")
+    n = length(h)
+    if n <= 0 or not is_contiguous(h):
+        raise ValueError("m.opt.timestep must be a contiguous, non-empty float array")
+    return addr(h), n
 
 
 def implicit_struct(m: Any, d: Any, velocity_gain: Any) -> abi.ImnImplicit:
@@ -282,7 +280,7 @@ def implicit_struct(m: Any, d: Any, velocity_gain: Any) -> abi.ImnImplicit:
     s.nu = int(getattr(m, "nu", 0) or 0)
     s.actuation = 0 if flags & c["disable_actuation"] else 1
     s.damper = 0 if flags & c["disable_damper"] else 1
-    s.timestep = _timestep(m)
+    s.timestep, s.n_timestep = _timestep(m)
     s.dof_damping = addr(m.dof_damping)
     s.M_elemid = addr(m.M_elemid)
     if s.nu and s.actuation:
@@ -306,7 +304,7 @@ def implicit_struct(m: Any, d: Any, velocity_gain: Any) -> abi.ImnImplicit:
 def advance_struct(m: Any, d: Any) -> abi.ImnAdvance:
     s = abi.ImnAdvance()
     s.nv, s.nq, s.njnt = int(m.nv), int(m.nq), int(m.njnt)
-    s.timestep = _timestep(m)
+    s.timestep, s.n_timestep = _timestep(m)
     s.jnt_type, s.jnt_dofadr, s.jnt_qposadr = addr(m.jnt_type), addr(m.jnt_dofadr), addr(m.jnt_qposadr)
     s.qvel, s.qvel_ld = addr(d.qvel), _row_ld(d.qvel)
     s.qpos, s.qpos_ld = addr(d.qpos), _row_ld(d.qpos)

@@ -165,7 +165,7 @@ __global__ void __launch_bounds__(32 * kBallWarps) ball_limit_kernel(const ImnBa
         const float weight = P.invweight[(size_t)(w % P.n_invweight) * P.nv + dof] * jn;
         const float margin = P.margin[index], pos = r - margin;
         float D, aref;
-        efc_row(pos, margin, vel, weight, P.solref + 2 * index, P.solimp + 5 * index, P.timestep, P.refsafe != 0, D,
+        efc_row(pos, margin, vel, weight, P.solref + 2 * index, P.solimp + 5 * index, P.timestep[w % P.n_timestep], P.refsafe != 0, D,
                 aref);
         const size_t o = (size_t)w * P.efc_ld + efcid;
         P.efc_type[o] = P.limit_joint_type;
@@ -196,10 +196,10 @@ extern "C" int imn_ball_limit_rows(const ImnBallLimits* p, int32_t nworld, void*
   const void* need[] = {p->qadr,   p->dadr,     p->joint,   p->neutral,   p->frame,      p->swing,   p->twist,
                         p->minimum_h, p->margin, p->solref,  p->solimp,    p->invweight,  p->qpos,    p->qvel,
                         p->nefc,   p->efc_type, p->efc_id,  p->efc_J,     p->efc_pos,    p->efc_margin, p->efc_D,
-                        p->efc_vel, p->efc_aref, p->efc_frictionloss};
+                        p->efc_vel, p->efc_aref, p->efc_frictionloss, p->timestep};
   for (const void* q : need)
     if (!q) return imn::set_error("imn_ball_limit_rows: a required pointer is NULL"), IMN_ERR_NULL;
-  if (p->njoint < 0 || p->nv <= 0 || p->njmax < 0 || nworld < 0 || p->n_invweight <= 0 || p->J_ld_row < p->nv ||
+  if (p->njoint < 0 || p->nv <= 0 || p->njmax < 0 || nworld < 0 || p->n_invweight <= 0 || p->n_timestep <= 0 || p->J_ld_row < p->nv ||
       p->efc_ld < p->njmax || p->J_ld_world < (int64_t)p->njmax * p->J_ld_row)
     return imn::set_error("imn_ball_limit_rows: bad extent or stride"), IMN_ERR_SHAPE;
   if (p->njmax < 3 * p->njoint)

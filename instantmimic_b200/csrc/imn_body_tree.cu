@@ -93,16 +93,19 @@ __device__ __forceinline__ Sp6 motion_cross_force(const Sp6& vel, const Sp6& f) 
   return r;
 }
 // 10-number spatial inertia (Ixx Iyy Izz Ixy Ixz Iyz, m*cx m*cy m*cz, m) times a motion
-// vector (MuJoCo mju_mulInertVec), each sum a left-to-right chain.
+// vector (MuJoCo mju_mulInertVec), each sum a left-to-right chain contracted the way
+// nvcc contracts "a*b + c*d + ..." (the first sum or difference of two products fuses
+// its LEFT product and rounds the right one; every later product is fused into the
+// running value) -- the rule the reference's generated tree L'DL code follows when run.
 __device__ __forceinline__ Sp6 inert_vec(const float* i, const Sp6& a) {
   const float* v = a.v;
   Sp6 r;
-  r.v[0] = fmaf(i[7], v[5], fmaf(-i[8], v[4], fmaf(i[4], v[2], fmaf(i[3], v[1], i[0] * v[0]))));
-  r.v[1] = fmaf(-i[6], v[5], fmaf(i[8], v[3], fmaf(i[5], v[2], fmaf(i[1], v[1], i[3] * v[0]))));
-  r.v[2] = fmaf(i[6], v[4], fmaf(-i[7], v[3], fmaf(i[2], v[2], fmaf(i[5], v[1], i[4] * v[0]))));
-  r.v[3] = fmaf(i[9], v[3], fmaf(-i[7], v[2], i[8] * v[1]));
-  r.v[4] = fmaf(i[9], v[4], fmaf(-i[8], v[0], i[6] * v[2]));
-  r.v[5] = fmaf(i[9], v[5], fmaf(-i[6], v[1], i[7] * v[0]));
+  r.v[0] = fmaf(i[7], v[5], fmaf(-i[8], v[4], fmaf(i[4], v[2], fmaf(i[0], v[0], i[3] * v[1]))));
+  r.v[1] = fmaf(-i[6], v[5], fmaf(i[8], v[3], fmaf(i[5], v[2], fmaf(i[3], v[0], i[1] * v[1]))));
+  r.v[2] = fmaf(i[6], v[4], fmaf(-i[7], v[3], fmaf(i[2], v[2], fmaf(i[4], v[0], i[5] * v[1]))));
+  r.v[3] = fmaf(i[9], v[3], fmaf(i[8], v[1], -(i[7] * v[2])));
+  r.v[4] = fmaf(i[9], v[4], fmaf(i[6], v[2], -(i[8] * v[0])));
+  r.v[5] = fmaf(i[9], v[5], fmaf(i[7], v[0], -(i[6] * v[1])));
   return r;
 }
 

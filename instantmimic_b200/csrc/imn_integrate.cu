@@ -73,7 +73,8 @@ __global__ void __launch_bounds__(32 * kMatrixWarps)
   __syncwarp();
   const float* Mw = M + (size_t)w * M_ld;
   float* ow = out + (size_t)w * out_ld;
-  for (int e = lane; e < P.nM; e += 32) ow[e] = Mw[e] - P.timestep * qd[e];
+  const float h = P.timestep[w % P.n_timestep];
+  for (int e = lane; e < P.nM; e += 32) ow[e] = Mw[e] - h * qd[e];
 }
 
 __device__ __forceinline__ void quat_integrate(float q[4], const float w[3], float h) {
@@ -104,7 +105,7 @@ __global__ void __launch_bounds__(256)
   const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= (int64_t)nworld * P.njnt) return;
   const int w = (int)(t / P.njnt), j = (int)(t - (int64_t)w * P.njnt);
-  const float h = P.timestep;
+  const float h = P.timestep[w % P.n_timestep];
   const int type = P.jnt_type[j], dof = P.jnt_dofadr[j], pos = P.jnt_qposadr[j];
   float* qvel = P.qvel + (size_t)w * P.qvel_ld + dof;
   float* qpos = P.qpos + (size_t)w * P.qpos_ld + pos;
@@ -134,7 +135,9 @@ __global__ void __launch_bounds__(256)
 
 extern "C" int imn_implicit_matrix(const ImnImplicit* p, const float* M, int64_t M_ld, float* out, int64_t out_ld,
                                    int32_t nworld, void* stream) {
-  if (!p || !M || !out || !p->M_elemid) return imn::set_error("imn_implicit_matrix: NULL argument"), IMN_ERR_NULL;
+  if (!p || !M || !out || !p->M_elemid || !p->timestep)
+    return imn::set_error("imn_implicit_matrix: NULL argument"), IMN_ERR_NULL;
+  if (p->n_timestep <= 0) return imn::set_error("imn_implicit_matrix: empty opt.timestep"), IMN_ERR_SHAPE;
   if (p->nv <= 0 || p->nM <= 0 || p->nu < 0 || nworld < 0 || M_ld < p->nM || out_ld < p->nM)
     return imn::set_error("imn_implicit_matrix: bad extent or stride"), IMN_ERR_SHAPE;
   if (p->damper && !p->dof_damping) return imn::set_error("imn_implicit_matrix: dof_damping is NULL"), IMN_ERR_NULL;
@@ -159,8 +162,9 @@ extern "C" int imn_implicit_matrix(const ImnImplicit* p, const float* M, int64_t
 }
 
 extern "C" int imn_advance(const ImnAdvance* p, const float* qacc, int64_t qacc_ld, int32_t nworld, void* stream) {
-  if (!p || !qacc || !p->qvel || !p->qpos || !p->jnt_type || !p->jnt_dofadr || !p->jnt_qposadr)
+  if (!p || !qacc || !p->qvel || !p->qpos || !p->jnt_type || !p->jnt_dofadr || !p->jnt_qposadr || !p->timestep)
     return imn::set_error("imn_advance: NULL argument"), IMN_ERR_NULL;
+  if (p->n_timestep <= 0) return imn::set_error("imn_advance: empty opt.timestep"), IMN_ERR_SHAPE;
   if (p->njnt <= 0 || p->nv <= 0 || p->nq < p->nv || nworld < 0 || qacc_ld < p->nv || p->qvel_ld < p->nv ||
       p->qpos_ld < p->nq)
     return imn::set_error("imn_advance: bad extent or stride"), IMN_ERR_SHAPE;

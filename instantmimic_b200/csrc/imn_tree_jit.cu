@@ -38,7 +38,7 @@
 
 namespace {
 
-enum { OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X };
+enum { OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X, OP_MULSUB };
 
 // ---- NVRTC through dlopen ---------------------------------------------------------
 typedef void* nvrtcProgram_t;
@@ -103,6 +103,7 @@ void operands(const Ins& i, int reads[4], int& nread, int& write) {
     case OP_SUBMUL: reads[nread++] = i.a, reads[nread++] = i.b, reads[nread++] = i.dst, write = i.dst; break;
     case OP_MUL: reads[nread++] = i.a, reads[nread++] = i.b, write = i.dst; break;
     case OP_ADD: reads[nread++] = i.a, reads[nread++] = i.dst, write = i.dst; break;
+    case OP_MULSUB: reads[nread++] = i.a, reads[nread++] = i.b, reads[nread++] = i.dst, write = i.dst; break;
     case OP_STORE_X: reads[nread++] = i.a; break;
     default: break;
   }
@@ -167,6 +168,7 @@ std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int ow
         case OP_SUBMUL: out += d + " = fmaf(-" + ref(i.a) + ", " + ref(i.b) + ", " + d + ");\n"; break;
         case OP_MUL: out += d + " = " + ref(i.a) + " * " + ref(i.b) + ";\n"; break;
         case OP_ADD: out += d + " = " + d + " + " + ref(i.a) + ";\n"; break;
+        case OP_MULSUB: out += d + " = fmaf(" + ref(i.a) + ", " + ref(i.b) + ", -" + d + ");\n"; break;
         case OP_STORE_X:
           out += staged ? "yt[" + std::to_string(i.dst) + "] = " + ref(i.a) + ";\n"
                         : "if (live) xr[" + std::to_string(i.dst) + "] = " + ref(i.a) + ";\n";
@@ -304,7 +306,7 @@ extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr
     const int dst = w[1], a = w[2] & 0xFFFF, b = (w[2] >> 16) & 0xFFFF, c = w[3];
     const bool index_a = w[0] == OP_LOAD_M || w[0] == OP_LOAD_Y;  // a addresses M or y
     const bool index_d = w[0] == OP_STORE_X;                      // dst addresses x
-    if (w[0] < 0 || w[0] > OP_STORE_X || dst < 0 || (!index_d && dst >= nslot) || (index_d && dst >= nv) ||
+    if (w[0] < 0 || w[0] > OP_MULSUB || dst < 0 || (!index_d && dst >= nslot) || (index_d && dst >= nv) ||
         (!index_a && a >= nslot) || (w[0] == OP_LOAD_M && a >= nM) || (w[0] == OP_LOAD_Y && a >= nv) || b >= nslot ||
         c < 0 || c >= nslot)
       return imn::set_error("imn_tree_ldl_compile: instruction %d is out of range", pc), IMN_ERR_SHAPE;

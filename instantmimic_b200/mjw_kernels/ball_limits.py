@@ -140,7 +140,7 @@ def rows_struct(tables: dict, njoint: int, m: Any, d: Any, overflow: Any, singul
     s.njoint, s.nv, s.njmax = int(njoint), int(m.nv), int(d.njmax)
     s.refsafe = 0 if int(m.opt.disableflags) & c["disable_refsafe"] else 1
     s.limit_joint_type = c["constraint_limit_joint"]
-    s.timestep = binding._timestep(m)
+    s.timestep, s.n_timestep = binding._timestep(m)
     for name in ("qadr", "dadr", "joint", "neutral", "frame", "swing", "twist", "minimum_h", "margin", "solref", "solimp"):
         setattr(s, name, addr(tables[name]))
     s.invweight = addr(m.dof_invweight0)

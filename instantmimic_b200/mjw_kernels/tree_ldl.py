@@ -37,7 +37,7 @@ MAX_SHORT_SPAN = 4096
 MIN_DENSE_TO_SPAN_RATIO = 8.0
 
 # instruction opcodes of the interpreter (four int32 per instruction: op, dst, a | b << 16, c)
-OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X = range(10)
+OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X, OP_MULSUB = range(11)
 
 
 @dataclass(frozen=True)
@@ -257,6 +257,21 @@ class _Program:
             for p in range(count):
                 out.append((OP_SUBMUL, target_s(colind[start + p]), m(start + p), s(k), 0))
 
+        def back_substitute(i, out):
+            # x_i = s_i d_i - sum_p m_p x_anc(p).  The reference writes "x = s * d;
+            # x = x - m0 * x0; x = x - m1 * x1; ..." (tree_ldl.py:258-266, 297-303); compiled
+            # with contraction on, the first difference of two products fuses its LEFT
+            # product, fma(s, d, -(m0 x0)), and every later term is fma(-m, x, acc)
+            # (established against the reference's generated code run on a B200)
+            start, count = rowadr[i], rownnz[i] - 1
+            if count == 0:
+                out.append((OP_MUL, x(i), s(i), d(i), 0))
+                return
+            out.append((OP_MUL, x(i), m(start), x(colind[start]), 0))
+            out.append((OP_MULSUB, x(i), s(i), d(i), 0))
+            for p in range(1, count):
+                out.append((OP_SUBMUL, x(i), m(start + p), x(colind[start + p]), 0))
+
         self.forward, self.backward = [], []
         touched = []
         for j, nodes in enumerate(plan.groups):
@@ -288,9 +303,7 @@ class _Program:
             self.forward.append(f)
             b, own = [], set()
             for i in reversed(nodes):
-                b.append((OP_MUL, x(i), s(i), d(i), 0))
-                for p in range(rownnz[i] - 1):
-                    b.append((OP_SUBMUL, x(i), m(rowadr[i] + p), x(colind[rowadr[i] + p]), 0))
+                back_substitute(i, b)
                 own.add(i)
                 b.append((OP_STORE_X, i, x(i), 0, 0))
             self.backward.append(b)
@@ -309,9 +322,7 @@ class _Program:
             eliminate(k, t, lambda anc, index: index, lambda anc: s(anc))
         for i in plan.trunk:
             # the trunk solution lands in x(i), where the groups' backward streams read it
-            t.append((OP_MUL, x(i), s(i), d(i), 0))
-            for p in range(rownnz[i] - 1):
-                t.append((OP_SUBMUL, x(i), m(rowadr[i] + p), x(colind[rowadr[i] + p]), 0))
+            back_substitute(i, t)
             t.append((OP_STORE_X, i, x(i), 0, 0))
         self.trunk = t
         self.owner = min(range(G), key=lambda j: sum(rownnz[k] ** 2 for k in plan.groups[j]))

@@ -445,9 +445,10 @@ def actuator_velocity_gain(m: Any, d: Any, out: Any) -> None:
     bias = b0 + b1 length + b2 velocity, hence g2 ctrl + b2.  Muscle and user types, and
     actuators with activation dynamics, are refused."""
     from . import types as T
-    from .arrays import as_torch, to_host
+    from .arrays import as_torch, table_to_host
 
-    gain_t, bias_t, dyn_t = (to_host(getattr(m, n)) for n in ("actuator_gaintype", "actuator_biastype", "actuator_dyntype"))
+    gain_t, bias_t, dyn_t = (table_to_host(getattr(m, n))
+                             for n in ("actuator_gaintype", "actuator_biastype", "actuator_dyntype"))
     if (dyn_t != int(T.DynType.NONE)).any():
         raise RuntimeError("actuators with activation dynamics are outside this integrator tail")
     if (gain_t > int(T.GainType.AFFINE)).any() or (bias_t > int(T.BiasType.AFFINE)).any():

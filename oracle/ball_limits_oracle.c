@@ -131,7 +131,7 @@ int oracle_ball_limit_rows(const ImnBallLimits* P, int nworld) {
         const float weight = P->invweight[(size_t)(w % P->n_invweight) * P->nv + dof] * jn;
         const float margin = P->margin[index], pos = r - margin;
         float D, aref;
-        efc_row(pos, vel, weight, P->solref + 2 * index, P->solimp + 5 * index, P->timestep, P->refsafe, &D, &aref);
+        efc_row(pos, vel, weight, P->solref + 2 * index, P->solimp + 5 * index, P->timestep[w % P->n_timestep], P->refsafe, &D, &aref);
         const size_t o = (size_t)w * P->efc_ld + efcid;
         P->efc_type[o] = P->limit_joint_type, P->efc_id[o] = P->joint[index];
         P->efc_pos[o] = pos + margin, P->efc_margin[o] = margin;

@@ -65,12 +65,12 @@ static void motion_cross_force(const float* vel, const float* f, float* r) {
   cross3(vel, f + 3, r + 3);
 }
 static void inert_vec(const float* i, const float* v, float* r) {
-  r[0] = fmaf(i[7], v[5], fmaf(-i[8], v[4], fmaf(i[4], v[2], fmaf(i[3], v[1], i[0] * v[0]))));
-  r[1] = fmaf(-i[6], v[5], fmaf(i[8], v[3], fmaf(i[5], v[2], fmaf(i[1], v[1], i[3] * v[0]))));
-  r[2] = fmaf(i[6], v[4], fmaf(-i[7], v[3], fmaf(i[2], v[2], fmaf(i[5], v[1], i[4] * v[0]))));
-  r[3] = fmaf(i[9], v[3], fmaf(-i[7], v[2], i[8] * v[1]));
-  r[4] = fmaf(i[9], v[4], fmaf(-i[8], v[0], i[6] * v[2]));
-  r[5] = fmaf(i[9], v[5], fmaf(-i[6], v[1], i[7] * v[0]));
+  r[0] = fmaf(i[7], v[5], fmaf(-i[8], v[4], fmaf(i[4], v[2], fmaf(i[0], v[0], i[3] * v[1]))));
+  r[1] = fmaf(-i[6], v[5], fmaf(i[8], v[3], fmaf(i[5], v[2], fmaf(i[3], v[0], i[1] * v[1]))));
+  r[2] = fmaf(i[6], v[4], fmaf(-i[7], v[3], fmaf(i[2], v[2], fmaf(i[4], v[0], i[5] * v[1]))));
+  r[3] = fmaf(i[9], v[3], fmaf(i[8], v[1], -(i[7] * v[2])));
+  r[4] = fmaf(i[9], v[4], fmaf(i[6], v[2], -(i[8] * v[0])));
+  r[5] = fmaf(i[9], v[5], fmaf(i[7], v[0], -(i[6] * v[1])));
 }
 static void axpy6(float* a, const float* b, float s) {
   for (int k = 0; k < 6; ++k) a[k] = fmaf(b[k], s, a[k]);

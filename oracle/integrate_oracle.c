@@ -51,7 +51,7 @@ int oracle_implicit_matrix(const ImnImplicit* p, const float* M, int64_t M_ld, f
         const int e = p->M_elemid[i * p->nv + i];
         qd[e] = qd[e] - p->dof_damping[i];
       }
-    for (int e = 0; e < p->nM; ++e) out[(size_t)w * out_ld + e] = M[(size_t)w * M_ld + e] - p->timestep * qd[e];
+    for (int e = 0; e < p->nM; ++e) out[(size_t)w * out_ld + e] = M[(size_t)w * M_ld + e] - p->timestep[w % p->n_timestep] * qd[e];
   }
   free(qd);
   return 0;
@@ -78,8 +78,8 @@ static void quat_integrate(float q[4], const float w[3], float h) {
 }
 
 int oracle_advance(const ImnAdvance* p, const float* qacc, int64_t qacc_ld, int nworld) {
-  const float h = p->timestep;
   for (int w = 0; w < nworld; ++w) {
+    const float h = p->timestep[w % p->n_timestep];
     for (int j = 0; j < p->njnt; ++j) {
       const int type = p->jnt_type[j], dof = p->jnt_dofadr[j], pos = p->jnt_qposadr[j];
       float* qvel = p->qvel + (size_t)w * p->qvel_ld + dof;

@@ -58,6 +58,20 @@ static void eliminate(TreeCtx* t, int k, int j) {
   }
 }
 
+/* x_k = s_k d_k - sum_p m_p x_anc(p)  (tree_ldl.py:258-266, 297-303).  The reference
+ * writes "x = s * d; x = x - m0 * x0; x = x - m1 * x1; ..."; compiled with contraction
+ * on, the first difference of two products fuses its LEFT product -- fma(s, d, -(m0 x0)),
+ * the right product rounded on its own -- and every later term is fma(-m, x, acc).
+ * Established against the reference's generated code run on a B200
+ * (tests/golden/ref_snippets.npz). */
+static float back_substitute(const TreeCtx* t, int k) {
+  const int start = t->rowadr[k], count = t->rownnz[k] - 1;
+  if (count == 0) return t->s[k] * t->d[k];
+  float u = fmaf(t->s[k], t->d[k], -(t->m[start] * t->x[t->colind[start]]));
+  for (int p = 1; p < count; ++p) u = fmaf(-t->m[start + p], t->x[t->colind[start + p]], u);
+  return u;
+}
+
 int oracle_tree_ldl_solve(int nv, int nM, const int* rowadr, const int* rownnz, const int* colind,
                           int ngroups, const int* group_ptr, const int* group_nodes, int ntrunk,
                           const int* trunk, const float* M, int64_t M_ld, const float* y, int64_t y_ld,
@@ -120,16 +134,14 @@ int oracle_tree_ldl_solve(int nv, int nM, const int* rowadr, const int* rownnz, 
     for (int i = ntrunk - 1; i >= 0; --i) eliminate(&t, trunk[i], -1);
     for (int i = 0; i < ntrunk; ++i) {
       const int k = trunk[i];
-      float u = t.s[k] * t.d[k];
-      for (int p = 0; p < rownnz[k] - 1; ++p) u = fmaf(-t.m[rowadr[k] + p], t.x[colind[rowadr[k] + p]], u);
+      const float u = back_substitute(&t, k);
       t.x[k] = u;
       xr[k] = u;
     }
     for (int j = 0; j < ngroups; ++j)
       for (int n = group_ptr[j + 1] - 1; n >= group_ptr[j]; --n) {
         const int k = group_nodes[n];
-        float u = t.s[k] * t.d[k];
-        for (int p = 0; p < rownnz[k] - 1; ++p) u = fmaf(-t.m[rowadr[k] + p], t.x[colind[rowadr[k] + p]], u);
+        const float u = back_substitute(&t, k);
         t.x[k] = u;
         xr[k] = u;
       }

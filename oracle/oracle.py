@@ -152,6 +152,48 @@ def com_vel(m: Any, d: Any, scratch: Any) -> None:
        d.cdof_dot.ctypes.data, d.nworld)
 
 
+def sparse_stage(plan_struct, stage: int, x: dict, grad, U, nv: int):
+    """One stage of the fused sparse path on host arrays (oracle_sparse_stage): 3 initial
+    assembly + factor + solve, 0 update with flipped rows + refactor + solve, 1 solve with
+    the factor stored in U.  ``x`` holds J, D, state, nefc, M, ids, count, uni; U is
+    updated in place.  Returns (search, search_dot, decrement)."""
+    import numpy as np
+
+    W = U.shape[0]
+    search = np.zeros((W, nv), np.float32)
+    sd, dec = np.zeros(W, np.float32), np.zeros(W, np.float32)
+    fn = lib().oracle_sparse_stage
+    fn.restype = C.c_int
+    fn.argtypes = [C.POINTER(abi.ImnSparsePlan), C.c_int, abi.P, C.c_int, abi.P, abi.P, abi.P, abi.P, C.c_int, abi.P,
+                   abi.P, abi.P, abi.P, abi.I64, abi.P, abi.P, abi.P, abi.P, C.c_int]
+    c = lambda a: np.ascontiguousarray(a).ctypes.data  # noqa: E731
+    keep = {k: np.ascontiguousarray(v) for k, v in x.items()}
+    grad = np.ascontiguousarray(grad, np.float32)
+    fn(C.byref(plan_struct), int(stage), c(keep["J"]), keep["J"].shape[1], c(keep["D"]), c(keep["state"]),
+       c(keep["nefc"]), c(keep["M"]), keep["M"].shape[1], c(keep["ids"]), c(keep["count"]), c(keep["uni"]),
+       grad.ctypes.data, grad.shape[1], U.ctypes.data, search.ctypes.data, sd.ctypes.data, dec.ctypes.data, W)
+    return search, sd, dec
+
+
+def sparse_factor_nonfused(plan_struct, grad, h, U, nv: int, quad_changed=None, skip_unchanged: bool = False):
+    """The non-fused factor / solve on host arrays; U updated in place."""
+    import numpy as np
+
+    W = U.shape[0]
+    search = np.zeros((W, nv), np.float32)
+    sd, dec = np.zeros(W, np.float32), np.zeros(W, np.float32)
+    grad, h = np.ascontiguousarray(grad, np.float32), np.ascontiguousarray(h, np.float32)
+    qc = None if quad_changed is None else np.ascontiguousarray(quad_changed, np.int32)
+    fn = lib().oracle_sparse_factor_nonfused
+    fn.restype = C.c_int
+    fn.argtypes = [C.POINTER(abi.ImnSparsePlan)] + [abi.P] * 2 + [abi.I64] + [abi.P] * 5 + [abi.I64, abi.P, abi.P,
+                                                                                          C.c_int, C.c_int, C.c_int]
+    fn(C.byref(plan_struct), None, grad.ctypes.data, grad.shape[1], h.ctypes.data,
+       None if qc is None else qc.ctypes.data, None, U.ctypes.data, search.ctypes.data, nv, sd.ctypes.data,
+       dec.ctypes.data, W, int(bool(skip_unchanged)), 0)
+    return search, sd, dec
+
+
 def _i32(a):
     import numpy as np
 

@@ -186,3 +186,57 @@ int oracle_sparse_factor_nonfused(const ImnSparsePlan* P, const uint8_t* done, c
   free(N), free(iD);
   return 0;
 }
+
+/* One stage of the fused path per world, for stage-level checks against the reference's
+ * own generated code (sparse_hessian.py:483-547 factor_snippet, :571-637 init_snippet):
+ *   stage 0  incremental update of the packed H in U with the flipped rows `ids` over
+ *            the dof union `uni`, refactor, solve;
+ *   stage 1  the factor is reloaded from U (the reference's mode 2), forward solve with
+ *            it (mode 1), solve;
+ *   stage 3  initial assembly H = M + J'DJ on the pattern, factor, solve; U receives
+ *            packed H | N | 1/D.
+ * J (W, njmax, nv), D / state / ids (W, njmax), uni (W, nv + 1), M (W, nM), grad
+ * (W, grad_ld), U (W, P, P), search (W, nv).  The violation counter in U's last element
+ * counts as in the kernels. */
+int oracle_sparse_stage(const ImnSparsePlan* P, int stage, const float* J, int njmax, const float* D,
+                        const int32_t* state, const int32_t* nefc, const float* M, int nM, const int32_t* ids,
+                        const int32_t* count, const int32_t* uni, const float* grad, int64_t grad_ld, float* U,
+                        float* search, float* search_dot, float* decrement, int nworld) {
+  const int P2 = P->nv_pad * P->nv_pad, nfac = P->nfac, n = P->nv;
+  float* N = (float*)malloc(sizeof(float) * P->nslots);
+  float* iD = (float*)malloc(sizeof(float) * n);
+  for (int w = 0; w < nworld; ++w) {
+    const float* g = grad + (size_t)w * grad_ld;
+    const float* Jw = J ? J + (size_t)w * njmax * n : NULL;
+    const float* Dw = D ? D + (size_t)w * njmax : NULL;
+    const int32_t* sw = state ? state + (size_t)w * njmax : NULL;
+    float* Uf = U + (size_t)w * P2;
+    if (stage == 3) {
+      const int rows = nefc[w] < njmax ? nefc[w] : njmax;
+      const int bad = sparse_assemble(P, N, M + (size_t)w * nM, Jw, n, Dw, sw, rows);
+      Uf[P2 - 1] += (float)bad;
+      for (int s = 0; s < nfac; ++s) Uf[s] = N[s];
+      sparse_load_rhs(P, N, g);
+      sparse_factor_levels(P, N, iD);
+      for (int s = 0; s < nfac; ++s) Uf[nfac + s] = N[s];
+      for (int j = 0; j < n; ++j) Uf[2 * nfac + j] = iD[j];
+    } else if (stage == 0) {
+      const int32_t* u = uni + (size_t)w * (n + 1);
+      const int bad = sparse_update(P, Uf, Jw, n, Dw, sw, ids + (size_t)w * njmax, count[w], u, u[n]);
+      Uf[P2 - 1] += (float)bad;
+      for (int s = 0; s < nfac; ++s) N[s] = Uf[s];
+      sparse_load_rhs(P, N, g);
+      sparse_factor_levels(P, N, iD);
+    } else {
+      for (int s = 0; s < nfac; ++s) N[s] = Uf[nfac + s];
+      for (int j = 0; j < n; ++j) iD[j] = Uf[2 * nfac + j];
+      sparse_forward(P, N, iD, g);
+    }
+    float sums[2];
+    sparse_backward(P, N, iD, g, search + (size_t)w * n, P->block, sums);
+    search_dot[w] = sums[0];
+    decrement[w] = sums[1];
+  }
+  free(N), free(iD);
+  return 0;
+}

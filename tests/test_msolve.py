@@ -126,6 +126,8 @@ def test_compiled_program_matches_the_plan_interpreter(oracle):
                     col[dst] = col[a] * col[b]
                 elif op == tree_ldl.OP_ADD:
                     col[dst] = col[dst] + col[a]
+                elif op == tree_ldl.OP_MULSUB:
+                    col[dst] = col[a] * col[b] - col[dst]
                 elif op == tree_ldl.OP_STORE_X:
                     x[:, dst] = col[a]
 
@@ -180,7 +182,7 @@ def test_plan_compiles_to_a_straight_line_kernel_without_a_gpu():
     assert info["code_bytes"] > 0
     assert 0 < info["shared_slots"] < program.nslot // 2
     src = info["source"]
-    assert src.count("fmaf(") == int(((prog[:, 0] == tree_ldl.OP_UPD) | (prog[:, 0] == tree_ldl.OP_SUBMUL)).sum())
+    assert src.count("fmaf(") == int(np.isin(prog[:, 0], (tree_ldl.OP_UPD, tree_ldl.OP_SUBMUL, tree_ldl.OP_MULSUB)).sum())
     assert src.count("bar.sync") == 2 * len(plan.groups)
     # malformed programs are rejected before any compilation
     from instantmimic_b200 import _lib
