@@ -133,12 +133,20 @@ __device__ __forceinline__ void sweep_up(const ImnBodyTree& T, float* v, int C, 
   }
 }
 
+// Per-world runs are a few hundred floats: four loads in flight per lane, so that a warp
+// keeps its whole run outstanding instead of one 128-byte line at a time.
 __device__ __forceinline__ void copy_in(float* dst, const float* __restrict__ src, int n, int lane) {
+  int i = lane;
 #pragma unroll 1
-  for (int i = lane; i < n; i += 32) dst[i] = src[i];
+  for (; i + 96 < n; i += 128) {
+    const float a = src[i], b = src[i + 32], c = src[i + 64], d = src[i + 96];
+    dst[i] = a, dst[i + 32] = b, dst[i + 64] = c, dst[i + 96] = d;
+  }
+#pragma unroll 1
+  for (; i < n; i += 32) dst[i] = src[i];
 }
 __device__ __forceinline__ void copy_out(float* __restrict__ dst, const float* src, int n, int lane) {
-#pragma unroll 1
+#pragma unroll 4
   for (int i = lane; i < n; i += 32) dst[i] = src[i];
 }
 

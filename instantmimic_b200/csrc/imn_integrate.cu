@@ -42,27 +42,59 @@ __global__ void __launch_bounds__(32 * kMatrixWarps)
     const int* colind = P.moment_colind + (size_t)w * P.moment_ld;
     const float* moment = P.actuator_moment + (size_t)w * P.moment_ld;
     const float* gain = P.actuator_velocity_gain + (size_t)w * P.nu;
+    // Actuators are taken 32 at a time, in ascending order.  A batch whose actuators all
+    // act on a single dof (position / velocity servos: the usual case) is added in one
+    // step: lane = actuator, lanes that hit the same diagonal entry are ranked by lane and
+    // add one rank after the other, which is ascending actuator order.  Any other batch
+    // goes actuator by actuator.
 #pragma unroll 1
-    for (int a = 0; a < P.nu; ++a) {
-      const float vel = gain[a];
-      const int n = rownnz[a];
-      if (vel == 0.0f || n <= 0) continue;  // warp-uniform
-      const int base = rowadr[a];
-      // pairs (ri >= rj) of the actuator's moment row; distinct pairs hit distinct
-      // entries of M, so the lanes never collide within one actuator
+    for (int a0 = 0; a0 < P.nu; a0 += 32) {
+      const int a = a0 + lane;
+      const bool mine = a < P.nu;
+      const int n_mine = mine ? rownnz[a] : 0;
+      const float vel_mine = mine ? gain[a] : 0.0f;
+      if (__all_sync(IMN_FULL_MASK, n_mine <= 1)) {
+        int e = -1;
+        float c = 0.0f;
+        if (n_mine == 1 && vel_mine != 0.0f) {
+          const int base = rowadr[a], di = colind[base];
+          e = P.M_elemid[di * P.nv + di];
+          c = (moment[base] * moment[base]) * vel_mine;
+          if (c == 0.0f) e = -1;
+        }
+        const unsigned peers = __match_any_sync(IMN_FULL_MASK, e);
+        const int rank = __popc(peers & ((1u << lane) - 1u));
+        const int rounds = __reduce_max_sync(IMN_FULL_MASK, e >= 0 ? __popc(peers) : 0);
 #pragma unroll 1
-      for (int p = lane; p < n * (n + 1) / 2; p += 32) {
-        int ri = (int)((sqrtf(8.0f * (float)p + 1.0f) - 1.0f) * 0.5f);
-        while ((ri + 1) * (ri + 2) / 2 <= p) ++ri;
-        while (ri * (ri + 1) / 2 > p) --ri;
-        const int rj = p - ri * (ri + 1) / 2;
-        const int di = colind[base + ri], dj = colind[base + rj];
-        const int e = P.M_elemid[di * P.nv + dj];
-        if (e < 0) continue;
-        const float c = (moment[base + ri] * moment[base + rj]) * vel;
-        if (c != 0.0f) qd[e] = qd[e] + c;
+        for (int r = 0; r < rounds; ++r) {
+          if (e >= 0 && rank == r) qd[e] = qd[e] + c;
+          __syncwarp();
+        }
+        continue;
       }
-      __syncwarp();
+      const int a1 = min(a0 + 32, P.nu);
+#pragma unroll 1
+      for (int s = a0; s < a1; ++s) {
+        const float vel = gain[s];
+        const int n = rownnz[s];
+        if (vel == 0.0f || n <= 0) continue;  // warp-uniform
+        const int base = rowadr[s];
+        // pairs (ri >= rj) of the actuator's moment row; distinct pairs hit distinct
+        // entries of M, so the lanes never collide within one actuator
+#pragma unroll 1
+        for (int p = lane; p < n * (n + 1) / 2; p += 32) {
+          int ri = (int)((sqrtf(8.0f * (float)p + 1.0f) - 1.0f) * 0.5f);
+          while ((ri + 1) * (ri + 2) / 2 <= p) ++ri;
+          while (ri * (ri + 1) / 2 > p) --ri;
+          const int rj = p - ri * (ri + 1) / 2;
+          const int di = colind[base + ri], dj = colind[base + rj];
+          const int e = P.M_elemid[di * P.nv + dj];
+          if (e < 0) continue;
+          const float c = (moment[base + ri] * moment[base + rj]) * vel;
+          if (c != 0.0f) qd[e] = qd[e] + c;
+        }
+        __syncwarp();
+      }
     }
   }
   if (P.damper)
@@ -74,6 +106,7 @@ __global__ void __launch_bounds__(32 * kMatrixWarps)
   const float* Mw = M + (size_t)w * M_ld;
   float* ow = out + (size_t)w * out_ld;
   const float h = P.timestep[w % P.n_timestep];
+#pragma unroll 4
   for (int e = lane; e < P.nM; e += 32) ow[e] = Mw[e] - h * qd[e];
 }
 

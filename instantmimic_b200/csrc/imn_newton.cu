@@ -508,8 +508,11 @@ __global__ void __launch_bounds__(32, IMN_RESIDENT_MIN_BLOCKS) newton_kernel_res
                                                                    const Geom g, const ImnSparsePlan sp) {
   newton_worlds<true, SPARSE, STATS>(m, d, cx, g, sp);
 }
+#ifndef IMN_STREAMED_MIN_BLOCKS
+#define IMN_STREAMED_MIN_BLOCKS 16
+#endif
 template <bool SPARSE, bool STATS>
-__global__ void __launch_bounds__(32, 16) newton_kernel_streamed(const ImnModel m, const ImnData d, const ImnCtx cx,
+__global__ void __launch_bounds__(32, IMN_STREAMED_MIN_BLOCKS) newton_kernel_streamed(const ImnModel m, const ImnData d, const ImnCtx cx,
                                                                  const Geom g, const ImnSparsePlan sp) {
   newton_worlds<false, SPARSE, STATS>(m, d, cx, g, sp);
 }

@@ -10,7 +10,10 @@
  *                   217-493 (gather through the block-major index table, upper
  *                   Cholesky, forward and backward substitution)
  *
- * Parity pins: both are checked against numpy.linalg.solve of the dense matrix
+ * Parity pins: the tree L'DL is PINNED bit for bit against the reference's own generated
+ * CUDA code, compiled with nvcc and run on a B200 (oracle/ref_snippets.py,
+ * tests/golden/ref_snippets.npz, tests/test_ref_snippets.py).  Both paths are also
+ * checked against numpy.linalg.solve of the dense matrix
  * (the reference's own tests use the same pin, tests/test_tree_ldl.py:99-120 and
  * tests/test_blocked_dense_factor_solve.py:616-626).  PARITY UNPINNED at the bit
  * level for the blocked dense path: Warp's tile_cholesky / tile_matmul internal

@@ -20,9 +20,11 @@
  * math.py), whose source is not part of the reference tree and is not
  * installed.  Functions marked RESTATED follow MuJoCo's published convex
  * solver (pyramidal cones, piecewise-quadratic row costs) and the argument
- * lists visible at the reference's call sites.  What IS pinned: the KKT
- * residual of converged solves against an independent float64 solver, and
- * the self-contained linear-algebra pieces against numpy.
+ * lists visible at the reference's call sites.  What IS pinned: the sparse-pattern
+ * Hessian factor stages this file calls (sparse_oracle.c) bit for bit against the
+ * reference's own generated CUDA code run on a B200; the KKT residual of converged
+ * solves against an independent float64 solver; the self-contained linear-algebra
+ * pieces against numpy.
  *
  * Rounding contract (shared with the CUDA kernels): compile with
  * -ffp-contract=off; every fused multiply-add is an explicit fmaf(); sqrtf and

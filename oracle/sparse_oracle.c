@@ -10,6 +10,10 @@
  *   initial assembly on pattern slots   :571-637
  *   incremental update of packed H      :501-527
  *   non-fused gather / reload           :651-676
+ * PINNED bit for bit against that generated CUDA code, compiled with nvcc and run on a
+ * B200 (oracle/ref_snippets.py, tests/golden/ref_snippets.npz, tests/test_ref_snippets.py):
+ * initial assembly, update with flipped rows, solve with the resident factor, non-fused
+ * factor and solve-only call, on four models.
  * Entries hold N = L D; an entry's terms are summed by a team of T lanes (lane tl
  * takes elements tl, tl+T, ... of every run) and joined by a shuffle-down tree of
  * width T, which this file reproduces lane by lane.

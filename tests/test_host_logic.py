@@ -191,3 +191,25 @@ def test_constraint_rows_impossible_gate():
                    dict(nxn_pairid_filtered=np.array([[-2, -2], [-1, 4]], np.int32)),
                    dict(solver_compact=True), dict(opt=SimpleNamespace(run_collision_detection=False))):
         assert runtime._constraint_rows_impossible(SimpleNamespace(**{**vars(free), **change}), ()) is False, change
+
+
+def test_timestep_is_handed_over_as_an_array_and_model_tables_are_read_once():
+    """opt.timestep goes to the kernels as mujoco-warp stores it (a per-world float array);
+    constant model tables that host code has to look at are copied from the device once per
+    buffer, so that a step neither synchronises the stream nor breaks a graph capture."""
+    import torch
+
+    from instantmimic_b200 import arrays, binding
+
+    m, _, _ = synthetic.make_workload("humanoid", 2, seed=0)
+    ptr, n = binding._timestep(m)
+    assert ptr == m.opt.timestep.ctypes.data and n == 1
+    m.opt.timestep = 0.002
+    with pytest.raises(ValueError, match="float array"):
+        binding._timestep(m)
+    table = torch.arange(5, dtype=torch.int32)
+    first = arrays.table_to_host(table)
+    table += 1  # a later change of the buffer is not seen: the table is declared constant
+    assert arrays.table_to_host(table) is first and first.tolist() == [0, 1, 2, 3, 4]
+    host = np.arange(3)
+    assert arrays.table_to_host(host) is host

@@ -16,7 +16,7 @@ ADVANCE_TOL = 2e-6
 SOLVE_RTOL = 2e-4
 
 
-def _problem(worlds=70, nu=20, seed=3, damping=True):
+def _problem(worlds=70, nu=20, seed=3, damping=True, single=False):
     rng = np.random.default_rng(seed)
     m, d, Mdense = synthetic.make_workload("humanoid", worlds, seed=seed)
     m.dof_damping = rng.uniform(0.0, 2.0, m.nv).astype(np.float32) if damping else np.zeros(m.nv, np.float32)
@@ -26,7 +26,7 @@ def _problem(worlds=70, nu=20, seed=3, damping=True):
     chains = [[[] for _ in range(nu)] for _ in range(worlds)]
     for w in range(worlds):
         for a in range(nu):
-            want = 1 if rng.random() < 0.7 else int(rng.integers(2, 5))
+            want = 1 if single or rng.random() < 0.7 else int(rng.integers(2, 5))
             chain = [int(rng.integers(6, m.nv))]
             while len(chain) < want and parent[chain[-1]] >= 0:
                 chain.append(int(parent[chain[-1]]))
@@ -123,6 +123,27 @@ def test_oracle_matrix_and_advance_against_float64(oracle):
             assert np.abs(np.linalg.norm(d1.qpos[:, p : p + 4], axis=1) - 1).max() < 1e-5
         else:
             assert np.abs(d1.qpos[:, p] - (d.qpos[:, p] + h * v[:, k])).max() < 1e-5
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("nu", [33, 70])
+def test_cuda_single_dof_actuators_add_in_actuator_order(oracle, cuda_device, nu):
+    """Batches of single-dof actuators take the ranked one-step path; several actuators on
+    one dof (70 actuators on 28 dofs) must still add in ascending actuator order."""
+    import torch
+
+    from instantmimic_b200 import mjw_step_optimized as runtime
+
+    m, d, _, gain = _problem(nu=nu, single=True, seed=9)
+    assert (d.moment_rownnz == 1).all()
+    md, dd = mjw_model.to_device(m, cuda_device), mjw_model.to_device(copy.deepcopy(d), cuda_device)
+    scratch = runtime.make_optimized_fwd_position_scratch(md, dd, cuda_device)
+    runtime.attach_implicit_scratch(md, dd, scratch, cuda_device)
+    scratch.implicit_actuator_vel.copy_(torch.from_numpy(gain))
+    runtime.deriv_smooth_vel_dense_actuator_centric(md, dd, scratch.implicit_qderiv, scratch)
+    torch.cuda.synchronize()
+    A = oracle.implicit_matrix(m, d, gain)
+    np.testing.assert_array_equal(scratch.implicit_qderiv.cpu().numpy().view(np.uint32), A.view(np.uint32))
 
 
 @pytest.mark.gpu
