@@ -309,11 +309,15 @@ typedef struct ImnBodyTree {
   const int32_t* dof_parentid;  /* (nv) */
   const float* dof_armature;    /* (n_armature, nv), world w reads row w % n        */
   int32_t n_armature;
-  const int32_t* M_rownnz;      /* (nv) */
-  const int32_t* M_rowadr;      /* (nv) */
+  const int32_t* M_rowidx;      /* (nM) dof (row) of every stored entry of M        */
+  const int32_t* M_colind;      /* (nM) its column: an ancestor of the row, or itself */
   const float* gravity;         /* (n_gravity, 3) opt.gravity, world w reads w % n  */
   int32_t n_gravity;
   int32_t gravity_enabled;      /* !(opt.disableflags & GRAVITY)                    */
+  int32_t team_lanes;           /* lanes of a warp that work on one world: 8, 16 or
+                                 * 32 (any other value: 32); pass the smallest that
+                                 * covers the widest level.  rne (16) and crb (32) raise
+                                 * it to their own minimum.  Results do not depend on it   */
 } ImnBodyTree;
 
 /* Directional ball-joint limits (ball_limits.py:205-318 BallLimitBuffers /

@@ -203,8 +203,8 @@ class ImnBodyTree(C.Structure):
         ("nbody", I32), ("nv", I32), ("nM", I32), ("nlevels", I32), ("body_parentid", P), ("level_bodies", P),
         ("level_offsets", P), ("child_ptr", P), ("child_ids", P), ("body_jntnum", P), ("body_jntadr", P),
         ("body_dofadr", P), ("body_dofnum", P), ("jnt_type", P), ("dof_bodyid", P), ("dof_parentid", P),
-        ("dof_armature", P), ("n_armature", I32), ("M_rownnz", P), ("M_rowadr", P), ("gravity", P),
-        ("n_gravity", I32), ("gravity_enabled", I32),
+        ("dof_armature", P), ("n_armature", I32), ("M_rowidx", P), ("M_colind", P), ("gravity", P),
+        ("n_gravity", I32), ("gravity_enabled", I32), ("team_lanes", I32),
     ]
 
 

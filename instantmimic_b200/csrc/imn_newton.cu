@@ -509,7 +509,7 @@ __global__ void __launch_bounds__(32, IMN_RESIDENT_MIN_BLOCKS) newton_kernel_res
   newton_worlds<true, SPARSE, STATS>(m, d, cx, g, sp);
 }
 #ifndef IMN_STREAMED_MIN_BLOCKS
-#define IMN_STREAMED_MIN_BLOCKS 16
+#define IMN_STREAMED_MIN_BLOCKS 12
 #endif
 template <bool SPARSE, bool STATS>
 __global__ void __launch_bounds__(32, IMN_STREAMED_MIN_BLOCKS) newton_kernel_streamed(const ImnModel m, const ImnData d, const ImnCtx cx,

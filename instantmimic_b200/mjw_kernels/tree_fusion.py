@@ -40,6 +40,8 @@ class TreeReductionScratch:
     # counterpart in the reference, which scans the whole next level for every parent
     child_ptr: Any = None
     child_ids: Any = None
+    # lanes of a warp per world: the smallest of 8, 16, 32 that covers the widest level
+    team_lanes: int = 32
     keep: tuple = field(default=(), repr=False, compare=False)
 
 
@@ -63,7 +65,9 @@ def level_tables(body_tree, body_parentid) -> dict[str, np.ndarray]:
             children[position[parent[body]]].append(body)
     child_ptr = np.cumsum([0] + [len(c) for c in children]).astype(np.int32)
     child_ids = np.asarray([b for c in children for b in c] or [0], dtype=np.int32)
-    return {"bodies": bodies, "offsets": offsets, "child_ptr": child_ptr, "child_ids": child_ids}
+    widest = max(len(level) for level in levels)
+    team = 8 if widest <= 8 else (16 if widest <= 16 else 32)
+    return {"bodies": bodies, "offsets": offsets, "child_ptr": child_ptr, "child_ids": child_ids, "team_lanes": team}
 
 
 def _place(table: np.ndarray, like: Any):
@@ -87,6 +91,7 @@ def create_tree_reduction_scratch(m: Any, *, deterministic: bool = False, cooper
         cooperative,
         _place(t["child_ptr"], m.body_parentid),
         _place(t["child_ids"], m.body_parentid),
+        int(t["team_lanes"]),
     )
 
 
@@ -105,6 +110,7 @@ def tree_struct(m: Any, scratch: TreeReductionScratch, *, dofs: bool = False, jo
     s.body_parentid = addr(m.body_parentid)
     s.level_bodies, s.level_offsets = addr(scratch.bodies), addr(scratch.offsets)
     s.child_ptr, s.child_ids = addr(scratch.child_ptr), addr(scratch.child_ids)
+    s.team_lanes = int(getattr(scratch, "team_lanes", 32))
     if dofs:
         s.nv = int(m.nv)
         s.body_dofadr, s.body_dofnum = addr(m.body_dofadr), addr(m.body_dofnum)
@@ -118,7 +124,7 @@ def tree_struct(m: Any, scratch: TreeReductionScratch, *, dofs: bool = False, jo
         if dims[-1] != m.nv or not is_contiguous(arm):
             raise ValueError("m.dof_armature must be a contiguous (n, nv) or (nv) array")
         s.dof_armature, s.n_armature = addr(arm), (dims[0] if len(dims) == 2 else 1)
-        s.M_rownnz, s.M_rowadr = addr(m.M_rownnz), addr(m.M_rowadr)
+        s.M_rowidx, s.M_colind = addr(m.M_hinit_i), addr(m.M_colind)
     if gravity:
         g = m.opt.gravity
         dims = shape(g)

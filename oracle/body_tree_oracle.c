@@ -88,7 +88,12 @@ int oracle_crb(const ImnBodyTree* T, const float* cinert, const float* cdof, flo
     for (int i = 0; i < T->nv; ++i) {
       float buf[6];
       inert_vec(c + 10 * T->dof_bodyid[i], dof + 6 * i, buf);
-      int adr = T->M_rowadr[i] + T->M_rownnz[i] - 1;
+      /* row i of M: the ancestors of i in ascending order, the diagonal last
+       * (tree_fusion.py:192-206 hands upstream's kernel M_rownnz / M_rowadr; here the
+       * row's end is found from the entry table) */
+      int adr = -1;
+      for (int e = 0; e < T->nM; ++e)
+        if (T->M_rowidx[e] == i && T->M_colind[e] == i) adr = e;
       Mw[adr] = arm[i] + dot6(dof + 6 * i, buf);
       for (int j = T->dof_parentid[i]; j >= 0; j = T->dof_parentid[j]) Mw[--adr] = dot6(dof + 6 * j, buf);
     }

@@ -262,6 +262,7 @@ def test_cuda_accumulate_bit_exact(kind, components, skip_root):
     dev = SimpleNamespace(body_parentid=torch.from_numpy(parents).to(_device()),
                           body_tree=[torch.from_numpy(x).to(_device()) for x in levels])
     scratch = tree_fusion.create_tree_reduction_scratch(dev, deterministic=True)
+    assert scratch.team_lanes == (32 if kind == "wide" else 8)
     for nworld in (3, 1027):
         initial = np.random.default_rng(7).uniform(0.1, 1.0, (nworld, COUNT, components)).astype(np.float32)
         values = torch.from_numpy(initial).to(_device())
@@ -293,11 +294,18 @@ def test_cuda_accumulate_cancellation_order():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", ["humanoid", "snu", "g1"])
-@pytest.mark.parametrize("nworld", [5, 2051])
-def test_cuda_smooth_stages_bit_exact(name, nworld):
+@pytest.mark.parametrize("nworld,team", [(5, None), (2051, None), (37, 16), (37, 32)])
+def test_cuda_smooth_stages_bit_exact(name, nworld, team):
+    """Every width of the per-world lane team (8 is what these models get; 16 and 32 forced)
+    and batches that leave the last warp with surplus teams."""
+    from dataclasses import replace
+
     m, d, scratch = smooth_case(name, nworld=nworld)
     md, dd = mjw_model.to_device(m, _device()), mjw_model.to_device(d, _device())
     sd = tree_fusion.create_tree_reduction_scratch(md, deterministic=True)
+    assert sd.team_lanes == 8
+    if team is not None:
+        sd = replace(sd, team_lanes=team)
     dd.M.fill_(float("nan"))  # every stored entry of M is written
     velocity_fusion.com_vel(md, dd, sd)
     tree_fusion.crb(md, dd, sd)
