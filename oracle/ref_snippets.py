@@ -244,6 +244,39 @@ def case_models():
         yield name, m, single(m)
     m, _, _ = synthetic.make_sweep_point(64, 32, 1)
     yield "limbs64", m, single(m)
+    # rows that couple two limbs (both feet, both hands with the head): the pattern gets
+    # entries outside the tree's own (fill), the factor levels wider teams
+    m, _, _ = synthetic.make_workload("humanoid", 1)
+    leaves = leaf_bodies(m)
+    yield "humanoid_pairs", m, [leaves[:2], leaves[2:]] + [[b] for b in range(1, len(m.body_dofadr)) if b not in leaves]
+
+
+def leaf_bodies(m) -> list[int]:
+    parents = set(np.asarray(m.body_parentid)[1:].tolist())
+    return [b for b in range(1, len(m.body_dofadr)) if b not in parents]
+
+
+def body_chain(m, body: int) -> list[int]:
+    """Dofs of a body and of all its ancestors."""
+    first, count = int(m.body_dofadr[body]), int(m.body_dofnum[body])
+    dof, chain = first + count - 1, []
+    while dof >= 0:
+        chain.append(dof)
+        dof = int(m.dof_parentid[dof])
+    return sorted(chain)
+
+
+def rows_for_groups(m, groups, nworld: int, njmax: int, rng) -> np.ndarray:
+    """Constraint Jacobians whose rows stay inside the declared coupling: every row takes
+    one or two bodies of one group and is nonzero on the dofs of their chains."""
+    J = np.zeros((nworld, njmax, m.nv), np.float32)
+    for w in range(nworld):
+        for r in range(njmax):
+            group = groups[int(rng.integers(len(groups)))]
+            pick = rng.choice(group, size=min(len(group), int(rng.integers(1, 3))), replace=False)
+            dofs = sorted({d for b in pick for d in body_chain(m, int(b))})
+            J[w, r, dofs] = rng.normal(size=len(dofs))
+    return J
 
 
 def indent(text: str) -> str:

@@ -35,14 +35,16 @@ W = 6
 QUADRATIC = 1
 
 
-def inputs(name: str, case: dict):
+def inputs(name: str, case: dict, groups):
     """Seeded inputs of one case: a solver batch of the model with a plausible active set,
     a flip of a few rows, fresh gradients."""
     rng = np.random.default_rng(100 + case["index"])
     if name == "limbs64":
         m, d, Mdense = synthetic.make_sweep_point(64, 32, W, seed=3, couple=False)
     else:
-        m, d, Mdense = synthetic.make_workload(name, W, seed=3)
+        m, d, Mdense = synthetic.make_workload(name.split("_")[0], W, seed=3)
+    if name.endswith("_pairs"):
+        d.efc.J[:] = ref_snippets.rows_for_groups(m, groups, W, d.njmax, rng)
     nv, R, P = m.nv, d.njmax, m.nv_pad
     nefc = np.minimum(d.nefc, R).astype(np.int32)
     live = np.arange(R)[None, :] < nefc[:, None]
@@ -78,9 +80,10 @@ def main():
     lib = C.CDLL(str(ref_snippets.LIB))
     dev = torch.device("cuda:0")
     out = {}
+    groups_of = {name: groups for name, _, groups in ref_snippets.case_models()}
     for case in ref_snippets.manifest():
         name, c, nv, P = case["name"], case["index"], case["nv"], case["nv_pad"]
-        m, x = inputs(name, case)
+        m, x = inputs(name, case, groups_of[name])
         R = x["J"].shape[1]
         t = {k: torch.from_numpy(v).to(dev) for k, v in x.items()}
         ptr = lambda a: C.c_void_p(a.data_ptr())  # noqa: E731

@@ -12,10 +12,10 @@ import pytest
 
 from instantmimic_b200 import synthetic
 from instantmimic_b200.mjw_kernels import sparse_hessian, tree_ldl
-from oracle import oracle
+from oracle import oracle, ref_snippets
 
 GOLDEN = Path(__file__).parent / "golden" / "ref_snippets.npz"
-CASES = ["humanoid", "snu", "g1", "limbs64"]
+CASES = ["humanoid", "snu", "g1", "limbs64", "humanoid_pairs"]
 
 
 @pytest.fixture(scope="module")
@@ -24,12 +24,11 @@ def golden():
 
 
 def model_of(name):
-    if name == "limbs64":
-        m, _, _ = synthetic.make_sweep_point(64, 32, 1, couple=False)
-    else:
-        m, _, _ = synthetic.make_workload(name, 1)
-    groups = [[b] for b in range(1, len(m.body_dofadr))]
-    return m, groups
+    """Model and body groups of a case: the list the golden file was made from."""
+    for case, m, groups in ref_snippets.case_models():
+        if case == name:
+            return m, groups
+    raise KeyError(name)
 
 
 def inputs(g, name):
