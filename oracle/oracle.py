@@ -113,43 +113,44 @@ def _tree_call(name: str, argtypes):
 
 def body_tree_accumulate(m: Any, scratch: Any, values, components: int, skip_root_parent: bool) -> None:
     """values[:, parent] += values[:, body] in depth order, in place; values (W, nbody, C) host."""
+    from instantmimic_b200.arrays import addr, shape
     from instantmimic_b200.mjw_kernels import tree_fusion
 
     t = tree_fusion.tree_struct(m, scratch)
     fn = _tree_call("oracle_body_tree_accumulate", [abi.P, abi.I64, C.c_int, C.c_int, C.c_int])
-    fn(C.byref(t), values.ctypes.data, values.shape[1] * values.shape[2], int(components), int(bool(skip_root_parent)),
-       values.shape[0])
+    dims = shape(values)
+    fn(C.byref(t), addr(values), dims[1] * int(components), int(components), int(bool(skip_root_parent)), dims[0])
 
 
 def crb(m: Any, d: Any, scratch: Any) -> None:
     """d.crb and d.M of host containers."""
+    from instantmimic_b200.arrays import addr, elem_strides
     from instantmimic_b200.mjw_kernels import tree_fusion
 
     t = tree_fusion.tree_struct(m, scratch, dofs=True, inertia=True)
     fn = _tree_call("oracle_crb", [abi.P, abi.P, abi.P, abi.P, abi.I64, C.c_int])
-    fn(C.byref(t), d.cinert.ctypes.data, d.cdof.ctypes.data, d.crb.ctypes.data, d.M.ctypes.data, d.M.strides[0] // 4,
-       d.nworld)
+    fn(C.byref(t), addr(d.cinert), addr(d.cdof), addr(d.crb), addr(d.M), elem_strides(d.M)[0], d.nworld)
 
 
 def rne(m: Any, d: Any, scratch: Any) -> None:
     """d.cacc, d.cfrc_int, d.qfrc_bias of host containers."""
+    from instantmimic_b200.arrays import addr, elem_strides
     from instantmimic_b200.mjw_kernels import tree_fusion
 
     t = tree_fusion.tree_struct(m, scratch, dofs=True, gravity=True)
     fn = _tree_call("oracle_rne", [abi.P] * 5 + [abi.I64, abi.P, abi.P, abi.P, abi.I64, C.c_int])
-    fn(C.byref(t), d.cinert.ctypes.data, d.cvel.ctypes.data, d.cdof.ctypes.data, d.cdof_dot.ctypes.data,
-       d.qvel.ctypes.data, d.qvel.strides[0] // 4, d.cacc.ctypes.data, d.cfrc_int.ctypes.data,
-       d.qfrc_bias.ctypes.data, d.qfrc_bias.strides[0] // 4, d.nworld)
+    fn(C.byref(t), addr(d.cinert), addr(d.cvel), addr(d.cdof), addr(d.cdof_dot), addr(d.qvel), elem_strides(d.qvel)[0],
+       addr(d.cacc), addr(d.cfrc_int), addr(d.qfrc_bias), elem_strides(d.qfrc_bias)[0], d.nworld)
 
 
 def com_vel(m: Any, d: Any, scratch: Any) -> None:
     """d.cvel and d.cdof_dot of host containers."""
+    from instantmimic_b200.arrays import addr, elem_strides
     from instantmimic_b200.mjw_kernels import tree_fusion
 
     t = tree_fusion.tree_struct(m, scratch, dofs=True, joints=True)
     fn = _tree_call("oracle_com_vel", [abi.P, abi.I64, abi.P, abi.P, abi.P, C.c_int])
-    fn(C.byref(t), d.qvel.ctypes.data, d.qvel.strides[0] // 4, d.cdof.ctypes.data, d.cvel.ctypes.data,
-       d.cdof_dot.ctypes.data, d.nworld)
+    fn(C.byref(t), addr(d.qvel), elem_strides(d.qvel)[0], addr(d.cdof), addr(d.cvel), addr(d.cdof_dot), d.nworld)
 
 
 def sparse_stage(plan_struct, stage: int, x: dict, grad, U, nv: int):

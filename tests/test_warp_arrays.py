@@ -63,6 +63,47 @@ def test_structs_from_warp_style_buffers_equal_the_numpy_ones(oracle):
     np.testing.assert_array_equal(ctx.search.view(np.uint32), wctx.search.view(np.uint32))
 
 
+def test_body_tree_stages_on_warp_style_vector_arrays(oracle):
+    """mujoco-warp holds cinert, crb, cdof, cvel, ... as 2-D arrays of vector types (vec10,
+    spatial_vector): shape (nworld, nbody), the components folded into the dtype.  The
+    mirror must read them as the same bytes."""
+    import torch
+
+    from instantmimic_b200.mjw_kernels import tree_fusion
+
+    def vector_type(n):
+        return type(f"vec{n}", (ctypes.Array,), {"_type_": ctypes.c_float, "_length_": n})
+
+    def folded(a):
+        w = FakeWarpArray(torch.from_numpy(a), dtype=vector_type(a.shape[-1]))
+        w.shape, w.strides, w.ndim = a.shape[:-1], tuple(s for s in a.strides[:-1]), a.ndim - 1
+        return w
+
+    m, d, _ = synthetic.make_workload("humanoid", 3, seed=2)
+    synthetic.add_smooth_state(m, d, seed=4)
+    want = copy.deepcopy(d)
+    scratch = tree_fusion.create_tree_reduction_scratch(m, deterministic=True)
+    oracle.com_vel(m, want, scratch)
+    oracle.crb(m, want, scratch)
+    oracle.rne(m, want, scratch)
+    dw = copy.copy(d)
+    for name in ("cinert", "crb", "cdof", "cdof_dot", "cvel", "cacc", "cfrc_int"):
+        setattr(dw, name, folded(getattr(d, name)))
+    dw.qvel, dw.M, dw.qfrc_bias = FakeWarpArray(torch.from_numpy(d.qvel)), FakeWarpArray(torch.from_numpy(d.M)), \
+        FakeWarpArray(torch.from_numpy(d.qfrc_bias))
+    mw = wrap(m)
+    mw.body_tree = m.body_tree  # a list of arrays on the reference side too
+    sw = tree_fusion.create_tree_reduction_scratch(mw, deterministic=True)
+    assert tree_fusion._per_body(dw.cinert, 3, 14, 10, "d.cinert") == d.cinert.ctypes.data
+    oracle.com_vel(mw, dw, sw)
+    oracle.crb(mw, dw, sw)
+    oracle.rne(mw, dw, sw)
+    for name in ("cvel", "cdof_dot", "crb", "M", "cacc", "cfrc_int", "qfrc_bias"):
+        np.testing.assert_array_equal(getattr(d, name), getattr(want, name), err_msg=name)
+    with pytest.raises(ValueError, match="d.cvel"):
+        tree_fusion._per_body(folded(d.cvel[:, :5]), 3, 14, 6, "d.cvel")
+
+
 # ---------------------------------------------------------------------------- GPU
 
 
