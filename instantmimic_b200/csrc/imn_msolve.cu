@@ -71,7 +71,8 @@ __global__ void tree_ldl_kernel(const int4* __restrict__ prog, const int* __rest
 }
 
 // ---- blocked dense Cholesky ------------------------------------------------------
-// One warp per world, kWorldsPerCta worlds per CTA.  Shared memory of a world:
+// One warp per world (or two worlds per warp, see dense_factor_carry), four warps per
+// CTA.  Shared memory of a world:
 //   A    (n + carry + 1) x ldu.  U[r][c] (r <= c) at A[r*ldu + c]; the value column c
 //        starts from (M's column c above the diagonal, or right-hand side c - n) is
 //        kept transposed at A[(c+1)*ldu + r], so a lane reads the 16 rows of its
@@ -83,10 +84,16 @@ __global__ void tree_ldl_kernel(const int4* __restrict__ prog, const int* __rest
 // (that is the forward substitution); further ones, and mode 1, take the
 // substitution with the stored factor.  Every value receives its terms in the same
 // order as the plain row-by-row statement of the algorithm (ascending t).
-static const int kWorldsPerCta = 4;
+static const int kDenseWarps = 4;
 
+// LW lanes work on one world: 32 (a warp per world), or 16 for models whose n + carry
+// columns fit three columns per lane of a half-warp (<= 48), where a whole warp would leave
+// half its lanes without a column for most of the factorisation; a warp then factors two
+// worlds at once.  `l` is the lane within the team, `base` the team's first lane (shuffle
+// sources are base | lane-in-team).
+template <int LW>
 __device__ __forceinline__ void dense_factor_carry(float* A, float* dinv, const int n, const int nc, const int ldu,
-                                                   const int lane) {
+                                                   const int l, const int base) {
 #pragma unroll 1
   for (int b0 = 0; b0 < n; b0 += 16) {
     const int nr = min(16, n - b0);
@@ -96,8 +103,8 @@ __device__ __forceinline__ void dense_factor_carry(float* A, float* dinv, const 
     bool act[3], valid[3];
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
-      const int c = b0 + lane + 32 * k;
-      act[k] = b0 + 32 * k < nc;  // warp-uniform
+      const int c = b0 + l + LW * k;
+      act[k] = b0 + LW * k < nc;  // uniform over the team (and over the warp: one model)
       valid[k] = c < nc;
       cc[k] = valid[k] ? c : nc - 1;
       if (act[k]) {
@@ -136,10 +143,12 @@ __device__ __forceinline__ void dense_factor_carry(float* A, float* dinv, const 
             }
         }
     }
-    // the block's own rows, one by one; acc[k][0] is always the current row
+    // the block's own rows, one by one; acc[k][0] is always the current row.  Row b0 + r's
+    // column is held by lane r of the team (k = 0); the rows below it inside the block by
+    // lanes r + 1 .. 15 (later sources wrap and feed slots that are never read).
 #pragma unroll 1
     for (int r = 0; r < nr; ++r) {
-      const float pv = __shfl_sync(IMN_FULL_MASK, acc[0][0], r);
+      const float pv = __shfl_sync(IMN_FULL_MASK, acc[0][0], base | r);
       const float dg = sqrtf(pv);
       const float rinv = 1.0f / dg;
       float u[3];
@@ -148,13 +157,13 @@ __device__ __forceinline__ void dense_factor_carry(float* A, float* dinv, const 
       for (int k = 0; k < 3; ++k)
         if (act[k]) {
           u[k] = acc[k][0] * rinv;
-          if (k == 0 && lane == r) u[k] = dg;
+          if (k == 0 && l == r) u[k] = dg;
           if (valid[k] && cc[k] >= b0 + r) Ur[cc[k]] = u[k];
         }
-      if (lane == 0) dinv[b0 + r] = rinv;
+      if (l == 0) dinv[b0 + r] = rinv;
       float um[16];
 #pragma unroll
-      for (int j = 1; j < 16; ++j) um[j] = __shfl_sync(IMN_FULL_MASK, u[0], (r + j) & 31);
+      for (int j = 1; j < 16; ++j) um[j] = __shfl_sync(IMN_FULL_MASK, u[0], base | ((r + j) & (LW - 1)));
 #pragma unroll
       for (int k = 0; k < 3; ++k)
         if (act[k]) {
@@ -167,24 +176,34 @@ __device__ __forceinline__ void dense_factor_carry(float* A, float* dinv, const 
   }
 }
 
-__global__ void __launch_bounds__(32 * kWorldsPerCta)
+template <int LW>
+__global__ void __launch_bounds__(32 * kDenseWarps)
     blocked_dense_kernel(const int nv, const int pad, const int nM, const int* __restrict__ indices,
                          const float* __restrict__ identity, const float* __restrict__ M, const int64_t M_ld,
                          const float* __restrict__ y, float* __restrict__ Ug, float* __restrict__ x,
                          const int* __restrict__ active, const int rhs, const int mode, const int carry,
                          const int ldu, const int per_world, const int nworld) {
   extern __shared__ __align__(16) float sm[];
-  const int lane = threadIdx.x & 31, w = blockIdx.x * kWorldsPerCta + (threadIdx.x >> 5);
-  if (w >= nworld) return;
-  if (active && active[w] == 0) return;
+  constexpr int kPer = 32 / LW;  // worlds per warp
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int l = lane & (LW - 1), base = lane & ~(LW - 1), sub = lane / LW;
+  const int first = (blockIdx.x * kDenseWarps + warp) * kPer;
+  if (first >= nworld) return;
+  const int wreal = first + sub;
+  // a team without a world, or with an inactive one, runs along on the warp's first
+  // world (the shuffles are full-warp) and stores nothing
+  bool live = wreal < nworld;
+  if (live && active && active[wreal] == 0) live = false;
+  if (!__any_sync(IMN_FULL_MASK, live)) return;
+  const int w = wreal < nworld ? wreal : first;
   const int n = nv, nc = n + carry;
-  float* A = sm + (threadIdx.x >> 5) * per_world;
+  float* A = sm + (warp * kPer + sub) * per_world;
   float* dinv = A + (nc + 1) * ldu;
   float* X = dinv + ((n + 3) & ~3);
   float* Uw = Ug + (size_t)w * pad * pad;
   const int nblk = pad >> 4;
   const float* yw = y + (size_t)w * n * rhs;
-  for (int q = lane; q < n * rhs; q += 32) X[q] = yw[q];
+  for (int q = l; q < n * rhs; q += LW) X[q] = yw[q];
   if (mode == 0) {
     // gather the blocks on and above the diagonal: table entry
     // ((kb*nblk + ib)*16 + r)*16 + c addresses M's value of (16 kb + r, 16 ib + c);
@@ -194,39 +213,41 @@ __global__ void __launch_bounds__(32 * kWorldsPerCta)
       for (int ib = kb; ib < nblk; ++ib) {
         const int* tab = indices + ((kb * nblk + ib) << 8);
 #pragma unroll 4
-        for (int q = lane; q < 256; q += 32) {
+        for (int q = l; q < 256; q += LW) {
           const int row = 16 * kb + (q >> 4), colm = 16 * ib + (q & 15);
           const int idx = __ldg(tab + q);
           if (row <= colm && colm < n) A[(colm + 1) * ldu + row] = idx < nM ? __ldg(Mw + idx) : 0.0f;
         }
       }
     __syncwarp();
-    for (int e = lane; e < n * carry; e += 32) {
+    for (int e = l; e < n * carry; e += LW) {
       const int r = e / carry, q = e - r * carry;
       A[(n + q + 1) * ldu + r] = X[r * rhs + q];
     }
     __syncwarp();
-    dense_factor_carry(A, dinv, n, nc, ldu, lane);
+    dense_factor_carry<LW>(A, dinv, n, nc, ldu, l, base);
     // the factor, padded: zeros below the diagonal, the padded diagonal's own root
-    for (int r = 0; r < n; ++r) {
-      const float* Ar = A + r * ldu;
-      float* Ur = Uw + r * pad;
+    if (live) {
+      for (int r = 0; r < n; ++r) {
+        const float* Ar = A + r * ldu;
+        float* Ur = Uw + r * pad;
 #pragma unroll 3
-      for (int c = lane; c < pad; c += 32) Ur[c] = (c >= r && c < n) ? Ar[c] : 0.0f;
+        for (int c = l; c < pad; c += LW) Ur[c] = (c >= r && c < n) ? Ar[c] : 0.0f;
+      }
+      for (int r = n; r < pad; ++r) {
+        const float dg = sqrtf(identity[((r & 15) << 4) | (r & 15)]);
+        for (int c = l; c < pad; c += LW) Uw[r * pad + c] = c == r ? dg : 0.0f;
+      }
     }
-    for (int r = n; r < pad; ++r) {
-      const float dg = sqrtf(identity[((r & 15) << 4) | (r & 15)]);
-      for (int c = lane; c < pad; c += 32) Uw[r * pad + c] = c == r ? dg : 0.0f;
-    }
-    for (int e = lane; e < n * carry; e += 32) {
+    for (int e = l; e < n * carry; e += LW) {
       const int r = e / carry, q = e - r * carry;
       X[r * rhs + q] = A[r * ldu + n + q];
     }
   } else {
     for (int r = 0; r < n; ++r)
-      for (int c = r + lane; c < n; c += 32) A[r * ldu + c] = Uw[r * pad + c];
+      for (int c = r + l; c < n; c += LW) A[r * ldu + c] = Uw[r * pad + c];
     __syncwarp();
-    for (int r = lane; r < n; r += 32) dinv[r] = 1.0f / A[r * ldu + r];
+    for (int r = l; r < n; r += LW) dinv[r] = 1.0f / A[r * ldu + r];
   }
   __syncwarp();
   // forward substitution with the stored factor for the right-hand sides that did
@@ -236,9 +257,9 @@ __global__ void __launch_bounds__(32 * kWorldsPerCta)
     const int nq = rhs - q0;
     for (int t = 0; t < n; ++t) {
       const float di = dinv[t];
-      for (int q = lane; q < nq; q += 32) X[t * rhs + q0 + q] = X[t * rhs + q0 + q] * di;
+      for (int q = l; q < nq; q += LW) X[t * rhs + q0 + q] = X[t * rhs + q0 + q] * di;
       __syncwarp();
-      for (int e = lane; e < (n - t - 1) * nq; e += 32) {
+      for (int e = l; e < (n - t - 1) * nq; e += LW) {
         const int r = t + 1 + e / nq, q = q0 + e % nq;
         X[r * rhs + q] = fmaf(-A[t * ldu + r], X[t * rhs + q], X[r * rhs + q]);
       }
@@ -246,14 +267,15 @@ __global__ void __launch_bounds__(32 * kWorldsPerCta)
     }
   }
   // back substitution in 16-row blocks from the last: later blocks' columns first
-  // (ascending), then the block's own columns from its last inwards; two right-hand
-  // sides at a time on the two half-warps
-  for (int qb = 0; qb < rhs; qb += 2) {
-    const int q = qb + (lane >> 4), l = lane & 15;
+  // (ascending), then the block's own columns from its last inwards; a team of 32 lanes
+  // takes two right-hand sides at a time on its two halves, a team of 16 one
+  constexpr int kRhsAtOnce = LW / 16;
+  for (int qb = 0; qb < rhs; qb += kRhsAtOnce) {
+    const int q = qb + (l >> 4), l16 = l & 15;
     const bool hasq = q < rhs;
     for (int b0 = ((n - 1) / 16) * 16; b0 >= 0; b0 -= 16) {
       const int b1 = min(b0 + 16, n);
-      const int r = b0 + l;
+      const int r = b0 + l16;
       const float* Ur = A + r * ldu;
       float acc = 0.0f, di = 0.0f;
       if (r < b1 && hasq) {
@@ -263,15 +285,17 @@ __global__ void __launch_bounds__(32 * kWorldsPerCta)
         for (int c = b1; c < n; ++c) acc = fmaf(-Ur[c], X[c * rhs + q], acc);
       }
       for (int c = b1 - 1; c >= b0; --c) {
-        const float xc = __shfl_sync(IMN_FULL_MASK, acc * di, (lane & 16) | (c - b0));
+        const float xc = __shfl_sync(IMN_FULL_MASK, acc * di, (lane & ~15) | (c - b0));
         if (r < c && hasq) acc = fmaf(-Ur[c], xc, acc);
-        if (l == 0 && hasq) X[c * rhs + q] = xc;
+        if (l16 == 0 && hasq) X[c * rhs + q] = xc;
       }
       __syncwarp();
     }
   }
-  float* xw = x + (size_t)w * n * rhs;
-  for (int q = lane; q < n * rhs; q += 32) xw[q] = X[q];
+  if (live) {
+    float* xw = x + (size_t)w * n * rhs;
+    for (int q = l; q < n * rhs; q += LW) xw[q] = X[q];
+  }
 }
 
 }  // namespace imn
@@ -324,24 +348,28 @@ extern "C" int imn_blocked_dense_factor_solve(const ImnBlockedPlan* plan, const 
   const int carry = mode == 0 ? (rhs_count < 96 - n ? rhs_count : 96 - n) : 0;
   const int ldu = (n + carry + 3) & ~3;
   const int per_world = (n + carry + 1) * ldu + ((n + 3) & ~3) + ((n * rhs_count + 3) & ~3);
-  const size_t bytes = sizeof(float) * (size_t)per_world * imn::kWorldsPerCta;
+  // two worlds per warp when every column of the factorisation has a place on 16 lanes
+  // and the batch is large enough to keep the GPU full that way
+  const bool half = n + carry <= 48 && nworld >= 2048;
+  const int per_cta = imn::kDenseWarps * (half ? 2 : 1);
+  const size_t bytes = sizeof(float) * (size_t)per_world * per_cta;
+  auto kernel = half ? imn::blocked_dense_kernel<16> : imn::blocked_dense_kernel<32>;
   if (bytes > 227 * 1024)
     return imn::set_error("imn_blocked_dense_factor_solve: %zu bytes of shared memory needed (max %d)", bytes,
                           227 * 1024),
            IMN_ERR_LIMIT;
   {
-    cudaError_t e = cudaFuncSetAttribute(imn::blocked_dense_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                          cudaSharedmemCarveoutMaxShared);
     if (e == cudaSuccess && bytes > 48 * 1024)
-      e = cudaFuncSetAttribute(imn::blocked_dense_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
     if (e != cudaSuccess)
       return imn::set_error("imn_blocked_dense_factor_solve: cudaFuncSetAttribute: %s", cudaGetErrorString(e)),
              IMN_ERR_LAUNCH;
   }
-  imn::blocked_dense_kernel<<<(nworld + imn::kWorldsPerCta - 1) / imn::kWorldsPerCta, 32 * imn::kWorldsPerCta, bytes,
-                              (cudaStream_t)stream>>>(plan->nv, plan->pad, plan->nM, plan->indices, plan->identity, M,
-                                                      M_ld, y, U, x, active, rhs_count, mode, carry, ldu, per_world,
-                                                      nworld);
+  kernel<<<(nworld + per_cta - 1) / per_cta, 32 * imn::kDenseWarps, bytes, (cudaStream_t)stream>>>(
+      plan->nv, plan->pad, plan->nM, plan->indices, plan->identity, M, M_ld, y, U, x, active, rhs_count, mode, carry, ldu,
+      per_world, nworld);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess)
     return imn::set_error("imn_blocked_dense_factor_solve: launch failed: %s", cudaGetErrorString(e)),

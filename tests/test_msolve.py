@@ -320,6 +320,41 @@ def test_blocked_kernel_matches_oracle_bitwise(oracle, cuda_device, nv, rhs):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("nv,rhs", [(32, 1), (35, 1), (35, 3), (47, 1), (47, 2), (56, 1)])
+def test_two_worlds_per_warp_return_the_same_bits(oracle, cuda_device, nv, rhs):
+    """From 2048 worlds on, models whose columns fit 16 lanes (nv + right-hand sides that ride
+    along <= 48) are factored two worlds per warp; (47, 2) and nv 56 stay on a warp per world.
+    An odd batch leaves the last warp with one world; inactive worlds are skipped."""
+    import torch
+
+    from instantmimic_b200 import mjw_model
+
+    worlds = 2051
+    m, Mv, Md, pad, layout, ident, y = _blocked_case(nv, worlds, rhs)
+    md = mjw_model.to_device(m, cuda_device)
+    dd = mjw_model.to_device(mjw_model.make_data(m, worlds, 4), cuda_device)
+    scratch = indexed_factor.create_blocked_dense_factor_solve_scratch(md, dd, cuda_device)
+    Mt, yt = torch.from_numpy(Mv).to(cuda_device), torch.from_numpy(y).to(cuda_device)
+    active = torch.ones(worlds, dtype=torch.int32, device=cuda_device)
+    off = [3, 4, 5, 40, 2049, 2050]  # a lone inactive world, an inactive pair, the ragged end
+    active[off] = 0
+    live = active.cpu().numpy() != 0
+    xt = torch.full_like(yt, 7.0)
+    U = torch.full((worlds, pad, pad), 5.0, dtype=torch.float32, device=cuda_device)
+    indexed_factor.factor_multi_solve(scratch, Mt, yt, active, U, xt, rhs)
+    torch.cuda.synchronize()
+    want_x, want_U = oracle.blocked_dense_factor_solve(nv, pad, layout, ident, Mv, y)
+    np.testing.assert_array_equal(xt.cpu().numpy()[live], want_x[live])
+    np.testing.assert_array_equal(xt.cpu().numpy()[~live], 7.0)
+    np.testing.assert_array_equal(U.cpu().numpy()[live], want_U[live])
+    np.testing.assert_array_equal(U.cpu().numpy()[~live], 5.0)
+    x2 = torch.zeros_like(yt)
+    indexed_factor.multi_solve(scratch, U, yt, active, x2, rhs)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(x2.cpu().numpy()[live], want_x[live])
+
+
+@pytest.mark.gpu
 def test_small_models_have_no_blocked_scratch(cuda_device):
     from instantmimic_b200 import mjw_model
 
