@@ -74,6 +74,7 @@ class OptimizedFwdPositionScratch:
     implicit_qderiv: Any = None
     implicit_qacc: Any = None
     implicit_actuator_vel: Any = None
+    implicit_gain_coefficients: Any = None  # (g2, b2) per actuator, prepared at set-up
     advance_call: Any = None
     pre_advance_modifier: Any = None
     # directional ball-joint limit rows (mjw_step_optimized.py:2241-2249)
@@ -427,7 +428,8 @@ def append_ball_limit_rows(m: Any, d: Any, scratch: OptimizedFwdPositionScratch,
 def attach_implicit_scratch(m: Any, d: Any, scratch: OptimizedFwdPositionScratch, device: Any = "cuda") -> None:
     """Buffers of the implicit-fast tail: ``implicit_qderiv`` (nworld, nM),
     ``implicit_qacc`` (nworld, nv) and, for actuated models, ``implicit_actuator_vel``
-    (nworld, nu)."""
+    (nworld, nu) with the per-actuator coefficients its values are formed from.  The
+    actuator tables are looked at here, once, so that a step reads nothing on the host."""
     import torch
 
     nM = int(m.M_colind.shape[0])
@@ -435,15 +437,14 @@ def attach_implicit_scratch(m: Any, d: Any, scratch: OptimizedFwdPositionScratch
     scratch.implicit_qacc = torch.zeros((d.nworld, m.nv), dtype=torch.float32, device=device)
     nu = int(getattr(m, "nu", 0) or 0)
     scratch.implicit_actuator_vel = torch.zeros((d.nworld, nu), dtype=torch.float32, device=device) if nu else None
+    scratch.implicit_gain_coefficients = None
+    if nu and getattr(m, "actuator_gaintype", None) is not None:
+        scratch.implicit_gain_coefficients = _velocity_gain_coefficients(m)
 
 
-def actuator_velocity_gain(m: Any, d: Any, out: Any) -> None:
-    """out[w, a] = d(actuator force)/d(actuator velocity): the ``vel`` buffer of upstream's
-    ``derivative._qderiv_actuator_passive_vel`` (call site mjw_step_optimized.py:4198-4225),
-    RESTATED from MuJoCo's actuator model for stateless actuators with fixed or affine
-    gain and bias: force = gain ctrl + bias with gain = g0 + g1 length + g2 velocity and
-    bias = b0 + b1 length + b2 velocity, hence g2 ctrl + b2.  Muscle and user types, and
-    actuators with activation dynamics, are refused."""
+def _velocity_gain_coefficients(m: Any):
+    """(g2, b2) per actuator with d(force)/d(velocity) = g2 ctrl + b2, as tensors next to
+    the model's tables; refuses actuator kinds whose derivative is upstream's."""
     from . import types as T
     from .arrays import as_torch, table_to_host
 
@@ -455,7 +456,24 @@ def actuator_velocity_gain(m: Any, d: Any, out: Any) -> None:
         raise RuntimeError("muscle and user actuators need upstream's velocity derivative")
     g2 = as_torch(m.actuator_gainprm)[..., 2] * as_torch(m.actuator_gaintype).eq(int(T.GainType.AFFINE))
     b2 = as_torch(m.actuator_biasprm)[..., 2] * as_torch(m.actuator_biastype).eq(int(T.BiasType.AFFINE))
-    as_torch(out).copy_(g2 * as_torch(d.ctrl) + b2)
+    return g2, b2
+
+
+def actuator_velocity_gain(m: Any, d: Any, out: Any, scratch: Any = None) -> None:
+    """out[w, a] = d(actuator force)/d(actuator velocity): the ``vel`` buffer of upstream's
+    ``derivative._qderiv_actuator_passive_vel`` (call site mjw_step_optimized.py:4198-4225),
+    RESTATED from MuJoCo's actuator model for stateless actuators with fixed or affine
+    gain and bias: force = gain ctrl + bias with gain = g0 + g1 length + g2 velocity and
+    bias = b0 + b1 length + b2 velocity, hence g2 ctrl + b2.  Muscle and user types, and
+    actuators with activation dynamics, are refused.  With a scratch whose coefficients
+    were prepared (``attach_implicit_scratch``) the call is device work only."""
+    from .arrays import as_torch
+
+    coefficients = getattr(scratch, "implicit_gain_coefficients", None) if scratch is not None else None
+    g2, b2 = coefficients if coefficients is not None else _velocity_gain_coefficients(m)
+    torch_out = as_torch(out)
+    torch_out.copy_(as_torch(d.ctrl))
+    torch_out.mul_(g2).add_(b2)
 
 
 def deriv_smooth_vel_dense_actuator_centric(m: Any, d: Any, out: Any, scratch: OptimizedFwdPositionScratch,
@@ -509,7 +527,7 @@ def implicitfast_integrate(m: Any, d: Any, scratch: OptimizedFwdPositionScratch,
     if scratch.implicit_qderiv is None or scratch.implicit_qacc is None:
         raise RuntimeError("implicit-fast scratch is not attached (attach_implicit_scratch)")
     if int(getattr(m, "nu", 0) or 0) and not (int(m.opt.disableflags) & B.upstream_constants()["disable_actuation"]):
-        actuator_velocity_gain(m, d, scratch.implicit_actuator_vel)
+        actuator_velocity_gain(m, d, scratch.implicit_actuator_vel, scratch)
     deriv_smooth_vel_dense_actuator_centric(m, d, scratch.implicit_qderiv, scratch, stream=stream)
     _factor_solve_i_dense(
         m, d, scratch.implicit_qderiv, scratch.implicit_qacc, d.efc.Ma, scratch.dense_factor_solve,
