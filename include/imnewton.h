@@ -538,6 +538,18 @@ typedef struct ImnLaunchInfo {
 int imn_launch_info(const ImnModel* m, const ImnData* d, const ImnCtx* ctx,
                     ImnLaunchInfo* out);
 
+/* No counterpart in the reference (its fused path takes a dense Jacobian that is already
+ * on the GPU).  For callers whose constraint rows are sparse on the host -- MuJoCo C with
+ * jacobian="sparse" stores efc_J as values + efc_J_colind + efc_J_rowadr -- so that only
+ * the nonzeros cross PCIe: writes `nrows` dense rows of `nv` floats (row stride `ld_row`
+ * floats) from the device copies of values, colind and rowadr (nrows + 1 starts).
+ * `colind_bytes` is 4 (int32, MuJoCo's) or 1 (uint8: a fused-path model has at most 79
+ * dofs, and a producer that emits bytes moves 5 instead of 8 bytes per nonzero).  Rows
+ * are cleared first; indices outside [0, nv) are skipped. */
+int imn_expand_rows(const float* values, const void* colind, int32_t colind_bytes,
+                    const int32_t* rowadr, int32_t nrows, int32_t nv, float* dense,
+                    int64_t ld_row, void* stream);
+
 /* No counterpart in the reference, whose solver buffers never leave the GPU.  For
  * callers that keep a batch in pinned host memory: copies the leading `width` bytes
  * of each of `nworld` per-world blocks (block strides `dst_pitch` / `src_pitch`

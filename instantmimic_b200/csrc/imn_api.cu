@@ -250,6 +250,50 @@ extern "C" int imn_rowless_handoff(const ImnModel* m, const ImnData* d, void* st
                            d->solver_niter, d->qfrc_constraint, d->nworld, (cudaStream_t)stream);
 }
 
+namespace imn {
+
+// Rows of a sparse Jacobian (values + column indices + row starts, the layout of MuJoCo
+// C's sparse mjData.efc_J) written out as dense rows: a warp clears its row, then
+// scatters the row's entries.  An index outside [0, nv) is skipped.
+template <typename Index>
+__global__ void __launch_bounds__(256)
+    expand_rows_kernel(const float* __restrict__ values, const Index* __restrict__ colind, const int* __restrict__ rowadr,
+                       const int nrows, const int nv, float* __restrict__ dense, const int64_t ld_row) {
+  const int lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (r >= nrows) return;
+  float* row = dense + (size_t)r * ld_row;
+  for (int c = lane; c < nv; c += 32) row[c] = 0.0f;
+  __syncwarp();
+  const int k1 = rowadr[r + 1];
+  for (int k = rowadr[r] + lane; k < k1; k += 32) {
+    const int c = (int)colind[k];
+    if (c >= 0 && c < nv) row[c] = values[k];
+  }
+}
+
+}  // namespace imn
+
+extern "C" int imn_expand_rows(const float* values, const void* colind, int32_t colind_bytes, const int32_t* rowadr,
+                               int32_t nrows, int32_t nv, float* dense, int64_t ld_row, void* stream) {
+  if (!values || !colind || !rowadr || !dense) return imn::set_error("imn_expand_rows: NULL buffer"), IMN_ERR_NULL;
+  if (nrows < 0 || nv <= 0 || ld_row < nv) return imn::set_error("imn_expand_rows: bad extent or stride"), IMN_ERR_SHAPE;
+  if (colind_bytes != 4 && colind_bytes != 1)
+    return imn::set_error("imn_expand_rows: column indices are int32 (4) or uint8 (1), not %d bytes", colind_bytes),
+           IMN_ERR_SHAPE;
+  if (colind_bytes == 1 && nv > 256) return imn::set_error("imn_expand_rows: nv %d does not fit 8-bit indices", nv), IMN_ERR_LIMIT;
+  if (nrows == 0) return IMN_OK;
+  if (colind_bytes == 4)
+    imn::expand_rows_kernel<int><<<(nrows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(
+        values, static_cast<const int*>(colind), rowadr, nrows, nv, dense, ld_row);
+  else
+    imn::expand_rows_kernel<uint8_t><<<(nrows + 7) / 8, 256, 0, (cudaStream_t)stream>>>(
+        values, static_cast<const uint8_t*>(colind), rowadr, nrows, nv, dense, ld_row);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return imn::set_error("imn_expand_rows: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  return IMN_OK;
+}
+
 extern "C" int imn_copy_rows(void* dst, int64_t dst_pitch, const void* src, int64_t src_pitch, int64_t width,
                              int32_t nworld, int32_t to_host, void* stream) {
   if (!dst || !src) return imn::set_error("imn_copy_rows: NULL buffer"), IMN_ERR_NULL;

@@ -16,13 +16,22 @@ construction:
   padded layout and copies rows ``[0, max nefc of the chunk)`` of chunks of worlds
   with strided copies (``imn_copy_rows`` = ``cudaMemcpy2DAsync``; tight when the caller
   groups its worlds by row count, slower per byte than a contiguous copy);
-  ``"whole"`` copies the padded array.  The per-row vectors (D, aref, frictionloss) are
-  copied whole: their per-world segments are a few hundred bytes.
+  ``"whole"`` copies the padded array; ``"sparse"`` keeps the rows on the host as values +
+  column indices + row starts (what MuJoCo C holds with ``jacobian="sparse"``: ``efc_J``,
+  ``efc_J_colind``, ``efc_J_rowadr``), copies those and writes the dense rows on the device
+  (``imn_expand_rows``), so that only the nonzeros cross PCIe; ``"sparse8"`` is the same with
+  the column indices as bytes (a fused-path model has at most 79 dofs): 5 instead of 8 bytes
+  per nonzero, for producers that emit their rows in this form.  The per-row vectors (D, aref, frictionloss) are copied whole: their
+  per-world segments are a few hundred bytes.
 * ``solve_with_scratch`` on the device buffers.
 * device -> host copies of the results (whole arrays).
 
 Slots are independent (own device buffers, stream and pinned result buffers), so the
-copies of one batch overlap the solve of another.
+copies of one batch overlap the solve of another.  A slot's chain is copy in -> solve ->
+copy out, so two slots keep the PCIe link busy only while the copy in is at least as long
+as solve + copy out; with the sparse modes (copy in about as long as the solve) take three.
+The sparse modes also move every input in ONE pinned buffer and every result in another
+(the device arrays are views of two device buffers): one copy each way per batch.
 """
 
 from __future__ import annotations
@@ -56,10 +65,61 @@ class HostBatch:
             return total + self.nworld * njmax * ldj * 4
         if mode == "rows":
             return total + sum(n * rows * 4 * ldj for _, n, rows in self.chunk_rows)
+        if mode in ("sparse", "sparse8"):
+            return int(self.tensors["packed_meta" if mode == "sparse" else "packed8_meta"][5])  # the one buffer copied
         return total + int(self.tensors["Jc"].numel()) * 4 + 8 * self.nworld
 
-    def d2h_bytes(self, nv: int, njmax: int) -> int:
+    def d2h_bytes(self, nv: int, njmax: int, mode: str = "compact") -> int:
+        if mode in ("sparse", "sparse8"):
+            return result_layout(self.nworld, njmax, nv)[1]
         return self.nworld * 4 * (3 * nv + 2 + 2 * njmax)
+
+
+_ALIGN = 256
+
+
+def _up(n: int) -> int:
+    return (n + _ALIGN - 1) // _ALIGN * _ALIGN
+
+
+def packed_layout(nworld: int, njmax: int, nv: int, nM: int) -> tuple[dict, int]:
+    """Byte offsets of the fixed-size inputs inside one packed transfer buffer (each
+    segment starts on a 256-byte boundary) and the offset where the batch-dependent part
+    (row starts, values, column indices of the sparse rows) begins."""
+    W, R = nworld, njmax
+    fixed = [("nefc", "int32", (W,)), ("ne", "int32", (W,)), ("nf", "int32", (W,)), ("Joff", "int64", (W,)),
+             ("M", "float32", (W, nM)), ("qacc_smooth", "float32", (W, nv)), ("qacc_warmstart", "float32", (W, nv)),
+             ("qfrc_smooth", "float32", (W, nv)), ("D", "float32", (W, R)), ("aref", "float32", (W, R)),
+             ("frictionloss", "float32", (W, R))]
+    offsets, o = {}, 0
+    for name, dtype, shape in fixed:
+        offsets[name] = (o, dtype, shape)
+        o += _up(int(np.prod(shape)) * np.dtype(dtype).itemsize)
+    return offsets, o
+
+
+def result_layout(nworld: int, njmax: int, nv: int) -> tuple[dict, int]:
+    """The same for the results that go back in one transfer."""
+    W, R = nworld, njmax
+    out = [("qacc", "float32", (W, nv)), ("qfrc_constraint", "float32", (W, nv)), ("Ma", "float32", (W, nv)),
+           ("solver_niter", "int32", (W,)), ("overflow", "int32", (W,)), ("force", "float32", (W, R)),
+           ("state", "int32", (W, R))]
+    offsets, o = {}, 0
+    for name, dtype, shape in out:
+        offsets[name] = (o, dtype, shape)
+        o += _up(int(np.prod(shape)) * np.dtype(dtype).itemsize)
+    return offsets, o
+
+
+def _views(buffer, offsets: dict) -> dict:
+    """Typed tensor views of a uint8 torch buffer at the layout's offsets."""
+    import torch
+
+    out = {}
+    for name, (o, dtype, shape) in offsets.items():
+        n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        out[name] = buffer[o:o + n].view(getattr(torch, dtype)).view(shape)
+    return out
 
 
 def pin_batch(d: Any, chunk: int = 256) -> HostBatch:
@@ -72,6 +132,17 @@ def pin_batch(d: Any, chunk: int = 256) -> HostBatch:
     t["J"] = pin(d.efc.J)
     compact = mjw_model.compact_jacobian(d)
     t["Jc"], t["Joff"] = pin(compact.efc.J), pin(compact.efc.J_world_offset)
+    # the same rows as values + column indices + row starts; an entry is kept when any bit
+    # of it is set, so that a stored -0.0 comes back as -0.0
+    rows = np.ascontiguousarray(compact.efc.J, np.float32)
+    keep = rows.view(np.uint32) != 0
+    if int(nefc_total(d)) == 0:
+        keep[:] = False
+    t["Jval"] = pin(rows[keep])
+    t["Jcol"] = pin(np.nonzero(keep)[1].astype(np.int32))
+    if rows.shape[1] <= 256:
+        t["Jcol8"] = pin(np.nonzero(keep)[1].astype(np.uint8))
+    t["Jadr"] = pin(np.concatenate(([0], np.cumsum(keep.sum(axis=1)))).astype(np.int32))
     for n in _IN_ROW:
         t[n] = pin(getattr(d.efc, n))
     nefc = np.minimum(np.asarray(d.nefc), d.njmax)
@@ -79,7 +150,31 @@ def pin_batch(d: Any, chunk: int = 256) -> HostBatch:
     for lo in range(0, d.nworld, chunk):
         hi = min(lo + chunk, d.nworld)
         chunks.append((lo, hi - lo, int(nefc[lo:hi].max()) if hi > lo else 0))
+    # everything a sparse-row submit moves, in ONE pinned buffer (one host -> device copy)
+    nv, nM = int(d.efc.J.shape[-1]), int(d.M.shape[1])
+    offsets, var0 = packed_layout(int(d.nworld), int(d.njmax), nv, nM)
+    for key, col in (("packed", "Jcol"), ("packed8", "Jcol8")):
+        if col not in t:
+            continue
+        nadr, nnz = int(t["Jadr"].numel()), int(t["Jval"].numel())
+        adr_off = var0
+        val_off = adr_off + _up(4 * nadr)
+        col_off = val_off + _up(4 * nnz)
+        used = col_off + _up(int(t[col].element_size()) * nnz)
+        buf = torch.zeros(used, dtype=torch.uint8).pin_memory()
+        views = _views(buf, offsets)
+        for name in views:
+            views[name].copy_(t[name])
+        buf[adr_off:adr_off + 4 * nadr].view(torch.int32).copy_(t["Jadr"])
+        buf[val_off:val_off + 4 * nnz].view(torch.float32).copy_(t["Jval"])
+        buf[col_off:col_off + int(t[col].element_size()) * nnz].view(t[col].dtype).copy_(t[col])
+        t[key] = buf
+        t[key + "_meta"] = (adr_off, val_off, col_off, nadr, nnz, used)
     return HostBatch(tensors=t, chunk_rows=chunks, nworld=int(d.nworld))
+
+
+def nefc_total(d: Any) -> int:
+    return int(np.minimum(np.asarray(d.nefc), d.njmax).sum())
 
 
 def group_by_row_count(d: Any):
@@ -104,8 +199,8 @@ class HostBatchPipeline:
                  mode: str = "compact"):
         import torch
 
-        if mode not in ("compact", "rows", "whole"):
-            raise ValueError("mode must be compact, rows or whole")
+        if mode not in ("compact", "rows", "whole", "sparse", "sparse8"):
+            raise ValueError("mode must be compact, rows, whole, sparse or sparse8")
         self.m = m_dev
         self.mode = mode
         self.device = device
@@ -113,20 +208,48 @@ class HostBatchPipeline:
         for _ in range(slots):
             dd = mjw_model.to_device(mjw_model.make_data(_host_model_view(m_dev), template.nworld, template.njmax),
                                      device)
-            if mode == "compact":
+            sparse = None
+            if mode in ("compact", "sparse", "sparse8"):
                 # the same storage as (all rows, nv); every submit says where worlds start
                 dd.efc.J = dd.efc.J.view(template.nworld * template.njmax, -1)
                 dd.efc.J_world_offset = torch.zeros(template.nworld, dtype=torch.int64, device=device)
+            outdev = None
+            if mode in ("sparse", "sparse8"):
+                # the inputs are views of ONE device buffer that a submit fills with one copy, the
+                # results views of another that goes back with one copy
+                W, R, nv, nM = template.nworld, template.njmax, int(m_dev.nv), int(m_dev.M_colind.shape[0])
+                offsets, var0 = packed_layout(W, R, nv, nM)
+                cb = 4 if mode == "sparse" else 1
+                cap = var0 + _up(4 * (W * R + 1)) + _up(4 * W * R * nv) + _up(cb * W * R * nv)
+                inbuf = torch.zeros(cap, dtype=torch.uint8, device=device)
+                v = _views(inbuf, offsets)
+                for n in ("nefc", "ne", "nf", "M") + _IN_DOF:
+                    setattr(dd, n, v[n])
+                for n in _IN_ROW:
+                    setattr(dd.efc, n, v[n])
+                dd.efc.J_world_offset = v["Joff"]
+                roff, rbytes = result_layout(W, R, nv)
+                outdev = torch.zeros(rbytes, dtype=torch.uint8, device=device)
+                rv = _views(outdev, roff)
+                for n in _OUT_DOF + ("solver_niter", "overflow"):
+                    setattr(dd, n, rv[n])
+                dd.efc.Ma, dd.efc.force, dd.efc.state = rv["Ma"], rv["force"], rv["state"]
+                sparse = {"in": inbuf, "colbytes": cb, "roff": roff}
             sc = runtime.make_optimized_fwd_position_scratch(m_dev, dd, device)
             if sparse_groups is not None:
                 runtime.refresh_sparse_hessian(m_dev, dd, sc, sparse_groups, device)
             pin = lambda t: torch.empty(t.shape, dtype=t.dtype).pin_memory()  # noqa: E731
-            out = {n: pin(getattr(dd, n)) for n in _OUT_DOF + ("solver_niter", "overflow")}
-            out["Ma"] = pin(dd.efc.Ma)
-            for n in _OUT_ROW:
-                out[n] = pin(getattr(dd.efc, n))
+            if outdev is not None:
+                sparse["outdev"] = outdev
+                sparse["outpin"] = torch.zeros(outdev.numel(), dtype=torch.uint8).pin_memory()
+                out = _views(sparse["outpin"], sparse["roff"])
+            else:
+                out = {n: pin(getattr(dd, n)) for n in _OUT_DOF + ("solver_niter", "overflow")}
+                out["Ma"] = pin(dd.efc.Ma)
+                for n in _OUT_ROW:
+                    out[n] = pin(getattr(dd.efc, n))
             self.slots.append({"dd": dd, "sc": sc, "stream": torch.cuda.Stream(device=device),
-                               "done": torch.cuda.Event(), "out": out, "batch": None})
+                               "done": torch.cuda.Event(), "out": out, "batch": None, "sparse": sparse})
         self.lib = _lib.lib()
 
     def _rows(self, dst, src, lo, n, rows, to_host, stream):
@@ -145,6 +268,20 @@ class HostBatchPipeline:
         dd, t = sl["dd"], batch.tensors
         handle = int(sl["stream"].cuda_stream)
         with torch.cuda.stream(sl["stream"]):
+            if self.mode in ("sparse", "sparse8"):
+                sp = sl["sparse"]
+                key = "packed" if self.mode == "sparse" else "packed8"
+                adr_off, val_off, col_off, nadr, _, used = t[key + "_meta"]
+                sp["in"][:used].copy_(t[key], non_blocking=True)
+                base = sp["in"].data_ptr()
+                rc = self.lib.imn_expand_rows(base + val_off, base + col_off, sp["colbytes"], base + adr_off, nadr - 1,
+                                              int(self.m.nv), dd.efc.J.data_ptr(), int(dd.efc.J.stride(0)), handle)
+                _lib.check(rc, "imn_expand_rows")
+                runtime.solve_with_scratch(self.m, dd, sl["sc"], use_optimized_kernel=True, stream=sl["stream"])
+                sp["outpin"].copy_(sp["outdev"], non_blocking=True)
+                sl["done"].record(sl["stream"])
+                sl["batch"] = batch
+                return
             for n in ("nefc", "ne", "nf", "M") + _IN_DOF:
                 getattr(dd, n).copy_(t[n], non_blocking=True)
             for name in _IN_ROW:

@@ -12,7 +12,8 @@ from helpers import run_oracle
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("mode,grouped", [("compact", False), ("rows", False), ("rows", True), ("whole", False)])
+@pytest.mark.parametrize("mode,grouped", [("compact", False), ("rows", False), ("rows", True), ("whole", False),
+                                          ("sparse", False), ("sparse8", False)])
 def test_host_batch_pipeline_matches_oracle(oracle, cuda_device, mode, grouped):
     import torch
 
@@ -29,6 +30,11 @@ def test_host_batch_pipeline_matches_oracle(oracle, cuda_device, mode, grouped):
     assert moved <= full + 8 * d.nworld and batch.h2d_bytes(m.nv, m.nv, m.nM, d.njmax, "whole") == full
     if grouped or mode == "compact":
         assert moved < 0.8 * full  # no dead rows (compact) or few (rows of grouped worlds)
+    if mode in ("sparse", "sparse8"):
+        assert moved < (0.65 if mode == "sparse" else 0.5) * full  # only the nonzeros of the live rows, with their indices
+        d.efc.J[0, 0, 3] = -0.0  # a stored negative zero survives the round trip
+        batch = host_batch.pin_batch(d, chunk=128)
+        want, _, _ = run_oracle(oracle, m, d)
     for k in range(3):  # both slots, one reused
         pipe.submit(k, batch)
     for k in range(3):
