@@ -213,3 +213,29 @@ def test_timestep_is_handed_over_as_an_array_and_model_tables_are_read_once():
     assert arrays.table_to_host(table) is first and first.tolist() == [0, 1, 2, 3, 4]
     host = np.arange(3)
     assert arrays.table_to_host(host) is host
+
+
+def test_packed_transfer_layouts_are_aligned_and_disjoint():
+    """The one-buffer transport of host batches: every segment starts on a 256-byte boundary,
+    segments do not overlap, and the typed views address exactly their segment."""
+    import torch
+
+    from instantmimic_b200 import host_batch
+
+    W, R, nv, nM = 37, 64, 34, 310
+    for offsets, end in (host_batch.packed_layout(W, R, nv, nM), host_batch.result_layout(W, R, nv)):
+        spans = []
+        for name, (o, dtype, shape) in offsets.items():
+            n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+            assert o % 256 == 0, name
+            spans.append((o, o + n))
+        spans.sort()
+        assert all(a_end <= b_start for (_, a_end), (b_start, _) in zip(spans, spans[1:]))
+        assert end % 256 == 0 and end >= spans[-1][1]
+        buf = torch.zeros(end, dtype=torch.uint8)
+        views = host_batch._views(buf, offsets)
+        for name, (o, dtype, shape) in offsets.items():
+            v = views[name]
+            assert tuple(v.shape) == tuple(shape) and str(v.dtype) == "torch." + dtype
+            assert v.data_ptr() == buf.data_ptr() + o
+    assert host_batch.packed_layout(W, R, nv, nM)[0]["Joff"][1] == "int64"
