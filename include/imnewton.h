@@ -550,6 +550,16 @@ int imn_expand_rows(const float* values, const void* colind, int32_t colind_byte
                     const int32_t* rowadr, int32_t nrows, int32_t nv, float* dense,
                     int64_t ld_row, void* stream);
 
+/* Companion of imn_expand_rows for efc.D, efc.aref and efc.frictionloss: the values of the
+ * live rows only (worlds back to back, in the order of the compact Jacobian whose per-world
+ * element offsets are `J_world_offset`, row stride `J_ld_row`) written into the padded
+ * (nworld, efc_ld) arrays.  Rows at or beyond a world's nefc are left as they are. */
+int imn_expand_row_vectors(const float* D_rows, const float* aref_rows,
+                           const float* frictionloss_rows, const int64_t* J_world_offset,
+                           int64_t J_ld_row, const int32_t* nefc, int32_t njmax, float* D,
+                           float* aref, float* frictionloss, int64_t efc_ld, int32_t nworld,
+                           void* stream);
+
 /* No counterpart in the reference, whose solver buffers never leave the GPU.  For
  * callers that keep a batch in pinned host memory: copies the leading `width` bytes
  * of each of `nworld` per-world blocks (block strides `dst_pitch` / `src_pitch`

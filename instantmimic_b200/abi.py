@@ -258,6 +258,7 @@ SYMBOLS = {
     "imn_implicit_matrix": (C.c_int, [C.POINTER(ImnImplicit), P, I64, P, I64, I32, P]),
     "imn_advance": (C.c_int, [C.POINTER(ImnAdvance), P, I64, I32, P]),
     "imn_ball_limit_rows": (C.c_int, [C.POINTER(ImnBallLimits), I32, P]),
+    "imn_expand_row_vectors": (C.c_int, [P, P, P, P, I64, P, I32, P, P, P, I64, I32, P]),
     "imn_expand_rows": (C.c_int, [P, P, I32, P, I32, I32, P, I64, P]),
     "imn_body_tree_accumulate": (C.c_int, [C.POINTER(ImnBodyTree), P, I64, I32, I32, I32, P]),
     "imn_crb": (C.c_int, [C.POINTER(ImnBodyTree), P, P, P, P, I64, I32, P]),

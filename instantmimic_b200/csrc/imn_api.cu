@@ -272,7 +272,41 @@ __global__ void __launch_bounds__(256)
   }
 }
 
+// The per-row vectors of the live rows (one value per row, worlds back to back like the
+// compact Jacobian) written into the padded (nworld, efc_ld) arrays the solver reads.
+// Rows at or beyond a world's nefc are left alone: the solver never reads them.
+__global__ void __launch_bounds__(256)
+    expand_row_vectors_kernel(const float* __restrict__ cD, const float* __restrict__ cA, const float* __restrict__ cF,
+                              const int64_t* __restrict__ first, const int64_t ld_row, const int* __restrict__ nefc,
+                              const int njmax, float* __restrict__ D, float* __restrict__ A, float* __restrict__ F,
+                              const int64_t efc_ld, const int nworld) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= (int64_t)nworld * njmax) return;
+  const int w = (int)(t / njmax), r = (int)(t - (int64_t)w * njmax);
+  if (r >= min(nefc[w], njmax)) return;
+  const int64_t src = first[w] / ld_row + r, dst = (int64_t)w * efc_ld + r;
+  D[dst] = cD[src], A[dst] = cA[src], F[dst] = cF[src];
+}
+
 }  // namespace imn
+
+extern "C" int imn_expand_row_vectors(const float* D_rows, const float* aref_rows, const float* frictionloss_rows,
+                                      const int64_t* J_world_offset, int64_t J_ld_row, const int32_t* nefc,
+                                      int32_t njmax, float* D, float* aref, float* frictionloss, int64_t efc_ld,
+                                      int32_t nworld, void* stream) {
+  if (!D_rows || !aref_rows || !frictionloss_rows || !J_world_offset || !nefc || !D || !aref || !frictionloss)
+    return imn::set_error("imn_expand_row_vectors: NULL buffer"), IMN_ERR_NULL;
+  if (nworld < 0 || njmax < 0 || J_ld_row <= 0 || efc_ld < njmax)
+    return imn::set_error("imn_expand_row_vectors: bad extent or stride"), IMN_ERR_SHAPE;
+  const int64_t threads = (int64_t)nworld * njmax;
+  if (threads == 0) return IMN_OK;
+  imn::expand_row_vectors_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      D_rows, aref_rows, frictionloss_rows, J_world_offset, J_ld_row, nefc, njmax, D, aref, frictionloss, efc_ld, nworld);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess)
+    return imn::set_error("imn_expand_row_vectors: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  return IMN_OK;
+}
 
 extern "C" int imn_expand_rows(const float* values, const void* colind, int32_t colind_bytes, const int32_t* rowadr,
                                int32_t nrows, int32_t nv, float* dense, int64_t ld_row, void* stream) {

@@ -85,12 +85,13 @@ def _up(n: int) -> int:
 def packed_layout(nworld: int, njmax: int, nv: int, nM: int) -> tuple[dict, int]:
     """Byte offsets of the fixed-size inputs inside one packed transfer buffer (each
     segment starts on a 256-byte boundary) and the offset where the batch-dependent part
-    (row starts, values, column indices of the sparse rows) begins."""
+    begins: row starts, values and column indices of the sparse rows, then D, aref and
+    frictionloss of the live rows."""
     W, R = nworld, njmax
     fixed = [("nefc", "int32", (W,)), ("ne", "int32", (W,)), ("nf", "int32", (W,)), ("Joff", "int64", (W,)),
              ("M", "float32", (W, nM)), ("qacc_smooth", "float32", (W, nv)), ("qacc_warmstart", "float32", (W, nv)),
-             ("qfrc_smooth", "float32", (W, nv)), ("D", "float32", (W, R)), ("aref", "float32", (W, R)),
-             ("frictionloss", "float32", (W, R))]
+             ("qfrc_smooth", "float32", (W, nv))]
+    del R  # the per-row inputs travel compacted, in the batch-dependent part
     offsets, o = {}, 0
     for name, dtype, shape in fixed:
         offsets[name] = (o, dtype, shape)
@@ -150,17 +151,24 @@ def pin_batch(d: Any, chunk: int = 256) -> HostBatch:
     for lo in range(0, d.nworld, chunk):
         hi = min(lo + chunk, d.nworld)
         chunks.append((lo, hi - lo, int(nefc[lo:hi].max()) if hi > lo else 0))
-    # everything a sparse-row submit moves, in ONE pinned buffer (one host -> device copy)
+    # everything a sparse-row submit moves, in ONE pinned buffer (one host -> device copy);
+    # D, aref and frictionloss as the values of the live rows, in the compact Jacobian's order
+    live = np.arange(d.njmax)[None, :] < nefc[:, None]
+    live_rows = {name: np.ascontiguousarray(np.asarray(getattr(d.efc, name), np.float32)[live]) for name in _IN_ROW}
+    if rows.shape[0] != int(live.sum()):  # a batch without any row carries one dummy row
+        live_rows = {name: np.zeros(rows.shape[0], np.float32) for name in _IN_ROW}
     nv, nM = int(d.efc.J.shape[-1]), int(d.M.shape[1])
     offsets, var0 = packed_layout(int(d.nworld), int(d.njmax), nv, nM)
     for key, col in (("packed", "Jcol"), ("packed8", "Jcol8")):
         if col not in t:
             continue
         nadr, nnz = int(t["Jadr"].numel()), int(t["Jval"].numel())
+        nrows = nadr - 1
         adr_off = var0
         val_off = adr_off + _up(4 * nadr)
         col_off = val_off + _up(4 * nnz)
-        used = col_off + _up(int(t[col].element_size()) * nnz)
+        vec_off = col_off + _up(int(t[col].element_size()) * nnz)  # D | aref | frictionloss, nrows each
+        used = vec_off + 3 * _up(4 * nrows)
         buf = torch.zeros(used, dtype=torch.uint8).pin_memory()
         views = _views(buf, offsets)
         for name in views:
@@ -168,8 +176,11 @@ def pin_batch(d: Any, chunk: int = 256) -> HostBatch:
         buf[adr_off:adr_off + 4 * nadr].view(torch.int32).copy_(t["Jadr"])
         buf[val_off:val_off + 4 * nnz].view(torch.float32).copy_(t["Jval"])
         buf[col_off:col_off + int(t[col].element_size()) * nnz].view(t[col].dtype).copy_(t[col])
+        for i, name in enumerate(_IN_ROW):
+            o = vec_off + i * _up(4 * nrows)
+            buf[o:o + 4 * nrows].view(torch.float32).copy_(torch.from_numpy(live_rows[name]))
         t[key] = buf
-        t[key + "_meta"] = (adr_off, val_off, col_off, nadr, nnz, used)
+        t[key + "_meta"] = (adr_off, val_off, col_off, nadr, nnz, used, vec_off, _up(4 * nrows))
     return HostBatch(tensors=t, chunk_rows=chunks, nworld=int(d.nworld))
 
 
@@ -220,13 +231,11 @@ class HostBatchPipeline:
                 W, R, nv, nM = template.nworld, template.njmax, int(m_dev.nv), int(m_dev.M_colind.shape[0])
                 offsets, var0 = packed_layout(W, R, nv, nM)
                 cb = 4 if mode == "sparse" else 1
-                cap = var0 + _up(4 * (W * R + 1)) + _up(4 * W * R * nv) + _up(cb * W * R * nv)
+                cap = var0 + _up(4 * (W * R + 1)) + _up(4 * W * R * nv) + _up(cb * W * R * nv) + 3 * _up(4 * W * R)
                 inbuf = torch.zeros(cap, dtype=torch.uint8, device=device)
                 v = _views(inbuf, offsets)
                 for n in ("nefc", "ne", "nf", "M") + _IN_DOF:
                     setattr(dd, n, v[n])
-                for n in _IN_ROW:
-                    setattr(dd.efc, n, v[n])
                 dd.efc.J_world_offset = v["Joff"]
                 roff, rbytes = result_layout(W, R, nv)
                 outdev = torch.zeros(rbytes, dtype=torch.uint8, device=device)
@@ -271,9 +280,15 @@ class HostBatchPipeline:
             if self.mode in ("sparse", "sparse8"):
                 sp = sl["sparse"]
                 key = "packed" if self.mode == "sparse" else "packed8"
-                adr_off, val_off, col_off, nadr, _, used = t[key + "_meta"]
+                adr_off, val_off, col_off, nadr, _, used, vec_off, vec_step = t[key + "_meta"]
                 sp["in"][:used].copy_(t[key], non_blocking=True)
                 base = sp["in"].data_ptr()
+                rc = self.lib.imn_expand_row_vectors(
+                    base + vec_off, base + vec_off + vec_step, base + vec_off + 2 * vec_step,
+                    dd.efc.J_world_offset.data_ptr(), int(dd.efc.J.stride(0)), dd.nefc.data_ptr(), int(dd.njmax),
+                    dd.efc.D.data_ptr(), dd.efc.aref.data_ptr(), dd.efc.frictionloss.data_ptr(),
+                    int(dd.efc.D.stride(0)), int(dd.nworld), handle)
+                _lib.check(rc, "imn_expand_row_vectors")
                 rc = self.lib.imn_expand_rows(base + val_off, base + col_off, sp["colbytes"], base + adr_off, nadr - 1,
                                               int(self.m.nv), dd.efc.J.data_ptr(), int(dd.efc.J.stride(0)), handle)
                 _lib.check(rc, "imn_expand_rows")

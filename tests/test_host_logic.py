@@ -238,4 +238,5 @@ def test_packed_transfer_layouts_are_aligned_and_disjoint():
             v = views[name]
             assert tuple(v.shape) == tuple(shape) and str(v.dtype) == "torch." + dtype
             assert v.data_ptr() == buf.data_ptr() + o
-    assert host_batch.packed_layout(W, R, nv, nM)[0]["Joff"][1] == "int64"
+    fixed = host_batch.packed_layout(W, R, nv, nM)[0]
+    assert fixed["Joff"][1] == "int64" and "D" not in fixed  # per-row inputs travel compacted
