@@ -8,16 +8,18 @@
 //
 // B200 mapping.  The solve is latency-bound small dense algebra (nv <= 79), not a
 // tensor-core contraction, so the design goal is to touch HBM exactly once: a CTA
-// is one warp that owns one world.  Its J, M and row data arrive in shared memory
-// through TMA bulk copies (cp.async.bulk, one mbarrier), the Hessian, its
+// is one warp that owns one world.  Its J and row data arrive in shared memory
+// through TMA bulk copies (cp.async.bulk, one mbarrier; M, read once per iteration,
+// stays in global memory and comes through L1), the Hessian, its
 // Cholesky factor and every vector stay on chip for all iterations, and the
 // results are written once.  A warp needs no block barrier (only __syncwarp),
 // lane reductions are shuffle trees, and the hardware CTA scheduler balances
 // worlds whose iteration counts differ; worlds are launched by descending row count
 // so that the long solves start first.  Models whose J would leave room for few
-// worlds per SM stream it through a 32-row tile (TMA bulk copies from L2) instead.  The initialisation runs through the
-// same code as an iteration (as "iteration 0" without a line search): the kernel
-// is bound by instruction fetch and latency, so every stage exists once.
+// worlds per SM stream it through a 32-row tile (TMA bulk copies from L2) instead.
+// The initialisation runs through the same code as an iteration (as "iteration 0"
+// without a line search): the kernel is bound by instruction fetch and latency, so
+// every stage exists once.
 //
 // Arithmetic contract.  Every value that decides an active set or an iteration
 // count is formed by the same float32 operations in the same order as the CPU
@@ -52,7 +54,7 @@ struct Geom {
   int nv, njmax, ldj, ldu, nM, bd;
   int jrows;  // rows of J held in shared memory (njmax when resident, else 32)
   // offsets in 4-byte words; every region starts on a 16-byte boundary
-  int oBar, oJ, oA, oVec, nv4, oM, oRowF, oRowI, r4, oUni, total;
+  int oBar, oJ, oA, oVec, nv4, oRowF, oRowI, r4, oUni, total;
   // polls a copy wait may take before the world gives up, and the failure-path test
   // switch: when set no bulk copy is issued (plain loads bring the data) while the
   // barrier is told to expect bytes, so the wait runs out with nothing in flight
@@ -85,7 +87,6 @@ static Geom make_geom(const ImnModel& m, const ImnData& d, bool resident, const 
   g.oA = o, o += sp ? up4(sp->nfac) + up4(sp->nslots) + up4(m.nv) : (m.nv + 1) * g.ldu;
   // dof vectors; the dense factor needs two more (forward-solve scratch, 1 / pivot)
   g.oVec = o, o += (sp ? 6 : 8) * g.nv4;
-  g.oM = o, o += up4(m.nM);
   g.oRowF = o, o += 5 * g.r4;
   g.oRowI = o, o += up4(3 * g.r4 / 2);  // three 16-bit row lists
   g.oUni = o, o += up4(m.nv + 1);
@@ -129,7 +130,6 @@ __device__ __forceinline__ void newton_worlds(const ImnModel& m, const ImnData& 
   s.qfs = s.grad + nv4;
   s.xsm = SPARSE ? nullptr : s.qfs + nv4;
   s.dinv = SPARSE ? nullptr : s.xsm + nv4;
-  s.Msm = smem + g.oM;
   s.Jaref = smem + g.oRowF;
   s.jv = s.Jaref + r4;
   s.Dsm = s.jv + r4;
@@ -185,6 +185,7 @@ __device__ __forceinline__ void newton_worlds(const ImnModel& m, const ImnData& 
         rowless = nefc_in == 0;
         dofo = (size_t)w * d.dof_ld, efco = (size_t)w * d.efc_ld;
         s.Jg = d.efc_J + (d.J_world_offset ? (size_t)d.J_world_offset[w] : (size_t)w * d.J_ld_world);
+        s.M = d.M + (size_t)w * d.M_ld;
 
         // ---- load: TMA bulk copies for the 16-byte-aligned bulk of every array, plain
         // loads for the ragged ends ---------------------------------------------------
@@ -194,9 +195,8 @@ __device__ __forceinline__ void newton_worlds(const ImnModel& m, const ImnData& 
           const float* src;
           int n;
         };
-        const Src srcs[7] = {
+        const Src srcs[6] = {
             {s.Jsm, s.Jg, JRES ? nefc * s.ldj : 0},
-            {s.Msm, d.M + (size_t)w * d.M_ld, g.nM},
             {s.Dsm, d.efc_D + efco, nefc},
             {s.floss, d.efc_frictionloss + efco, nefc},
             {s.jv, d.efc_aref + efco, nefc},  // aref is parked in jv until Jaref is formed
@@ -211,19 +211,19 @@ __device__ __forceinline__ void newton_worlds(const ImnModel& m, const ImnData& 
         const bool bulk = !(g.withhold_copies & 1);
         uint32_t tx = 0;
 #pragma unroll
-        for (int k = 0; k < 7; ++k)
+        for (int k = 0; k < 6; ++k)
           if (bulk && (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0) tx += (uint32_t)(srcs[k].n & ~3) * 4u;
         if (lane == 0) {
           mbar_expect_tx(bar, bulk ? tx : 16u);
 #pragma unroll
-          for (int k = 0; k < 7; ++k) {
+          for (int k = 0; k < 6; ++k) {
             const uint32_t bytes =
                 bulk && (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0 ? (uint32_t)(srcs[k].n & ~3) * 4u : 0u;
             if (bytes) bulk_g2s(srcs[k].dst, srcs[k].src, bytes, bar);
           }
         }
 #pragma unroll
-        for (int k = 0; k < 7; ++k) {
+        for (int k = 0; k < 6; ++k) {
           const int done_n = bulk && (reinterpret_cast<uintptr_t>(srcs[k].src) & 15) == 0 ? (srcs[k].n & ~3) : 0;
 #pragma unroll 1
           for (int i = done_n + lane; i < srcs[k].n; i += 32) srcs[k].dst[i] = srcs[k].src[i];
