@@ -648,6 +648,10 @@ def main():
     e2e = None
     if not args.no_e2e:
         grouped = [host_batch.group_by_row_count(d)[0] for _, d in host]
+        # pinned staging memory on the NUMA node of this rank's GPU (with one process per GPU
+        # the ranks' copies otherwise all read one socket's memory)
+        near = host_batch.host_near_device(local)
+        near.__enter__()
         pinned = [host_batch.pin_batch(d, chunk=128) for d in grouped]
         ldj = int(dev[0].efc.J.stride(1))
         njmax = int(host[0][1].njmax)
@@ -709,7 +713,9 @@ def main():
         modes = {mode: e2e_measure(mode) for mode in ("sparse8", "sparse", "compact", "rows", "whole")}
         best = max(modes, key=lambda k: modes[k]["value"])
         e2e = dict(modes[best])
+        near.__exit__(None, None, None)
         e2e["api"] = "instantmimic_b200.host_batch.HostBatchPipeline.submit / result"
+        e2e["host_numa_node"] = near.node  # None: the platform does not say
         e2e["pipeline"] = f"{e2e.pop('nslot')} slots (copies of step k+1 overlap the solve of step k)"
         e2e["other_copy_modes"] = [
             {k: modes[mode][k] for k in ("copies", "value", "ms_per_step", "h2d_bytes_per_step", "h2d_gbs_per_gpu")}

@@ -37,6 +37,7 @@ The sparse modes also move every input in ONE pinned buffer and every result in 
 from __future__ import annotations
 
 import ctypes as C
+import os
 from dataclasses import dataclass
 from typing import Any
 
@@ -324,6 +325,71 @@ class HostBatchPipeline:
         sl = self.slots[k % len(self.slots)]
         sl["done"].synchronize()
         return sl["out"]
+
+
+def _cpu_list(text: str) -> set[int]:
+    """CPUs of a sysfs ``cpulist`` ("0-31,64-95")."""
+    cpus: set[int] = set()
+    for part in text.strip().split(","):
+        if part:
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+class host_near_device:
+    """Context manager: run the calling thread on the CPUs of the NUMA node the GPU hangs
+    off, so that pinned buffers allocated inside (``pin_batch``, ``HostBatchPipeline``) are
+    first touched, hence placed, in that node's memory.  With one process per GPU on a
+    two-socket host the host-to-device copies of all ranks otherwise read one socket's
+    memory.  Does nothing (``node`` stays None) when the platform does not say which node
+    the device belongs to.  The previous affinity is restored on exit.
+
+    ``pci_bus_id`` is the device's "domain:bus:device.function" address; by default it is
+    asked of torch for CUDA device ``device_index``.
+    """
+
+    def __init__(self, device_index: int = 0, *, pci_bus_id: str | None = None, sysfs: str = "/sys"):
+        self.device_index, self.pci_bus_id, self.sysfs = device_index, pci_bus_id, sysfs
+        self.node: int | None = None
+        self._saved: set[int] | None = None
+
+    def _address(self) -> str | None:
+        if self.pci_bus_id is not None:
+            return self.pci_bus_id.lower()
+        try:
+            import torch
+
+            p = torch.cuda.get_device_properties(self.device_index)
+            return f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        except Exception:  # no CUDA device, or a torch without the PCI fields
+            return None
+
+    def __enter__(self):
+        address = self._address()
+        if address is None or not hasattr(os, "sched_setaffinity"):
+            return self
+        try:
+            with open(os.path.join(self.sysfs, "bus/pci/devices", address, "numa_node")) as f:
+                node = int(f.read())
+            if node < 0:
+                return self
+            with open(os.path.join(self.sysfs, "devices/system/node", f"node{node}", "cpulist")) as f:
+                cpus = _cpu_list(f.read()) & os.sched_getaffinity(0)
+            if not cpus:
+                return self
+            self._saved = os.sched_getaffinity(0)
+            os.sched_setaffinity(0, cpus)
+            self.node = node
+        except (OSError, ValueError):
+            self._saved = None
+        return self
+
+    def __exit__(self, *exc):
+        if self._saved is not None:
+            os.sched_setaffinity(0, self._saved)
+            self._saved = None
+        return False
 
 
 def _host_model_view(m_dev: Any):

@@ -240,3 +240,30 @@ def test_packed_transfer_layouts_are_aligned_and_disjoint():
             assert v.data_ptr() == buf.data_ptr() + o
     fixed = host_batch.packed_layout(W, R, nv, nM)[0]
     assert fixed["Joff"][1] == "int64" and "D" not in fixed  # per-row inputs travel compacted
+
+
+def test_host_near_device_binds_to_the_gpus_node_and_restores(tmp_path):
+    """Pinned staging buffers should live on the NUMA node of their GPU: the context manager
+    narrows the thread's CPUs to that node's (read from sysfs) and puts them back."""
+    import os
+
+    from instantmimic_b200 import host_batch
+
+    assert host_batch._cpu_list("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    before = os.sched_getaffinity(0)
+    one = min(before)
+    dev = tmp_path / "bus/pci/devices/0000:1b:00.0"
+    dev.mkdir(parents=True)
+    (dev / "numa_node").write_text("1\n")
+    node = tmp_path / "devices/system/node/node1"
+    node.mkdir(parents=True)
+    (node / "cpulist").write_text(f"{one}\n")
+    with host_batch.host_near_device(pci_bus_id="0000:1B:00.0", sysfs=str(tmp_path)) as near:
+        assert near.node == 1 and os.sched_getaffinity(0) == {one}
+    assert os.sched_getaffinity(0) == before
+    # a platform that does not say (numa_node -1, or no such file): nothing changes
+    (dev / "numa_node").write_text("-1\n")
+    with host_batch.host_near_device(pci_bus_id="0000:1b:00.0", sysfs=str(tmp_path)) as near:
+        assert near.node is None and os.sched_getaffinity(0) == before
+    with host_batch.host_near_device(pci_bus_id="0000:ff:00.0", sysfs=str(tmp_path)) as near:
+        assert near.node is None and os.sched_getaffinity(0) == before
