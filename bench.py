@@ -774,6 +774,10 @@ def main():
         t = timed(lambda k: runtime.mul_m(md, big[k % 2], outv, big[k % 2].y))
         alg = 4.0 * W * (nM + 2 * nv)
         aux["mul_m_kernel"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg}
+        gen = runtime.generated_mul_m_kernel(md, big[0])
+        if gen is not None:
+            t = timed(lambda k: runtime.mul_m(md, big[k % 2], outv, big[k % 2].y, kernel=gen))
+            aux["mul_m_generated"] = {"ms": t * 1e3, "achieved_gbs": alg / t / 1e9, "algorithmic_bytes": alg}
         del big, outv
         torch.cuda.empty_cache()
         aux.update(stage_kernels(args, torch, md, m_host, device, timed))

@@ -408,6 +408,17 @@ int imn_tree_ldl_kernel_info(const ImnTreeKernel* kernel, int32_t* shared_slots,
                              int64_t* code_bytes, const char** source);
 void imn_tree_ldl_kernel_destroy(ImnTreeKernel* kernel);
 
+/* out = M v (upstream support.mul_m, called at mjw_step_optimized.py:2252-2255) as
+ * generated straight-line code of the same kind.  The program is built by the caller from
+ * the model's symmetric-row tables (M_mulm_rowadr / col / madr): streams 0..groups-1 load
+ * the entries of v each warp needs (LOAD_Y), the trunk stream is empty, streams
+ * groups+1..2*groups form each row's sum in table order -- ZERO, then LOAD_M + MULADD
+ * (dst = fmaf(a, b, dst)) per stored entry -- and STORE_X it.  The results equal
+ * imn_mul_m's bit for bit.  Launch with imn_tree_ldl_compiled_solve (y = v, x = out; out
+ * must not alias v); kernel_info / kernel_destroy as for the tree kernels. */
+int imn_mul_m_compile(const int32_t* prog, const int32_t* prog_ptr, int32_t nv, int32_t nM,
+                      int32_t groups, int32_t nslot, ImnTreeKernel** out);
+
 /* tree_ldl.tree_factor_solve (tree_ldl.py:419-433) through the generated kernel;
  * arguments and results as imn_tree_ldl_solve, bit for bit. */
 int imn_tree_ldl_compiled_solve(ImnTreeKernel* kernel, const float* M, int64_t M_ld,
@@ -520,8 +531,8 @@ int imn_com_vel(const ImnBodyTree* tree, const float* qvel, int64_t qvel_ld, con
  * pointers and the counts; the call copies every table into one device allocation
  * of the current device and returns a plan whose pointers are device pointers, ready
  * for ImnCtx.sparse_plan and imn_sparse_factor_nonfused.  This and
- * imn_tree_ldl_compile are the only entry points that allocate; both belong to model
- * set-up, not to the step.  imn_sparse_plan_destroy frees the allocation. */
+ * imn_tree_ldl_compile / imn_mul_m_compile are the only entry points that allocate; they
+ * belong to model set-up, not to the step.  imn_sparse_plan_destroy frees the allocation. */
 int imn_sparse_plan_create(const ImnSparsePlan* host_tables, ImnSparsePlan** out);
 void imn_sparse_plan_destroy(ImnSparsePlan* plan);
 

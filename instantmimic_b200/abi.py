@@ -237,6 +237,7 @@ SYMBOLS = {
     "imn_mul_m": (C.c_int, [C.POINTER(ImnModel), P, I64, P, I64, P, I64, I32, P]),
     "imn_tree_ldl_solve": (C.c_int, [C.POINTER(ImnTreePlan), P, I64, P, I64, P, I64, I32, P]),
     "imn_tree_ldl_compile": (C.c_int, [P, P, I32, I32, I32, I32, I32, C.POINTER(C.c_void_p)]),
+    "imn_mul_m_compile": (C.c_int, [P, P, I32, I32, I32, I32, C.POINTER(C.c_void_p)]),
     "imn_tree_ldl_kernel_info": (
         C.c_int,
         [C.c_void_p, C.POINTER(C.c_int32), C.POINTER(C.c_int64), C.POINTER(C.c_char_p)],

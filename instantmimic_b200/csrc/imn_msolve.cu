@@ -21,7 +21,7 @@
 
 namespace imn {
 
-enum { OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X, OP_MULSUB };
+enum { OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X, OP_MULSUB, OP_MULADD };
 
 __device__ __forceinline__ void tree_run(const int4* __restrict__ prog, int lo, int hi, float* col,
                                          const float* __restrict__ Mr, const float* __restrict__ yr,
@@ -41,6 +41,7 @@ __device__ __forceinline__ void tree_run(const int4* __restrict__ prog, int lo, 
       case OP_MUL: col[dst * 32] = col[a * 32] * col[b * 32]; break;
       case OP_ADD: col[dst * 32] = col[dst * 32] + col[a * 32]; break;
       case OP_MULSUB: col[dst * 32] = fmaf(col[a * 32], col[b * 32], -col[dst * 32]); break;
+      case OP_MULADD: col[dst * 32] = fmaf(col[a * 32], col[b * 32], col[dst * 32]); break;
       case OP_STORE_X:
         if (live) xr[dst] = col[a * 32];
         break;

@@ -38,7 +38,7 @@
 
 namespace {
 
-enum { OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X, OP_MULSUB };
+enum { OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_ADD, OP_STORE_X, OP_MULSUB, OP_MULADD };
 
 // ---- NVRTC through dlopen ---------------------------------------------------------
 typedef void* nvrtcProgram_t;
@@ -103,7 +103,8 @@ void operands(const Ins& i, int reads[4], int& nread, int& write) {
     case OP_SUBMUL: reads[nread++] = i.a, reads[nread++] = i.b, reads[nread++] = i.dst, write = i.dst; break;
     case OP_MUL: reads[nread++] = i.a, reads[nread++] = i.b, write = i.dst; break;
     case OP_ADD: reads[nread++] = i.a, reads[nread++] = i.dst, write = i.dst; break;
-    case OP_MULSUB: reads[nread++] = i.a, reads[nread++] = i.b, reads[nread++] = i.dst, write = i.dst; break;
+    case OP_MULSUB:
+    case OP_MULADD: reads[nread++] = i.a, reads[nread++] = i.b, reads[nread++] = i.dst, write = i.dst; break;
     case OP_STORE_X: reads[nread++] = i.a; break;
     default: break;
   }
@@ -114,6 +115,7 @@ void operands(const Ins& i, int reads[4], int& nread, int& write) {
 struct ImnTreeKernel {
   int nv = 0, nM = 0, groups = 0, nshared = 0;
   bool staged = false;  // M and y tiles in shared memory
+  std::string name;     // entry point of the generated source
   std::string source;
   std::vector<char> cubin;
   cudaLibrary_t library = nullptr;
@@ -123,8 +125,8 @@ struct ImnTreeKernel {
 
 namespace {
 
-std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int owner, int nslot, int nv, int nM,
-                     bool allow_stage, bool* staged_out, int* nshared_out) {
+std::string generate(const std::string& name, const int32_t* prog, const int32_t* ptr, int groups, int owner,
+                     int nslot, int nv, int nM, bool allow_stage, bool* staged_out, int* nshared_out) {
   const int nstream = 2 * groups + 1;
   auto warp_of = [&](int st) { return st < groups ? st : (st == groups ? owner : st - groups - 1); };
   std::vector<std::vector<Ins>> streams(nstream);
@@ -169,6 +171,7 @@ std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int ow
         case OP_MUL: out += d + " = " + ref(i.a) + " * " + ref(i.b) + ";\n"; break;
         case OP_ADD: out += d + " = " + d + " + " + ref(i.a) + ";\n"; break;
         case OP_MULSUB: out += d + " = fmaf(" + ref(i.a) + ", " + ref(i.b) + ", -" + d + ");\n"; break;
+        case OP_MULADD: out += d + " = fmaf(" + ref(i.a) + ", " + ref(i.b) + ", " + d + ");\n"; break;
         case OP_STORE_X:
           out += staged ? "yt[" + std::to_string(i.dst) + "] = " + ref(i.a) + ";\n"
                         : "if (live) xr[" + std::to_string(i.dst) + "] = " + ref(i.a) + ";\n";
@@ -180,7 +183,7 @@ std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int ow
   std::string src;
   const std::string threads = std::to_string(32 * groups);
   src += "extern \"C\" __global__ void __launch_bounds__(" + threads +
-         ") tree_ldl_generated(const float* __restrict__ M, long long M_ld, const float* __restrict__ y,\n"
+         ") " + name + "(const float* __restrict__ M, long long M_ld, const float* __restrict__ y,\n"
          "    long long y_ld, float* __restrict__ x, long long x_ld, int nworld, int bulk) {\n"
          "  extern __shared__ __align__(16) float slots[];\n"
          "  const int lw = threadIdx.x & 31, part = threadIdx.x >> 5;\n"
@@ -291,30 +294,31 @@ std::string generate(const int32_t* prog, const int32_t* ptr, int groups, int ow
 
 }  // namespace
 
-extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr, int32_t nv, int32_t nM,
-                                    int32_t groups, int32_t owner, int32_t nslot, ImnTreeKernel** out) {
-  if (!prog || !prog_ptr || !out) return imn::set_error("imn_tree_ldl_compile: NULL argument"), IMN_ERR_NULL;
+// Checks a program, writes its source and compiles it; `what` names the caller in errors.
+static int compile_program(const char* what, const char* name, const int32_t* prog, const int32_t* prog_ptr, int32_t nv,
+                           int32_t nM, int32_t groups, int32_t owner, int32_t nslot, ImnTreeKernel** out) {
+  if (!prog || !prog_ptr || !out) return imn::set_error("%s: NULL argument", what), IMN_ERR_NULL;
   *out = nullptr;
   if (nv <= 0 || groups < 1 || groups > 4 || owner < 0 || owner >= groups || nslot <= 0 || nslot > (1 << 16))
-    return imn::set_error("imn_tree_ldl_compile: malformed plan"), IMN_ERR_SHAPE;
+    return imn::set_error("%s: malformed plan", what), IMN_ERR_SHAPE;
   const int nstream = 2 * groups + 1;
   for (int st = 0; st < nstream; ++st)
     if (prog_ptr[st] > prog_ptr[st + 1] || prog_ptr[st] < 0)
-      return imn::set_error("imn_tree_ldl_compile: stream offsets are not ascending"), IMN_ERR_SHAPE;
+      return imn::set_error("%s: stream offsets are not ascending", what), IMN_ERR_SHAPE;
   for (int pc = 0; pc < prog_ptr[nstream]; ++pc) {
     const int32_t* w = prog + 4 * pc;
     const int dst = w[1], a = w[2] & 0xFFFF, b = (w[2] >> 16) & 0xFFFF, c = w[3];
     const bool index_a = w[0] == OP_LOAD_M || w[0] == OP_LOAD_Y;  // a addresses M or y
     const bool index_d = w[0] == OP_STORE_X;                      // dst addresses x
-    if (w[0] < 0 || w[0] > OP_MULSUB || dst < 0 || (!index_d && dst >= nslot) || (index_d && dst >= nv) ||
+    if (w[0] < 0 || w[0] > OP_MULADD || dst < 0 || (!index_d && dst >= nslot) || (index_d && dst >= nv) ||
         (!index_a && a >= nslot) || (w[0] == OP_LOAD_M && a >= nM) || (w[0] == OP_LOAD_Y && a >= nv) || b >= nslot ||
         c < 0 || c >= nslot)
-      return imn::set_error("imn_tree_ldl_compile: instruction %d is out of range", pc), IMN_ERR_SHAPE;
+      return imn::set_error("%s: instruction %d is out of range", what, pc), IMN_ERR_SHAPE;
   }
   Nvrtc* rt = nvrtc();
-  if (!rt) return imn::set_error("imn_tree_ldl_compile: NVRTC (libnvrtc.so.12) could not be loaded"), IMN_ERR_UNSUPPORTED;
+  if (!rt) return imn::set_error("%s: NVRTC (libnvrtc.so.12) could not be loaded", what), IMN_ERR_UNSUPPORTED;
   ImnTreeKernel* k = new ImnTreeKernel;
-  k->nv = nv, k->nM = nM, k->groups = groups;
+  k->nv = nv, k->nM = nM, k->groups = groups, k->name = name;
   {
     // stage when two blocks' tiles fit an SM and the lane stride nM does not pile the
     // lanes onto a few banks; IMN_TREE_STAGE=0 keeps the plain loads (for comparisons)
@@ -326,11 +330,11 @@ extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr
     const char* env = getenv("IMN_TREE_STAGE");
     k->staged = !(env && env[0] == '0') && gcd < 8;
   }
-  k->source = generate(prog, prog_ptr, groups, owner, nslot, nv, nM, k->staged, &k->staged, &k->nshared);
+  k->source = generate(k->name, prog, prog_ptr, groups, owner, nslot, nv, nM, k->staged, &k->staged, &k->nshared);
   nvrtcProgram_t p = nullptr;
-  int rc = rt->create(&p, k->source.c_str(), "tree_ldl_generated.cu", 0, nullptr, nullptr);
+  int rc = rt->create(&p, k->source.c_str(), (k->name + ".cu").c_str(), 0, nullptr, nullptr);
   if (rc) {
-    imn::set_error("imn_tree_ldl_compile: nvrtcCreateProgram: %s", rt->error_string(rc));
+    imn::set_error("%s: nvrtcCreateProgram: %s", what, rt->error_string(rc));
     delete k;
     return IMN_ERR_LAUNCH;
   }
@@ -341,7 +345,7 @@ extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr
     rt->log_size(p, &n);
     std::string log(n, '\0');
     if (n) rt->log(p, &log[0]);
-    imn::set_error("imn_tree_ldl_compile: %s: %.380s", rt->error_string(rc), log.c_str());
+    imn::set_error("%s: %s: %.380s", what, rt->error_string(rc), log.c_str());
     rt->destroy(&p);
     delete k;
     return IMN_ERR_LAUNCH;
@@ -352,12 +356,27 @@ extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr
   if (n) rt->cubin(p, k->cubin.data());
   rt->destroy(&p);
   if (!n) {
-    imn::set_error("imn_tree_ldl_compile: NVRTC produced no machine code");
+    imn::set_error("%s: NVRTC produced no machine code", what);
     delete k;
     return IMN_ERR_LAUNCH;
   }
   *out = k;
   return IMN_OK;
+}
+
+extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr, int32_t nv, int32_t nM,
+                                    int32_t groups, int32_t owner, int32_t nslot, ImnTreeKernel** out) {
+  return compile_program("imn_tree_ldl_compile", "tree_ldl_generated", prog, prog_ptr, nv, nM, groups, owner, nslot, out);
+}
+
+// out = M v as a program of the same kind: before the first block barrier every warp
+// loads the entries of v its rows need into registers, after the second it forms its
+// rows' sums in the order of the symmetric-row table (one fmaf per stored entry, M read
+// once from the staged tile, no table and no v reads at run time) and stores them over
+// the tile of v, which leaves by the bulk store.
+extern "C" int imn_mul_m_compile(const int32_t* prog, const int32_t* prog_ptr, int32_t nv, int32_t nM, int32_t groups,
+                                 int32_t nslot, ImnTreeKernel** out) {
+  return compile_program("imn_mul_m_compile", "mul_m_generated", prog, prog_ptr, nv, nM, groups, 0, nslot, out);
 }
 
 extern "C" int imn_tree_ldl_kernel_info(const ImnTreeKernel* k, int32_t* shared_slots, int64_t* code_bytes,
@@ -391,7 +410,7 @@ extern "C" int imn_tree_ldl_compiled_solve(ImnTreeKernel* k, const float* M, int
   if (!k->kernel) {
     // first use: hand the machine code to the runtime (do this outside stream capture)
     cudaError_t e = cudaLibraryLoadData(&k->library, k->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0);
-    if (e == cudaSuccess) e = cudaLibraryGetKernel(&k->kernel, k->library, "tree_ldl_generated");
+    if (e == cudaSuccess) e = cudaLibraryGetKernel(&k->kernel, k->library, k->name.c_str());
     if (e == cudaSuccess && bytes > 48 * 1024)
       e = cudaFuncSetAttribute(reinterpret_cast<const void*>(k->kernel), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                (int)bytes);

@@ -10,6 +10,7 @@ a launch of hand-written CUDA through the C ABI; there is no other code path.
 from __future__ import annotations
 
 import ctypes as C
+import functools
 import logging
 from dataclasses import dataclass
 from typing import Any, Sequence
@@ -164,11 +165,40 @@ def log_kernel_selection(m: Any, d: Any, scratch: "OptimizedFwdPositionScratch")
     return line
 
 
-def mul_m(m: Any, d: Any, res: Any, vec: Any, stream=None) -> None:
+# Below this many worlds the tiles of the generated M v do not fill the GPU.
+_GENERATED_MUL_M_MIN_WORLDS = 4096
+
+
+def generated_mul_m_kernel(m: Any, d: Any):
+    """The model's generated M v kernel (compiled once per model, kept on it), or None."""
+    if int(d.nworld) < _GENERATED_MUL_M_MIN_WORLDS or getattr(m, "M_mulm_rowadr", None) is None:
+        return None
+    cached = getattr(m, "_imn_mul_m_kernel", "unset")
+    if cached != "unset":
+        return cached
+    from .mjw_kernels import mul_m_generated
+
+    kernel = mul_m_generated.compile_mul_m(m)
+    try:
+        m._imn_mul_m_kernel = kernel
+    except AttributeError:
+        pass
+    return kernel
+
+
+def mul_m(m: Any, d: Any, res: Any, vec: Any, stream=None, kernel: Any = None) -> None:
     """res = M vec per world (upstream ``support.mul_m`` through the preallocated
-    call, mjw_step_optimized.py:2252-2255)."""
+    call, mjw_step_optimized.py:2252-2255).  With ``kernel`` (the model's generated
+    straight-line kernel, ``mul_m_generated.compile_mul_m``) batches that fill the GPU run
+    through it; the bits are the same."""
     from .arrays import addr, elem_strides
 
+    if kernel is not None and int(d.nworld) >= _GENERATED_MUL_M_MIN_WORLDS and addr(res) != addr(vec):
+        from .mjw_kernels import mul_m_generated
+
+        with _lib.nvtx("mul_m_generated"):
+            mul_m_generated.mul_m(kernel, d.M, res, vec, stream)
+        return
     ms = binding.model_struct(m)
     rc = _lib.lib().imn_mul_m(
         C.byref(ms), addr(d.M), elem_strides(d.M)[0], addr(vec), elem_strides(vec)[0], addr(res),
@@ -215,13 +245,14 @@ def make_optimized_fwd_position_scratch(
         from .mjw_kernels import tree_fusion
 
         tree_reduction = tree_fusion.create_tree_reduction_scratch(m)
+    mul_m_kernel = generated_mul_m_kernel(m, d) if include_optimized_kernel_scratch else None
     scratch = OptimizedFwdPositionScratch(
         tree_reduction=tree_reduction,
         ball_limit_buffers=ball_buffers,
         solver_context=ctx,
         solver_nsolving=nsolving,
         constraint_free=_constraint_rows_impossible(m, ball_joint_limits),
-        mul_m_call=mul_m,
+        mul_m_call=functools.partial(mul_m, kernel=mul_m_kernel) if mul_m_kernel is not None else mul_m,
         dense_factor_solve=dense,
         tree_factor_solve=tree,
         tile_factor_solve=tile,

@@ -193,7 +193,77 @@ def test_plan_compiles_to_a_straight_line_kernel_without_a_gpu():
         tree_ldl.GeneratedKernel(bad, ptr, m.nv, m.nM, len(plan.groups), program.owner, program.nslot)
 
 
+def test_mul_m_program_forms_every_row_in_table_order_and_compiles(oracle):
+    """M v as a generated program: interpreted in float32 with one fmaf per stored entry it
+    equals the oracle's mul_m bit for bit, every warp loads v only before the barriers, and
+    the source compiles without a GPU with one fmaf per stored entry."""
+    from instantmimic_b200.mjw_kernels import mul_m_generated as mg
+
+    for tree in ("humanoid", "limbs", "branched"):
+        worlds = 5
+        m, Mv, _ = _model_and_matrices(TREES[tree], worlds)
+        v = np.random.default_rng(5).normal(size=(worlds, m.nv)).astype(np.float32)
+        want = np.zeros_like(v)
+        oracle.mul_m(m, Mv, v, want)
+        prog, ptr, nslot = mg.mul_m_program(m.M_mulm_rowadr, m.M_mulm_col, m.M_mulm_madr, m.nv)
+        G = mg.WARPS
+        assert ptr.size == 2 * G + 2 and ptr[G] == ptr[G + 1]  # empty trunk
+        assert set(prog[: ptr[G], 0]) <= {tree_ldl.OP_LOAD_Y}
+        assert tree_ldl.OP_LOAD_Y not in set(prog[ptr[G + 1] :, 0])
+        col = np.zeros((nslot, worlds), np.float32)
+        x = np.full((worlds, m.nv), np.nan, np.float32)
+        fma = lambda a, b, c: (a.astype(np.float64) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)  # noqa: E731
+        for op, dst, ab, _c in prog:
+            a, b = ab & 0xFFFF, (ab >> 16) & 0xFFFF
+            if op == tree_ldl.OP_LOAD_M:
+                col[dst] = Mv[:, a]
+            elif op == tree_ldl.OP_LOAD_Y:
+                col[dst] = v[:, a]
+            elif op == tree_ldl.OP_ZERO:
+                col[dst] = 0
+            elif op == mg.OP_MULADD:
+                col[dst] = fma(col[a], col[b], col[dst])  # exact: a float32 product fits a double
+            elif op == tree_ldl.OP_STORE_X:
+                x[:, dst] = col[a]
+        np.testing.assert_array_equal(x.view(np.uint32), want.view(np.uint32))
+        kernel = mg.GeneratedMulM(prog, ptr, m.nv, m.nM, nslot)
+        src = kernel.info()["source"]
+        assert "mul_m_generated(" in src and src.count("fmaf(") == int(m.M_mulm_rowadr[m.nv])
+        assert kernel.info()["shared_slots"] == 0  # nothing crosses warps
+
+
 # ---------------------------------------------------------------------------- GPU
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("layout", ["contiguous", "padded"])
+def test_generated_mul_m_returns_the_bits_of_mul_m(oracle, cuda_device, layout):
+    """The generated M v (tiles by bulk copies when contiguous, plain loads for padded
+    strides and the last partial tile) against the oracle, bit for bit."""
+    import torch
+
+    from instantmimic_b200 import mjw_model
+    from instantmimic_b200.mjw_kernels import mul_m_generated as mg
+
+    worlds = 4096 + 13
+    m, Mv, _ = _model_and_matrices(TREES["humanoid"], worlds)
+    v = np.random.default_rng(4).normal(size=(worlds, m.nv)).astype(np.float32)
+    want = np.zeros_like(v)
+    oracle.mul_m(m, Mv, v, want)
+    md = mjw_model.to_device(m, cuda_device)
+    kernel = mg.compile_mul_m(md)
+    assert kernel is not None and kernel.staged
+    pad = 0 if layout == "contiguous" else 3
+    Mt = torch.zeros((worlds, m.nM + pad), device=cuda_device)[:, : m.nM]
+    vt = torch.zeros((worlds, m.nv + pad), device=cuda_device)[:, : m.nv]
+    Mt.copy_(torch.from_numpy(Mv)), vt.copy_(torch.from_numpy(v))
+    out = torch.full((worlds, m.nv + pad), 7.0, device=cuda_device)[:, : m.nv]
+    mg.mul_m(kernel, Mt, out, vt)
+    torch.cuda.synchronize()
+    np.testing.assert_array_equal(out.cpu().numpy().view(np.uint32), want.view(np.uint32))
+    np.testing.assert_array_equal(vt.cpu().numpy(), v)  # the input is left alone
+    with pytest.raises(ValueError, match="alias"):
+        mg.mul_m(kernel, Mt, vt, vt)
 
 
 @pytest.mark.gpu
