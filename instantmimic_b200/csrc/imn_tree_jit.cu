@@ -113,7 +113,10 @@ void operands(const Ins& i, int reads[4], int& nread, int& write) {
 }  // namespace
 
 struct ImnTreeKernel {
-  int nv = 0, nM = 0, groups = 0, nshared = 0;
+  int nv = 0, nM = 0, groups = 0;
+  int nshared = 0;   // values that cross warps
+  int nexchange = 0;  // of those, the ones that need shared memory of their own
+  int min_blocks = 1;  // register bound of the generated kernel
   bool staged = false;  // M and y tiles in shared memory
   std::string name;     // entry point of the generated source
   std::string source;
@@ -126,7 +129,8 @@ struct ImnTreeKernel {
 namespace {
 
 std::string generate(const std::string& name, const int32_t* prog, const int32_t* ptr, int groups, int owner,
-                     int nslot, int nv, int nM, bool allow_stage, bool* staged_out, int* nshared_out) {
+                     int nslot, int nv, int nM, bool allow_stage, int min_blocks, bool* staged_out, int* nshared_out,
+                     int* nexchange_out) {
   const int nstream = 2 * groups + 1;
   auto warp_of = [&](int st) { return st < groups ? st : (st == groups ? owner : st - groups - 1); };
   std::vector<std::vector<Ins>> streams(nstream);
@@ -147,13 +151,57 @@ std::string generate(const std::string& name, const int32_t* prog, const int32_t
   for (int sl = 0; sl < nslot; ++sl)
     if (users[sl] & (users[sl] - 1u)) shared_index[sl] = nshared++;
   *nshared_out = nshared;
+  // A staged tile has room for most of the exchange: once a warp has read an entry of M
+  // into a register, nobody reads that cell of the tile again (an entry is loaded once),
+  // so a cross-warp value first written by the same warp later on can live there.  Cells
+  // are handed out in program order, phase by phase; within a phase a cross-warp value is
+  // touched by one warp only (the exchange goes through the block barriers), so the first
+  // touch found here is the first in time.  Values that find no cell keep a slot of their own.
+  std::vector<int> cell(nslot, -1);
+  int nexchange = nshared;
+  const size_t tile_only = 16 + sizeof(float) * ((size_t)((32 * nM + 3) & ~3) + ((32 * nv + 3) & ~3));
+  if (allow_stage && tile_only + 128 <= 113 * 1024) {
+    std::vector<int> loads(nM, 0);
+    for (const auto& code : streams)
+      for (const Ins& i : code)
+        if (i.op == OP_LOAD_M) ++loads[i.a];
+    std::vector<std::vector<int>> freed(groups);
+    std::vector<char> seen(nslot, 0);
+    for (int st = 0; st < nstream; ++st) {
+      const int w = warp_of(st);
+      for (const Ins& i : streams[st]) {
+        int reads[4], nread, write;
+        operands(i, reads, nread, write);
+        for (int k = 0; k < nread; ++k) seen[reads[k]] = 1;
+        if (write >= 0 && shared_index[write] >= 0 && !seen[write] && !freed[w].empty()) {
+          cell[write] = freed[w].back();
+          freed[w].pop_back();
+        }
+        if (write >= 0) seen[write] = 1;
+        if (i.op == OP_LOAD_M && loads[i.a] == 1) freed[w].push_back(i.a);
+      }
+    }
+    // the values left over are renumbered densely
+    nexchange = 0;
+    for (int sl = 0; sl < nslot; ++sl)
+      if (shared_index[sl] >= 0 && cell[sl] < 0) shared_index[sl] = nexchange++;
+  }
+  *nexchange_out = nexchange;
   // stage the tiles when two blocks' worth fit an SM's shared memory
-  const size_t tile_bytes =
-      16 + sizeof(float) * ((size_t)((32 * nM + 3) & ~3) + ((32 * nv + 3) & ~3) + 32 * (size_t)(nshared > 0 ? nshared : 1));
+  const size_t tile_bytes = tile_only + sizeof(float) * 32 * (size_t)(nexchange > 0 ? nexchange : 1);
   const bool staged = allow_stage && tile_bytes <= 113 * 1024;
   *staged_out = staged;
+  if (!staged && nexchange != nshared) {
+    // plain loads: no tile to lend cells, every cross-warp value has its own slot
+    nexchange = 0;
+    for (int sl = 0; sl < nslot; ++sl)
+      if (shared_index[sl] >= 0) cell[sl] = -1, shared_index[sl] = nexchange++;
+    *nexchange_out = nexchange;
+  }
   auto ref = [&](int sl) {
-    return shared_index[sl] >= 0 ? "S[" + std::to_string(shared_index[sl] * 32) + "]" : "r" + std::to_string(sl);
+    if (shared_index[sl] < 0) return "r" + std::to_string(sl);
+    if (cell[sl] >= 0) return "Mw[" + std::to_string(cell[sl]) + "]";
+    return "S[" + std::to_string(shared_index[sl] * 32) + "]";
   };
   auto emit = [&](std::string& out, const std::vector<Ins>& code) {
     for (const Ins& i : code) {
@@ -182,7 +230,7 @@ std::string generate(const std::string& name, const int32_t* prog, const int32_t
   };
   std::string src;
   const std::string threads = std::to_string(32 * groups);
-  src += "extern \"C\" __global__ void __launch_bounds__(" + threads +
+  src += "extern \"C\" __global__ void __launch_bounds__(" + threads + ", " + std::to_string(min_blocks) +
          ") " + name + "(const float* __restrict__ M, long long M_ld, const float* __restrict__ y,\n"
          "    long long y_ld, float* __restrict__ x, long long x_ld, int nworld, int bulk) {\n"
          "  extern __shared__ __align__(16) float slots[];\n"
@@ -203,6 +251,7 @@ std::string generate(const std::string& name, const int32_t* prog, const int32_t
            "  float* tileY = tileM + " + std::to_string((nMt + 3) & ~3) + ";\n"
            "  float* S = tileY + " + std::to_string((nyt + 3) & ~3) + " + lw;\n"
            "  const float* Mt = tileM + lw * " + sM + ";\n"
+           "  float* Mw = tileM + lw * " + sM + ";  // cells of entries already read hold exchanged values\n"
            "  float* yt = tileY + lw * " + sV + ";\n"
            "  const int w0 = blockIdx.x * 32;\n"
            "  const bool whole = bulk && w0 + 32 <= nworld;\n"
@@ -296,7 +345,8 @@ std::string generate(const std::string& name, const int32_t* prog, const int32_t
 
 // Checks a program, writes its source and compiles it; `what` names the caller in errors.
 static int compile_program(const char* what, const char* name, const int32_t* prog, const int32_t* prog_ptr, int32_t nv,
-                           int32_t nM, int32_t groups, int32_t owner, int32_t nslot, ImnTreeKernel** out) {
+                           int32_t nM, int32_t groups, int32_t owner, int32_t nslot, int min_blocks,
+                           ImnTreeKernel** out) {
   if (!prog || !prog_ptr || !out) return imn::set_error("%s: NULL argument", what), IMN_ERR_NULL;
   *out = nullptr;
   if (nv <= 0 || groups < 1 || groups > 4 || owner < 0 || owner >= groups || nslot <= 0 || nslot > (1 << 16))
@@ -330,7 +380,20 @@ static int compile_program(const char* what, const char* name, const int32_t* pr
     const char* env = getenv("IMN_TREE_STAGE");
     k->staged = !(env && env[0] == '0') && gcd < 8;
   }
-  k->source = generate(k->name, prog, prog_ptr, groups, owner, nslot, nv, nM, k->staged, &k->staged, &k->nshared);
+  // The register bound follows from the shared memory the kernel will ask for: a first
+  // pass of the generator sizes the exchange, the second writes the source with
+  // __launch_bounds__(threads, blocks an SM's shared memory holds, at most `min_blocks`).
+  // IMN_TREE_MIN_BLOCKS overrides the bound (for comparisons).
+  generate(k->name, prog, prog_ptr, groups, owner, nslot, nv, nM, k->staged, 1, &k->staged, &k->nshared, &k->nexchange);
+  {
+    size_t bytes = (size_t)(k->nexchange > 0 ? k->nexchange : 1) * 32 * sizeof(float);
+    if (k->staged) bytes += 16 + sizeof(float) * ((size_t)((32 * nM + 3) & ~3) + ((32 * nv + 3) & ~3));
+    const int fit = (int)((228 * 1024) / (bytes + 1024));
+    const char* env = getenv("IMN_TREE_MIN_BLOCKS");
+    k->min_blocks = env && atoi(env) > 0 ? atoi(env) : (fit < 1 ? 1 : (fit > min_blocks ? min_blocks : fit));
+  }
+  k->source = generate(k->name, prog, prog_ptr, groups, owner, nslot, nv, nM, k->staged, k->min_blocks, &k->staged,
+                       &k->nshared, &k->nexchange);
   nvrtcProgram_t p = nullptr;
   int rc = rt->create(&p, k->source.c_str(), (k->name + ".cu").c_str(), 0, nullptr, nullptr);
   if (rc) {
@@ -366,7 +429,8 @@ static int compile_program(const char* what, const char* name, const int32_t* pr
 
 extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr, int32_t nv, int32_t nM,
                                     int32_t groups, int32_t owner, int32_t nslot, ImnTreeKernel** out) {
-  return compile_program("imn_tree_ldl_compile", "tree_ldl_generated", prog, prog_ptr, nv, nM, groups, owner, nslot, out);
+  return compile_program("imn_tree_ldl_compile", "tree_ldl_generated", prog, prog_ptr, nv, nM, groups, owner, nslot, 4,
+                         out);
 }
 
 // out = M v as a program of the same kind: before the first block barrier every warp
@@ -376,7 +440,7 @@ extern "C" int imn_tree_ldl_compile(const int32_t* prog, const int32_t* prog_ptr
 // the tile of v, which leaves by the bulk store.
 extern "C" int imn_mul_m_compile(const int32_t* prog, const int32_t* prog_ptr, int32_t nv, int32_t nM, int32_t groups,
                                  int32_t nslot, ImnTreeKernel** out) {
-  return compile_program("imn_mul_m_compile", "mul_m_generated", prog, prog_ptr, nv, nM, groups, 0, nslot, out);
+  return compile_program("imn_mul_m_compile", "mul_m_generated", prog, prog_ptr, nv, nM, groups, 0, nslot, 6, out);
 }
 
 extern "C" int imn_tree_ldl_kernel_info(const ImnTreeKernel* k, int32_t* shared_slots, int64_t* code_bytes,
@@ -400,7 +464,7 @@ extern "C" int imn_tree_ldl_compiled_solve(ImnTreeKernel* k, const float* M, int
   if (nworld < 0 || M_ld < k->nM || y_ld < k->nv || x_ld < k->nv)
     return imn::set_error("imn_tree_ldl_compiled_solve: a stride is smaller than its extent"), IMN_ERR_SHAPE;
   if (nworld == 0) return IMN_OK;
-  size_t bytes = (size_t)(k->nshared > 0 ? k->nshared : 1) * 32 * sizeof(float);
+  size_t bytes = (size_t)(k->nexchange > 0 ? k->nexchange : 1) * 32 * sizeof(float);
   if (k->staged) bytes += 16 + sizeof(float) * ((size_t)((32 * k->nM + 3) & ~3) + ((32 * k->nv + 3) & ~3));
   if (bytes > 227 * 1024)
     return imn::set_error("imn_tree_ldl_compiled_solve: %zu bytes of shared memory per block (max %d)", bytes,

@@ -184,6 +184,12 @@ def test_plan_compiles_to_a_straight_line_kernel_without_a_gpu():
     src = info["source"]
     assert src.count("fmaf(") == int(np.isin(prog[:, 0], (tree_ldl.OP_UPD, tree_ldl.OP_SUBMUL, tree_ldl.OP_MULSUB)).sum())
     assert src.count("bar.sync") == 2 * len(plan.groups)
+    # the values that cross warps live in cells of the staged tile whose entry the writing
+    # warp has already read: the exchange takes no shared memory of its own
+    import re
+
+    body = src[src.index("switch (part)"):]
+    assert len(set(re.findall(r"Mw\[\d+\]", body))) == info["shared_slots"] and "S[" not in body
     # malformed programs are rejected before any compilation
     from instantmimic_b200 import _lib
 
