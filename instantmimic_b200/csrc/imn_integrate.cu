@@ -131,18 +131,9 @@ __device__ __forceinline__ void quat_integrate(float q[4], const float w[3], flo
   q[0] = o[0] * inv, q[1] = o[1] * inv, q[2] = o[2] * inv, q[3] = o[3] * inv;
 }
 
-// One thread per (world, joint): the joint's dofs get their new velocity, then its
-// coordinates move with it.
-__global__ void __launch_bounds__(256)
-    advance_kernel(const ImnAdvance P, const float* __restrict__ qacc, const int64_t qacc_ld, const int nworld) {
-  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (t >= (int64_t)nworld * P.njnt) return;
-  const int w = (int)(t / P.njnt), j = (int)(t - (int64_t)w * P.njnt);
-  const float h = P.timestep[w % P.n_timestep];
-  const int type = P.jnt_type[j], dof = P.jnt_dofadr[j], pos = P.jnt_qposadr[j];
-  float* qvel = P.qvel + (size_t)w * P.qvel_ld + dof;
-  float* qpos = P.qpos + (size_t)w * P.qpos_ld + pos;
-  const float* acc = qacc + (size_t)w * qacc_ld + dof;
+// The advance of one joint of one world: its dofs get their new velocity, then its
+// coordinates move with it.  `qvel`, `qpos`, `acc` point at the joint's first entry.
+__device__ __forceinline__ void advance_joint(int type, float h, float* qvel, float* qpos, const float* acc) {
   const int ndof = type == IMN_JNT_FREE ? 6 : (type == IMN_JNT_BALL ? 3 : 1);
   float v[6];
   for (int k = 0; k < ndof; ++k) {
@@ -161,7 +152,56 @@ __global__ void __launch_bounds__(256)
   } else {
     qpos[0] = qpos[0] + h * v[0];
   }
-  if (j == 0 && P.time) P.time[w] = P.time[w] + h;
+}
+
+// A block advances 32 consecutive worlds: their qpos, qvel and qacc rows come into shared
+// memory with coalesced loads, lane = world, the warps share the joints (a warp works on
+// one joint of 32 worlds at a time, so its lanes take the same branch: with a thread per
+// (world, joint) every warp held a free joint next to hinges and ran the quaternion path
+// for one lane in 29), and the rows leave with coalesced stores.
+static const int kAdvanceWarps = 4;
+
+__global__ void __launch_bounds__(32 * kAdvanceWarps)
+    advance_kernel(const ImnAdvance P, const float* __restrict__ qacc, const int64_t qacc_ld, const int nworld) {
+  extern __shared__ __align__(16) float rows[];
+  float* sq = rows;                // [32][nq]
+  float* sv = sq + 32 * P.nq;      // [32][nv]
+  float* sa = sv + 32 * P.nv;      // [32][nv]
+  const int w0 = blockIdx.x * 32, nw = min(32, nworld - w0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  auto move = [&](float* tile, float* global, const float* source, int64_t ld, int n, bool store) {
+    if (ld == n) {  // the block's rows are one contiguous run
+      float* g = global ? global + (size_t)w0 * ld : nullptr;
+      const float* c = source ? source + (size_t)w0 * ld : g;
+      for (int e = threadIdx.x; e < nw * n; e += blockDim.x)
+        if (store) g[e] = tile[e];
+        else tile[e] = c[e];
+      return;
+    }
+    for (int e = threadIdx.x; e < nw * n; e += blockDim.x) {
+      const int r = e / n, c = e - r * n;
+      const size_t at = (size_t)(w0 + r) * ld + c;
+      if (store) global[at] = tile[e];
+      else tile[e] = source ? source[at] : global[at];
+    }
+  };
+  move(sq, P.qpos, nullptr, P.qpos_ld, P.nq, false);
+  move(sv, P.qvel, nullptr, P.qvel_ld, P.nv, false);
+  move(sa, nullptr, qacc, qacc_ld, P.nv, false);
+  __syncthreads();
+  if (lane < nw) {
+    const int w = w0 + lane;
+    const float h = P.timestep[w % P.n_timestep];
+#pragma unroll 1
+    for (int j = warp; j < P.njnt; j += kAdvanceWarps) {
+      const int dof = P.jnt_dofadr[j], pos = P.jnt_qposadr[j];
+      advance_joint(P.jnt_type[j], h, sv + lane * P.nv + dof, sq + lane * P.nq + pos, sa + lane * P.nv + dof);
+    }
+    if (warp == 0 && P.time) P.time[w] = P.time[w] + h;
+  }
+  __syncthreads();
+  move(sq, P.qpos, nullptr, P.qpos_ld, P.nq, true);
+  move(sv, P.qvel, nullptr, P.qvel_ld, P.nv, true);
 }
 
 }  // namespace imn
@@ -202,8 +242,15 @@ extern "C" int imn_advance(const ImnAdvance* p, const float* qacc, int64_t qacc_
       p->qpos_ld < p->nq)
     return imn::set_error("imn_advance: bad extent or stride"), IMN_ERR_SHAPE;
   if (nworld == 0) return IMN_OK;
-  const int64_t threads = (int64_t)nworld * p->njnt;
-  imn::advance_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(*p, qacc, qacc_ld, nworld);
+  const size_t bytes = sizeof(float) * 32 * ((size_t)p->nq + 2 * (size_t)p->nv);
+  if (bytes > 227 * 1024) return imn::set_error("imn_advance: nq %d too large", p->nq), IMN_ERR_LIMIT;
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(imn::advance_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess)
+      return imn::set_error("imn_advance: cudaFuncSetAttribute: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  }
+  imn::advance_kernel<<<(unsigned)((nworld + 31) / 32), 32 * imn::kAdvanceWarps, bytes, (cudaStream_t)stream>>>(
+      *p, qacc, qacc_ld, nworld);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return imn::set_error("imn_advance: launch failed: %s", cudaGetErrorString(e)), IMN_ERR_LAUNCH;
   return IMN_OK;
