@@ -373,6 +373,12 @@ __global__ void __launch_bounds__(32 * kTreeWarps)
   copy_out<GW>(cdof_dot_out + (size_t)w * nv6, dot, nv6, sl, t.live);
 }
 
+}  // namespace imn
+
+#include "imn_body_tree_tile.cuh"
+
+namespace imn {
+
 static int check_tree(const ImnBodyTree* T, const char* who, bool need_dofs) {
   if (!T) return set_error("%s: NULL tree", who), IMN_ERR_NULL;
   if (T->nbody <= 0 || T->nlevels <= 0) return set_error("%s: empty body tree", who), IMN_ERR_SHAPE;
@@ -422,6 +428,25 @@ static int launch_tree(const char* who, void (*kernel)(Args...), int gw, size_t 
 }
 
 static size_t up4z(size_t n) { return (n + 3) & ~(size_t)3; }
+
+// The lane-per-world kernels take over from 4096 worlds on (128 blocks of 32 worlds: below
+// that the teams fill the GPU better) when two blocks' rows fit an SM's shared memory.
+static bool use_tiles(int nworld, size_t bytes) { return nworld >= 4096 && bytes <= 113 * 1024; }
+
+template <typename... Args>
+static int launch_tile(const char* who, void (*kernel)(Args...), size_t bytes, int nworld, void* stream, Args... args) {
+  if (bytes > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return set_error("%s: cudaFuncSetAttribute: %s", who, cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  }
+  kernel<<<(nworld + 31) / 32, 32 * kTileWarps, bytes, (cudaStream_t)stream>>>(args...);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error("%s: launch failed: %s", who, cudaGetErrorString(e)), IMN_ERR_LAUNCH;
+  return IMN_OK;
+}
+static size_t oddz(size_t n) { return n | 1; }
 
 // KERNEL<8 | 16 | 32> by the tree's team width
 #define IMN_TEAM_LAUNCH(LANES, KERNEL, FLOATS, NWORLD, STREAM, ...)                                \
@@ -481,6 +506,13 @@ extern "C" int imn_com_vel(const ImnBodyTree* T, const float* qvel, int64_t qvel
   if (!qvel || !cdof || !cvel || !cdof_dot || !T->body_jntadr || !T->body_jntnum || !T->jnt_type)
     return imn::set_error("%s: NULL array", who), IMN_ERR_NULL;
   if (qvel_ld < T->nv) return imn::set_error("%s: qvel stride < nv", who), IMN_ERR_SHAPE;
+  {
+    const size_t bytes =
+        128 * (imn::oddz((size_t)T->nbody * 6) + 2 * imn::oddz((size_t)T->nv * 6) + imn::oddz(T->nv));
+    if (imn::use_tiles(nworld, bytes))
+      return imn::launch_tile(who, imn::com_vel_tile_kernel, bytes, nworld, stream, *T, qvel, qvel_ld, cdof, cvel,
+                              cdof_dot, (int)nworld);
+  }
   return IMN_TEAM_LAUNCH(imn::team_lanes(T), imn::com_vel_kernel, imn::up4z((size_t)T->nbody * 6) + 2 * imn::up4z((size_t)T->nv * 6),
                          nworld, stream, *T, qvel, qvel_ld, cdof, cvel, cdof_dot, (int)nworld);
 }

@@ -294,10 +294,11 @@ def test_cuda_accumulate_cancellation_order():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("name", ["humanoid", "snu", "g1"])
-@pytest.mark.parametrize("nworld,team", [(5, None), (2051, None), (37, 16), (37, 32)])
+@pytest.mark.parametrize("nworld,team", [(5, None), (2051, None), (37, 16), (37, 32), (4096 + 13, None)])
 def test_cuda_smooth_stages_bit_exact(name, nworld, team):
     """Every width of the per-world lane team (8 is what these models get; 16 and 32 forced)
-    and batches that leave the last warp with surplus teams."""
+    and batches that leave the last warp with surplus teams; from 4096 worlds on the
+    lane-per-world kernels run (32 worlds per block; the last block is partial)."""
     from dataclasses import replace
 
     m, d, scratch = smooth_case(name, nworld=nworld)
