@@ -160,34 +160,45 @@ __device__ __forceinline__ void advance_joint(int type, float h, float* qvel, fl
 // (world, joint) every warp held a free joint next to hinges and ran the quaternion path
 // for one lane in 29), and the rows leave with coalesced stores.
 static const int kAdvanceWarps = 4;
+__host__ __device__ inline int advance_stride(int n) { return (n & 3) == 0 ? (n | 1) : n; }
 
 __global__ void __launch_bounds__(32 * kAdvanceWarps)
     advance_kernel(const ImnAdvance P, const float* __restrict__ qacc, const int64_t qacc_ld, const int nworld) {
   extern __shared__ __align__(16) float rows[];
-  float* sq = rows;                // [32][nq]
-  float* sv = sq + 32 * P.nq;      // [32][nv]
-  float* sa = sv + 32 * P.nv;      // [32][nv]
+  // row strides: the lanes of a warp read the same element of 32 rows; a row length that
+  // shares a factor of 4 or more with the 32 banks is padded to an odd stride
+  const int tq = advance_stride(P.nq), tv = advance_stride(P.nv);
+  float* sq = rows;            // [32][tq]
+  float* sv = sq + 32 * tq;    // [32][tv]
+  float* sa = sv + 32 * tv;    // [32][tv]
   const int w0 = blockIdx.x * 32, nw = min(32, nworld - w0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  auto move = [&](float* tile, float* global, const float* source, int64_t ld, int n, bool store) {
-    if (ld == n) {  // the block's rows are one contiguous run
+  // the block's rows as one run of nw * n elements over all threads (consecutive threads,
+  // consecutive addresses).  Row and column come from a multiplication by 1 / n, exact for
+  // these few thousand elements ((e + 1/2) / n is at least 1 / (2 n) away from an integer),
+  // so that the iterations do not depend on each other and their loads overlap.
+  auto move = [&](float* tile, int stride, float* global, const float* source, int64_t ld, int n, bool store) {
+    if (stride == n && ld == n) {  // rows back to back on both sides: one straight copy
       float* g = global ? global + (size_t)w0 * ld : nullptr;
-      const float* c = source ? source + (size_t)w0 * ld : g;
-      for (int e = threadIdx.x; e < nw * n; e += blockDim.x)
+      const float* src = source ? source + (size_t)w0 * ld : g;
+#pragma unroll 4
+      for (int e = threadIdx.x; e < nw * n; e += 32 * kAdvanceWarps)
         if (store) g[e] = tile[e];
-        else tile[e] = c[e];
+        else tile[e] = src[e];
       return;
     }
-    for (int e = threadIdx.x; e < nw * n; e += blockDim.x) {
-      const int r = e / n, c = e - r * n;
+    const float inv = 1.0f / (float)n;
+#pragma unroll 4
+    for (int e = threadIdx.x; e < nw * n; e += 32 * kAdvanceWarps) {
+      const int r = (int)(((float)e + 0.5f) * inv), c = e - r * n;
       const size_t at = (size_t)(w0 + r) * ld + c;
-      if (store) global[at] = tile[e];
-      else tile[e] = source ? source[at] : global[at];
+      if (store) global[at] = tile[r * stride + c];
+      else tile[r * stride + c] = source ? source[at] : global[at];
     }
   };
-  move(sq, P.qpos, nullptr, P.qpos_ld, P.nq, false);
-  move(sv, P.qvel, nullptr, P.qvel_ld, P.nv, false);
-  move(sa, nullptr, qacc, qacc_ld, P.nv, false);
+  move(sq, tq, P.qpos, nullptr, P.qpos_ld, P.nq, false);
+  move(sv, tv, P.qvel, nullptr, P.qvel_ld, P.nv, false);
+  move(sa, tv, nullptr, qacc, qacc_ld, P.nv, false);
   __syncthreads();
   if (lane < nw) {
     const int w = w0 + lane;
@@ -195,13 +206,13 @@ __global__ void __launch_bounds__(32 * kAdvanceWarps)
 #pragma unroll 1
     for (int j = warp; j < P.njnt; j += kAdvanceWarps) {
       const int dof = P.jnt_dofadr[j], pos = P.jnt_qposadr[j];
-      advance_joint(P.jnt_type[j], h, sv + lane * P.nv + dof, sq + lane * P.nq + pos, sa + lane * P.nv + dof);
+      advance_joint(P.jnt_type[j], h, sv + lane * tv + dof, sq + lane * tq + pos, sa + lane * tv + dof);
     }
     if (warp == 0 && P.time) P.time[w] = P.time[w] + h;
   }
   __syncthreads();
-  move(sq, P.qpos, nullptr, P.qpos_ld, P.nq, true);
-  move(sv, P.qvel, nullptr, P.qvel_ld, P.nv, true);
+  move(sq, tq, P.qpos, nullptr, P.qpos_ld, P.nq, true);
+  move(sv, tv, P.qvel, nullptr, P.qvel_ld, P.nv, true);
 }
 
 }  // namespace imn
@@ -242,7 +253,7 @@ extern "C" int imn_advance(const ImnAdvance* p, const float* qacc, int64_t qacc_
       p->qpos_ld < p->nq)
     return imn::set_error("imn_advance: bad extent or stride"), IMN_ERR_SHAPE;
   if (nworld == 0) return IMN_OK;
-  const size_t bytes = sizeof(float) * 32 * ((size_t)p->nq + 2 * (size_t)p->nv);
+  const size_t bytes = sizeof(float) * 32 * ((size_t)imn::advance_stride(p->nq) + 2 * (size_t)imn::advance_stride(p->nv));
   if (bytes > 227 * 1024) return imn::set_error("imn_advance: nq %d too large", p->nq), IMN_ERR_LIMIT;
   if (bytes > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(imn::advance_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
