@@ -478,3 +478,29 @@ def test_mul_m_tile_paths_match_the_oracle(oracle, cuda_device, layout):
         np.testing.assert_array_equal(dd.efc.Ma.cpu().numpy().view(np.uint32), want.view(np.uint32))
         np.testing.assert_array_equal(dd.qacc.cpu().numpy(), v)
         assert float(dd.qfrc_constraint.abs().max()) == 0.0 and int(dd.solver_niter.abs().max()) == 0
+
+
+@pytest.mark.gpu
+def test_scratch_mul_m_call_takes_the_generated_kernel_from_4096_worlds(cuda_device):
+    """make_optimized_fwd_position_scratch hands out the generated M v for batches that fill
+    the GPU (the plain call below that); both return the bits of imn_mul_m."""
+    import functools
+
+    import torch
+
+    from instantmimic_b200 import mjw_model
+    from instantmimic_b200 import mjw_step_optimized as runtime
+
+    for worlds, generated in ((4096, True), (64, False)):
+        m, Mv, _ = _model_and_matrices(TREES["humanoid"], worlds)
+        d = mjw_model.make_data(m, worlds, 0)
+        d.M[:] = Mv
+        d.qacc_smooth[:] = np.random.default_rng(8).normal(size=(worlds, m.nv)).astype(np.float32)
+        md, dd = mjw_model.to_device(m, cuda_device), mjw_model.to_device(d, cuda_device)
+        scratch = runtime.make_optimized_fwd_position_scratch(md, dd, cuda_device)
+        assert isinstance(scratch.mul_m_call, functools.partial) == generated
+        a, b = torch.empty_like(dd.qacc_smooth), torch.empty_like(dd.qacc_smooth)
+        scratch.mul_m_call(md, dd, a, dd.qacc_smooth)
+        runtime.mul_m(md, dd, b, dd.qacc_smooth)
+        torch.cuda.synchronize()
+        assert torch.equal(a.view(torch.int32), b.view(torch.int32))
