@@ -129,7 +129,7 @@ def optimized_kernel_capabilities(m: Any, scratch: "OptimizedFwdPositionScratch"
     plan = getattr(ctx, "sparse_hessian_plan", None) if ctx is not None else None
     tree = getattr(scratch, "tree_factor_solve", None)
     return {
-        "tree": False,  # body-tree reductions are not part of this library
+        "tree": bool(enabled and getattr(scratch, "tree_reduction", None) is not None),
         "indexed_factor": bool(enabled and getattr(scratch, "dense_factor_solve", None) is not None),
         "persistent_newton": fused,
         "constraint_free": bool(getattr(scratch, "constraint_free", False)),
@@ -160,6 +160,8 @@ def log_kernel_selection(m: Any, d: Any, scratch: "OptimizedFwdPositionScratch")
     else:
         parts.append("solve: outside the fused path")
     parts.append(f"M factor/solve: {caps['m_factor_solve']}")
+    parts.append("M v: " + ("generated kernel" if isinstance(scratch.mul_m_call, functools.partial) else "table kernels"))
+    parts.append("body-tree stages: " + ("fused" if caps["tree"] else "none"))
     line = "IMN_KERNEL_PATH " + "; ".join(parts)
     logger.info(line)
     return line

@@ -99,6 +99,15 @@ def test_tree_selection_keeps_the_kernel_flag():
     assert _select_tree_reduction(SimpleNamespace(tree_reduction=atomic), True) is atomic
     assert _select_tree_reduction(SimpleNamespace(tree_reduction=ordered), False) is ordered
     assert _select_tree_reduction(None, True) is None
+    # the capability record names the tree scratch (mjw_step_optimized.py:2862-2875)
+    from instantmimic_b200.mjw_step_optimized import optimized_kernel_capabilities
+
+    bare = dict(solver_context=None, solver_uses_compact=False, dense_factor_solve=None, tile_factor_solve=None,
+                tree_factor_solve=None, constraint_free=False)
+    model = SimpleNamespace(nv=3)
+    assert optimized_kernel_capabilities(model, SimpleNamespace(tree_reduction=ordered, **bare))["tree"] is True
+    assert optimized_kernel_capabilities(model, SimpleNamespace(tree_reduction=None, **bare))["tree"] is False
+    assert optimized_kernel_capabilities(model, SimpleNamespace(tree_reduction=ordered, **bare), enabled=False)["tree"] is False
 
 
 def test_missing_scratch_is_an_error_not_a_fallback():
