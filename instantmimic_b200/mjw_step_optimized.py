@@ -160,7 +160,7 @@ def log_kernel_selection(m: Any, d: Any, scratch: "OptimizedFwdPositionScratch")
     else:
         parts.append("solve: outside the fused path")
     parts.append(f"M factor/solve: {caps['m_factor_solve']}")
-    parts.append("M v: " + ("generated kernel" if isinstance(scratch.mul_m_call, functools.partial) else "table kernels"))
+    parts.append("M v: " + ("generated kernel" if isinstance(getattr(scratch, "mul_m_call", None), functools.partial) else "table kernels"))
     parts.append("body-tree stages: " + ("fused" if caps["tree"] else "none"))
     line = "IMN_KERNEL_PATH " + "; ".join(parts)
     logger.info(line)
