@@ -36,11 +36,11 @@ sys.path.insert(0, str(ROOT))
 METRIC = "newton_solver_world_steps_per_s"
 UNIT = "world-steps/s"
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the humanoid solve kernel
-# in an ncu capture of a 16384-world batch: 139.5 MB (128.26 read + 11.24 written), 8.51 KB
+# in an ncu capture of a 16384-world batch: 140.3 MB (128.33 read + 12.01 written), 8.56 KB
 # per world.  DRAM traffic of
 # this kernel grows in proportion to the worlds of a launch (every world's inputs are
 # read once), so the figure is scaled by the worlds of the bench's launch.
-NCU_TRAFFIC_BYTES_PER_WORLD_HUMANOID = 139.5e6 / 16384
+NCU_TRAFFIC_BYTES_PER_WORLD_HUMANOID = 140.3e6 / 16384
 STRONG_TOTAL_WORLDS = 8192
 
 
