@@ -1,4 +1,4 @@
-"""The reference's own CUDA text as the judge of the factor arithmetic.
+"""The reference's own CUDA text as the arbiter of the factor arithmetic.
 
 tests/golden/ref_snippets.npz holds inputs and outputs of the reference's generated CUDA
 for the sparse-pattern Hessian factor and the tree L'DL of M (compiled with nvcc, run on a
