@@ -238,6 +238,42 @@ def test_mul_m_program_forms_every_row_in_table_order_and_compiles(oracle):
         assert kernel.info()["shared_slots"] == 0  # nothing crosses warps
 
 
+@pytest.mark.parametrize("tree", ["branched", "limbs", "humanoid", "snu"])
+def test_lent_tile_cells_are_dead_before_they_are_reused(tree):
+    """A cross-warp value may live in the tile cell of an entry of M only if that entry is
+    read exactly once in the whole kernel, by the warp that first writes the value, before
+    that write (nobody else ever looks at the cell again)."""
+    import re
+
+    build = TREES.get(tree) or synthetic.snu_tree
+    m, _, _ = _model_and_matrices(build, 1)
+    structure = _structure(m)
+    plan = tree_ldl.best_tree_ldl_plan(*structure)
+    program = tree_ldl._Program(*structure, plan)
+    prog, ptr = program.encode()
+    G = len(plan.groups)
+    src = tree_ldl.GeneratedKernel(prog, ptr, m.nv, m.nM, G, program.owner, program.nslot).info()["source"]
+    if "tileM" not in src:
+        pytest.skip("tile not staged for this model")
+    body = src[src.index("switch (part)"):]
+    cases = re.split(r"\n  case \d+: \{\n", body)[1:]
+    assert len(cases) == G
+    lent = set(re.findall(r"Mw\[(\d+)\]", body))
+    for e in lent:
+        loads = [(j, mt.start()) for j, c in enumerate(cases) for mt in re.finditer(r"= Mt\[%s\];" % e, c)]
+        assert len(loads) == 1, e
+        j, at = loads[0]
+        first_use = {k: c.find("Mw[%s]" % e) for k, c in enumerate(cases) if "Mw[%s]" % e in c}
+        # the loading warp writes it first (an assignment), after its load
+        assert j in first_use and first_use[j] > at
+        assert re.match(r"Mw\[%s\] = " % e, cases[j][first_use[j]:])
+        # program order across phases: the writer's first use sits in an earlier phase than, or
+        # the same warp as, every other use (phases are separated by the two barriers)
+        phase = lambda c, pos: c[:pos].count("bar.sync")  # noqa: E731
+        for k, pos in first_use.items():
+            assert k == j or phase(cases[k], pos) > phase(cases[j], first_use[j])
+
+
 # ---------------------------------------------------------------------------- GPU
 
 
