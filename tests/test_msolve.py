@@ -216,21 +216,7 @@ def test_mul_m_program_forms_every_row_in_table_order_and_compiles(oracle):
         assert ptr.size == 2 * G + 2 and ptr[G] == ptr[G + 1]  # empty trunk
         assert set(prog[: ptr[G], 0]) <= {tree_ldl.OP_LOAD_Y}
         assert tree_ldl.OP_LOAD_Y not in set(prog[ptr[G + 1] :, 0])
-        col = np.zeros((nslot, worlds), np.float32)
-        x = np.full((worlds, m.nv), np.nan, np.float32)
-        fma = lambda a, b, c: (a.astype(np.float64) * b.astype(np.float64) + c.astype(np.float64)).astype(np.float32)  # noqa: E731
-        for op, dst, ab, _c in prog:
-            a, b = ab & 0xFFFF, (ab >> 16) & 0xFFFF
-            if op == tree_ldl.OP_LOAD_M:
-                col[dst] = Mv[:, a]
-            elif op == tree_ldl.OP_LOAD_Y:
-                col[dst] = v[:, a]
-            elif op == tree_ldl.OP_ZERO:
-                col[dst] = 0
-            elif op == mg.OP_MULADD:
-                col[dst] = fma(col[a], col[b], col[dst])  # exact: a float32 product fits a double
-            elif op == tree_ldl.OP_STORE_X:
-                x[:, dst] = col[a]
+        x = _interpret_mul_m(prog, nslot, Mv, v, m.nv)
         np.testing.assert_array_equal(x.view(np.uint32), want.view(np.uint32))
         kernel = mg.GeneratedMulM(prog, ptr, m.nv, m.nM, nslot)
         src = kernel.info()["source"]
@@ -272,6 +258,60 @@ def test_lent_tile_cells_are_dead_before_they_are_reused(tree):
         phase = lambda c, pos: c[:pos].count("bar.sync")  # noqa: E731
         for k, pos in first_use.items():
             assert k == j or phase(cases[k], pos) > phase(cases[j], first_use[j])
+
+
+def _interpret_mul_m(prog, nslot, Mv, v, nv):
+    """float32 interpretation of an M v program (a float32 product is exact in a double, so
+    one rounding of the double sum is the fused multiply-add)."""
+    from instantmimic_b200.mjw_kernels import mul_m_generated as mg
+
+    col = np.zeros((nslot, Mv.shape[0]), np.float32)
+    x = np.full((Mv.shape[0], nv), np.nan, np.float32)
+    for op, dst, ab, _c in prog:
+        a, b = ab & 0xFFFF, (ab >> 16) & 0xFFFF
+        if op == tree_ldl.OP_LOAD_M:
+            col[dst] = Mv[:, a]
+        elif op == tree_ldl.OP_LOAD_Y:
+            col[dst] = v[:, a]
+        elif op == tree_ldl.OP_ZERO:
+            col[dst] = 0
+        elif op == mg.OP_MULADD:
+            col[dst] = (col[a].astype(np.float64) * col[b].astype(np.float64) + col[dst].astype(np.float64)).astype(np.float32)
+        elif op == tree_ldl.OP_STORE_X:
+            x[:, dst] = col[a]
+    return x
+
+
+def test_mul_m_program_on_random_forests(oracle):
+    """Random kinematic forests (several roots, chains, bushy trees, nv 1 .. 70), 1 to 4
+    warps: the program returns the oracle's bits and every row is stored once."""
+    from instantmimic_b200.mjw_kernels import mul_m_generated as mg
+
+    rng = np.random.default_rng(11)
+    for trial in range(12):
+        nv = int(rng.integers(1, 71))
+        style = trial % 3
+        parent = np.full(nv, -1, np.int32)
+        for i in range(1, nv):
+            if style == 0:
+                parent[i] = i - 1 if rng.random() < 0.9 else -1           # chains, now and then a new root
+            elif style == 1:
+                parent[i] = int(rng.integers(-1, i))                       # anything goes
+            else:
+                parent[i] = int(rng.integers(max(i - 3, -1), i))           # shallow and bushy
+        m = put_model(parent)
+        worlds = 3
+        Mv, _ = synthetic.random_mass_matrices(m, worlds, rng)
+        v = rng.normal(size=(worlds, nv)).astype(np.float32)
+        want = np.zeros_like(v)
+        oracle.mul_m(m, Mv, v, want)
+        warps = 1 + trial % 4
+        prog, ptr, nslot = mg.mul_m_program(m.M_mulm_rowadr, m.M_mulm_col, m.M_mulm_madr, nv, warps)
+        assert ptr.size == 2 * warps + 2
+        stores = prog[prog[:, 0] == tree_ldl.OP_STORE_X, 1]
+        assert sorted(stores.tolist()) == list(range(nv))
+        got = _interpret_mul_m(prog, nslot, Mv, v, nv)
+        np.testing.assert_array_equal(got.view(np.uint32), want.view(np.uint32), err_msg=f"trial {trial}")
 
 
 # ---------------------------------------------------------------------------- GPU
