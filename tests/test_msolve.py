@@ -224,14 +224,24 @@ def test_mul_m_program_forms_every_row_in_table_order_and_compiles(oracle):
         assert kernel.info()["shared_slots"] == 0  # nothing crosses warps
 
 
-@pytest.mark.parametrize("tree", ["branched", "limbs", "humanoid", "snu"])
+def _random_forest(seed):
+    """A bushy random forest of 20 to 60 dofs (several limbs, so that the plan has groups)."""
+    rng = np.random.default_rng(seed)
+    nv = int(rng.integers(20, 61))
+    parent = np.full(nv, -1, np.int32)
+    for i in range(1, nv):
+        parent[i] = int(rng.integers(max(i - 6, 0), i)) if rng.random() < 0.97 else -1
+    return lambda: (parent, None)
+
+
+@pytest.mark.parametrize("tree", ["branched", "limbs", "humanoid", "snu", "random1", "random2", "random3"])
 def test_lent_tile_cells_are_dead_before_they_are_reused(tree):
     """A cross-warp value may live in the tile cell of an entry of M only if that entry is
     read exactly once in the whole kernel, by the warp that first writes the value, before
     that write (nobody else ever looks at the cell again)."""
     import re
 
-    build = TREES.get(tree) or synthetic.snu_tree
+    build = TREES.get(tree) or (_random_forest(int(tree[6:])) if tree.startswith("random") else synthetic.snu_tree)
     m, _, _ = _model_and_matrices(build, 1)
     structure = _structure(m)
     plan = tree_ldl.best_tree_ldl_plan(*structure)
