@@ -90,11 +90,13 @@ def test_structure_check_rejects_rows_that_are_not_nested_ancestor_chains():
     assert tree_ldl.tree_ldl_structure(np.zeros(0), np.zeros(0), np.zeros(0)) is None
 
 
-def test_compiled_program_matches_the_plan_interpreter(oracle):
+@pytest.mark.parametrize("tree", ["humanoid", "snu", "random4", "random5", "random6"])
+def test_compiled_program_matches_the_plan_interpreter(oracle, tree):
     """The instruction list the CUDA kernel runs, interpreted in numpy float64,
     solves M x = y (checks compilation independently of any kernel)."""
     worlds = 5
-    m, Mv, Md = _model_and_matrices(synthetic.humanoid_tree, worlds)
+    build = {"humanoid": synthetic.humanoid_tree, "snu": synthetic.snu_tree}.get(tree) or _random_forest(int(tree[6:]))
+    m, Mv, Md = _model_and_matrices(build, worlds)
     structure = _structure(m)
     y = np.random.default_rng(2).normal(size=(worlds, m.nv))
     for groups in (1, 3, 4):
