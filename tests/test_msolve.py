@@ -39,11 +39,11 @@ def _structure(m):
     return tree_ldl.tree_ldl_structure(m.M_rowadr, m.M_rownnz, m.M_colind)
 
 
-@pytest.mark.parametrize("tree", ["branched", "limbs", "humanoid"])
+@pytest.mark.parametrize("tree", ["branched", "limbs", "humanoid", "random7", "random8"])
 @pytest.mark.parametrize("groups", [1, 2, 4])
 def test_tree_oracle_matches_a_dense_solve(oracle, tree, groups):
     worlds = 37
-    m, Mv, Md = _model_and_matrices(TREES[tree], worlds)
+    m, Mv, Md = _model_and_matrices(TREES.get(tree) or _random_forest(int(tree[6:])), worlds)
     structure = _structure(m)
     assert structure is not None
     plan = tree_ldl.plan_tree_ldl(*structure, groups)
