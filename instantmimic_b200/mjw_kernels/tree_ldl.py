@@ -42,14 +42,12 @@ OP_LOAD_M, OP_LOAD_Y, OP_ZERO, OP_INV, OP_UPD, OP_SCALE, OP_SUBMUL, OP_MUL, OP_A
 
 @dataclass(frozen=True)
 class TreeLdlPlan:
-    groups: tuple[tuple[int, ...], ...]
-    """Dofs of each group's parts, leaves first (descending)."""
-    trunk: tuple[int, ...]
-    """Trunk dofs, ascending; ancestor-closed."""
-    span: int
-    """Critical path in update units: the trunk plus the heaviest group."""
-    dense_cost: int
-    """Dense Cholesky flops per world over all trees."""
+    """What `plan_tree_ldl` decides (the fields of the reference's plan, tree_ldl.py:43-53)."""
+
+    groups: tuple[tuple[int, ...], ...]  # per group the dofs of its parts in elimination order (descending)
+    trunk: tuple[int, ...]  # the dofs eliminated after all groups, ascending; closed under taking ancestors
+    span: int  # update units on the longest path: the trunk's plus the heaviest group's
+    dense_cost: int  # flops per world of a dense Cholesky over every tree of the model
 
 
 @dataclass
@@ -275,16 +273,17 @@ class _Program:
         self.forward, self.backward = [], []
         touched = []
         for j, nodes in enumerate(plan.groups):
-            tm = sorted(
-                {
-                    rowadr[colind[rowadr[k] + p]] + q
-                    for k in nodes
-                    for p in range(rownnz[k] - 1)
-                    if colind[rowadr[k] + p] in trunk
-                    for q in range(p + 1)
-                }
-            )
-            ts = sorted({colind[rowadr[k] + p] for k in nodes for p in range(rownnz[k] - 1)} & trunk)
+            # what this group hands to the trunk: for every trunk ancestor of one of its dofs
+            # (position p in that dof's row) the leading p + 1 entries of the ancestor's row,
+            # and the ancestor's right-hand side
+            trunk_entries, trunk_dofs = set(), set()
+            for k in nodes:
+                row = colind[rowadr[k] : rowadr[k] + rownnz[k] - 1]
+                for p, anc in enumerate(row):
+                    if anc in trunk:
+                        trunk_dofs.add(int(anc))
+                        trunk_entries.update(range(rowadr[anc], rowadr[anc] + p + 1))
+            tm, ts = sorted(trunk_entries), sorted(trunk_dofs)
             touched.append((set(tm), set(ts)))
             f = []
             for k in nodes:
